@@ -1,0 +1,426 @@
+// Memory-bound fused ops of the DiT block, written for HBM3e streaming:
+// 16-byte vector loads/stores, one pass over the activations, fp32 math.
+//
+//  * layernorm_modulate : LN (optional affine) -> y*(1+scale)+shift
+//      (reference: LayerNorm + modulate, telefuser/ops/normalization.py:116-265,
+//       Triton kernels telefuser/kernel/triton/scale_shift.py)
+//  * rmsnorm_rope       : RMSNorm over H*D + interleaved-pair 3-D RoPE, in place
+//      (reference: RMSNorm telefuser/ops/normalization.py:39-113 followed by
+//       apply_rotary_emb telefuser/ops/rotary.py:105-135)
+//  * gated_residual     : x + gate*y   (GateModule, telefuser/models/wan_video_dit.py:343-348)
+//  * act_mul            : silu/gelu(x[:d]) * x[d:]   (telefuser/ops/activations.py:46-81)
+//  * cfg_euler_step     : guidance + flow-matching Euler update in one pass
+//      (telefuser/pipelines/wan_video/single_dit_denoising.py:131-158 and
+//       telefuser/schedulers/flow_match.py:309-333)
+//  * quant_mxfp8        : e4m3 + UE8M0/32 row-wise quantiser
+#include "tfb_api.h"
+#include "tfb_common.cuh"
+#include "tfb_host.h"
+
+namespace tfb {
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  f[0] = bf16_lo(u.x);
+  f[1] = bf16_hi(u.x);
+  f[2] = bf16_lo(u.y);
+  f[3] = bf16_hi(u.y);
+  f[4] = bf16_lo(u.z);
+  f[5] = bf16_hi(u.z);
+  f[6] = bf16_lo(u.w);
+  f[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) t += red[i];
+  return t;
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm (+affine) (+modulate). One CTA of 256 threads per row; NV uint4 per thread.
+// ---------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(256) layernorm_modulate_kernel(
+    const __nv_bfloat16* __restrict__ x, long ldx, __nv_bfloat16* __restrict__ out, long ldo, int rows, int C,
+    float eps, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
+    const float* __restrict__ shift, const float* __restrict__ scale, long ldmod, int rows_per_mod) {
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const int nvec = C >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
+  float v[NV][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      unpack8(xr[vi], v[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s += v[i][e];
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+    }
+  }
+  const float mean = block_sum<256>(s, red) / C;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float d = v[i][e] - mean;
+        ss += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(block_sum<256>(ss, red) / C + eps);
+  const long mrow = static_cast<long>(row / rows_per_mod) * ldmod;
+  uint4* orow = reinterpret_cast<uint4*>(out + row * ldo);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      float y[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = (v[i][e] - mean) * rstd;
+      if (w) {
+        float wf[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(w) + vi), wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] *= wf[e];
+      }
+      if (b) {
+        float bf[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(b) + vi), bf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] += bf[e];
+      }
+      if (scale) {
+        const float4* sp = reinterpret_cast<const float4*>(scale + mrow) + vi * 2;
+        const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] *= (1.f + sc[e]);
+      }
+      if (shift) {
+        const float4* sp = reinterpret_cast<const float4*>(shift + mrow) + vi * 2;
+        const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+        const float sh[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] += sh[e];
+      }
+      orow[vi] = pack8(y);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm over C = H*D + RoPE (interleaved pairs), in place.
+// grid = (rows, nmat); 256 threads.
+// ---------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_rope_kernel(__nv_bfloat16* __restrict__ x, long ldx, long mat_stride,
+                                                           int rows, int H, int D, float eps,
+                                                           const __nv_bfloat16* __restrict__ w0,
+                                                           const __nv_bfloat16* __restrict__ w1,
+                                                           const float* __restrict__ cs, const float* __restrict__ sn) {
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  const int mat = blockIdx.y;
+  const int C = H * D;
+  const int nvec = C >> 3;
+  uint4* xr = reinterpret_cast<uint4*>(x + row * ldx + mat * mat_stride);
+  const __nv_bfloat16* w = mat == 0 ? w0 : w1;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      unpack8(xr[vi], v[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+  const float rstd = rsqrtf(block_sum<256>(ss, red) / C + eps);
+  const int halfD = D >> 1;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      float y[8];
+      float wf[8];
+      if (w) {
+        unpack8(__ldg(reinterpret_cast<const uint4*>(w) + vi), wf);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) wf[e] = 1.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = v[i][e] * rstd * wf[e];
+      if (cs) {
+        const int d0 = (vi * 8) % D;  // head-local element index, multiple of 8
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(cs + static_cast<long>(row) * halfD + (d0 >> 1)));
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sn + static_cast<long>(row) * halfD + (d0 >> 1)));
+        const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+        const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float a = y[2 * p], bq = y[2 * p + 1];
+          y[2 * p] = a * cc[p] - bq * sv[p];
+          y[2 * p + 1] = a * sv[p] + bq * cc[p];
+        }
+      }
+      xr[vi] = pack8(y);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// x + gate * y
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gated_residual_kernel(const uint4* __restrict__ x, const uint4* __restrict__ y,
+                                                             uint4* __restrict__ out, long nvec_total, int vec_per_row,
+                                                             const float* __restrict__ gate, long ldg,
+                                                             int rows_per_gate) {
+  for (long i = blockIdx.x * 256L + threadIdx.x; i < nvec_total; i += static_cast<long>(gridDim.x) * 256L) {
+    float xf[8], yf[8];
+    unpack8(x[i], xf);
+    unpack8(y[i], yf);
+    if (gate) {
+      const long row = i / vec_per_row;
+      const int vi = static_cast<int>(i - row * vec_per_row);
+      const float4* gp = reinterpret_cast<const float4*>(gate + (row / rows_per_gate) * ldg) + vi * 2;
+      const float4 g0 = __ldg(gp), g1 = __ldg(gp + 1);
+      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xf[e] += g[e] * yf[e];
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xf[e] += yf[e];
+    }
+    out[i] = pack8(xf);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// act(x[:, :d]) * x[:, d:]
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) act_mul_kernel(const __nv_bfloat16* __restrict__ x,
+                                                      __nv_bfloat16* __restrict__ out, long rows, int d, int act) {
+  const int vec_per_row = d >> 3;
+  const long total = rows * vec_per_row;
+  for (long i = blockIdx.x * 256L + threadIdx.x; i < total; i += static_cast<long>(gridDim.x) * 256L) {
+    const long row = i / vec_per_row;
+    const int vi = static_cast<int>(i - row * vec_per_row);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * 2L * d);
+    float a[8], g[8];
+    unpack8(xr[vi], a);
+    unpack8(xr[vi + vec_per_row], g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float t;
+      if (act == 0)
+        t = silu(a[e]);
+      else if (act == 1)
+        t = gelu_tanh(a[e]);
+      else
+        t = 0.5f * a[e] * (1.f + erff(a[e] * 0.70710678118654752f));
+      a[e] = t * g[e];
+    }
+    reinterpret_cast<uint4*>(out + row * static_cast<long>(d))[vi] = pack8(a);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CFG combine + Euler step
+// ---------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(256) cfg_euler_kernel(const float* __restrict__ x, const void* __restrict__ cond,
+                                                        const void* __restrict__ uncond, float s, float dsigma,
+                                                        float* __restrict__ x_out, float* __restrict__ v_out, long n) {
+  for (long i = blockIdx.x * 256L + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * 256L) {
+    float c, u;
+    if (BF16) {
+      c = __bfloat162float(static_cast<const __nv_bfloat16*>(cond)[i]);
+      u = uncond ? __bfloat162float(static_cast<const __nv_bfloat16*>(uncond)[i]) : c;
+    } else {
+      c = static_cast<const float*>(cond)[i];
+      u = uncond ? static_cast<const float*>(uncond)[i] : c;
+    }
+    const float v = u + s * (c - u);
+    if (v_out) v_out[i] = v;
+    x_out[i] = x[i] + v * dsigma;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// MXFP8 row-wise quantiser: one warp per 32-element block group; each lane
+// owns 8 elements -> 4 lanes per 32-block.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ldx,
+                                                          uint8_t* __restrict__ q, uint8_t* __restrict__ sf, long rows,
+                                                          int C) {
+  const int vec_per_row = C >> 3;
+  const long total = rows * vec_per_row;
+  const long total_pad = (total + 31) & ~31L;  // whole warps stay in the loop for the shuffles
+  for (long i = blockIdx.x * 256L + threadIdx.x; i < total_pad; i += static_cast<long>(gridDim.x) * 256L) {
+    const bool valid = i < total;
+    const long row = valid ? i / vec_per_row : 0;
+    const int vi = valid ? static_cast<int>(i - row * vec_per_row) : 0;
+    float f[8];
+    if (valid) {
+      unpack8(reinterpret_cast<const uint4*>(x + row * ldx)[vi], f);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+    // 4 consecutive lanes form one 32-element block (vec_per_row is a multiple of 4).
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // scale = 2^ceil(log2(amax / 448)), stored as biased exponent (UE8M0).
+    int ebits = 0;
+    if (amax > 0.f) {
+      const float r = amax * (1.f / 448.f);
+      const uint32_t rb = __float_as_uint(r);
+      ebits = static_cast<int>((rb >> 23) & 0xff) + ((rb & 0x7fffff) ? 1 : 0);
+      ebits = ebits < 1 ? 1 : (ebits > 253 ? 253 : ebits);
+    } else {
+      ebits = 127;
+    }
+    const float inv = __uint_as_float(static_cast<uint32_t>(254 - ebits) << 23);  // 2^-(ebits-127)
+    uint32_t packed[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint16_t lo, hi;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(f[h * 4 + 1] * inv), "f"(f[h * 4] * inv));
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(f[h * 4 + 3] * inv), "f"(f[h * 4 + 2] * inv));
+      packed[h] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+    }
+    if (!valid) continue;
+    reinterpret_cast<uint2*>(q + row * static_cast<long>(C))[vi] = make_uint2(packed[0], packed[1]);
+    if ((vi & 3) == 0) sf[row * (C >> 5) + (vi >> 2)] = static_cast<uint8_t>(ebits);
+  }
+}
+
+static inline int grid_for(long work_items, int per_block = 256, int max_blocks = 148 * 16) {
+  long b = (work_items + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > max_blocks) b = max_blocks;
+  return static_cast<int>(b);
+}
+
+}  // namespace tfb
+
+using namespace tfb;
+
+extern "C" int tfb_layernorm_modulate(const void* x, long ldx, void* out, long ldo, int rows, int C, float eps,
+                                      const void* w, const void* b, const float* shift, const float* scale,
+                                      long ldmod, int rows_per_mod, void* stream) {
+  if (rows <= 0) return TFB_OK;
+  if (C % 8 || C > 8192 || ldx % 8 || ldo % 8 || (ldmod % 4)) return TFB_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nv = (C / 8 + 255) / 256;
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(b);
+  if (rows_per_mod <= 0) rows_per_mod = 1;
+#define TFB_LN_LAUNCH(NV_)                                                                                        \
+  layernorm_modulate_kernel<NV_><<<rows, 256, 0, st>>>(xp, ldx, op, ldo, rows, C, eps, wp, bp, shift, scale, ldmod, \
+                                                       rows_per_mod)
+  switch (nv) {
+    case 1: TFB_LN_LAUNCH(1); break;
+    case 2: TFB_LN_LAUNCH(2); break;
+    case 3: TFB_LN_LAUNCH(3); break;
+    default: TFB_LN_LAUNCH(4); break;
+  }
+#undef TFB_LN_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+extern "C" int tfb_rmsnorm_rope(void* x, long ldx, long mat_stride, int nmat, int rows, int H, int D, float eps,
+                                const void* w0, const void* w1, const float* cos, const float* sin, void* stream) {
+  if (rows <= 0) return TFB_OK;
+  const int C = H * D;
+  if (C % 8 || C > 8192 || ldx % 8 || mat_stride % 8 || D % 8 || nmat < 1 || nmat > 2) return TFB_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nv = (C / 8 + 255) / 256;
+  dim3 grid(rows, nmat);
+  __nv_bfloat16* xp = static_cast<__nv_bfloat16*>(x);
+  const __nv_bfloat16* w0p = static_cast<const __nv_bfloat16*>(w0);
+  const __nv_bfloat16* w1p = static_cast<const __nv_bfloat16*>(w1);
+#define TFB_RMS_LAUNCH(NV_) \
+  rmsnorm_rope_kernel<NV_><<<grid, 256, 0, st>>>(xp, ldx, mat_stride, rows, H, D, eps, w0p, w1p, cos, sin)
+  switch (nv) {
+    case 1: TFB_RMS_LAUNCH(1); break;
+    case 2: TFB_RMS_LAUNCH(2); break;
+    case 3: TFB_RMS_LAUNCH(3); break;
+    default: TFB_RMS_LAUNCH(4); break;
+  }
+#undef TFB_RMS_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+extern "C" int tfb_gated_residual(const void* x, const void* y, void* out, int rows, int C, const float* gate,
+                                  long ldg, int rows_per_gate, void* stream) {
+  if (rows <= 0) return TFB_OK;
+  if (C % 8 || (gate && ldg % 4)) return TFB_ERR_BAD_SHAPE;
+  const long nvec = static_cast<long>(rows) * (C / 8);
+  gated_residual_kernel<<<grid_for(nvec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<const uint4*>(y), static_cast<uint4*>(out), nvec, C / 8, gate, ldg,
+      rows_per_gate > 0 ? rows_per_gate : 1);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+extern "C" int tfb_act_mul(const void* x, void* out, int rows, int d, int act, void* stream) {
+  if (rows <= 0) return TFB_OK;
+  if (d % 8) return TFB_ERR_BAD_SHAPE;
+  const long nvec = static_cast<long>(rows) * (d / 8);
+  act_mul_kernel<<<grid_for(nvec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), rows, d, act);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+extern "C" int tfb_cfg_euler_step(const float* x, const void* cond, const void* uncond, int pred_is_bf16,
+                                  float cfg_scale, float dsigma, float* x_out, float* v_out, long n, void* stream) {
+  if (n <= 0) return TFB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pred_is_bf16)
+    cfg_euler_kernel<true><<<grid_for(n), 256, 0, st>>>(x, cond, uncond, cfg_scale, dsigma, x_out, v_out, n);
+  else
+    cfg_euler_kernel<false><<<grid_for(n), 256, 0, st>>>(x, cond, uncond, cfg_scale, dsigma, x_out, v_out, n);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+extern "C" int tfb_quant_mxfp8(const void* x, long ldx, void* q, void* sf, int rows, int C, void* stream) {
+  if (rows <= 0) return TFB_OK;
+  if (C % 32 || ldx % 8) return TFB_ERR_BAD_SHAPE;
+  const long nvec = static_cast<long>(rows) * (C / 8);
+  // Blocks must cover whole groups of 4 lanes: total is a multiple of 4 and
+  // the grid-stride step (gridDim*256) keeps lane groups aligned.
+  quant_mxfp8_kernel<<<grid_for(nvec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), rows, C);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}

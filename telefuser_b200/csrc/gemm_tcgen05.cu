@@ -1,0 +1,342 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a:
+//   out[M,N] = epilogue(A[M,K] @ B[N,K]^T)      (nn.Linear weight layout)
+// TMA (128B swizzle) -> shared-memory ring -> tcgen05.mma (UMMA 128 x BN x 16)
+// -> fp32 accumulators in TMEM (double buffered) -> tcgen05.ld epilogue.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM
+// owner, warps 2..5 = epilogue (one TMEM lane quarter each).
+//
+// Epilogue functors fused here (replacing separate elementwise passes of the
+// reference's DiT block, telefuser/models/wan_video_dit.py:351-407):
+//   bias add, GELU-tanh, residual add, gate * y + residual.
+#include "tfb_api.h"
+#include "tfb_common.cuh"
+#include "tfb_host.h"
+
+namespace tfb {
+
+struct GemmParams {
+  int M, N, K;
+  __nv_bfloat16* out;
+  int ldo;
+  const __nv_bfloat16* bias;   // [N] or null
+  const __nv_bfloat16* resid;  // [M, ldr] or null
+  int ldr;
+  const float* gate;  // row r reads gate[(r / rows_per_gate) * ldg + col]; null == 1
+  int ldg;
+  int rows_per_gate;
+  int epi;
+  int m_tiles, n_tiles;
+  int* status;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int BM = 128;
+  static constexpr int BK = 64;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+    gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  AbortCtx ctx{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.m_tiles * p.n_tiles;
+  const int k_blocks = (p.K + Cfg::BK - 1) / Cfg::BK;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m_blk = t / p.n_tiles, n_blk = t % p.n_tiles;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, ctx, 1)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + Cfg::A_BYTES;
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          tma_load_2d(a_dst, &tmA, &full[s], kb * Cfg::BK, m_blk * Cfg::BM);
+          tma_load_2d(b_dst, &tmB, &full[s], kb * Cfg::BK, n_blk * BN);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc = make_idesc(128, BN, 1, 1, 0, 0);
+    uint32_t it = 0;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+      const uint32_t acc = tile_iter & 1;
+      const uint32_t accph = (tile_iter >> 1) & 1;
+      if (!mbar_wait_warp(&tempty[acc], accph ^ 1, ctx, 2)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait_warp(&full[s], ph, ctx, 3)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < Cfg::BK / 16; ++kk) {
+            const uint64_t ad = make_desc_k_sw128(a_addr + kk * 32);
+            const uint64_t bd = make_desc_k_sw128(b_addr + kk * 32);
+            umma_f16_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (kb == k_blocks - 1) umma_commit(&tfull[acc]);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ---------------- Epilogue ----------------
+    const int q = warp & 3;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+      const int m_blk = t / p.n_tiles, n_blk = t % p.n_tiles;
+      const uint32_t acc = tile_iter & 1;
+      const uint32_t accph = (tile_iter >> 1) & 1;
+      if (!mbar_wait_warp(&tfull[acc], accph, ctx, 4)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m_blk * Cfg::BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float* gate_row =
+          p.gate ? p.gate + static_cast<size_t>(row_ok ? row / p.rows_per_gate : 0) * p.ldg : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32;
+        tmem_ld_32x32(taddr, r);
+        tmem_ld_wait();
+        const int col0 = n_blk * BN + c * 32;
+        if (row_ok && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          const bool full_chunk = col0 + 32 <= p.N;
+          if (full_chunk) {
+            if (p.bias) {
+              const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 b = __ldg(bp + j);
+                const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  v[j * 8 + e * 2] += bf16_lo(w[e]);
+                  v[j * 8 + e * 2 + 1] += bf16_hi(w[e]);
+                }
+              }
+            }
+            if (p.epi == TFB_EPI_GELU) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+            }
+            if (gate_row) {
+              const float4* gp = reinterpret_cast<const float4*>(gate_row + col0);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 g = __ldg(gp + j);
+                v[j * 4] *= g.x;
+                v[j * 4 + 1] *= g.y;
+                v[j * 4 + 2] *= g.z;
+                v[j * 4 + 3] *= g.w;
+              }
+            }
+            if (p.resid) {
+              const uint4* rp = reinterpret_cast<const uint4*>(p.resid + static_cast<size_t>(row) * p.ldr + col0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 b = rp[j];
+                const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  v[j * 8 + e * 2] += bf16_lo(w[e]);
+                  v[j * 8 + e * 2 + 1] += bf16_hi(w[e]);
+                }
+              }
+            }
+            uint4* op = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(row) * p.ldo + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(v[j * 8], v[j * 8 + 1]);
+              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+              op[j] = o;
+            }
+          } else {
+            // Ragged N edge: scalar path.
+            for (int i = 0; i < 32; ++i) {
+              const int col = col0 + i;
+              if (col >= p.N) break;
+              float x = v[i];
+              if (p.bias) x += __bfloat162float(p.bias[col]);
+              if (p.epi == TFB_EPI_GELU) x = gelu_tanh(x);
+              if (gate_row) x *= gate_row[col];
+              if (p.resid) x += __bfloat162float(p.resid[static_cast<size_t>(row) * p.ldr + col]);
+              p.out[static_cast<size_t>(row) * p.ldo + col] = __float2bfloat16(x);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  // Teardown: everyone meets, then the allocating warp frees TMEM.
+  if (*abort_flag) __nanosleep(200000);  // let copies in flight land before the CTA exits
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& tmA, const void* B, int ldb, GemmParams p, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmB;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.N)};
+    uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
+    uint32_t box[2] = {64, static_cast<uint32_t>(BN)};
+    int e = make_tmap(&tmB, B, TM_BF16, 2, dims, str, box, TM_SW_128);
+    if (e) return e;
+  }
+  p.m_tiles = (p.M + 127) / 128;
+  p.n_tiles = (p.N + BN - 1) / BN;
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 15;
+  if (!attr_set[dev]) {
+    cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    attr_set[dev] = true;
+  }
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_bf16_kernel<BN><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+}  // namespace tfb
+
+extern "C" int tfb_gemm_bf16(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N,
+                             int K, const void* bias, int epi, const void* resid, int ldr, const float* gate,
+                             int ldg, int rows_per_gate, int force_bn, void* stream) {
+  using namespace tfb;
+  if (M <= 0 || N <= 0 || K <= 0) return TFB_ERR_BAD_SHAPE;
+  if ((K % 8) || (lda % 8) || (ldb % 8) || (ldo % 8) || (N % 8)) return TFB_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return TFB_ERR_BAD_SHAPE;
+  if (resid && ((ldr % 8) || (reinterpret_cast<uintptr_t>(resid) & 15))) return TFB_ERR_BAD_SHAPE;
+  if (gate && ((ldg % 4) || (reinterpret_cast<uintptr_t>(gate) & 15))) return TFB_ERR_BAD_SHAPE;
+  if (bias && (reinterpret_cast<uintptr_t>(bias) & 15)) return TFB_ERR_BAD_SHAPE;
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.resid = static_cast<const __nv_bfloat16*>(resid);
+  p.ldr = ldr;
+  p.gate = gate;
+  p.ldg = ldg;
+  p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1;
+  p.epi = epi;
+  p.status = status_word();
+  CUtensorMap tmA;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+    uint32_t box[2] = {64, 128};
+    int e = make_tmap(&tmA, A, TM_BF16, 2, dims, str, box, TM_SW_128);
+    if (e) return e;
+  }
+  int bn = force_bn;
+  if (bn != 256 && bn != 128 && bn != 64) {
+    const long m_tiles = (M + 127) / 128;
+    const int sms = sm_count();
+    if (N % 256 == 0 && m_tiles * (N / 256) >= sms)
+      bn = 256;
+    else if (N >= 128 && m_tiles * ((N + 127) / 128) >= sms / 2)
+      bn = 128;
+    else
+      bn = N >= 128 ? 128 : 64;
+    if (N < 128) bn = 64;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (bn) {
+    case 256: return launch_gemm<256>(tmA, B, ldb, p, st);
+    case 128: return launch_gemm<128>(tmA, B, ldb, p, st);
+    default: return launch_gemm<64>(tmA, B, ldb, p, st);
+  }
+}

@@ -1,0 +1,399 @@
+"""Functional ops: each has an fp32 PyTorch reference (`*_reference`, used on CPU and as
+the numerics oracle) and dispatches CUDA tensors to the sm_100a kernels of libtfb200.
+
+There is one native implementation per op and no backend selection: a CUDA tensor
+either runs the native kernel or raises (missing library / unsupported shape).
+Set ``TFB_FORCE_REFERENCE=1`` to run the reference path on CUDA for debugging.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+
+_FORCE_REF = os.environ.get("TFB_FORCE_REFERENCE", "0") == "1"
+
+
+def _native(t: torch.Tensor) -> bool:
+    return t.is_cuda and not _FORCE_REF
+
+
+def set_force_reference(flag: bool) -> None:
+    """Route CUDA tensors through the PyTorch reference implementations (debug / A-B checks)."""
+    global _FORCE_REF
+    _FORCE_REF = bool(flag)
+
+
+# ---------------------------------------------------------------------------
+# Linear (GEMM + fused epilogue)
+# ---------------------------------------------------------------------------
+def linear_reference(x, weight, bias=None, act=None, residual=None, gate=None):
+    y = x.float() @ weight.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if act == "gelu_tanh":
+        y = F.gelu(y, approximate="tanh")
+    elif act is not None:
+        raise ValueError(f"unknown activation {act}")
+    if gate is not None:
+        y = y * gate.float()
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
+    """``residual + gate * act(x @ weight.T + bias)`` in one kernel.
+
+    x: [..., K] bf16; weight: [N, K]; gate: fp32 broadcastable over rows as
+    [..., 1, N] (one gate row per leading batch entry) or per row [..., N].
+    """
+    if not _native(x) or x.dtype != torch.bfloat16:
+        r = linear_reference(x, weight, bias, act, residual, gate)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    lib = native.load()
+    K = x.shape[-1]
+    N = weight.shape[0]
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    if weight.stride(-1) != 1:
+        weight = weight.contiguous()
+    if out is None:
+        out = torch.empty(*x.shape[:-1], N, device=x.device, dtype=torch.bfloat16)
+    out2 = out.view(-1, N)
+    res2 = None
+    if residual is not None:
+        res2 = residual.reshape(-1, N)
+        if res2.stride(-1) != 1:
+            res2 = res2.contiguous()
+    gate_ptr, ldg, rpg = None, 0, 1
+    if gate is not None:
+        g = gate
+        if g.dtype != torch.float32:
+            g = g.float()
+        g2 = g.reshape(-1, N)
+        if g2.stride(-1) != 1:
+            g2 = g2.contiguous()
+        if M % g2.shape[0]:
+            raise ValueError("gate rows must divide the number of rows")
+        gate_ptr, ldg, rpg = g2.data_ptr(), g2.stride(0) if g2.shape[0] > 1 else N, M // g2.shape[0]
+        gate = g2  # keep alive
+    if bias is not None and bias.dtype != torch.bfloat16:
+        bias = bias.to(torch.bfloat16)
+    code = lib.tfb_gemm_bf16(
+        x2.data_ptr(), x2.stride(0), weight.data_ptr(), weight.stride(0), out2.data_ptr(), out2.stride(0),
+        M, N, K, native.ptr(bias), 1 if act == "gelu_tanh" else 0,
+        native.ptr(res2), res2.stride(0) if res2 is not None else 0, gate_ptr, ldg, rpg, 0, native.stream_ptr(),
+    )  # fmt: skip
+    if act not in (None, "gelu_tanh"):
+        raise ValueError(f"unknown activation {act}")
+    native.check(code, "tfb_gemm_bf16")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# LayerNorm + modulation
+# ---------------------------------------------------------------------------
+def layernorm_modulate_reference(x, shift=None, scale=None, weight=None, bias=None, eps=1e-6):
+    y = F.layer_norm(x.float(), (x.shape[-1],), None if weight is None else weight.float(),
+                     None if bias is None else bias.float(), eps)  # fmt: skip
+    if scale is not None:
+        y = y * (1 + scale.float())
+    if shift is not None:
+        y = y + shift.float()
+    return y.to(x.dtype)
+
+
+def layernorm_modulate(x, shift=None, scale=None, weight=None, bias=None, eps=1e-6):
+    """LN over the last dim (optional affine) then ``y*(1+scale)+shift``.
+
+    x: [B, S, C]; shift/scale: fp32 [B, 1, C] (per batch) or [B, S, C] (per token).
+    """
+    if not _native(x) or x.dtype != torch.bfloat16:
+        return layernorm_modulate_reference(x, shift, scale, weight, bias, eps)
+    lib = native.load()
+    C = x.shape[-1]
+    x2 = x.reshape(-1, C)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    out = torch.empty_like(x2)
+    sh_ptr = sc_ptr = None
+    ldmod, rpm = 0, 1
+    keep = []
+    if (shift is None) != (scale is None):
+        z = torch.zeros_like(shift if shift is not None else scale)
+        shift = z if shift is None else shift
+        scale = z if scale is None else scale
+    if scale is not None:
+        sh = shift.float() if shift.dtype != torch.float32 else shift
+        sc = scale.float() if scale.dtype != torch.float32 else scale
+        sh2, sc2 = sh.reshape(-1, C), sc.reshape(-1, C)
+        if sh2.stride(-1) != 1 or sc2.stride(-1) != 1 or sh2.stride(0) != sc2.stride(0):
+            sh2, sc2 = sh2.contiguous(), sc2.contiguous()
+        if rows % sh2.shape[0]:
+            raise ValueError("modulation rows must divide the number of rows")
+        ldmod = sh2.stride(0) if sh2.shape[0] > 1 else C
+        rpm = rows // sh2.shape[0]
+        sh_ptr, sc_ptr = sh2.data_ptr(), sc2.data_ptr()
+        keep = [sh2, sc2]
+    code = lib.tfb_layernorm_modulate(
+        x2.data_ptr(), x2.stride(0), out.data_ptr(), out.stride(0), rows, C, eps,
+        native.ptr(weight), native.ptr(bias), sh_ptr, sc_ptr, ldmod, rpm, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_layernorm_modulate")
+    del keep
+    return out.view(x.shape)
+
+
+# ---------------------------------------------------------------------------
+# RMSNorm (+ RoPE)
+# ---------------------------------------------------------------------------
+def rope_reference(x, cos, sin):
+    """Interleaved-pair RoPE. x: [B, S, H, D]; cos/sin: [S, D/2] (fp32)."""
+    B, S, H, D = x.shape
+    xf = x.float().reshape(B, S, H, D // 2, 2)
+    a, b = xf[..., 0], xf[..., 1]
+    c = cos.float().reshape(1, S, 1, D // 2)
+    s = sin.float().reshape(1, S, 1, D // 2)
+    return torch.stack([a * c - b * s, a * s + b * c], dim=-1).reshape(B, S, H, D).to(x.dtype)
+
+
+def rmsnorm_reference(x, weight=None, eps=1e-6):
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    if weight is not None:
+        y = y * weight.float()
+    return y.to(x.dtype)
+
+
+def rmsnorm_rope_(x, weight, num_heads, cos=None, sin=None, eps=1e-6, x2=None, weight2=None):
+    """In-place RMSNorm over the full channel dim followed by optional RoPE.
+
+    x: [B, S, C] view (may be a column slice of a fused qkv buffer). When ``x2``
+    is given (same shape/strides, e.g. the k slice) both are processed in one launch.
+    cos/sin: fp32 [B*S, D/2] or [S, D/2] with B == 1.
+    """
+    B, S, C = x.shape
+    D = C // num_heads
+    if not _native(x) or x.dtype != torch.bfloat16:
+        for t, w in ((x, weight), (x2, weight2)):
+            if t is None:
+                continue
+            y = rmsnorm_reference(t, w, eps)
+            if cos is not None:
+                y = rope_reference(y.reshape(B, S, num_heads, D), cos.reshape(-1, D // 2)[:S] if cos.shape[0] != S
+                                   else cos, sin.reshape(-1, D // 2)[:S] if sin.shape[0] != S else sin).reshape(B, S, C)  # fmt: skip
+            t.copy_(y)
+        return x
+    lib = native.load()
+    if x.stride(-1) != 1 or (B > 1 and x.stride(0) != S * x.stride(1)):
+        raise ValueError("rmsnorm_rope_ needs row-strided input")
+    nmat, mat_stride = 1, 0
+    if x2 is not None:
+        if x2.stride() != x.stride() or x2.shape != x.shape:
+            raise ValueError("x2 must match x")
+        mat_stride = (x2.data_ptr() - x.data_ptr()) // x.element_size()
+        nmat = 2
+    if cos is not None:
+        if cos.dtype != torch.float32 or not cos.is_contiguous():
+            cos, sin = cos.float().contiguous(), sin.float().contiguous()
+        if cos.numel() != B * S * (D // 2):
+            if B == 1:
+                raise ValueError("cos/sin must have one row per token")
+            cos = cos.reshape(1, S, D // 2).expand(B, S, D // 2).contiguous()
+            sin = sin.reshape(1, S, D // 2).expand(B, S, D // 2).contiguous()
+    code = lib.tfb_rmsnorm_rope(
+        x.data_ptr(), x.stride(1), mat_stride, nmat, B * S, num_heads, D, eps, native.ptr(weight),
+        native.ptr(weight2), native.ptr(cos), native.ptr(sin), native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_rmsnorm_rope")
+    return x
+
+
+# ---------------------------------------------------------------------------
+# Attention
+# ---------------------------------------------------------------------------
+def attention_reference(q, k, v, scale=None, return_lse=False):
+    """q: [B, Sq, H, D], k/v: [B, Skv, H, D] -> [B, Sq, H, D] (fp32 softmax)."""
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    s = (qf @ kf.transpose(-1, -2)) * scale
+    o = (torch.softmax(s, dim=-1) @ vf).permute(0, 2, 1, 3).to(q.dtype)
+    if return_lse:
+        return o, torch.logsumexp(s, dim=-1)
+    return o
+
+
+def attention(q, k, v, scale=None, return_lse=False, variant=0):
+    """Dense non-causal attention, layout BSHD. Native kernel: head_dim 128, bf16."""
+    if not _native(q) or q.dtype != torch.bfloat16 or q.shape[-1] != 128:
+        return attention_reference(q, k, v, scale, return_lse)
+    lib = native.load()
+    B, Sq, H, D = q.shape
+    Skv = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+
+    def prep(t):
+        S = t.shape[1]
+        if t.stride(-1) != 1 or t.stride(2) != D or (B > 1 and t.stride(0) % 8) or t.stride(1) % 8:
+            t = t.contiguous()
+        return t, t.stride(1), (t.stride(0) if B > 1 else S * t.stride(1))
+
+    q, ldq, bsq = prep(q)
+    k, ldk, bsk = prep(k)
+    v, ldv, bsv = prep(v)
+    out = torch.empty(B, Sq, H, D, device=q.device, dtype=torch.bfloat16)
+    lse = torch.empty(B, H, Sq, device=q.device, dtype=torch.float32) if return_lse else None
+    code = lib.tfb_attn_fwd(
+        q.data_ptr(), ldq, bsq, k.data_ptr(), ldk, bsk, v.data_ptr(), ldv, bsv, out.data_ptr(), H * D, Sq * H * D,
+        native.ptr(lse), B, H, Sq, Skv, scale, variant, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_attn_fwd")
+    return (out, lse) if return_lse else out
+
+
+def merge_attn_states(o1, lse1, o2, lse2):
+    """Combine two partial attention results by their log-sum-exp (ring attention step).
+
+    o*: [B, S, H, D]; lse*: [B, H, S]. Same maths as the reference's
+    ``merge_attn_states`` (telefuser/distributed/ring.py:159-214).
+    """
+    l1 = lse1.float().transpose(1, 2).unsqueeze(-1)
+    l2 = lse2.float().transpose(1, 2).unsqueeze(-1)
+    m = torch.maximum(l1, l2)
+    w1, w2 = torch.exp(l1 - m), torch.exp(l2 - m)
+    o = (o1.float() * w1 + o2.float() * w2) / (w1 + w2)
+    lse = (m + torch.log(w1 + w2)).squeeze(-1).transpose(1, 2)
+    return o.to(o1.dtype), lse
+
+
+# ---------------------------------------------------------------------------
+# Elementwise
+# ---------------------------------------------------------------------------
+def gated_residual(x, y, gate=None):
+    """``x + gate * y``; gate fp32 [B, 1, C] or [B, S, C] or None."""
+    if not _native(x) or x.dtype != torch.bfloat16:
+        r = x.float() + (y.float() if gate is None else gate.float() * y.float())
+        return r.to(x.dtype)
+    lib = native.load()
+    C = x.shape[-1]
+    x2, y2 = x.reshape(-1, C).contiguous(), y.reshape(-1, C).contiguous()
+    rows = x2.shape[0]
+    out = torch.empty_like(x2)
+    gp, ldg, rpg = None, 0, 1
+    if gate is not None:
+        g2 = gate.float().reshape(-1, C).contiguous()
+        gp, ldg, rpg = g2.data_ptr(), C, rows // g2.shape[0]
+    code = lib.tfb_gated_residual(x2.data_ptr(), y2.data_ptr(), out.data_ptr(), rows, C, gp, ldg, rpg,
+                                  native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_gated_residual")
+    return out.view(x.shape)
+
+
+_ACTS = {"silu": 0, "gelu_tanh": 1, "gelu": 2}
+
+
+def act_mul_reference(x, act="silu"):
+    d = x.shape[-1] // 2
+    a, g = x[..., :d].float(), x[..., d:].float()
+    if act == "silu":
+        a = F.silu(a)
+    elif act == "gelu_tanh":
+        a = F.gelu(a, approximate="tanh")
+    else:
+        a = F.gelu(a)
+    return (a * g).to(x.dtype)
+
+
+def act_mul(x, act="silu"):
+    """``act(x[..., :d]) * x[..., d:]`` (silu_and_mul / gelu_and_mul of the reference)."""
+    if not _native(x) or x.dtype != torch.bfloat16 or (x.shape[-1] // 2) % 8:
+        return act_mul_reference(x, act)
+    lib = native.load()
+    d = x.shape[-1] // 2
+    x2 = x.reshape(-1, 2 * d).contiguous()
+    out = torch.empty(x2.shape[0], d, device=x.device, dtype=x.dtype)
+    code = lib.tfb_act_mul(x2.data_ptr(), out.data_ptr(), x2.shape[0], d, _ACTS[act], native.stream_ptr())
+    native.check(code, "tfb_act_mul")
+    return out.view(*x.shape[:-1], d)
+
+
+def silu_and_mul(x):
+    return act_mul(x, "silu")
+
+
+def gelu_and_mul(x, approximate="none"):
+    return act_mul(x, "gelu_tanh" if approximate == "tanh" else "gelu")
+
+
+def cfg_euler_step_reference(x, cond, uncond, cfg_scale, dsigma):
+    c = cond.float()
+    v = c if uncond is None else uncond.float() + cfg_scale * (c - uncond.float())
+    return x.float() + v * dsigma, v
+
+
+def cfg_euler_step(x, cond, uncond, cfg_scale, dsigma, return_v=False):
+    """Guidance ``u + s(c-u)`` and Euler update ``x + v*dsigma`` in one pass over fp32 latents."""
+    if not _native(x) or x.dtype != torch.float32:
+        xo, v = cfg_euler_step_reference(x, cond, uncond, cfg_scale, dsigma)
+        xo = xo.to(x.dtype)
+        return (xo, v) if return_v else xo
+    lib = native.load()
+    cond = cond.contiguous()
+    if uncond is not None:
+        uncond = uncond.contiguous()
+        if uncond.dtype != cond.dtype:
+            uncond = uncond.to(cond.dtype)
+    if cond.dtype not in (torch.bfloat16, torch.float32):
+        cond = cond.float()
+        uncond = None if uncond is None else uncond.float()
+    x = x.contiguous()
+    xo = torch.empty_like(x)
+    v = torch.empty_like(x) if return_v else None
+    code = lib.tfb_cfg_euler_step(
+        x.data_ptr(), cond.data_ptr(), native.ptr(uncond), 1 if cond.dtype == torch.bfloat16 else 0,
+        float(cfg_scale), float(dsigma), xo.data_ptr(), native.ptr(v), x.numel(), native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_cfg_euler_step")
+    return (xo, v) if return_v else xo
+
+
+# ---------------------------------------------------------------------------
+# MXFP8 quantisation
+# ---------------------------------------------------------------------------
+def quant_mxfp8_reference(x):
+    """Returns (e4m3 payload as uint8 [rows, C], UE8M0 scales uint8 [rows, C/32])."""
+    C = x.shape[-1]
+    xf = x.float().reshape(-1, C // 32, 32)
+    amax = xf.abs().amax(-1)
+    e = torch.where(amax > 0, torch.ceil(torch.log2(amax / 448.0)), torch.zeros_like(amax)).clamp(-126, 126)
+    q = (xf * torch.exp2(-e)[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).reshape(-1, C), (e + 127).to(torch.uint8)
+
+
+def dequant_mxfp8(q, sf):
+    C = q.shape[-1]
+    v = q.view(torch.float8_e4m3fn).float().reshape(-1, C // 32, 32)
+    return (v * torch.exp2(sf.float() - 127)[..., None]).reshape(-1, C)
+
+
+def quant_mxfp8(x):
+    if not _native(x) or x.dtype != torch.bfloat16:
+        return quant_mxfp8_reference(x)
+    lib = native.load()
+    C = x.shape[-1]
+    x2 = x.reshape(-1, C).contiguous()
+    q = torch.empty(x2.shape, device=x.device, dtype=torch.uint8)
+    sf = torch.empty(x2.shape[0], C // 32, device=x.device, dtype=torch.uint8)
+    code = lib.tfb_quant_mxfp8(x2.data_ptr(), x2.stride(0), q.data_ptr(), sf.data_ptr(), x2.shape[0], C,
+                               native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_quant_mxfp8")
+    return q, sf
