@@ -1,0 +1,112 @@
+"""Base class of every model: parallel / offload / quantisation / capture hooks.
+
+Mirrors the hook surface of the reference's ``telefuser/core/base_model.py:18-262``
+(`enable_usp`, `enable_pp`, `enable_quant`, `enable_async_offload`,
+`set_attention_config`, `compile`, FSDP / TP plan getters, state-dict converter)
+so stages can drive any model the same way.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.nn as nn
+
+from .config import AttentionConfig, CompileConfig, OffloadConfig, QuantConfig
+
+
+class BaseModel(nn.Module):
+    def __init__(self) -> None:
+        super().__init__()
+        self.usp_flag = False
+        self.pp_flag = False
+        self.fsdp_flag = False
+        self.async_offload_flag = False
+        self.graph_capture = False
+        self.device_mesh = None
+        self.attention_config = AttentionConfig.dense_attention()
+        self.quant_config: QuantConfig | None = None
+        self._feature_cache = None
+        self.layer_name_list: list[str] = ["blocks"]
+
+    # ---- feature cache ---------------------------------------------------
+    @property
+    def feature_cache(self):
+        if self._feature_cache is None:
+            from telefuser_b200.feature_cache.base import NoOpCache
+
+            self._feature_cache = NoOpCache()
+        return self._feature_cache
+
+    def set_feature_cache(self, cache) -> None:
+        self._feature_cache = cache
+
+    def set_ada_taylor_cache(self, cache) -> None:
+        self._feature_cache = cache
+
+    # ---- devices -----------------------------------------------------------
+    def onload_device(self, device) -> None:
+        self.to(device)
+
+    def offload_device(self, pin: bool = True) -> None:
+        self.to("cpu")
+        if pin and torch.cuda.is_available():
+            for p in self.parameters():
+                if not p.data.is_pinned():
+                    p.data = p.data.pin_memory()
+
+    # ---- parallel hooks ------------------------------------------------------
+    def enable_usp(self) -> None:
+        self.usp_flag = True
+
+    def enable_pp(self, *args, **kwargs) -> None:
+        raise NotImplementedError(f"{type(self).__name__} has no pipeline-parallel path")
+
+    def get_fsdp_module_names(self) -> list[str]:
+        return list(self.layer_name_list)
+
+    def get_tp_plan(self) -> dict[str, Any]:
+        return {}
+
+    # ---- runtime features ------------------------------------------------------
+    def set_attention_config(self, config: AttentionConfig) -> None:
+        self.attention_config = config
+        for m in self.modules():
+            if m is not self and hasattr(m, "attention_config"):
+                m.attention_config = config
+
+    def enable_quant(self, quant: QuantConfig | torch.dtype | str) -> None:
+        raise NotImplementedError(f"{type(self).__name__} has no quantised path")
+
+    def enable_async_offload(self, device: torch.device, offload_config: OffloadConfig) -> None:
+        from telefuser_b200.offload.async_offload import AsyncOffloadManager
+
+        blocks = getattr(self, self.layer_name_list[0])
+        self.async_offload_manager = AsyncOffloadManager(
+            blocks,
+            enabled=True,
+            offload_ratio=offload_config.offload_ratio,
+            prefetch_size=offload_config.prefetch_size,
+            device=device,
+            pin_cpu_memory=offload_config.pin_cpu_memory,
+        )
+        self.async_offload_flag = True
+
+    def enable_sequential_cpu_offload(self, device, **kwargs) -> None:
+        from telefuser_b200.offload.sequential_offload import enable_sequential_cpu_offload
+
+        enable_sequential_cpu_offload(self, device, **kwargs)
+
+    def compile(self, config: CompileConfig | None = None, **kwargs):  # noqa: A003 - mirrors nn.Module.compile
+        """Enables CUDA-graph capture of the block loop (there is no tracing compiler here)."""
+        if config is None or config.enabled:
+            self.graph_capture = True
+        return self
+
+    def mark_compile_static(self, *args, **kwargs) -> None:
+        return None
+
+    @staticmethod
+    def state_dict_converter():
+        return None

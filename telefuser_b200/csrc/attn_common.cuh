@@ -1,0 +1,35 @@
+// Shared declarations of the attention kernels.
+#pragma once
+#include "tfb_common.cuh"
+#include "tfb_host.h"
+
+namespace tfb {
+
+struct AttnParams {
+  __nv_bfloat16* out;
+  long ldo, bso;
+  float* lse;
+  int H, Sq, Skv;
+  float scale_log2;
+  int* status;
+  int dbg;  // timing ablations (0 = normal operation)
+};
+
+constexpr int ATT_BM = 128, ATT_BN = 128, ATT_D = 128;
+constexpr int ATT_TILE_BYTES = 128 * 128 * 2;  // 32 KB: two 16 KB boxes of [128 rows][64 cols]
+constexpr int ATT_BOX_BYTES = 16384;
+constexpr float ATT_RESCALE_THRESHOLD = 8.0f;
+
+// 3-D tensor map over [B][S][H*128] bf16 with a [1][128][64] box and 128B swizzle.
+inline int make_qkv_tmap(CUtensorMap* m, const void* base, long ld, long bs, int B, int S, int H) {
+  uint64_t dims[3] = {static_cast<uint64_t>(H) * ATT_D, static_cast<uint64_t>(S), static_cast<uint64_t>(B)};
+  uint64_t str[2] = {static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(bs) * 2};
+  uint32_t box[3] = {64, 128, 1};
+  return make_tmap(m, base, TM_BF16, 3, dims, str, box, TM_SW_128);
+}
+
+// Two-query-tile kernel (attn2_tcgen05.cu).
+int launch_attn2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
+                 cudaStream_t st);
+
+}  // namespace tfb

@@ -13,26 +13,12 @@
 // (telefuser/ops/attention/attention_impl.py:112-315).
 #include <math.h>
 
+#include "attn_common.cuh"
 #include "tfb_api.h"
-#include "tfb_common.cuh"
-#include "tfb_host.h"
 
 namespace tfb {
 
-struct AttnParams {
-  __nv_bfloat16* out;
-  long ldo, bso;
-  float* lse;
-  int H, Sq, Skv;
-  float scale_log2;
-  int* status;
-};
-
-constexpr int ATT_BM = 128, ATT_BN = 128, ATT_D = 128;
-constexpr int ATT_TILE_BYTES = 128 * 128 * 2;  // 32 KB: two 16 KB boxes of [128 rows][64 cols]
-constexpr int ATT_BOX_BYTES = 16384;
 constexpr int ATT_KV_STAGES = 2;
-constexpr float ATT_RESCALE_THRESHOLD = 8.0f;
 
 template <bool P_TMEM>
 struct AttnSmem {
@@ -308,13 +294,6 @@ __global__ void __launch_bounds__(192, 1)
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-static int make_qkv_tmap(CUtensorMap* m, const void* base, long ld, long bs, int B, int S, int H) {
-  uint64_t dims[3] = {static_cast<uint64_t>(H) * ATT_D, static_cast<uint64_t>(S), static_cast<uint64_t>(B)};
-  uint64_t str[2] = {static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(bs) * 2};
-  uint32_t box[3] = {64, 128, 1};
-  return make_tmap(m, base, TM_BF16, 3, dims, str, box, TM_SW_128);
-}
-
 template <bool P_TMEM>
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
                        cudaStream_t st) {
@@ -448,9 +427,11 @@ extern "C" int tfb_attn_fwd(const void* q, long ldq, long bsq, const void* k, lo
   p.Skv = Skv;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word();
+  p.dbg = variant >= 10 ? variant - 10 : 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (variant == 1) return launch_attn<false>(tq, tk, tv, p, B, st);
-  return launch_attn<true>(tq, tk, tv, p, B, st);
+  if (variant == 3) return launch_attn<true>(tq, tk, tv, p, B, st);
+  return launch_attn2(tq, tk, tv, p, B, st);
 }
 
 extern "C" int tfb_umma_probe(const void* A, const void* B, float* D, int N, int K, int mode, void* stream) {
