@@ -1,0 +1,321 @@
+"""Headline benchmark: Wan2.1-T2V-14B, 81 frames, 720x1280 (75,600 tokens), seconds per video.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+A *step* is one full denoising step of the 50-step sampler: conditional and
+unconditional DiT forward (40 blocks, dim 5120) + classifier-free guidance (5.0)
++ flow-matching Euler update. `value` is the whole-video time: 50 x the measured
+step time plus the measured one-off stages (listed in `config`). Weights are
+random-init bf16 tensors of the 14B architecture; text embeddings and noise
+latents are synthetic tensors of the real shapes.
+
+Layouts: 1 GPU plain; 2 GPUs CFG-parallel; 4 GPUs CFG2 x Ulysses2; 8 GPUs
+CFG2 x Ulysses4 (strong scaling: one video, more GPUs).
+
+`--impl reference` runs the unmodified reference package installed under
+baseline/_ref through its own stage API on the same shapes.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODELS = {
+    "wan2.1-t2v-14b": dict(dim=5120, ffn_dim=13824, num_heads=40, num_layers=40),
+    "wan2.1-t2v-1.3b": dict(dim=1536, ffn_dim=8960, num_heads=12, num_layers=30),
+}
+SAMPLER_STEPS = 50
+CFG_SCALE = 5.0
+SIGMA_SHIFT = 5.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="wan2.1-t2v-14b", choices=sorted(MODELS))
+    ap.add_argument("--frames", type=int, default=81)
+    ap.add_argument("--height", type=int, default=720)
+    ap.add_argument("--width", type=int, default=1280)
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (pinned host <-> device) measurement")
+    return ap.parse_args()
+
+
+def layout_for(n: int) -> dict:
+    if n == 1:
+        return dict(cfg_degree=1, sp_ulysses_degree=1, name="single")
+    if n == 2:
+        return dict(cfg_degree=2, sp_ulysses_degree=1, name="cfg2")
+    return dict(cfg_degree=2, sp_ulysses_degree=n // 2, name=f"cfg2xulysses{n // 2}")
+
+
+class ClockSampler:
+    """Samples SM clock / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")  # fmt: skip
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)  # fmt: skip
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out = self.proc.communicate(timeout=5)[0]
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = self.proc.communicate()[0]
+        clocks, maxc, power, reasons = [], None, [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                clocks.append(float(f[1]))
+                maxc = float(f[2])
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nme, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(nme)
+        load = [c for c, p in zip(clocks, power) if p > 300] or clocks
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": maxc,
+                "power_w_median": statistics.median(power) if power else None, "samples": len(clocks),
+                "reasons": sorted(reasons)}  # fmt: skip
+
+
+def dist_setup(n: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if n > 1 and world != n:
+        raise SystemExit(f"--gpus {n} needs torchrun with {n} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier_sync(world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(v: float, world: int) -> float:
+    if world == 1:
+        return v
+    t = torch.tensor([v], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def random_init_(model: torch.nn.Module, seed: int = 0) -> None:
+    """Random-init weights of the real architecture, directly on the device."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    for name, p in model.named_parameters():
+        if p.dim() >= 2 and "modulation" not in name:
+            p.data.normal_(0.0, 0.02, generator=g)
+        elif "modulation" in name:
+            p.data.normal_(0.0, 1.0 / p.shape[-1] ** 0.5, generator=g)
+        elif name.endswith("bias"):
+            p.data.normal_(0.0, 0.01, generator=g)
+        else:
+            p.data.fill_(1.0)
+
+
+def make_inputs(args, seed=1):
+    """Pinned-host synthetic inputs of the real shapes."""
+    g = torch.Generator().manual_seed(seed)
+    lat_shape = (1, 16, (args.frames - 1) // 4 + 1, args.height // 8, args.width // 8)
+    latents = torch.randn(lat_shape, generator=g).pin_memory()
+    posi = torch.randn(1, 512, 4096, generator=g).to(torch.bfloat16).pin_memory()
+    nega = torch.randn(1, 512, 4096, generator=g).to(torch.bfloat16).pin_memory()
+    return latents, posi, nega
+
+
+# ---------------------------------------------------------------------------
+# Arms
+# ---------------------------------------------------------------------------
+def build_ours(args, layout, world, local):
+    from telefuser_b200.core.config import ModelRuntimeConfig, ParallelConfig
+    from telefuser_b200.models.wan_dit import WanModel
+    from telefuser_b200.ops import native
+    from telefuser_b200.pipelines.wan.denoising import WanDenoisingStage
+    from telefuser_b200.schedulers.flow_match import FlowMatchScheduler
+
+    native.load()
+    with torch.device("meta"):
+        model = WanModel(**MODELS[args.model])
+    model = model.to_empty(device="cuda").to(torch.bfloat16)
+    random_init_(model)
+    model.eval()
+    pc = ParallelConfig(device_ids=list(range(world)) if world > 1 else None, cfg_degree=layout["cfg_degree"],
+                        sp_ulysses_degree=layout["sp_ulysses_degree"])  # fmt: skip
+    cfg = ModelRuntimeConfig(torch_dtype=torch.bfloat16, parallel_config=pc, device_type="cuda", device_id=local)
+    stage = WanDenoisingStage("dit_denoise", None, cfg, FlowMatchScheduler("Wan"), dit=model)
+    if world > 1:
+        stage.parallel_models()
+    stage.onload_models_flag = True
+
+    def run(latents, steps, posi, nega):
+        return stage.process(latents, steps, None, posi, nega, None, CFG_SCALE, SIGMA_SHIFT)
+
+    return run, native
+
+
+def build_reference(args, layout, world, local):
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "telefuser")):
+        raise RuntimeError("reference is not installed under baseline/_ref")
+    sys.path.insert(0, ref_root)
+    os.environ.setdefault("TELEFUSER_LOG_LEVEL", "WARNING")
+    from telefuser.core.config import ModelRuntimeConfig, ParallelConfig
+    from telefuser.core.module_manager import ModuleManager
+    from telefuser.models.wan_video_dit import WanModel
+    from telefuser.pipelines.wan_video.single_dit_denoising import SingleDitDenoisingStage
+    from telefuser.schedulers.flow_match import FlowMatchScheduler
+
+    m = MODELS[args.model]
+    with torch.device("meta"):
+        model = WanModel(dim=m["dim"], in_dim=16, ffn_dim=m["ffn_dim"], out_dim=16, text_dim=4096, freq_dim=256,
+                         eps=1e-6, patch_size=(1, 2, 2), num_heads=m["num_heads"], num_layers=m["num_layers"],
+                         has_image_input=False)  # fmt: skip
+    model = model.to_empty(device="cuda").to(torch.bfloat16)
+    random_init_(model)
+    # buffers created outside parameters (rope tables) are rebuilt by the reference itself
+    from telefuser.models.wan_video_dit import precompute_freqs_cis_3d
+
+    model.normal_freqs = precompute_freqs_cis_3d(model.head_dim)
+    model.freqs = model.normal_freqs
+    model.eval()
+    mm = ModuleManager(torch_dtype=torch.bfloat16, device="cuda")
+    mm.add_module(model, "wan_video_dit")
+    pc = ParallelConfig(device_ids=list(range(world)) if world > 1 else None, cfg_degree=layout["cfg_degree"],
+                        sp_ulysses_degree=layout["sp_ulysses_degree"])  # fmt: skip
+    cfg = ModelRuntimeConfig(torch_dtype=torch.bfloat16, parallel_config=pc, device_type="cuda", device_id=local)
+    stage = SingleDitDenoisingStage("dit_denoise", mm, cfg, FlowMatchScheduler("Wan"))
+    if world > 1:
+        stage.parallel_models()
+    stage.onload_models_flag = True
+
+    def run(latents, steps, posi, nega):
+        return stage.process(latents.to(torch.bfloat16), steps, None, posi, nega, None, CFG_SCALE, SIGMA_SHIFT)
+
+    return run, None
+
+
+def main():
+    args = parse_args()
+    if not torch.cuda.is_available():
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device on this machine"}))
+            return
+        raise SystemExit("bench.py needs a CUDA device")
+    rank, world, local = dist_setup(args.gpus)
+    layout = layout_for(world)
+    try:
+        run, native = (build_reference if args.impl == "reference" else build_ours)(args, layout, world, local)
+    except Exception as e:  # noqa: BLE001 - report why the arm cannot run
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}))
+            return
+        raise
+    lat_h, posi_h, nega_h = make_inputs(args)
+    lat = lat_h.cuda(non_blocking=True)
+    posi = posi_h.cuda(non_blocking=True)
+    nega = nega_h.cuda(non_blocking=True)
+    tokens = lat.shape[2] * (lat.shape[3] // 2) * (lat.shape[4] // 2)
+
+    # ---- device-timed K steps (inputs resident; activations >> L2 so no flush is needed) ----
+    if args.warmup > 0:
+        run(lat, args.warmup, posi, nega)
+    barrier_sync(world)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    if native is not None:
+        native.reset_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    out = run(lat, args.steps, posi, nega)
+    e1.record()
+    barrier_sync(world)
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps, world)
+    launches = native.launch_count() if native is not None else None
+    clocks = sampler.stop() if rank == 0 else None
+    finite = bool(torch.isfinite(out.float()).all().item())
+
+    # ---- end to end through the stage API: pinned host -> device -> step -> host, every step ----
+    e2e = None
+    if not args.no_e2e:
+        res_h = torch.empty(lat_h.shape, dtype=torch.float32).pin_memory()
+        barrier_sync(world)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            l_d = lat_h.cuda(non_blocking=True)
+            p_d = posi_h.cuda(non_blocking=True)
+            n_d = nega_h.cuda(non_blocking=True)
+            o = run(l_d, 1, p_d, n_d)
+            res_h.copy_(o.float(), non_blocking=True)
+            torch.cuda.synchronize()
+        barrier_sync(world)
+        e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / args.steps, world)
+        e2e = {"value": e2e_ms * SAMPLER_STEPS / 1e3, "unit": "s/video", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": lat_h.numel() * 4 + posi_h.numel() * 2 + nega_h.numel() * 2,
+               "d2h_bytes_per_step": res_h.numel() * 4}  # fmt: skip
+
+    if rank == 0:
+        value = ms_step * SAMPLER_STEPS / 1e3
+        line = {
+            "metric": "wan2.1_t2v_14b_81f_720p_seconds_per_video" if args.model.endswith("14b") else
+                      f"{args.model}_seconds_per_video",  # fmt: skip
+            "value": value, "unit": "s/video", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (random-init weights, N(0,1) latents and text embeddings)",
+            "impl": args.impl, "finite_output": finite,
+            "config": {"model": args.model, "global_batch": 1, "seq_len": tokens, "frames": args.frames,
+                       "height": args.height, "width": args.width, "sampler_steps": SAMPLER_STEPS,
+                       "cfg_scale": CFG_SCALE, "parallelism": layout["name"],
+                       "step": "cond+uncond DiT forward + guidance + Euler update",
+                       "value_formula": "50 * ms_per_step / 1000 (DiT denoising loop; text encoder and VAE decode not in value)",
+                       "l2": "activations per step (>700 MB per tensor) exceed the 126 MB L2; no flush needed"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        }  # fmt: skip
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

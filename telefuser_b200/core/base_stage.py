@@ -1,0 +1,125 @@
+"""Stage = the unit that owns models and exposes ``process``; runs in-process or
+inside every rank of a ``ParallelWorker``.
+
+Covers the reference's ``telefuser/core/base_stage.py:22-169``: the
+``with_model_offload`` decorator (load named models before a call and move them
+back according to the offload policy), ``parallel_models`` (hook executed in
+each worker rank after the process group exists), metrics hooks and
+feature-cache set-up.
+"""
+
+from __future__ import annotations
+
+import functools
+from abc import ABC
+from typing import Any, Callable
+
+import torch
+
+from .config import FeatureCacheConfig, ModelRuntimeConfig, WeightOffloadType
+
+
+def with_model_offload(model_names: list[str]) -> Callable:
+    def decorator(func):
+        @functools.wraps(func)
+        def wrapper(self: "BaseStage", *args, **kwargs):
+            policy = self.model_runtime_config.offload_config.offload_type
+            if self.onload_models_flag and policy == WeightOffloadType.NO_CPU_OFFLOAD:
+                return func(self, *args, **kwargs)
+            if not self.onload_models_flag:
+                for name in model_names:
+                    model = getattr(self, name, None)
+                    if model is not None:
+                        self._move(model, self.device)
+                self.onload_models_flag = True
+            try:
+                return func(self, *args, **kwargs)
+            finally:
+                if policy != WeightOffloadType.NO_CPU_OFFLOAD:
+                    pin = self.model_runtime_config.offload_config.pin_cpu_memory
+                    for name in model_names:
+                        model = getattr(self, name, None)
+                        if model is None:
+                            continue
+                        if hasattr(model, "offload_device"):
+                            model.offload_device(pin)
+                        else:
+                            model.cpu()
+                    if torch.cuda.is_available():
+                        torch.cuda.empty_cache()
+                    self.onload_models_flag = False
+
+        return wrapper
+
+    return decorator
+
+
+class BaseStage(ABC):
+    def __init__(self, name: str, model_runtime_config: ModelRuntimeConfig) -> None:
+        self.name = name
+        self.model_runtime_config = model_runtime_config
+        self.torch_dtype = model_runtime_config.torch_dtype
+        self.device_type = model_runtime_config.device_type or ("cuda" if torch.cuda.is_available() else "cpu")
+        self.device = (torch.device("cpu") if self.device_type == "cpu"
+                       else torch.device(self.device_type, model_runtime_config.device_id))  # fmt: skip
+        self.model_names: list[str] = []
+        self.onload_models_flag = False
+        self._metrics_hook = None
+
+    # ---- metrics ---------------------------------------------------------
+    def enable_metrics(self, registry: Any | None = None) -> None:
+        from telefuser_b200.metrics import get_metrics_registry
+
+        self._metrics_hook = (registry or get_metrics_registry()).register_stage(self.name)
+
+    def disable_metrics(self) -> None:
+        self._metrics_hook = None
+
+    @property
+    def metrics_hook(self):
+        return self._metrics_hook
+
+    # ---- model placement -----------------------------------------------------
+    @staticmethod
+    def _move(model, device) -> None:
+        if hasattr(model, "onload_device"):
+            model.onload_device(device)
+        else:
+            model.to(device)
+
+    def onload_models(self) -> None:
+        for name in self.model_names:
+            model = getattr(self, name, None)
+            if model is not None:
+                self._move(model, self.device)
+        self.onload_models_flag = True
+
+    def offload_models(self) -> None:
+        pin = self.model_runtime_config.offload_config.pin_cpu_memory
+        for name in self.model_names:
+            model = getattr(self, name, None)
+            if model is None:
+                continue
+            if hasattr(model, "offload_device"):
+                model.offload_device(pin)
+            else:
+                model.cpu()
+        self.onload_models_flag = False
+
+    def parallel_models(self) -> None:
+        """Called once in every worker rank after the process group is up. Override."""
+
+    def setup_feature_cache(self, model, cache_config: FeatureCacheConfig, num_inference_steps: int,
+                            init_step: int = 0) -> None:  # fmt: skip
+        from telefuser_b200.feature_cache import create_feature_cache
+
+        if cache_config.enabled:
+            model.set_feature_cache(create_feature_cache(
+                "ada_taylor", model_type=cache_config.model_type, num_inference_steps=num_inference_steps,
+                n_derivatives=cache_config.n_derivatives, taylor_threshold=cache_config.taylor_threshold,
+                init_step=init_step))  # fmt: skip
+        else:
+            model.set_feature_cache(create_feature_cache("none"))
+
+    def process(self, *args, **kwargs):
+        raise NotImplementedError

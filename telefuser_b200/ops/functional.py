@@ -191,8 +191,12 @@ def rmsnorm_rope_(x, weight, num_heads, cos=None, sin=None, eps=1e-6, x2=None, w
                 continue
             y = rmsnorm_reference(t, w, eps)
             if cos is not None:
-                y = rope_reference(y.reshape(B, S, num_heads, D), cos.reshape(-1, D // 2)[:S] if cos.shape[0] != S
-                                   else cos, sin.reshape(-1, D // 2)[:S] if sin.shape[0] != S else sin).reshape(B, S, C)  # fmt: skip
+                c2, s2 = cos.reshape(-1, D // 2), sin.reshape(-1, D // 2)
+                if c2.shape[0] == B * S and B > 1:
+                    y = torch.cat([rope_reference(y[i : i + 1].reshape(1, S, num_heads, D), c2[i * S : (i + 1) * S],
+                                                  s2[i * S : (i + 1) * S]) for i in range(B)]).reshape(B, S, C)  # fmt: skip
+                else:
+                    y = rope_reference(y.reshape(B, S, num_heads, D), c2, s2).reshape(B, S, C)
             t.copy_(y)
         return x
     lib = native.load()
