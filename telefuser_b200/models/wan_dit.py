@@ -429,3 +429,13 @@ class WanModel(BaseModel):
         from telefuser_b200.models.wan_dit_convert import WanModelStateDictConverter
 
         return WanModelStateDictConverter()
+
+
+def _register() -> None:
+    from telefuser_b200.core.model_registry import register_architecture
+
+    for preset in ("wan2.1-t2v-1.3b", "wan2.1-t2v-14b", "wan2.1-i2v-14b", "wan2.2-ti2v-5b"):
+        register_architecture("wan_video_dit", WanModel, lambda p=preset: WanModel.from_config(WanModelConfig.preset(p)))
+
+
+_register()
