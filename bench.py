@@ -203,7 +203,17 @@ def build_reference(args, layout, world, local):
     from telefuser.core.module_manager import ModuleManager
     from telefuser.models.wan_video_dit import WanModel
     from telefuser.pipelines.wan_video.single_dit_denoising import SingleDitDenoisingStage
-    from telefuser.schedulers.flow_match import FlowMatchScheduler
+
+    # The reference's `telefuser.schedulers` package imports its UniPC scheduler, which needs
+    # `diffusers` (not installable offline). Its flow-matching scheduler file has no such
+    # dependency, so that unmodified file is loaded by path instead of through the package.
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location(
+        "telefuser_ref_flow_match", os.path.join(ref_root, "telefuser", "schedulers", "flow_match.py"))
+    fm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(fm)
+    FlowMatchScheduler = fm.FlowMatchScheduler
 
     m = MODELS[args.model]
     with torch.device("meta"):

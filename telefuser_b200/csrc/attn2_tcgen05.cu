@@ -248,6 +248,7 @@ __global__ void __launch_bounds__(384, 1)
       }
       // p = 2^(s*scale - m): packed fp32x2 FMAs, exp2 split between the MUFU
       // pipe and a cubic on the FMA pipe, packed row-sum accumulation.
+      const int poly_mode = p.poly;  // 0: MUFU only, 1: every 4th pair on the FMA pipe, 2: every 2nd pair
       const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
       const uint64_t negm2 = f2_pack(-m_used, -m_used);
       uint64_t ps[4] = {0ull, 0ull, 0ull, 0ull};
@@ -261,7 +262,7 @@ __global__ void __launch_bounds__(384, 1)
           float p0, p1;
           if (p.dbg == 1) {
             f2_unpack(x2, p0, p1);
-          } else if ((k & 3) == 3) {  // every 4th pair: FMA-pipe exp2
+          } else if ((poly_mode == 1 && (k & 3) == 3) || (poly_mode == 2 && (k & 1))) {  // FMA-pipe exp2 share
             exp2_poly_pair(x2, p0, p1);
           } else {
             float x0, x1;
