@@ -27,6 +27,8 @@ constexpr int A2_KV_OFF = 2 * ATT_TILE_BYTES;
 constexpr int A2_BAR_OFF = A2_KV_OFF + A2_KV_SLOTS * ATT_TILE_BYTES;
 constexpr int A2_SMEM_BYTES = A2_BAR_OFF + 256 + 1024;
 
+// POLY: share of exp2 evaluated on the FMA pipe instead of MUFU (0 none, 1 a quarter, 2 half).
+template <int POLY>
 __global__ void __launch_bounds__(384, 1)
     attn2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(384, 1)
         tma_load_3d(qd, &tmQ, &q_full[st], h * ATT_D, q0, b);
         tma_load_3d(qd + ATT_BOX_BYTES, &tmQ, &q_full[st], h * ATT_D + 64, q0, b);
       }
-      for (int n = 0; n < (p.dbg == 7 ? min(4, 2 * n_kv) : 2 * n_kv); ++n) {
+      for (int n = 0; n < 2 * n_kv; ++n) {
         const int slot = n & (A2_KV_SLOTS - 1);
         const uint32_t ph = (n / A2_KV_SLOTS) & 1;
         if (!mbar_wait(&kv_empty[slot], ph ^ 1, ctx, 10)) break;
@@ -142,12 +144,10 @@ __global__ void __launch_bounds__(384, 1)
     for (int j = 0; j < n_kv && ok; ++j) {
       const bool has_next = j + 1 < n_kv;
       const int nv = 2 * j + 1, nk = 2 * j + 2;
-      if (p.dbg != 7 || j < 1) {
-        if (!mbar_wait_warp(&kv_full[nv & (A2_KV_SLOTS - 1)], (nv / A2_KV_SLOTS) & 1, ctx, 23)) break;
-        if (has_next && !mbar_wait_warp(&kv_full[nk & (A2_KV_SLOTS - 1)], (nk / A2_KV_SLOTS) & 1, ctx, 24)) break;
-      }
+      if (!mbar_wait_warp(&kv_full[nv & (A2_KV_SLOTS - 1)], (nv / A2_KV_SLOTS) & 1, ctx, 23)) break;
+      if (has_next && !mbar_wait_warp(&kv_full[nk & (A2_KV_SLOTS - 1)], (nk / A2_KV_SLOTS) & 1, ctx, 24)) break;
       for (int st = 0; st < 2 && ok; ++st) {
-        if (p.dbg < 6 && !mbar_wait_warp(&p_ready[st], j & 1, ctx, 25)) {
+        if (!mbar_wait_warp(&p_ready[st], j & 1, ctx, 25)) {
           ok = false;
           break;
         }
@@ -187,22 +187,10 @@ __global__ void __launch_bounds__(384, 1)
         break;
       }
       tc_fence_after();
-      if (p.dbg >= 5) {
-        tc_fence_before();
-        mbar_arrive(&p_ready[st]);
-        continue;
-      }
       uint32_t s[4][32];
-      if (p.dbg != 4) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, s[c]);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) s[c][i] = __float_as_uint(static_cast<float>(row + c + i + j) * 1e-3f);
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, s[c]);
+      tmem_ld_wait();
       const int kv_valid = p.Skv - j * ATT_BN;
       if (kv_valid < ATT_BN) {
 #pragma unroll
@@ -223,8 +211,7 @@ __global__ void __launch_bounds__(384, 1)
           if (i + 3 < 32)
             mx8[c * 2 + 1] = fmax3(mx8[c * 2 + 1], __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
         }
-      float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
-      if (p.dbg == 2) mx = __uint_as_float(s[0][0]) + 4.f;
+      const float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       if (j == 0) {
         m_used = m_new;
@@ -248,7 +235,6 @@ __global__ void __launch_bounds__(384, 1)
       }
       // p = 2^(s*scale - m): packed fp32x2 FMAs, exp2 split between the MUFU
       // pipe and a cubic on the FMA pipe, packed row-sum accumulation.
-      const int poly_mode = p.poly;  // 0: MUFU only, 1: every 4th pair on the FMA pipe, 2: every 2nd pair
       const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
       const uint64_t negm2 = f2_pack(-m_used, -m_used);
       uint64_t ps[4] = {0ull, 0ull, 0ull, 0ull};
@@ -260,9 +246,7 @@ __global__ void __launch_bounds__(384, 1)
           const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[c][2 * k]), __uint_as_float(s[c][2 * k + 1])), scale2,
                                      negm2);
           float p0, p1;
-          if (p.dbg == 1) {
-            f2_unpack(x2, p0, p1);
-          } else if ((poly_mode == 1 && (k & 3) == 3) || (poly_mode == 2 && (k & 1))) {  // FMA-pipe exp2 share
+          if ((POLY == 1 && (k & 3) == 3) || (POLY == 2 && (k & 1))) {  // FMA-pipe exp2 share
             exp2_poly_pair(x2, p0, p1);
           } else {
             float x0, x1;
@@ -273,7 +257,7 @@ __global__ void __launch_bounds__(384, 1)
           ps[k & 3] = f2_add(ps[k & 3], f2_pack(p0, p1));
           t[k] = pack_bf16x2(p0, p1);
         }
-        if (p.dbg != 3) tmem_st_32x16(tmem_s + c * 16, t);
+        tmem_st_32x16(tmem_s + c * 16, t);
       }
       {
         float a0, a1, b0, b1;
@@ -320,19 +304,29 @@ __global__ void __launch_bounds__(384, 1)
   if (warp == 9) tmem_dealloc(tmem_base, 512);
 }
 
-int launch_attn2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
-                 cudaStream_t st) {
+template <int POLY>
+static int launch_attn2_impl(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                             int B, cudaStream_t st) {
   static bool attr_set[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   dev &= 15;
   if (!attr_set[dev]) {
-    cudaFuncSetAttribute(attn2_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM_BYTES);
+    cudaFuncSetAttribute(attn2_fwd_kernel<POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM_BYTES);
     attr_set[dev] = true;
   }
   dim3 grid((p.Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), p.H, B);
-  attn2_fwd_kernel<<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
+  attn2_fwd_kernel<POLY><<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+int launch_attn2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
+                 cudaStream_t st) {
+  switch (p.poly) {
+    case 0: return launch_attn2_impl<0>(tq, tk, tv, p, B, st);
+    case 2: return launch_attn2_impl<2>(tq, tk, tv, p, B, st);
+    default: return launch_attn2_impl<1>(tq, tk, tv, p, B, st);
+  }
 }
 
 }  // namespace tfb

@@ -12,7 +12,6 @@ struct AttnParams {
   int H, Sq, Skv;
   float scale_log2;
   int* status;
-  int dbg;   // timing ablations (0 = normal operation)
   int poly;  // share of exp2 evaluated on the FMA pipe: 0 none, 1 a quarter, 2 half
 };
 

@@ -427,8 +427,7 @@ extern "C" int tfb_attn_fwd(const void* q, long ldq, long bsq, const void* k, lo
   p.Skv = Skv;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word();
-  p.dbg = (variant >= 10 && variant < 20) ? variant - 10 : 0;
-  p.poly = (variant >= 20 && variant <= 22) ? variant - 20 : 1;
+  p.poly = (variant >= 20 && variant <= 22) ? variant - 20 : 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (variant == 1) return launch_attn<false>(tq, tk, tv, p, B, st);
   if (variant == 3) return launch_attn<true>(tq, tk, tv, p, B, st);
