@@ -1,0 +1,69 @@
+"""Hugging Face helpers: id-vs-path test, snapshot resolution, component discovery in a model folder.
+Role parity: telefuser/utils/hf_model_utils.py:21-209 and hf_model_analyzer.py:28-382 (condensed)."""
+
+from __future__ import annotations
+
+import json
+import os
+import re
+
+
+def is_hf_model_id(s: str) -> bool:
+    return not os.path.exists(s) and re.fullmatch(r"[\w.\-]+/[\w.\-]+", s) is not None
+
+
+def resolve_hf_path(model_id_or_path: str, cache_dir: str | None = None) -> str:
+    """Local path as is; a hub id is resolved from the local cache (or downloaded when a network exists)."""
+    if os.path.exists(model_id_or_path):
+        return model_id_or_path
+    zoo = os.environ.get("TF_MODEL_ZOO_PATH")
+    if zoo and os.path.exists(os.path.join(zoo, model_id_or_path)):
+        return os.path.join(zoo, model_id_or_path)
+    if is_hf_model_id(model_id_or_path):
+        from huggingface_hub import snapshot_download
+
+        return snapshot_download(model_id_or_path, cache_dir=cache_dir)
+    raise FileNotFoundError(model_id_or_path)
+
+
+def get_component_path(root: str, component: str) -> str | None:
+    p = os.path.join(root, component)
+    return p if os.path.isdir(p) else None
+
+
+def detect_model_task(root: str) -> str:
+    """'i2v' when the folder's config names an image-conditioned model, else 't2v' ('t2i' for image models)."""
+    for name in ("config.json", "model_index.json", os.path.join("transformer", "config.json")):
+        f = os.path.join(root, name)
+        if os.path.isfile(f):
+            try:
+                cfg = json.load(open(f))
+            except (OSError, ValueError):
+                continue
+            blob = json.dumps(cfg).lower()
+            if "i2v" in blob or cfg.get("model_type") == "i2v" or cfg.get("in_dim") == 36:
+                return "i2v"
+            if "image" in str(cfg.get("_class_name", "")).lower() and "video" not in blob:
+                return "t2i"
+    return "i2v" if "i2v" in os.path.basename(root).lower() else "t2v"
+
+
+class HFModelAnalyzer:
+    """Lists the components (transformer / vae / text_encoder / image_encoder / tokenizer) of a model folder."""
+
+    COMPONENTS = ("transformer", "transformer_2", "vae", "text_encoder", "image_encoder", "tokenizer", "scheduler")
+
+    def __init__(self, root: str):
+        self.root = root
+
+    def analyze(self) -> dict:
+        out = {"root": self.root, "task": detect_model_task(self.root), "components": {}}
+        idx = os.path.join(self.root, "model_index.json")
+        if os.path.isfile(idx):
+            out["model_index"] = json.load(open(idx))
+        for c in self.COMPONENTS:
+            p = get_component_path(self.root, c)
+            if p:
+                out["components"][c] = p
+        out["files"] = sorted(f for f in os.listdir(self.root) if f.endswith((".safetensors", ".pth", ".bin")))
+        return out

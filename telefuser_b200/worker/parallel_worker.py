@@ -288,4 +288,6 @@ class ParallelWorker:
         def method(*args, **kwargs):
             return self.call(name, *args, **kwargs)
 
+        method._parallel_worker = self  # lets auto_async_call issue the call asynchronously
+        method._method_name = name
         return method
