@@ -31,19 +31,22 @@ def make_tiny_inputs(seed: int = 0):
     return latents, context, torch.zeros_like(context)
 
 
-def make_tiny_model(seed: int = 0, dtype=torch.float32) -> WanModel:
+def make_tiny_model(seed: int = 0, dtype=torch.float32, preset: str = "tiny") -> WanModel:
     torch.manual_seed(seed)
-    model = WanModel.from_config(WanModelConfig.preset("tiny")).to(dtype)
+    if preset == "native-small":  # head_dim 128 so the native attention kernel runs on GPUs
+        model = WanModel(dim=512, ffn_dim=1024, num_heads=4, num_layers=2, text_dim=256).to(dtype)
+    else:
+        model = WanModel.from_config(WanModelConfig.preset(preset)).to(dtype)
     model.dtype = dtype
     return model.eval()
 
 
 def tiny_wan_denoise(parallel: ParallelConfig | None = None, device: str = "cpu", dtype=torch.float32,
-                     steps: int = 4) -> torch.Tensor:  # fmt: skip
+                     steps: int = 4, preset: str = "tiny") -> torch.Tensor:  # fmt: skip
     parallel = parallel or ParallelConfig()
     cfg = ModelRuntimeConfig(torch_dtype=dtype, parallel_config=parallel, device_type=device.split(":")[0],
                              device_id=int(device.split(":")[1]) if ":" in device else 0)  # fmt: skip
-    model = make_tiny_model(dtype=dtype).to(device)
+    model = make_tiny_model(dtype=dtype, preset=preset).to(device)
     stage = WanDenoisingStage("denoise", None, cfg, FlowMatchScheduler("Wan"), dit=model)
     if parallel.device_ids is not None and len(parallel.device_ids) > 1:
         stage.parallel_models()
@@ -58,7 +61,7 @@ def tiny_wan_denoise(parallel: ParallelConfig | None = None, device: str = "cpu"
 
 
 def _rank_main(rank: int, world_size: int, port: int, backend: str, parallel_kwargs: dict, out_path: str,
-               dtype_name: str) -> None:  # fmt: skip
+               dtype_name: str, preset: str = "tiny") -> None:  # fmt: skip
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world_size), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.set_num_threads(1)
     device = "cpu"
@@ -68,7 +71,7 @@ def _rank_main(rank: int, world_size: int, port: int, backend: str, parallel_kwa
     dist.init_process_group(backend=backend, rank=rank, world_size=world_size)
     try:
         parallel = ParallelConfig(device_ids=list(range(world_size)), **parallel_kwargs)
-        out = tiny_wan_denoise(parallel, device=device, dtype=getattr(torch, dtype_name))
+        out = tiny_wan_denoise(parallel, device=device, dtype=getattr(torch, dtype_name), preset=preset)
         if rank == 0:
             torch.save(out, out_path)
         dist.barrier()
@@ -76,13 +79,15 @@ def _rank_main(rank: int, world_size: int, port: int, backend: str, parallel_kwa
         dist.destroy_process_group()
 
 
-def spawn_tiny_wan_denoise(world_size: int, backend: str = "gloo", dtype=torch.float32, **parallel_kwargs):
+def spawn_tiny_wan_denoise(world_size: int, backend: str = "gloo", dtype=torch.float32, preset: str = "tiny",
+                           **parallel_kwargs):  # fmt: skip
     from telefuser_b200.utils.system import find_free_port
 
     with tempfile.TemporaryDirectory() as d:
         out_path = os.path.join(d, "out.pt")
         mp.spawn(_rank_main, nprocs=world_size, join=True,
-                 args=(world_size, find_free_port(), backend, parallel_kwargs, out_path, str(dtype).split(".")[-1]))  # fmt: skip
+                 args=(world_size, find_free_port(), backend, parallel_kwargs, out_path, str(dtype).split(".")[-1],
+                       preset))  # fmt: skip
         return torch.load(out_path)
 
 
