@@ -1,0 +1,333 @@
+"""LingBot-World-Fast pipeline and its streaming runtime.
+
+`LingBotWorldFastPipeline` owns three stages (condition encode, chunk denoise, chunk decode)
+and one `LingBotWorldFastStreamingRuntime`: a `StreamingPipelineOrchestrator` graph
+
+    encode_request -> [encode] -> condition -+
+                                   control  -+-> [denoise] -> latent -> [decode] -> frames
+
+with edge capacity 2, so encode(k+1), denoise(k) and decode(k-1) overlap. Stages that are plain
+objects run behind `LocalStageActor`s (tensors stay on the device), stages wrapped in a
+`ParallelWorker` behind `ParallelWorkerStageActor`s. Role parity:
+telefuser/pipelines/lingbot_world_fast/pipeline.py:66-620, streaming.py:52-419, session.py.
+"""
+
+from __future__ import annotations
+
+import itertools
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+from telefuser_b200.core.base_pipeline import BasePipeline
+from telefuser_b200.core.config import ModelRuntimeConfig
+from telefuser_b200.orchestrator import (LocalStageActor, StreamingEdgeSpec, StreamingPipelineOrchestrator,
+                                         StreamingPipelineSpec, StreamingSessionStatus, StreamingStageSpec)  # fmt: skip
+from telefuser_b200.orchestrator.worker_actor import ParallelWorkerStageActor
+from telefuser_b200.utils.logging import logger
+from telefuser_b200.worker.parallel_worker import ParallelWorker
+
+from .control import (LingBotWorldFastControlBuilder, LingBotWorldFastControlContext, pinhole_intrinsics,
+                      random_walk_trajectory)  # fmt: skip
+from .stages import LingBotWorldFastDenoisingStage, LingBotWorldFastVAEDecodeStage, LingBotWorldFastVAEEncodeStage
+
+
+@dataclass
+class LingBotWorldFastPipelineConfig:
+    dit_config: ModelRuntimeConfig = field(default_factory=ModelRuntimeConfig)
+    vae_encode_config: ModelRuntimeConfig = field(default_factory=ModelRuntimeConfig)
+    vae_decode_config: ModelRuntimeConfig = field(default_factory=ModelRuntimeConfig)
+    text_encoding_config: ModelRuntimeConfig = field(default_factory=ModelRuntimeConfig)
+    chunk_size: int = 4  # latent frames per chunk
+    local_attn_size: int = 18  # latent frames attended to (-1: unbounded)
+    sink_size: int = 6
+    timestep_indices: tuple = (0, 250, 500, 750)
+    sample_shift: float = 10.0
+    max_sequence_length: int = 512
+    fps: int = 16
+    control_type: str = "cam"
+    enable_denoising_parallel: bool = False
+    edge_capacity: int = 2
+
+
+@dataclass
+class LingBotWorldFastGenerationSession:
+    cache_handle: int
+    prompt_emb: torch.Tensor
+    chunk_count: int
+    chunk_size: int
+    height: int
+    width: int
+    latent_h: int
+    latent_w: int
+    frame_tokens: int
+    kv_size: int
+    max_attention_size: int
+    control_builder: LingBotWorldFastControlBuilder
+    created_at: float = field(default_factory=time.monotonic)
+
+
+@dataclass(frozen=True)
+class LingBotWorldFastStreamingSession:
+    session_id: str
+    session_epoch: int
+    cache_handle: int
+
+
+def _call(stage, name: str, *args):
+    """Calls a stage method, in process or through a ParallelWorker."""
+    if isinstance(stage, ParallelWorker):
+        return stage.call(name, *args)
+    return getattr(stage, name)(*args)
+
+
+class LingBotWorldFastStreamingRuntime:
+    def __init__(self, pipeline: "LingBotWorldFastPipeline") -> None:
+        self.pipeline = pipeline
+        self._lock = threading.RLock()
+        self._sessions: dict[str, tuple[LingBotWorldFastGenerationSession, int]] = {}
+        self._closed = False
+        cap = pipeline.config.edge_capacity
+        actors = {
+            "encode": self._actor("encode", pipeline.vae_encode_stage, "encode_condition_chunk", self._encode_inputs,
+                                  lambda r, inv: {"condition": r}, self._release("vae_encode_stage")),  # fmt: skip
+            "denoise": self._actor("denoise", pipeline.denoise_stage, "denoise_and_update_cache", self._denoise_inputs,
+                                   lambda r, inv: {"latent": r}, self._release("denoise_stage")),  # fmt: skip
+            "decode": self._actor("decode", pipeline.vae_decode_stage, "decode_chunk", self._decode_inputs,
+                                  lambda r, inv: {"frames": r}, self._release("vae_decode_stage")),  # fmt: skip
+        }
+        spec = StreamingPipelineSpec(
+            stages=(StreamingStageSpec("encode", {"encode_request"}, {"condition"}),
+                    StreamingStageSpec("denoise", {"condition", "control"}, {"latent"}),
+                    StreamingStageSpec("decode", {"latent"}, {"frames"})),
+            edges=(StreamingEdgeSpec("encode_request", "encode", None, cap),
+                   StreamingEdgeSpec("condition", "denoise", "encode", cap),
+                   StreamingEdgeSpec("control", "denoise", None, cap),
+                   StreamingEdgeSpec("latent", "decode", "denoise", cap)),
+            output_artifacts=frozenset({"frames"}), output_capacity_per_session=cap)  # fmt: skip
+        self.orchestrator = StreamingPipelineOrchestrator(spec, actors)
+
+    # ---- actor construction ---------------------------------------------------------
+    def _actor(self, stage_id, stage, method, input_builder, output_builder, session_closer):
+        if isinstance(stage, ParallelWorker):
+            return ParallelWorkerStageActor(stage, method, input_builder, output_builder, close_worker=False,
+                                            session_closer=session_closer)  # fmt: skip
+
+        def handler(inv):
+            args, kwargs = input_builder(inv)
+            return output_builder(getattr(stage, method)(*args, **kwargs), inv)
+
+        return LocalStageActor(stage_id, handler, 1, session_closer)
+
+    def _release(self, stage_attr: str):
+        def closer(ctx, reason):
+            entry = self._sessions.get(ctx.session_id)
+            if entry is not None and entry[1] == ctx.session_epoch:
+                _call(getattr(self.pipeline, stage_attr), "release_cache", entry[0].cache_handle)
+
+        return closer
+
+    def _entry(self, session_id: str) -> LingBotWorldFastGenerationSession:
+        return self._sessions[session_id][0]
+
+    def _encode_inputs(self, inv):
+        rt = self._entry(inv.key.session_id)
+        return (rt.cache_handle, inv.key.sequence_id, rt.chunk_count, rt.chunk_size, rt.height, rt.width), {}
+
+    def _denoise_inputs(self, inv):
+        rt = self._entry(inv.key.session_id)
+        control = inv.inputs["control"]
+        if callable(control):
+            control = control()
+        start = inv.key.sequence_id * rt.chunk_size * rt.frame_tokens
+        return (rt.cache_handle, inv.inputs["condition"], rt.prompt_emb, control, start, rt.max_attention_size), {}
+
+    def _decode_inputs(self, inv):
+        rt = self._entry(inv.key.session_id)
+        return (rt.cache_handle, inv.inputs["latent"]), {}
+
+    # ---- session API ---------------------------------------------------------------------
+    def create_session(self, runtime: LingBotWorldFastGenerationSession) -> LingBotWorldFastStreamingSession:
+        sid = f"lingbot-{runtime.cache_handle}"
+        with self._lock:
+            if self._closed:
+                raise RuntimeError("LingBot streaming runtime is closed")
+            if sid in self._sessions:
+                raise ValueError(f"LingBot streaming session {sid!r} already exists")
+            epoch = self.orchestrator.create_session(sid, final_sequence_id=runtime.chunk_count - 1)
+            self._sessions[sid] = (runtime, epoch)
+        return LingBotWorldFastStreamingSession(sid, epoch, runtime.cache_handle)
+
+    def can_submit_chunk(self, session) -> bool:
+        try:
+            if self.orchestrator.status(session.session_id) != StreamingSessionStatus.RUNNING:
+                return False
+            return self.orchestrator.can_push_inputs(session.session_id, ("encode_request", "control"))
+        except RuntimeError:
+            return False
+
+    def try_submit_chunk(self, session, chunk_index: int, control) -> bool:
+        return self.orchestrator.try_push_inputs(session.session_id, chunk_index,
+                                                 {"encode_request": chunk_index, "control": control})  # fmt: skip
+
+    def poll_frames(self, session) -> list:
+        """[(chunk_index, frames)] in order."""
+        return [(seq, v) for seq, _, v in self.orchestrator.poll_outputs(session.session_id)]
+
+    def status(self, session) -> StreamingSessionStatus:
+        return self.orchestrator.status(session.session_id)
+
+    def error(self, session):
+        return self.orchestrator.error(session.session_id)
+
+    def metrics(self, session) -> dict:
+        m = self.orchestrator.session_metrics(session.session_id)
+        idle = {s: [i.idle_seconds for i in self.orchestrator.stage_idle_intervals(session.session_id, s)]
+                for s in ("encode", "denoise", "decode")}  # fmt: skip
+        busy = {}
+        for s in ("encode", "denoise", "decode"):
+            t = self.orchestrator.stage_timings(session.session_id, s)
+            busy[s] = [x.completed_at - x.admitted_at for x in t if x.completed_at and x.admitted_at]
+        return {"first_output_latency_s": m.first_output_latency_seconds,
+                "chunk_period_p50_s": m.chunk_period.p50_seconds, "chunk_period_p95_s": m.chunk_period.p95_seconds,
+                "control_to_output_p50_s": m.control_to_output_latency.p50_seconds, "chunks": len(m.output_emitted_at),
+                "stage_busy_s": busy, "stage_idle_s": idle}  # fmt: skip
+
+    def close_session(self, session, cancel: bool = False) -> None:
+        try:
+            (self.orchestrator.cancel_session if cancel else self.orchestrator.close_session)(session.session_id, 30.0)
+        finally:
+            with self._lock:
+                self._sessions.pop(session.session_id, None)
+
+    def close(self) -> None:
+        with self._lock:
+            if self._closed:
+                return
+            self._closed = True
+        self.orchestrator.close()
+
+
+class LingBotWorldFastPipeline(BasePipeline):
+    def __init__(self, device="cuda", torch_dtype=torch.bfloat16) -> None:
+        super().__init__(device=device, torch_dtype=torch_dtype)
+        self._handles = itertools.count(1)
+        self.runtime: LingBotWorldFastStreamingRuntime | None = None
+
+    def _get_stages(self) -> list:
+        return [self.vae_encode_stage, self.denoise_stage, self.vae_decode_stage]
+
+    def init(self, module_manager, config: LingBotWorldFastPipelineConfig, text_stage=None):
+        self.config = config
+        self._model_info = module_manager.get_model_info()
+        self.vae_encode_stage = LingBotWorldFastVAEEncodeStage("vae_encode", module_manager, config.vae_encode_config)
+        self.vae_decode_stage = LingBotWorldFastVAEDecodeStage("vae_decode", module_manager, config.vae_decode_config)
+        self.denoise_stage = LingBotWorldFastDenoisingStage("denoise", module_manager, config.dit_config)
+        self.dit_meta = dict(patch=self.denoise_stage.dit.patch_size, control_type=self.denoise_stage.dit.control_type)
+        for st in (self.vae_encode_stage, self.vae_decode_stage, self.denoise_stage):
+            st.onload_models_flag = True
+        if config.enable_denoising_parallel:
+            self.denoise_stage = ParallelWorker(self.denoise_stage)
+        self.text_encoding_stage = text_stage
+        if text_stage is None and module_manager.fetch_module("wan_video_text_encoder") is not None:
+            from telefuser_b200.pipelines.wan.stages import TextEncodingStage
+
+            self.text_encoding_stage = TextEncodingStage("text_encoding", module_manager, config.text_encoding_config,
+                                                         config.max_sequence_length)  # fmt: skip
+        self.runtime = LingBotWorldFastStreamingRuntime(self)
+
+    # ---- sessions -------------------------------------------------------------------------
+    def _create_initialized_session(self, prompt, image, num_frames: int, height: int, width: int, seed: int = 0,
+                                    prompt_emb: torch.Tensor | None = None) -> LingBotWorldFastGenerationSession:  # fmt: skip
+        cfg = self.config
+        if (num_frames - 1) % 4:
+            raise ValueError(f"num_frames must be 4n+1, got {num_frames}")
+        latent_frames = (num_frames - 1) // 4 + 1
+        if latent_frames % cfg.chunk_size:
+            raise ValueError(f"{latent_frames} latent frames are not a multiple of chunk size {cfg.chunk_size}")
+        latent_h, latent_w = height // 8, width // 8
+        patch = self.dit_meta["patch"]
+        frame_tokens = (latent_h // patch[1]) * (latent_w // patch[2])
+        window = cfg.local_attn_size if cfg.local_attn_size != -1 else latent_frames
+        kv_size = frame_tokens * window
+        if prompt_emb is None:
+            prompt_emb = self.text_encoding_stage.process([prompt])[0]
+        if isinstance(image, torch.Tensor):
+            cond = image
+        else:
+            cond = self.preprocess_image(image, height, width)[0]
+        handle = next(self._handles)
+        noise_shape = (1, 16, cfg.chunk_size, latent_h, latent_w)
+        _call(self.vae_encode_stage, "initialize_cache", handle, cond)
+        _call(self.vae_decode_stage, "initialize_cache", handle)
+        _call(self.denoise_stage, "initialize_cache", handle, 1, kv_size, cfg.max_sequence_length, cfg.sample_shift,
+              seed, seed + 1, noise_shape, tuple(cfg.timestep_indices), frame_tokens)  # fmt: skip
+        ctx = LingBotWorldFastControlContext(
+            control_type=self.dit_meta["control_type"], device=self.device, control_dtype=self.torch_dtype,
+            orig_height=height, orig_width=width, height=height, width=width, latent_h=latent_h, latent_w=latent_w,
+            latent_frames=latent_frames, chunk_size=cfg.chunk_size, intrinsics=pinhole_intrinsics(height, width))  # fmt: skip
+        return LingBotWorldFastGenerationSession(
+            cache_handle=handle, prompt_emb=prompt_emb, chunk_count=latent_frames // cfg.chunk_size,
+            chunk_size=cfg.chunk_size, height=height, width=width, latent_h=latent_h, latent_w=latent_w,
+            frame_tokens=frame_tokens, kv_size=kv_size, max_attention_size=kv_size,
+            control_builder=LingBotWorldFastControlBuilder(ctx))  # fmt: skip
+
+    def release_session(self, session: LingBotWorldFastStreamingSession, cancel: bool = False) -> None:
+        self.runtime.close_session(session, cancel)
+
+    # ---- offline generation through the streaming graph ---------------------------------------
+    @torch.no_grad()
+    def generate_video(self, prompt, image, num_frames: int = 61, height: int = 480, width: int = 832, seed: int = 0,
+                       poses: torch.Tensor | None = None, prompt_emb=None, on_chunk: Callable | None = None,
+                       timeout_s: float = 3600.0):  # fmt: skip
+        """Returns (frames [1, 3, T, H, W], metrics). `poses`: [latent_frames, 4, 4] camera path (default: seeded walk)."""
+        rt = self._create_initialized_session(prompt, image, num_frames, height, width, seed, prompt_emb)
+        latent_frames = rt.chunk_count * rt.chunk_size
+        if poses is None:
+            poses = random_walk_trajectory(latent_frames, seed=seed)
+        controls = rt.control_builder.build_sequence(poses, rt.control_builder.context.intrinsics)
+        session = self.runtime.create_session(rt)
+        frames, nxt, t0 = {}, 0, time.monotonic()
+        try:
+            while len(frames) < rt.chunk_count:
+                if time.monotonic() - t0 > timeout_s:
+                    raise TimeoutError("LingBot generation timed out")
+                if self.runtime.status(session) == StreamingSessionStatus.FAILED:
+                    raise RuntimeError("LingBot streaming session failed") from self.runtime.error(session)
+                progressed = False
+                if nxt < rt.chunk_count and self.runtime.try_submit_chunk(session, nxt, controls[nxt]):
+                    nxt += 1
+                    progressed = True
+                for idx, f in self.runtime.poll_frames(session):
+                    frames[idx] = f
+                    progressed = True
+                    if on_chunk is not None:
+                        on_chunk(idx, f)
+                if not progressed:
+                    time.sleep(0.001)
+            metrics = self.runtime.metrics(session)
+        finally:
+            self.release_session(session, cancel=len(frames) < rt.chunk_count)
+        video = torch.cat([frames[i] for i in range(rt.chunk_count)], dim=2)
+        return video, metrics
+
+    def warmup(self, height: int = 480, width: int = 832, chunks: int = 2) -> None:
+        cs = self.config.chunk_size
+        n = (cs * chunks - 1) * 4 + 1
+        emb = torch.zeros(1, self.config.max_sequence_length, self.denoise_stage_text_dim(), device=self.device,
+                          dtype=self.torch_dtype)  # fmt: skip
+        self.generate_video("", torch.zeros(3, height, width), n, height, width, prompt_emb=emb)
+
+    def denoise_stage_text_dim(self) -> int:
+        st = self.denoise_stage.stage if isinstance(self.denoise_stage, ParallelWorker) else self.denoise_stage
+        return st.dit.text_dim
+
+    def close(self) -> None:
+        if self.runtime is not None:
+            self.runtime.close()
+        if isinstance(self.denoise_stage, ParallelWorker):
+            self.denoise_stage.close()
+        logger.info("LingBot pipeline closed")
