@@ -1,0 +1,201 @@
+"""Pipeline-file contract: what a served pipeline module declares and how requests are checked against it.
+
+A pipeline file exposes `get_pipeline(parallelism=...)` + `run_with_file(...)` (request/response) or
+`get_service(gpu_num=...)` (streaming) and may declare `PIPELINE_MANIFEST` / `PIPELINE_CONTRACT` /
+`get_pipeline_contract()`: supported tasks, media type, required inputs and typed parameters with
+defaults. Without a declaration a legacy contract is inferred from `run_with_file`'s signature.
+Role parity: telefuser/service/core/pipeline_contract.py, contract_templates.py,
+telefuser/service/api/task_contract_runtime.py:13-148.
+"""
+
+from __future__ import annotations
+
+import inspect
+import re
+from dataclasses import dataclass, field
+from types import ModuleType
+from typing import Any
+
+from .task_manager import IMAGE_TASKS, VIDEO_TASKS
+
+TASK_NAME = re.compile(r"^[a-z][a-z0-9_]{1,31}$")
+INPUT_FIELDS = ("prompt", "negative_prompt", "first_image_path", "last_image_path", "ref_video_path", "audio_path",
+                "mask_path")  # fmt: skip
+
+
+def infer_media_type_for_task(task: str) -> str:
+    if task in IMAGE_TASKS:
+        return "image"
+    if task in VIDEO_TASKS:
+        return "video"
+    return "stream" if task == "bidirectional" else "video"
+
+
+def validate_task_name_format(task: str) -> str:
+    t = str(task).strip().lower()
+    if not TASK_NAME.match(t):
+        raise ValueError(f"invalid task name {task!r}")
+    return t
+
+
+def _strs(v) -> tuple:
+    if v is None:
+        return ()
+    if isinstance(v, str):
+        return (v,)
+    return tuple(str(x) for x in v)
+
+
+def _infer_type(default: Any) -> str:
+    for t, name in ((bool, "boolean"), (int, "integer"), (float, "number"), (str, "string")):
+        if isinstance(default, t):
+            return name
+    return "object" if isinstance(default, (dict, list, tuple)) else "string"
+
+
+@dataclass(frozen=True)
+class ParameterContract:
+    type: str
+    required: bool = False
+    default: Any = None
+    description: str = ""
+    enum: tuple = ()
+    exposed: bool = True
+
+    @classmethod
+    def from_mapping(cls, raw: dict) -> "ParameterContract":
+        return cls(str(raw.get("type") or _infer_type(raw.get("default"))), bool(raw.get("required", False)),
+                   raw.get("default"), str(raw.get("description") or ""), _strs(raw.get("enum")),
+                   bool(raw.get("exposed", True)))  # fmt: skip
+
+    def to_metadata(self) -> dict:
+        return {"type": self.type, "required": self.required, "default": self.default, "description": self.description,
+                "enum": list(self.enum), "exposed": self.exposed}  # fmt: skip
+
+    def check(self, name: str, value: Any) -> None:
+        ok = {"integer": lambda v: isinstance(v, int) and not isinstance(v, bool),
+              "number": lambda v: isinstance(v, (int, float)) and not isinstance(v, bool),
+              "boolean": lambda v: isinstance(v, bool), "string": lambda v: isinstance(v, str)}.get(self.type)  # fmt: skip
+        if ok is not None and value is not None and not ok(value):
+            raise ValueError(f"parameter {name} must be of type {self.type}")
+        if self.enum and value is not None and str(value) not in self.enum:
+            raise ValueError(f"parameter {name} must be one of {list(self.enum)}")
+
+
+@dataclass(frozen=True)
+class TaskContract:
+    task: str
+    media_type: str
+    required_inputs: tuple = ()
+    optional_inputs: tuple = ()
+    parameters: dict = field(default_factory=dict)
+
+    @classmethod
+    def from_mapping(cls, task: str, raw: dict) -> "TaskContract":
+        t = validate_task_name_format(task)
+        params = {k: (v if isinstance(v, ParameterContract) else ParameterContract.from_mapping(v if isinstance(v, dict) else {"default": v}))
+                  for k, v in (raw.get("parameters") or {}).items()}  # fmt: skip
+        return cls(t, str(raw.get("media_type") or infer_media_type_for_task(t)), _strs(raw.get("required_inputs")),
+                   _strs(raw.get("optional_inputs")), params)  # fmt: skip
+
+    def to_metadata(self) -> dict:
+        return {"media_type": self.media_type, "required_inputs": list(self.required_inputs),
+                "optional_inputs": list(self.optional_inputs),
+                "parameters": {n: c.to_metadata() for n, c in self.parameters.items() if c.exposed}}  # fmt: skip
+
+
+@dataclass(frozen=True)
+class PipelineContract:
+    contract_version: str
+    pipeline_name: str
+    supported_tasks: tuple
+    supported_media_types: tuple
+    execution_mode: str
+    effective_max_concurrent_tasks: int
+    task_contracts: dict
+    get_pipeline: str = "get_pipeline"
+    run_with_file: str = "run_with_file"
+
+    @classmethod
+    def from_mapping(cls, raw: dict, fallback_name: str) -> "PipelineContract":
+        name = str(raw.get("pipeline_name") or fallback_name).strip()
+        if not name:
+            raise ValueError("Pipeline contract requires a non-empty pipeline_name")
+        tasks = tuple(validate_task_name_format(t) for t in _strs(raw.get("supported_tasks")))
+        if not tasks:
+            raise ValueError("Pipeline contract requires at least one supported task")
+        tcs = {t: TaskContract.from_mapping(t, (raw.get("task_contracts") or raw.get("tasks") or {}).get(t, {})) for t in tasks}
+        media = _strs(raw.get("supported_media_types")) or tuple(sorted({c.media_type for c in tcs.values()}))
+        ep = raw.get("entrypoints") or {}
+        return cls(str(raw.get("contract_version") or "1"), name, tasks, media, str(raw.get("execution_mode") or "sync"),
+                   int(raw.get("effective_max_concurrent_tasks") or 1), tcs, ep.get("get_pipeline", "get_pipeline"),
+                   ep.get("run_with_file", "run_with_file"))  # fmt: skip
+
+    def to_metadata(self) -> dict:
+        return {"contract_version": self.contract_version, "pipeline_name": self.pipeline_name,
+                "supported_tasks": list(self.supported_tasks), "supported_media_types": list(self.supported_media_types),
+                "execution_mode": self.execution_mode, "effective_max_concurrent_tasks": self.effective_max_concurrent_tasks,
+                "tasks": {t: c.to_metadata() for t, c in self.task_contracts.items()}}  # fmt: skip
+
+
+TASK_TEMPLATES = {
+    "t2v": {"required_inputs": ["prompt"], "optional_inputs": ["negative_prompt"]},
+    "i2v": {"required_inputs": ["prompt", "first_image_path"], "optional_inputs": ["negative_prompt", "last_image_path"]},
+    "fl2v": {"required_inputs": ["prompt", "first_image_path", "last_image_path"], "optional_inputs": ["negative_prompt"]},
+    "vc": {"required_inputs": ["ref_video_path"], "optional_inputs": ["prompt"]},
+    "s2v": {"required_inputs": ["first_image_path", "audio_path"], "optional_inputs": ["prompt"]},
+    "vsr": {"required_inputs": ["ref_video_path"]},
+    "t2i": {"required_inputs": ["prompt"], "optional_inputs": ["negative_prompt"]},
+    "i2i": {"required_inputs": ["prompt", "first_image_path"]},
+    "edit": {"required_inputs": ["prompt", "first_image_path"], "optional_inputs": ["mask_path"]},
+}
+
+
+def legacy_contract_from_module(module: ModuleType, task: str, name: str) -> PipelineContract:
+    """Infers a contract from `run_with_file`'s signature: defaults become parameters."""
+    fn = getattr(module, "run_with_file", None)
+    params = {}
+    if fn is not None:
+        for pname, p in inspect.signature(fn).parameters.items():
+            if pname in INPUT_FIELDS or pname in ("pipeline", "pipe", "output_path", "task", "kwargs"):
+                continue
+            if p.default is not inspect.Parameter.empty:
+                params[pname] = {"default": p.default}
+    tc = dict(TASK_TEMPLATES.get(task, {}))
+    tc["parameters"] = params
+    return PipelineContract.from_mapping({"pipeline_name": name, "supported_tasks": [task], "task_contracts": {task: tc}},
+                                         fallback_name=name)  # fmt: skip
+
+
+def load_contract(module: ModuleType, task: str | None, name: str) -> PipelineContract:
+    for attr in ("PIPELINE_MANIFEST", "PIPELINE_CONTRACT"):
+        raw = getattr(module, attr, None)
+        if isinstance(raw, dict):
+            return PipelineContract.from_mapping(raw, fallback_name=name)
+    fn = getattr(module, "get_pipeline_contract", None)
+    if callable(fn):
+        raw = fn()
+        return raw if isinstance(raw, PipelineContract) else PipelineContract.from_mapping(raw, fallback_name=name)
+    return legacy_contract_from_module(module, task or "t2v", name)
+
+
+def apply_task_contract_defaults(contract: PipelineContract, task: str, data: dict) -> dict:
+    if task not in contract.task_contracts:
+        raise ValueError(f"task {task!r} is not supported by pipeline {contract.pipeline_name} "
+                         f"(supported: {list(contract.supported_tasks)})")  # fmt: skip
+    out = dict(data)
+    for name, pc in contract.task_contracts[task].parameters.items():
+        if out.get(name) is None and pc.default is not None:
+            out[name] = pc.default
+    return out
+
+
+def validate_required_task_parameters(contract: PipelineContract, task: str, data: dict) -> None:
+    tc = contract.task_contracts[task]
+    missing = [f for f in tc.required_inputs if not data.get(f)]
+    missing += [n for n, pc in tc.parameters.items() if pc.required and data.get(n) is None]
+    if missing:
+        raise ValueError(f"missing required field(s) for task {task}: {missing}")
+    for n, pc in tc.parameters.items():
+        if n in data:
+            pc.check(n, data[n])
