@@ -72,6 +72,8 @@ class T5Attention(nn.Module):
         q = TF.linear(x, self.q.weight).view(B, L, H, D).transpose(1, 2)
         k = TF.linear(x, self.k.weight).view(B, L, H, D).transpose(1, 2)
         v = TF.linear(x, self.v.weight).view(B, L, H, D).transpose(1, 2)
+        if pos_bias is not None and pos_bias.shape[1] != H:  # heads split over TP ranks
+            pos_bias = pos_bias[:, getattr(self, "head_start", 0) :][:, :H]
         bias = pos_bias.to(q.dtype) if pos_bias is not None else torch.zeros(1, H, L, L, device=x.device, dtype=q.dtype)
         if mask is not None:
             m = mask.view(B, 1, 1, -1) if mask.dim() == 2 else mask.unsqueeze(1)
@@ -93,8 +95,9 @@ class T5FeedForward(nn.Module):
         w = self.gate[0].weight
         if self._fused is None or self._fused.data_ptr() != w.data_ptr() or self._fused.dtype != w.dtype:
             W = torch.cat([self.gate[0].weight.data, self.fc1.weight.data], dim=0)
-            self.gate[0].weight.data = W[: self.dim_ffn]
-            self.fc1.weight.data = W[self.dim_ffn :]
+            n = W.shape[0] // 2  # local width: the weights may be TP shards
+            self.gate[0].weight.data = W[:n]
+            self.fc1.weight.data = W[n:]
             self._fused = W
         return self._fused
 
@@ -137,6 +140,14 @@ class WanTextEncoder(BaseModel):
         for blk in self.blocks:
             x = blk(x, mask, e)
         return self.norm(x)
+
+    def get_tp_plan(self) -> dict:
+        """Megatron split: q/k/v and gate/fc1 by output features (heads), o and fc2 by input features
+        with one all-reduce after each attention and FFN."""
+        return {"blocks.*.attn.q": "colwise", "blocks.*.attn.k": "colwise", "blocks.*.attn.v": "colwise",
+                "blocks.*.attn.o": "rowwise", "blocks.*.attn": ["heads", "allreduce"],
+                "blocks.*.ffn.gate.0": "colwise", "blocks.*.ffn.fc1": "colwise", "blocks.*.ffn.fc2": "rowwise",
+                "blocks.*.ffn": "allreduce"}  # fmt: skip
 
     @staticmethod
     def state_dict_converter():

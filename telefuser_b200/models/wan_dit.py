@@ -122,10 +122,27 @@ class AffineLayerNorm(nn.Module):
         return TF.layernorm_modulate(x, shift, scale, self.weight, self.bias, self.eps)
 
 
+def _rows_adjacent(ts: list[torch.Tensor]) -> bool:
+    """True if the contiguous tensors `ts` follow one another in one storage without gaps."""
+    base = ts[0].untyped_storage().data_ptr()
+    nxt = ts[0].data_ptr()
+    for t in ts:
+        if not t.is_contiguous() or t.untyped_storage().data_ptr() != base or t.data_ptr() != nxt:
+            return False
+        nxt += t.numel() * t.element_size()
+    return True
+
+
 def _fuse_linear_weights(linears: list[nn.Linear]):
     """Re-homes the weights/biases of `linears` as row slices of one buffer; returns (W, b)."""
     w0 = linears[0].weight
     n = [lin.weight.shape[0] for lin in linears]
+    if _rows_adjacent([lin.weight.data for lin in linears]) and (
+            linears[0].bias is None or _rows_adjacent([lin.bias.data for lin in linears])):  # fmt: skip
+        # Already row slices of one buffer (e.g. re-homed by the weight-sharding wrapper): view, no copy.
+        W = torch.as_strided(w0.data, (sum(n), w0.shape[1]), (w0.shape[1], 1))
+        b = torch.as_strided(linears[0].bias.data, (sum(n),), (1,)) if linears[0].bias is not None else None
+        return W, b
     W = torch.empty(sum(n), w0.shape[1], dtype=w0.dtype, device=w0.device)
     b = torch.empty(sum(n), dtype=w0.dtype, device=w0.device) if linears[0].bias is not None else None
     o = 0
@@ -167,11 +184,9 @@ class WanSelfAttention(nn.Module):
         TF.rmsnorm_rope_(q, self.norm_q.weight, H, cos, sin, self.norm_q.eps, x2=k, weight2=self.norm_k.weight)
         q, k, v = (t.unflatten(-1, (H, D)) for t in (q, k, v))
         if usp:
-            hq = ulysses.scatter_heads(q, async_op=True)
-            hk = ulysses.scatter_heads(k, async_op=True)
-            hv = ulysses.scatter_heads(v, async_op=True)
-            o = TF.attention(hq.wait(), hk.wait(), hv.wait())
-            o = ulysses.gather_heads(o)
+            from telefuser_b200.parallel.ring import long_context_attention
+
+            o = long_context_attention(q, k, v)  # Ulysses, ring or both, by the mesh's SP degrees
         else:
             o = TF.attention(q, k, v)
         return o.reshape(B, S, C)
@@ -247,6 +262,11 @@ class WanBlock(nn.Module):
         x = TF.linear(c, self.cross_attn.o.weight, self.cross_attn.o.bias, residual=x)
         h = self.norm2(x, shift_mlp, scale_mlp)
         h = TF.linear(h, self.ffn[0].weight, self.ffn[0].bias, act="gelu_tanh")
+        if getattr(self, "tp_size", 1) > 1:  # FFN split over TP ranks: partial sums meet before the gate
+            from telefuser_b200.parallel.tp import all_reduce_sum
+
+            y = all_reduce_sum(TF.linear(h, self.ffn[2].weight, self.ffn[2].bias), self.tp_group)
+            return TF.gated_residual(x, y, gate_mlp)
         x = TF.linear(h, self.ffn[2].weight, self.ffn[2].bias, residual=x, gate=gate_mlp)
         return x
 
@@ -361,7 +381,14 @@ class WanModel(BaseModel):
         h = TF.linear(context.to(self.dtype), te[0].weight, te[0].bias, act="gelu_tanh")
         return TF.linear(h, te[2].weight, te[2].bias)
 
-    def enable_pp(self, start: int, end: int) -> None:
+    def enable_pp(self, start: int | None = None, end: int | None = None, pp_group=None) -> None:
+        from telefuser_b200.parallel.pp import PipelineP2PComm
+
+        if pp_group is None and self.device_mesh is not None and self.device_mesh.size("pp") > 1:
+            pp_group = self.device_mesh.group("pp")
+        self.pp_comm = PipelineP2PComm(pp_group)
+        if start is None or end is None:
+            start, end = self.pp_comm.get_stage_indices(self.num_layers)
         self.pp_flag = True
         self.pp_start_idx, self.pp_end_idx = start, end
 
@@ -397,12 +424,21 @@ class WanModel(BaseModel):
         if self.usp_flag:
             x, t_mod, t, cos, sin = pshard.sequence_parallel_shard([x, t_mod, t, cos, sin], [1, 1, 1, 0, 0])
         ori_x = x
-        cache = self.feature_cache
-        if cache.should_compute(cond_flag):
+        if self.pp_flag and self.pp_comm.world_size > 1:
+            # Each stage embeds for itself; only the token stream crosses the stage boundary.
+            if not self.pp_comm.is_first:
+                x = self.pp_comm.recv_latent(tuple(x.shape), x.dtype, x.device)
             x = self.forward_blocks(x, context, t_mod, cos, sin)
-            cache.update(x, ori_x, cond_flag)
+            if not self.pp_comm.is_last:
+                self.pp_comm.send_latent(x)
+                return None
         else:
-            x = cache.approximate(x, cond_flag)
+            cache = self.feature_cache
+            if cache.should_compute(cond_flag):
+                x = self.forward_blocks(x, context, t_mod, cos, sin)
+                cache.update(x, ori_x, cond_flag)
+            else:
+                x = cache.approximate(x, cond_flag)
         x = self.head(x, t)
         if self.usp_flag:
             (x,) = pshard.sequence_parallel_unshard([x], [1], [seq_len])
@@ -413,16 +449,11 @@ class WanModel(BaseModel):
         return ["blocks"]
 
     def get_tp_plan(self) -> dict[str, str]:
-        """Column / row split of every projection (same split as the reference plan,
-        telefuser/models/wan_video_dit.py:1228-1304)."""
-        plan = {}
-        for name in ("self_attn", "cross_attn"):
-            for p in ("q", "k", "v"):
-                plan[f"blocks.*.{name}.{p}"] = "colwise"
-            plan[f"blocks.*.{name}.o"] = "rowwise"
-        plan["blocks.*.ffn.0"] = "colwise"
-        plan["blocks.*.ffn.2"] = "rowwise"
-        return plan
+        """FFN column / row split (the FFN holds 2/3 of a block's weights). The attention projections
+        stay replicated: q/k RMSNorm runs over the full hidden width, which a head split would cut.
+        The reference plan (telefuser/models/wan_video_dit.py:1228-1304) lists the attention
+        projections as well but is not wired to any pipeline."""
+        return {"blocks.*.ffn.0": "colwise", "blocks.*.ffn.2": "rowwise", "blocks.*": "group"}
 
     @staticmethod
     def state_dict_converter():

@@ -64,7 +64,7 @@ class WanDenoisingStage(BaseStage):
             from telefuser_b200.parallel.pp import stage_block_range
 
             start, end = stage_block_range(self.dit.num_layers, cfg.pp_degree, self.mesh.coord("pp"))
-            self.dit.enable_pp(start, end)
+            self.dit.enable_pp(start, end, self.mesh.group("pp"))
         if cfg.tp_degree > 1:
             from telefuser_b200.parallel.tp import parallelize_module
 
@@ -85,6 +85,8 @@ class WanDenoisingStage(BaseStage):
             is_cond = self.mesh.coord("cfg") == 0
             ctx = prompt_emb_posi if is_cond else prompt_emb_nega
             mine = self.dit(latents, timestep, ctx, cond_flag=is_cond, **kw)
+            if mine is None:  # not the last pipeline stage: nothing to combine here
+                return None, None
             return pshard.cfg_parallel_unshard(mine, self.mesh)
         cond = self.dit(latents, timestep, prompt_emb_posi, cond_flag=True, **kw)
         if not use_cfg:

@@ -1,19 +1,90 @@
-"""CPU plumbing check: the tiny Wan-style DiT denoised on 2 gloo ranks with Ulysses
-sequence parallelism (and with CFG parallelism) must reproduce the single-process run."""
-import torch
+"""CPU plumbing checks: the tiny Wan-style DiT denoised on gloo ranks under each parallel strategy
+(Ulysses, ring, ring x Ulysses, CFG, pipeline, tensor, sharded weights) must reproduce the
+single-process run; plus unit checks of the stage split and of the TP text encoder."""
+import os
+import tempfile
 
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from telefuser_b200.parallel.pp import stage_block_range
 from telefuser_b200.testing.distributed_checks import spawn_tiny_wan_denoise, tiny_wan_denoise
 
 
-def test_ulysses2_matches_single_process():
-    ref = tiny_wan_denoise()
-    got = spawn_tiny_wan_denoise(2, sp_ulysses_degree=2)
-    assert ref.shape == (1, 16, 3, 8, 8)
-    assert torch.isfinite(ref).all()
-    assert (ref - got).abs().max().item() <= 1e-5
+@pytest.fixture(scope="module")
+def ref():
+    out = tiny_wan_denoise()
+    assert out.shape == (1, 16, 3, 8, 8) and torch.isfinite(out).all()
+    return out
 
 
-def test_cfg_parallel2_matches_single_process():
-    ref = tiny_wan_denoise()
-    got = spawn_tiny_wan_denoise(2, cfg_degree=2)
-    assert (ref - got).abs().max().item() <= 1e-5
+def test_ulysses2_matches_single_process(ref):
+    assert (ref - spawn_tiny_wan_denoise(2, sp_ulysses_degree=2)).abs().max().item() <= 1e-5
+
+
+def test_cfg_parallel2_matches_single_process(ref):
+    assert (ref - spawn_tiny_wan_denoise(2, cfg_degree=2)).abs().max().item() <= 1e-5
+
+
+def test_ring2_matches_single_process(ref):
+    assert (ref - spawn_tiny_wan_denoise(2, sp_ring_degree=2)).abs().max().item() <= 1e-5
+
+
+def test_usp_ring2_ulysses2_matches_single_process(ref):
+    assert (ref - spawn_tiny_wan_denoise(4, sp_ring_degree=2, sp_ulysses_degree=2)).abs().max().item() <= 1e-5
+
+
+def test_pipeline2_matches_single_process(ref):
+    assert (ref - spawn_tiny_wan_denoise(2, pp_degree=2)).abs().max().item() <= 1e-5
+
+
+def test_tensor_parallel2_matches_single_process(ref):
+    assert (ref - spawn_tiny_wan_denoise(2, tp_degree=2)).abs().max().item() <= 1e-5
+
+
+def test_sharded_weights2_match_single_process(ref):
+    assert (ref - spawn_tiny_wan_denoise(2, sp_ulysses_degree=2, enable_fsdp=True)).abs().max().item() <= 1e-5
+
+
+def test_stage_block_range():
+    assert [stage_block_range(40, 4, i) for i in range(4)] == [(0, 10), (10, 20), (20, 30), (30, 40)]
+    assert [stage_block_range(30, 4, i) for i in range(4)] == [(0, 8), (8, 16), (16, 23), (23, 30)]
+    with pytest.raises(ValueError):
+        stage_block_range(2, 4, 0)
+
+
+def _tp_encoder_rank(rank, world, port, path):
+    from telefuser_b200.models.umt5 import WanTextEncoder
+    from telefuser_b200.parallel.tp import parallelize_module
+
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        enc = WanTextEncoder(vocab=64, dim=32, dim_attn=32, dim_ffn=64, num_heads=4, num_layers=2, num_buckets=8).eval()
+        ids = torch.arange(12).view(1, 12) % 64
+        mask = torch.ones(1, 12, dtype=torch.long)
+        mask[:, 9:] = 0
+        full = enc(ids, mask)
+        parallelize_module(enc, dist.group.WORLD, enc.get_tp_plan())
+        assert enc.blocks[0].attn.q.weight.shape == (16, 32) and enc.blocks[0].attn.num_heads == 2
+        assert enc.blocks[0].ffn.fc2.weight.shape == (32, 32)
+        sharded = enc(ids, mask)
+        if rank == 0:
+            torch.save((full, sharded), path)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_text_encoder():
+    from telefuser_b200.utils.system import find_free_port
+
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "o.pt")
+        mp.spawn(_tp_encoder_rank, nprocs=2, join=True, args=(2, find_free_port(), path))
+        full, sharded = torch.load(path)
+    assert (full - sharded).abs().max().item() <= 1e-5
