@@ -45,14 +45,10 @@ class RollingKVCache:
         """Writes k/v ([B, n, H, D]) for absolute positions [current_start, current_start+n); returns local_end."""
         n = k.shape[1]
         evicted, lo, hi = self.plan(current_start, n)
-        if evicted > 0:
-            s = self.sink_tokens
-            keep = self.local_end - evicted - s
-            if keep > 0:
-                self.k[:, s : s + keep] = self.k[:, s + evicted : s + evicted + keep].clone()
-                self.v[:, s : s + keep] = self.v[:, s + evicted : s + evicted + keep].clone()
-        self.k[:, lo:hi] = k
-        self.v[:, lo:hi] = v
+        from telefuser_b200.ops import functional as TF
+
+        keep = max(0, self.local_end - evicted - self.sink_tokens) if evicted > 0 else 0
+        TF.kv_cache_roll_append(self.k, self.v, k, v, self.sink_tokens, evicted, keep, lo)  # shift + append, one call
         self.global_end = max(self.global_end, current_start + n)
         self.local_end = hi
         return hi

@@ -118,7 +118,9 @@ class BasePipeline:
         """[3, T, H, W] in [-1, 1] -> list of PIL images."""
         from PIL import Image
 
-        arr = ((frames.float().clamp(-1, 1) + 1) * 127.5).round().to(torch.uint8).permute(1, 2, 3, 0).cpu().numpy()
+        from telefuser_b200.ops import functional as TF
+
+        arr = TF.frames_to_uint8(frames).cpu().numpy()
         return [Image.fromarray(a) for a in arr]
 
     @staticmethod

@@ -28,6 +28,9 @@ struct GemmParams {
   int epi;
   int m_tiles, n_tiles;
   int* status;
+  // Grouped mode (mixture of experts): M tile m uses weight rows [tile_expert[m] * N, +N) of B, which
+  // then has E * N rows; tiles whose entry is negative (padding past the last expert) are skipped.
+  const int* tile_expert;
 };
 
 template <int BN>
@@ -95,6 +98,12 @@ __global__ void __launch_bounds__(192, 1)
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int m_blk = t / p.n_tiles, n_blk = t % p.n_tiles;
+        int b_row = n_blk * BN;
+        if (p.tile_expert) {
+          const int e = __ldg(p.tile_expert + m_blk);
+          if (e < 0) continue;
+          b_row += e * p.N;
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -106,7 +115,7 @@ __global__ void __launch_bounds__(192, 1)
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           tma_load_2d(a_dst, &tmA, &full[s], kb * Cfg::BK, m_blk * Cfg::BM);
-          tma_load_2d(b_dst, &tmB, &full[s], kb * Cfg::BK, n_blk * BN);
+          tma_load_2d(b_dst, &tmB, &full[s], kb * Cfg::BK, b_row);
         }
       }
     }
@@ -117,9 +126,11 @@ __global__ void __launch_bounds__(192, 1)
     uint32_t it = 0;
     uint32_t tile_iter = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      if (p.tile_expert && __ldg(p.tile_expert + t / p.n_tiles) < 0) continue;
       const uint32_t acc = tile_iter & 1;
       const uint32_t accph = (tile_iter >> 1) & 1;
+      ++tile_iter;
       if (!mbar_wait_warp(&tempty[acc], accph ^ 1, ctx, 2)) {
         ok = false;
         break;
@@ -154,10 +165,12 @@ __global__ void __launch_bounds__(192, 1)
     const int q = warp & 3;
     uint32_t tile_iter = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m_blk = t / p.n_tiles, n_blk = t % p.n_tiles;
+      if (p.tile_expert && __ldg(p.tile_expert + m_blk) < 0) continue;
       const uint32_t acc = tile_iter & 1;
       const uint32_t accph = (tile_iter >> 1) & 1;
+      ++tile_iter;
       if (!mbar_wait_warp(&tfull[acc], accph, ctx, 4)) {
         ok = false;
         break;
@@ -260,11 +273,12 @@ __global__ void __launch_bounds__(192, 1)
 }
 
 template <int BN>
-static int launch_gemm(const CUtensorMap& tmA, const void* B, int ldb, GemmParams p, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& tmA, const void* B, int ldb, GemmParams p, cudaStream_t stream,
+                       long b_rows = 0) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmB;
   {
-    uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.N)};
+    uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(b_rows > 0 ? b_rows : p.N)};
     uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
     uint32_t box[2] = {64, static_cast<uint32_t>(BN)};
     int e = make_tmap(&tmB, B, TM_BF16, 2, dims, str, box, TM_SW_128);
@@ -313,6 +327,7 @@ extern "C" int tfb_gemm_bf16(const void* A, int lda, const void* B, int ldb, voi
   p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1;
   p.epi = epi;
   p.status = status_word();
+  p.tile_expert = nullptr;
   CUtensorMap tmA;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
@@ -339,4 +354,44 @@ extern "C" int tfb_gemm_bf16(const void* A, int lda, const void* B, int ldb, voi
     case 128: return launch_gemm<128>(tmA, B, ldb, p, st);
     default: return launch_gemm<64>(tmA, B, ldb, p, st);
   }
+}
+
+// Grouped GEMM for expert layers: rows of A are tokens sorted by expert, every expert's segment
+// starts on a multiple of 128 rows; M tile m multiplies with expert tile_expert[m]'s weights
+// B[e] = rows [e*N, (e+1)*N) of B (bf16 [E*N, K]). `M` is the padded row count (upper bound).
+extern "C" int tfb_gemm_bf16_grouped(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N,
+                                     int K, int num_experts, const int* tile_expert, int epi, void* stream) {
+  using namespace tfb;
+  if (M <= 0 || N <= 0 || K <= 0 || num_experts <= 0 || !tile_expert) return TFB_ERR_BAD_SHAPE;
+  if ((K % 8) || (lda % 8) || (ldb % 8) || (ldo % 8) || (N % 64) || (M % 128)) return TFB_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return TFB_ERR_BAD_SHAPE;
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.bias = nullptr;
+  p.resid = nullptr;
+  p.ldr = 0;
+  p.gate = nullptr;
+  p.ldg = 0;
+  p.rows_per_gate = 1;
+  p.epi = epi;
+  p.status = status_word();
+  p.tile_expert = tile_expert;
+  CUtensorMap tmA;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    uint64_t str[1] = {static_cast<uint64_t>(lda) * 2};
+    uint32_t box[2] = {64, 128};
+    int e = make_tmap(&tmA, A, TM_BF16, 2, dims, str, box, TM_SW_128);
+    if (e) return e;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long b_rows = static_cast<long>(num_experts) * N;
+  if (N % 256 == 0) return launch_gemm<256>(tmA, B, ldb, p, st, b_rows);
+  if (N % 128 == 0) return launch_gemm<128>(tmA, B, ldb, p, st, b_rows);
+  return launch_gemm<64>(tmA, B, ldb, p, st, b_rows);
 }

@@ -67,6 +67,57 @@ int tfb_cfg_euler_step(const float* x, const void* cond, const void* uncond, int
 //   x: bf16 [rows, C];  q: uint8 [rows, C];  sf: uint8 [rows, C/32] (row-major)
 int tfb_quant_mxfp8(const void* x, long ldx, void* q, void* sf, int rows, int C, void* stream);
 
+// Grouped bf16 GEMM for expert layers. A: [M, K] token rows sorted by expert, each expert's segment
+// starting on a multiple of 128 rows (M = padded row count, multiple of 128); B: [E*N, K]; M tile m
+// uses expert tile_expert[m] (device int[M/128]; negative = skip the tile). N % 64 == 0.
+int tfb_gemm_bf16_grouped(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K,
+                          int num_experts, const int* tile_expert, int epi, void* stream);
+
+// ---- mixture-of-experts routing and token movement (moe.cu) ----
+// logits fp32 [T, E] -> ids int32 [T, K], weights fp32 [T, K]; optional counts int32 [E] (zeroed here,
+// then incremented once per selected (token, k)). Scores: sigmoid (use_softmax 0) or softmax over E.
+// Selection uses score + bias (bias fp32 [E] or null), restricted to the `topk_groups` expert groups
+// with the largest sum of their two best selection scores; weights are the unbiased scores of the
+// selected experts, normalised to sum 1, times `scale`. E <= 1024, K <= 32, num_groups <= 32.
+int tfb_moe_route(const float* logits, const float* bias, int T, int E, int num_groups, int topk_groups, int K,
+                  float scale, int use_softmax, int* ids, float* weights, int* counts, void* stream);
+// counts int32 [E] -> offsets int32 [E+1] (segment starts, multiples of `align`; offsets[E] = padded
+// total) and tile_expert int32 [max_tiles] (owner of rows [m*align, (m+1)*align) or -1).
+int tfb_moe_plan(const int* counts, int E, int align, int* offsets, int* tile_expert, int max_tiles, void* stream);
+// x bf16 [T, hidden] -> x_perm bf16 [padded rows, hidden] in expert order; row_map int32 [T*K] gives
+// the row of each (token, k). `cursor` is int32 [E] scratch owned by the caller (zeroed here).
+int tfb_moe_permute(const void* x, int hidden, const int* ids, const int* offsets, int* cursor, int E, long T, int K,
+                    void* x_perm, int* row_map, void* stream);
+// out[t] = residual[t] (or 0) + sum_k weights[t,k] * y[row_map[t*K+k]]   (bf16, fp32 accumulate)
+int tfb_moe_combine(const void* y, int hidden, const int* row_map, const float* weights, int T, int K,
+                    const void* residual, void* out, void* stream);
+
+// ---- streaming / caching kernels (stream_ops.cu) ----
+// Rolling KV cache [B, kv_size, row_elems] bf16 (batch stride cache_bs elements): optional left shift
+// of `keep` tokens by `evicted` positions starting at token `sink` + `evicted`, then append of n_new
+// tokens at local_start from new_k/new_v (token stride new_ld, batch stride new_bs elements).
+int tfb_kv_cache_roll_append(void* k_cache, void* v_cache, long cache_bs, const void* new_k, const void* new_v,
+                             long new_ld, long new_bs, int B, int row_elems, int sink, int evicted, int keep,
+                             int local_start, int n_new, void* stream);
+// x bf16 [rows, D] -> q e4m3 [rows, D], scale fp32 [rows] = max(amax/448, 1e-12).  D in {32..256}, D % 32 == 0.
+int tfb_fp8_kv_quant(const void* x, void* q, float* scale, long rows, int D, void* stream);
+// Log-sum-exp merge of two partial attention results (o* bf16 [B,S,H,D], lse* fp32 [B,H,S]).
+int tfb_merge_attn_states(const void* o1, const float* lse1, const void* o2, const float* lse2, void* out,
+                          float* lse_out, int B, int S, int H, int D, void* stream);
+// Taylor feature cache on bf16 buffers of n elements (n % 8 == 0), terms t0..t3:
+//   update (in place): t0 <- out - ori; t[i+1] <- (new t[i] - old t[i]) / window for i+1 < n_new, i < n_old
+//   apply: y = x + sum_{i<nterms} t[i] * c[i]
+int tfb_taylor_update(const void* out, const void* ori, void* t0, void* t1, void* t2, void* t3, int n_old, int n_new,
+                      float window, long n, void* stream);
+int tfb_taylor_apply(const void* x, const void* t0, const void* t1, const void* t2, const void* t3, float c0, float c1,
+                     float c2, float c3, int nterms, void* y, long n, void* stream);
+// Pluecker ray maps folded to the latent grid: c2w fp32 [F,4,4], ks fp32 [F,4] (fx,fy,cx,cy), optional
+// extra fp32 [F,n_extra] per-frame channels -> out fp32 [C*c1*c2, F, h, w], C = (only_d ? 3 : 6) + n_extra.
+int tfb_plucker_fold(const float* c2w, const float* ks, const float* extra, int n_extra, float* out, int F, int h,
+                     int w, int c1, int c2, int only_d, void* stream);
+// frames [3, T, H, W] (fp32 or bf16) in [-1, 1] -> uint8 [T, H, W, 3].  W % 4 == 0.
+int tfb_frames_to_u8(const void* frames, int is_bf16, void* out, int T, int H, int W, void* stream);
+
 // Descriptor self-test: one CTA computes D[128,N] = A[128,K] @ B^T with the
 // operand modes used by the attention kernel. mode 0: A,B K-major from smem;
 // mode 1: B MN-major from smem (B given as [K,N]); mode 2: A from TMEM.

@@ -136,7 +136,30 @@ class TaylorBranchState:
         self.terms = [None] * self.order
         self.last_residual = None
 
+    @staticmethod
+    def _fused_ok(t) -> bool:
+        return t.is_cuda and t.dtype == torch.bfloat16 and t.numel() % 8 == 0
+
+    def _update_fused(self, output, ori_input) -> None:
+        """One pass over persistent term buffers (residual and finite differences formed in registers)."""
+        from telefuser_b200.ops import functional as TF
+
+        bufs = getattr(self, "_bufs", None)
+        if bufs is None or bufs[0].shape != output.shape or bufs[0].device != output.device:
+            self._bufs = bufs = [torch.empty_like(output, memory_format=torch.contiguous_format) for _ in range(self.order)]
+            self.terms = [None] * self.order
+        n_old = sum(t is not None for t in self.terms) if self.step > 0 else 0
+        n_new = min(self.order, n_old + 1) if n_old > 0 else 1
+        window = max(self.step - self.last_compute_step, 1)
+        TF.taylor_update_(output.contiguous(), ori_input.contiguous(), bufs, n_old, n_new, window)
+        self.prev_terms = [None] * self.order
+        self.terms = bufs[:n_new] + [None] * (self.order - n_new)
+        self.last_residual = bufs[0]
+        self.last_compute_step = self.step
+
     def update(self, output, ori_input) -> None:
+        if self._fused_ok(output) and self.order <= 4:
+            return self._update_fused(output, ori_input)
         residual = (output - ori_input).detach()
         new_terms = self._finite_differences(residual)
         self.prev_terms = self.terms
@@ -157,6 +180,14 @@ class TaylorBranchState:
         return out
 
     def approximate(self, current_input):
+        valid = [t for t in self.terms if t is not None]
+        if valid and self._fused_ok(current_input) and current_input.is_contiguous() and len(valid) <= 4:
+            from telefuser_b200.ops import functional as TF
+
+            elapsed = self.step - self.last_compute_step
+            if elapsed > self.taylor_threshold:
+                return TF.taylor_apply(current_input, [self.last_residual], [1.0])
+            return TF.taylor_apply(current_input, valid, [float(elapsed**i) / math.factorial(i) for i in range(len(valid))])
         r = self.approximate_residual()
         return current_input if r is None else current_input + r
 

@@ -265,12 +265,31 @@ def attention(q, k, v, scale=None, return_lse=False, variant=0):
     return (out, lse) if return_lse else out
 
 
+def merge_attn_states_reference(o1, lse1, o2, lse2):
+    l1 = lse1.float().transpose(1, 2).unsqueeze(-1)
+    l2 = lse2.float().transpose(1, 2).unsqueeze(-1)
+    m = torch.maximum(l1, l2)
+    w1, w2 = torch.exp(l1 - m), torch.exp(l2 - m)
+    o = (o1.float() * w1 + o2.float() * w2) / (w1 + w2)
+    lse = (m + torch.log(w1 + w2)).squeeze(-1).transpose(1, 2)
+    return o.to(o1.dtype), lse
+
+
 def merge_attn_states(o1, lse1, o2, lse2):
     """Combine two partial attention results by their log-sum-exp (ring attention step).
 
     o*: [B, S, H, D]; lse*: [B, H, S]. Same maths as the reference's
     ``merge_attn_states`` (telefuser/distributed/ring.py:159-214).
     """
+    if _native(o1) and o1.dtype == torch.bfloat16 and o1.shape[-1] % 8 == 0:
+        B, S, H, D = o1.shape
+        o1c, o2c = o1.contiguous(), o2.contiguous()
+        l1c, l2c = lse1.float().contiguous(), lse2.float().contiguous()
+        out, lse = torch.empty_like(o1c), torch.empty_like(l1c)
+        code = native.load().tfb_merge_attn_states(o1c.data_ptr(), l1c.data_ptr(), o2c.data_ptr(), l2c.data_ptr(),
+                                                   out.data_ptr(), lse.data_ptr(), B, S, H, D, native.stream_ptr())  # fmt: skip
+        native.check(code, "tfb_merge_attn_states")
+        return out, lse
     l1 = lse1.float().transpose(1, 2).unsqueeze(-1)
     l2 = lse2.float().transpose(1, 2).unsqueeze(-1)
     m = torch.maximum(l1, l2)
@@ -401,3 +420,112 @@ def quant_mxfp8(x):
                                native.stream_ptr())  # fmt: skip
     native.check(code, "tfb_quant_mxfp8")
     return q, sf
+
+
+# ---------------------------------------------------------------------------
+# Streaming / caching ops
+# ---------------------------------------------------------------------------
+def fp8_kv_quant(x):
+    """x: [..., D] -> (e4m3 [..., D], fp32 scale [..., 1]); scale = amax over D / 448 (floor 1e-12)."""
+    D = x.shape[-1]
+    if not _native(x) or x.dtype != torch.bfloat16 or D % 32 or D > 256:
+        scale = (x.detach().abs().amax(dim=-1, keepdim=True).float() / 448.0).clamp_min(1e-12)
+        return (x / scale.to(x.dtype)).to(torch.float8_e4m3fn).contiguous(), scale.contiguous()
+    xc = x.contiguous()
+    q = torch.empty(xc.shape, device=x.device, dtype=torch.float8_e4m3fn)
+    scale = torch.empty(*xc.shape[:-1], 1, device=x.device, dtype=torch.float32)
+    code = native.load().tfb_fp8_kv_quant(xc.data_ptr(), q.data_ptr(), scale.data_ptr(), xc.numel() // D, D,
+                                          native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_fp8_kv_quant")
+    return q, scale
+
+
+def kv_cache_roll_append(k_cache, v_cache, new_k, new_v, sink: int, evicted: int, keep: int, local_start: int):
+    """In-place: shift `keep` tokens left by `evicted` (starting after `sink`), then write new_k/new_v
+    ([B, n, H, D]) at token `local_start`. k_cache / v_cache: [B, kv_size, H, D]."""
+    n = new_k.shape[1]
+    native_ok = (_native(k_cache) and k_cache.dtype == torch.bfloat16 and new_k.dtype == torch.bfloat16
+                 and new_v.dtype == torch.bfloat16 and n > 0 and k_cache.is_contiguous()
+                 and v_cache.is_contiguous() and new_k.stride() == new_v.stride() and new_k.stride(-1) == 1
+                 and new_k.stride(2) == new_k.shape[3] and (k_cache.shape[2] * k_cache.shape[3]) % 8 == 0
+                 and new_k.stride(1) % 8 == 0 and new_k.stride(0) % 8 == 0 and new_k.data_ptr() % 16 == 0
+                 and new_v.data_ptr() % 16 == 0)  # fmt: skip
+    if not native_ok:
+        if evicted > 0 and keep > 0:
+            for done in range(0, keep, evicted):  # pieces whose source and destination do not overlap
+                ln = min(evicted, keep - done)
+                d, s = sink + done, sink + done + evicted
+                k_cache[:, d : d + ln] = k_cache[:, s : s + ln]
+                v_cache[:, d : d + ln] = v_cache[:, s : s + ln]
+        k_cache[:, local_start : local_start + n] = new_k
+        v_cache[:, local_start : local_start + n] = new_v
+        return
+    B, _, H, D = k_cache.shape
+    code = native.load().tfb_kv_cache_roll_append(
+        k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), new_k.data_ptr(), new_v.data_ptr(), new_k.stride(1),
+        new_k.stride(0) if B > 1 else n * new_k.stride(1), B, H * D, sink, evicted, keep, local_start, n,
+        native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_kv_cache_roll_append")
+
+
+def taylor_update_(out, ori, terms: list, n_old: int, n_new: int, window: float) -> None:
+    """In place on the bf16 term buffers: terms[0] = out - ori; terms[i+1] = (new[i] - old[i]) / window."""
+    if _native(out) and out.dtype == torch.bfloat16 and out.numel() % 8 == 0 and out.is_contiguous() \
+            and ori.is_contiguous():  # fmt: skip
+        p = [t.data_ptr() if t is not None else None for t in (terms + [None] * 4)[:4]]
+        code = native.load().tfb_taylor_update(out.data_ptr(), ori.data_ptr(), p[0], p[1], p[2], p[3], n_old, n_new,
+                                               float(window), out.numel(), native.stream_ptr())  # fmt: skip
+        native.check(code, "tfb_taylor_update")
+        return
+    cur = out - ori
+    for i in range(n_new):
+        old = terms[i].clone() if (i < n_old and i + 1 < n_new) else None
+        terms[i].copy_(cur)
+        if old is None:
+            break
+        cur = (cur - old) / window
+
+
+def taylor_apply(x, terms: list, coefs: list):
+    """x + sum_i terms[i] * coefs[i]."""
+    if _native(x) and x.dtype == torch.bfloat16 and x.numel() % 8 == 0 and x.is_contiguous():
+        p = [t.data_ptr() for t in terms] + [None] * (4 - len(terms))
+        c = [float(v) for v in coefs] + [0.0] * (4 - len(coefs))
+        y = torch.empty_like(x)
+        code = native.load().tfb_taylor_apply(x.data_ptr(), p[0], p[1], p[2], p[3], c[0], c[1], c[2], c[3], len(terms),
+                                              y.data_ptr(), x.numel(), native.stream_ptr())  # fmt: skip
+        native.check(code, "tfb_taylor_apply")
+        return y
+    r = None
+    for t, c in zip(terms, coefs):
+        r = t * c if r is None else r + t * c
+    return x + r
+
+
+def plucker_fold(c2ws, ks, latent_h: int, latent_w: int, height: int, width: int, only_rays_d=False, extra=None):
+    """Camera poses [F,4,4] + intrinsics [F,4] -> ray maps folded to [1, C*c1*c2, F, h, w] (fp32), with
+    optional per-frame extra channels [F, n] appended after the ray channels. CUDA tensors only."""
+    F_ = c2ws.shape[0]
+    c1, c2 = max(1, height // latent_h), max(1, width // latent_w)
+    n_extra = 0 if extra is None else extra.shape[-1]
+    C = (3 if only_rays_d else 6) + n_extra
+    out = torch.empty(1, C * c1 * c2, F_, latent_h, latent_w, device=c2ws.device, dtype=torch.float32)
+    e = None if extra is None else extra.float().contiguous()
+    code = native.load().tfb_plucker_fold(c2ws.float().contiguous().data_ptr(), ks.float().contiguous().data_ptr(),
+                                          native.ptr(e), n_extra, out.data_ptr(), F_, latent_h, latent_w, c1, c2,
+                                          int(only_rays_d), native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_plucker_fold")
+    return out
+
+
+def frames_to_uint8(frames):
+    """[3, T, H, W] in [-1, 1] -> uint8 [T, H, W, 3]."""
+    if not _native(frames) or frames.dtype not in (torch.bfloat16, torch.float32) or frames.shape[-1] % 4:
+        return ((frames.float() + 1) * 127.5).round().clamp(0, 255).to(torch.uint8).permute(1, 2, 3, 0).contiguous()
+    f = frames.contiguous()
+    _, T, H, W = f.shape
+    out = torch.empty(T, H, W, 3, device=f.device, dtype=torch.uint8)
+    code = native.load().tfb_frames_to_u8(f.data_ptr(), int(f.dtype == torch.bfloat16), out.data_ptr(), T, H, W,
+                                          native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_frames_to_u8")
+    return out

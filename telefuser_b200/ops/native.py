@@ -71,6 +71,32 @@ def _declare(lib) -> None:
     lib.tfb_quant_mxfp8.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.tfb_umma_probe.restype = c_int
     lib.tfb_umma_probe.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    table = {
+        "tfb_gemm_bf16_grouped": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_int, c_void_p],
+        "tfb_moe_route": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+                          c_void_p, c_void_p],
+        "tfb_moe_plan": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+        "tfb_moe_permute": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_long, c_int, c_void_p, c_void_p,
+                            c_void_p],
+        "tfb_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "tfb_kv_cache_roll_append": [c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_long, c_long, c_int, c_int,
+                                     c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tfb_fp8_kv_quant": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p],
+        "tfb_merge_attn_states": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_int, c_void_p],
+        "tfb_taylor_update": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                              c_long, c_void_p],
+        "tfb_taylor_apply": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_float,
+                             c_int, c_void_p, c_long, c_void_p],
+        "tfb_plucker_fold": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p],
+        "tfb_frames_to_u8": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    }  # fmt: skip
+    for name, args in table.items():
+        fn = getattr(lib, name)
+        fn.restype = c_int
+        fn.argtypes = args
 
 
 def available() -> bool:

@@ -87,11 +87,24 @@ def fold_to_latent_grid(maps: torch.Tensor, latent_h: int, latent_w: int) -> tor
     return x.reshape(1, C * c1 * c2, F_, latent_h, latent_w).contiguous()
 
 
+def _fused_ok(poses, latent_h, latent_w, height, width) -> bool:
+    return poses.is_cuda and height % latent_h == 0 and width % latent_w == 0
+
+
 def build_camera_control_chunk(poses, intrinsics, latent_h, latent_w, height, width) -> torch.Tensor:
+    if _fused_ok(poses, latent_h, latent_w, height, width):  # rays + fold in one kernel, no [F,H,W,6] intermediate
+        from telefuser_b200.ops import functional as TF
+
+        return TF.plucker_fold(poses, intrinsics, latent_h, latent_w, height, width).to(poses.dtype)
     return fold_to_latent_grid(plucker_embeddings(poses, intrinsics, height, width), latent_h, latent_w)
 
 
 def build_action_control_chunk(poses, intrinsics, action, latent_h, latent_w, height, width) -> torch.Tensor:
+    if _fused_ok(poses, latent_h, latent_w, height, width):
+        from telefuser_b200.ops import functional as TF
+
+        return TF.plucker_fold(poses, intrinsics, latent_h, latent_w, height, width, only_rays_d=True,
+                               extra=action).to(poses.dtype)  # fmt: skip
     d = plucker_embeddings(poses, intrinsics, height, width, only_rays_d=True)
     a = action[:, None, None, :].expand(-1, height, width, -1)
     return fold_to_latent_grid(torch.cat([d, a], dim=-1), latent_h, latent_w)

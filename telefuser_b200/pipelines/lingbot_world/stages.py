@@ -225,7 +225,9 @@ class LingBotWorldFastVAEDecodeStage(BaseStage):
         """[1, 3, T, H, W] in [-1, 1] (or uint8 [T, H, W, 3] frames ready for the encoder / client)."""
         frames = self.vae.cached_decode(latents.to(self.device), self._caches[cache_handle])
         if to_uint8:
-            return ((frames[0].float() + 1) * 127.5).round().clamp(0, 255).to(torch.uint8).permute(1, 2, 3, 0).contiguous()
+            from telefuser_b200.ops import functional as TF
+
+            return TF.frames_to_uint8(frames[0])  # one pass on the device; the host copy moves 1 byte per channel
         return frames
 
     def release_cache(self, cache_handle: int) -> bool:
