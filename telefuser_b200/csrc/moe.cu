@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #include "tfb_api.h"
 #include "tfb_common.cuh"
@@ -288,6 +289,44 @@ extern "C" int tfb_moe_permute(const void* x, int hidden, const int* ids, const 
   if (hidden % 8 || E < 1 || K < 1 || !cursor) return TFB_ERR_BAD_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaMemsetAsync(cursor, 0, sizeof(int) * E, st);
+  moe_permute_kernel<<<moe_grid(T * K * 32), 256, 0, st>>>(static_cast<const uint4*>(x), hidden / 8, ids, offsets,
+                                                           cursor, T * K, K, static_cast<uint4*>(x_perm), row_map);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Variant of tfb_moe_permute that allocates nothing: the per-expert cursor lives in a fixed array in
+// device memory instead of a caller-supplied buffer. See the declaration in tfb_api.h.
+constexpr int MOE_STATIC_MAX_EXPERTS = 1024;  // 4 KB of scratch per device
+static __device__ __align__(256) int g_moe_static_cursor[MOE_STATIC_MAX_EXPERTS];
+constexpr int MOE_STATIC_MAX_DEVICES = 64;
+static int* g_moe_static_cursor_ptr[MOE_STATIC_MAX_DEVICES] = {nullptr};
+
+extern "C" int tfb_moe_permute_static(const void* x, int hidden, const int* ids, const int* offsets, int E, long T,
+                                      int K, void* x_perm, int* row_map, void* stream) {
+  if (T <= 0) return TFB_OK;
+  if (hidden % 8 || E < 1 || K < 1) return TFB_ERR_BAD_SHAPE;
+  if (E > MOE_STATIC_MAX_EXPERTS) {
+    fprintf(stderr, "tfb_moe_permute_static: %d experts exceed the static scratch limit of %d; use tfb_moe_permute\n",
+            E, MOE_STATIC_MAX_EXPERTS);
+    return TFB_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MOE_STATIC_MAX_DEVICES) return TFB_ERR_LAUNCH;
+  if (!g_moe_static_cursor_ptr[dev]) {
+    // One-time set-up per device: address of this device's copy of the array.
+    int* p = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_moe_static_cursor);
+    if (err != cudaSuccess || !p) {
+      fprintf(stderr, "tfb_moe_permute_static: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(err));
+      return TFB_ERR_LAUNCH;
+    }
+    g_moe_static_cursor_ptr[dev] = p;
+  }
+  int* cursor = g_moe_static_cursor_ptr[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The first E cursors must be zero when the kernel starts: cleared here, in stream order.
+  if (cudaMemsetAsync(cursor, 0, sizeof(int) * E, st) != cudaSuccess) return TFB_ERR_LAUNCH;
   moe_permute_kernel<<<moe_grid(T * K * 32), 256, 0, st>>>(static_cast<const uint4*>(x), hidden / 8, ids, offsets,
                                                            cursor, T * K, K, static_cast<uint4*>(x_perm), row_map);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;

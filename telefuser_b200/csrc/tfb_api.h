@@ -88,6 +88,18 @@ int tfb_moe_plan(const int* counts, int E, int align, int* offsets, int* tile_ex
 // the row of each (token, k). `cursor` is int32 [E] scratch owned by the caller (zeroed here).
 int tfb_moe_permute(const void* x, int hidden, const int* ids, const int* offsets, int* cursor, int E, long T, int K,
                     void* x_perm, int* row_map, void* stream);
+// Same operation as tfb_moe_permute, for callers that must not allocate: it takes no scratch buffer
+// and calls no allocating routine. This entry point has no counterpart in the reference; it is an
+// addition of this library. The per-expert cursor lives in a fixed device array of 1024 ints (4 KB)
+// per device, so E <= 1024; a larger E is rejected with TFB_ERR_TOO_LARGE and a message on stderr
+// (use tfb_moe_permute then). The first E cursors must be zero when the kernel starts; the call
+// clears them itself with an asynchronous memset on `stream` before the kernel.
+// The scratch is shared by every call on a device: two calls that overlap in time (different streams
+// or host threads, same device) race on it and must be serialised by the caller. The first call on
+// each device looks up the array's address (one-time set-up); make that first call before any
+// stream capture begins.
+int tfb_moe_permute_static(const void* x, int hidden, const int* ids, const int* offsets, int E, long T, int K,
+                           void* x_perm, int* row_map, void* stream);
 // out[t] = residual[t] (or 0) + sum_k weights[t,k] * y[row_map[t*K+k]]   (bf16, fp32 accumulate)
 int tfb_moe_combine(const void* y, int hidden, const int* row_map, const float* weights, int T, int K,
                     const void* residual, void* out, void* stream);
