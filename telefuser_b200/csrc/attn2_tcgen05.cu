@@ -28,7 +28,8 @@ constexpr int A2_BAR_OFF = A2_KV_OFF + A2_KV_SLOTS * ATT_TILE_BYTES;
 constexpr int A2_SMEM_BYTES = A2_BAR_OFF + 256 + 1024;
 
 // POLY: share of exp2 evaluated on the FMA pipe instead of MUFU (0 none, 1 a quarter, 2 half).
-template <int POLY>
+// PEER: the epilogue stores each output row into the buffer of the rank that owns the token.
+template <int POLY, bool PEER = false>
 __global__ void __launch_bounds__(384, 1)
     attn2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -275,7 +276,14 @@ __global__ void __launch_bounds__(384, 1)
       const float inv_l = 1.f / l;
       const int grow = (q_pair * 2 + st) * ATT_BM + row;
       const bool row_ok = grow < p.Sq;
-      __nv_bfloat16* orow = p.out + static_cast<long>(b) * p.bso + static_cast<long>(grow) * p.ldo + h * ATT_D;
+      __nv_bfloat16* orow;
+      if (PEER) {
+        const int dst = row_ok ? grow / p.rows_per_rank : 0;
+        orow = p.peer_out[dst] + static_cast<long>(b) * p.bso +
+               static_cast<long>(grow - dst * p.rows_per_rank) * p.ldo + (p.head_off + h) * ATT_D;
+      } else {
+        orow = p.out + static_cast<long>(b) * p.bso + static_cast<long>(grow) * p.ldo + h * ATT_D;
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -320,8 +328,24 @@ static int launch_attn2_impl(const CUtensorMap& tq, const CUtensorMap& tk, const
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 
+static int launch_attn2_peer(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                             int B, cudaStream_t st) {
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 15;
+  if (!attr_set[dev]) {
+    cudaFuncSetAttribute(attn2_fwd_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM_BYTES);
+    attr_set[dev] = true;
+  }
+  dim3 grid((p.Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), p.H, B);
+  attn2_fwd_kernel<0, true><<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
 int launch_attn2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
                  cudaStream_t st) {
+  if (p.n_peers > 0) return launch_attn2_peer(tq, tk, tv, p, B, st);
   switch (p.poly) {
     case 0: return launch_attn2_impl<0>(tq, tk, tv, p, B, st);
     case 2: return launch_attn2_impl<2>(tq, tk, tv, p, B, st);

@@ -13,6 +13,12 @@ struct AttnParams {
   float scale_log2;
   int* status;
   int poly;  // share of exp2 evaluated on the FMA pipe: 0 none, 1 a quarter, 2 half
+  // Sequence-parallel output scatter (Ulysses "gather heads" folded into the epilogue): query row g of
+  // this rank's head slice belongs to rank g / rows_per_rank and is stored straight into that rank's
+  // buffer [B, rows_per_rank, H_total * 128] (row stride ldo, batch stride bso) at head head_off + h
+  // with plain peer stores. n_peers == 0: ordinary local output.
+  __nv_bfloat16* peer_out[8];
+  int n_peers, rows_per_rank, head_off;
 };
 
 constexpr int ATT_BM = 128, ATT_BN = 128, ATT_D = 128;

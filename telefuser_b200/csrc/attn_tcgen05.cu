@@ -428,10 +428,52 @@ extern "C" int tfb_attn_fwd(const void* q, long ldq, long bsq, const void* k, lo
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word();
   p.poly = (variant >= 20 && variant <= 22) ? variant - 20 : 0;
+  p.n_peers = 0;
+  p.rows_per_rank = 1;
+  p.head_off = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (variant == 1) return launch_attn<false>(tq, tk, tv, p, B, st);
   if (variant == 3) return launch_attn<true>(tq, tk, tv, p, B, st);
   return launch_attn2(tq, tk, tv, p, B, st);
+}
+
+// Attention whose epilogue performs the sequence-parallel "gather heads" exchange: this rank holds
+// H local heads of all Sq tokens; output row g goes to rank g / rows_per_rank, into its buffer
+// peer_out[rank] laid out [B, rows_per_rank, H_total*128] (row stride ldo, batch stride bso), at head
+// head_off + h. peer_out: HOST array of n_peers device pointers (this rank's own buffer included).
+extern "C" int tfb_attn_fwd_peer(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v,
+                                 long ldv, long bsv, void* const* peer_out, int n_peers, int rows_per_rank,
+                                 int head_off, long ldo, long bso, int B, int H, int Sq, int Skv, float scale,
+                                 void* stream) {
+  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || n_peers < 1 || n_peers > 8 || rows_per_rank < 1) return TFB_ERR_BAD_SHAPE;
+  if (static_cast<long>(rows_per_rank) * n_peers < Sq) return TFB_ERR_BAD_SHAPE;
+  if ((ldq | ldk | ldv | ldo | bsq | bsk | bsv | bso) % 8) return TFB_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15)
+    return TFB_ERR_BAD_SHAPE;
+  CUtensorMap tq, tk, tv;
+  int e;
+  if ((e = make_qkv_tmap(&tq, q, ldq, bsq, B, Sq, H))) return e;
+  if ((e = make_qkv_tmap(&tk, k, ldk, bsk, B, Skv, H))) return e;
+  if ((e = make_qkv_tmap(&tv, v, ldv, bsv, B, Skv, H))) return e;
+  AttnParams p;
+  p.out = nullptr;
+  p.ldo = ldo;
+  p.bso = bso;
+  p.lse = nullptr;
+  p.H = H;
+  p.Sq = Sq;
+  p.Skv = Skv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_word();
+  p.poly = 0;
+  for (int i = 0; i < 8; ++i) {
+    p.peer_out[i] = i < n_peers ? static_cast<__nv_bfloat16*>(peer_out[i]) : nullptr;
+    if (i < n_peers && (reinterpret_cast<uintptr_t>(peer_out[i]) & 15)) return TFB_ERR_BAD_SHAPE;
+  }
+  p.n_peers = n_peers;
+  p.rows_per_rank = rows_per_rank;
+  p.head_off = head_off;
+  return launch_attn2(tq, tk, tv, p, B, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tfb_umma_probe(const void* A, const void* B, float* D, int N, int K, int mode, void* stream) {

@@ -104,6 +104,30 @@ int tfb_moe_permute_static(const void* x, int hidden, const int* ids, const int*
 int tfb_moe_combine(const void* y, int hidden, const int* row_map, const float* weights, int T, int K,
                     const void* residual, void* out, void* stream);
 
+// ---- peer-mapped buffers (ipc.cu): allocate (zero-filled) + export a 64-byte IPC handle; map a peer's ----
+int tfb_ipc_alloc(long bytes, void** ptr, void* handle64);
+int tfb_ipc_open(const void* handle64, void** ptr);
+int tfb_ipc_close(void* ptr);
+int tfb_ipc_free(void* ptr);
+
+// ---- peer-memory kernels over NVLink (peer_ops.cu, attn_tcgen05.cu); pointer tables are HOST arrays ----
+// All-rank barrier on flag arrays in peer-mapped memory: flags[r] = rank r's int[slots*8], zero at start;
+// `epoch` must grow by one per call on a slot (same sequence on every rank). The wait is bounded (4 s);
+// on expiry the status word is set and the kernel returns.
+int tfb_peer_barrier(void* const* flags, int my_rank, int n, int slot, int epoch, void* stream);
+// Sequence-sharded q/k/v [B, S_loc, H, D] (strides lds/bss in elements) -> head-sharded slabs
+// [B, S_loc*P, H/P, D] of every rank, written with peer stores. dsts[t*P + r] = rank r's slab of tensor t.
+int tfb_ulysses_scatter(void* const* srcs, const long* lds, const long* bss, void* const* dsts, int ntensors, int B,
+                        int S_loc, int H, int D, int P, int my_rank, void* stream);
+// rows [row0, row0+rows) of every rank's buffer dsts[r] <- src (byte strides; row bytes % 16 == 0).
+int tfb_peer_push_rows(const void* src, long ld_bytes, void* const* dsts, int P, long row0, long rows,
+                       int row_bytes, long dst_ld_bytes, void* stream);
+// Attention over this rank's head slice whose epilogue stores each output row into the buffer of the
+// rank that owns the token (see attn_tcgen05.cu).
+int tfb_attn_fwd_peer(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v, long ldv,
+                      long bsv, void* const* peer_out, int n_peers, int rows_per_rank, int head_off, long ldo, long bso,
+                      int B, int H, int Sq, int Skv, float scale, void* stream);
+
 // ---- streaming / caching kernels (stream_ops.cu) ----
 // Rolling KV cache [B, kv_size, row_elems] bf16 (batch stride cache_bs elements): optional left shift
 // of `keep` tokens by `evicted` positions starting at token `sink` + `evicted`, then append of n_new

@@ -92,6 +92,12 @@ def _declare(lib) -> None:
         "tfb_plucker_fold": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
         "tfb_frames_to_u8": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "tfb_peer_barrier": [c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "tfb_ulysses_scatter": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_void_p],
+        "tfb_peer_push_rows": [c_void_p, c_long, c_void_p, c_int, c_long, c_long, c_int, c_long, c_void_p],
+        "tfb_attn_fwd_peer": [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p,
+                              c_int, c_int, c_int, c_long, c_long, c_int, c_int, c_int, c_int, c_float, c_void_p],
     }  # fmt: skip
     for name, args in table.items():
         fn = getattr(lib, name)

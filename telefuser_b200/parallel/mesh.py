@@ -11,6 +11,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -27,6 +29,7 @@ class ParallelMesh:
     coords: dict[str, int] = field(default_factory=dict)
     groups: dict[str, object] = field(default_factory=dict)
     group_ranks: dict[str, list[int]] = field(default_factory=dict)
+    fused: bool = True  # peer-memory kernels instead of collective-library calls where both exist
 
     def size(self, name: str) -> int:
         if name == "sp":
@@ -88,6 +91,7 @@ def create_mesh(config: ParallelConfig | None = None, rank: int | None = None, w
     grid = torch.arange(world_size).reshape(dims)
     pos = (grid == rank).nonzero()[0].tolist()
     mesh = ParallelMesh(dims=dims, rank=rank, world_size=world_size)
+    mesh.fused = bool(config.fused_collectives) and os.environ.get("TFB_FUSED_COLLECTIVES", "1") != "0"
     for i, name in enumerate(DIM_NAMES):
         mesh.coords[name] = pos[i]
         g, ranks = _make_groups(grid, [i], rank)

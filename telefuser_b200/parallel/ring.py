@@ -66,6 +66,12 @@ def long_context_attention(q, k, v, scale=None, mesh=None, strategy: str | None 
         return TF.attention(q, k, v, scale)
     if strategy == "ulysses":
         g = mesh.group("ulysses")
+        if mesh.fused and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128:
+            from .symm import get_workspace, ulysses_attention_fused
+
+            B, S, H, D = q.shape  # 3 head-sharded slabs + the output buffer, each B*S*H*D elements
+            ws = get_workspace(g, 4 * (B * S * H * D * 2 + 256) + 4096)
+            return ulysses_attention_fused(q, k, v, ws, scale)
         hq = ulysses.scatter_heads(q, g, async_op=True)
         hk = ulysses.scatter_heads(k, g, async_op=True)
         hv = ulysses.scatter_heads(v, g, async_op=True)

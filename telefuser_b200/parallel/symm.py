@@ -1,0 +1,204 @@
+"""Peer-mapped workspaces and the fused compute + exchange paths built on them (one node, NVLink).
+
+`PeerWorkspace(group, nbytes)`: every rank of `group` allocates `nbytes` of device memory, the CUDA
+IPC handles are exchanged through the process group, and each rank maps all the others. Regions of
+the workspace are carved by name (`region(name, shape, dtype)`): the same call sequence on every rank
+gives the same offsets, so `peer_ptr(rank, name)` is the address of rank `rank`'s copy.
+
+Exchanges are done by the kernels that produce or consume the data:
+* `ulysses_attention_fused`: q/k/v go from the sequence-sharded projection output straight into the
+  head-sharded slabs of every peer (one pass, no pack/unpack, no all-to-all), attention's epilogue
+  stores each output row into the buffer of the rank that owns the token (no second all-to-all).
+  Two flag barriers per layer order the slab reuse.
+* `cfg_combine_step_fused`: each guidance rank publishes its prediction; the combine + Euler-step
+  kernel reads the partner's prediction with peer loads (no all-gather).
+* `all_gather_rows_fused`: a rank's token rows are pushed into every peer's full buffer.
+The NCCL paths in `ulysses.py` / `shard.py` remain the oracle and the fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+import torch.distributed as dist
+
+from telefuser_b200.ops import native
+
+FLAG_BYTES = 4096
+
+
+class _DevMem:
+    """Exposes a raw device pointer to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerWorkspace:
+    def __init__(self, group, nbytes: int, device=None) -> None:
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("peer workspaces span at most 8 ranks (one node)")
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = int(-(-nbytes // 256) * 256) + FLAG_BYTES
+        lib = native.load()
+        lib.tfb_ipc_alloc.argtypes = [ctypes.c_long, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
+        lib.tfb_ipc_open.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]
+        lib.tfb_ipc_close.argtypes = [ctypes.c_void_p]
+        lib.tfb_ipc_free.argtypes = [ctypes.c_void_p]
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            native.check(lib.tfb_ipc_alloc(self.nbytes, ctypes.byref(ptr), handle), "tfb_ipc_alloc")
+            handles: list = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            self.ptrs: list[int] = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.ptrs.append(ptr.value)
+                    continue
+                p = ctypes.c_void_p()
+                native.check(lib.tfb_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(p)), "tfb_ipc_open")
+                self.ptrs.append(p.value)
+        self._lib = lib
+        self.local = torch.as_tensor(_DevMem(ptr.value, self.nbytes), device=self.device)
+        self.flag_off = self.nbytes - FLAG_BYTES
+        self._flag_table = (ctypes.c_void_p * self.world)(*[p + self.flag_off for p in self.ptrs])
+        self._epoch = 0
+        self._regions: dict[str, tuple[int, tuple, torch.dtype]] = {}
+        self._cursor = 0
+        dist.barrier(group=group)  # every mapping exists before anyone stores
+
+    # ---- regions ------------------------------------------------------------------
+    def region(self, name: str, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        """This rank's view of a named region (allocated on first use; same order on every rank)."""
+        shape = tuple(int(s) for s in shape)
+        n = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
+        hit = self._regions.get(name)
+        if hit is not None and (hit[1] != shape or hit[2] != dtype):
+            raise ValueError(f"region {name!r} exists with another shape")
+        if hit is None:
+            off = self._cursor
+            if off + n > self.flag_off:
+                raise MemoryError(f"peer workspace of {self.flag_off} bytes cannot hold region {name!r} ({n} bytes)")
+            self._cursor = -(-(off + n) // 256) * 256
+            hit = self._regions[name] = (off, shape, dtype)
+        off = hit[0]
+        return self.local[off : off + n].view(dtype).view(shape)
+
+    def peer_ptr(self, rank: int, name: str) -> int:
+        return self.ptrs[rank] + self._regions[name][0]
+
+    def peer_table(self, name: str):
+        return (ctypes.c_void_p * self.world)(*[self.peer_ptr(r, name) for r in range(self.world)])
+
+    # ---- synchronisation --------------------------------------------------------------
+    def barrier(self, slot: int = 0) -> None:
+        """Stream-ordered all-rank barrier (a one-warp kernel; bounded wait)."""
+        self._epoch += 1
+        code = self._lib.tfb_peer_barrier(self._flag_table, self.rank, self.world, slot, self._epoch, native.stream_ptr())
+        native.check(code, "tfb_peer_barrier")
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank:
+                self._lib.tfb_ipc_close(ctypes.c_void_p(p))
+        self._lib.tfb_ipc_free(ctypes.c_void_p(self.ptrs[self.rank]))
+        self.ptrs = []
+
+
+_WORKSPACES: dict = {}
+
+
+def get_workspace(group, nbytes: int) -> PeerWorkspace:
+    """One workspace per process group, grown by re-creation when a larger one is asked for."""
+    key = id(group)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.flag_off < nbytes:
+        if ws is not None:
+            ws.close()
+        ws = _WORKSPACES[key] = PeerWorkspace(group, nbytes)
+    return ws
+
+
+def release_workspaces() -> None:
+    for ws in list(_WORKSPACES.values()):
+        ws.close()
+    _WORKSPACES.clear()
+
+
+# ---------------------------------------------------------------------------
+# fused paths
+# ---------------------------------------------------------------------------
+def ulysses_attention_fused(q, k, v, ws: PeerWorkspace, scale: float | None = None) -> torch.Tensor:
+    """q, k, v: [B, S_loc, H, 128] bf16 (may be column slices of one fused buffer) -> [B, S_loc, H, 128].
+
+    Equivalent to scatter_heads x3 -> attention -> gather_heads over `ws.group`."""
+    B, S, H, D = q.shape
+    P, r = ws.world, ws.rank
+    if D != 128 or q.dtype != torch.bfloat16 or H % P:
+        raise ValueError("fused Ulysses attention needs bf16, head_dim 128 and heads divisible by the group size")
+    Hp, St = H // P, S * P
+    slabs = [ws.region(f"ulysses_{n}", (B, St, Hp, D)) for n in ("q", "k", "v")]
+    out = ws.region("ulysses_o", (B, S, H, D))
+    lib = native.load()
+    st = native.stream_ptr()
+
+    def strides(t):
+        if t.stride(-1) != 1 or t.stride(2) != D:
+            t = t.contiguous()
+        return t, t.stride(1), (t.stride(0) if B > 1 else S * t.stride(1))
+
+    (q, ldq, bsq), (k, ldk, bsk), (v, ldv, bsv) = strides(q), strides(k), strides(v)
+    srcs = (ctypes.c_void_p * 3)(q.data_ptr(), k.data_ptr(), v.data_ptr())
+    lds = (ctypes.c_long * 3)(ldq, ldk, ldv)
+    bss = (ctypes.c_long * 3)(bsq, bsk, bsv)
+    dsts = (ctypes.c_void_p * (3 * P))(*[ws.peer_ptr(rr, f"ulysses_{n}") for n in ("q", "k", "v") for rr in range(P)])
+    native.check(lib.tfb_ulysses_scatter(srcs, lds, bss, dsts, 3, B, S, H, D, P, r, st), "tfb_ulysses_scatter")
+    ws.barrier()  # every peer's slice of q/k/v has landed in my slabs
+    sq, sk, sv = slabs
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    code = lib.tfb_attn_fwd_peer(sq.data_ptr(), Hp * D, St * Hp * D, sk.data_ptr(), Hp * D, St * Hp * D, sv.data_ptr(),
+                                 Hp * D, St * Hp * D, ws.peer_table("ulysses_o"), P, S, r * Hp, H * D, S * H * D, B, Hp,
+                                 St, St, scale, st)  # fmt: skip
+    native.check(code, "tfb_attn_fwd_peer")
+    ws.barrier()  # every peer has stored its heads of my tokens; slabs may be overwritten again
+    return out
+
+
+def cfg_combine_step_fused(latents, pred, ws: PeerWorkspace, cfg_scale: float, dsigma: float) -> torch.Tensor:
+    """CFG-parallel pair: rank 0 holds the conditional prediction, rank 1 the unconditional one.
+    Returns the updated latents (identical on both ranks)."""
+    if ws.world != 2:
+        raise ValueError("CFG combine runs on a group of two")
+    buf = ws.region("cfg_pred", pred.shape, pred.dtype)
+    buf.copy_(pred)
+    ws.barrier()
+    x = latents.float().contiguous()
+    out = torch.empty_like(x)
+    code = native.load().tfb_cfg_euler_step(x.data_ptr(), ws.peer_ptr(0, "cfg_pred"), ws.peer_ptr(1, "cfg_pred"),
+                                            int(pred.dtype == torch.bfloat16), float(cfg_scale), float(dsigma),
+                                            out.data_ptr(), None, x.numel(), native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_cfg_euler_step")
+    ws.barrier()  # the partner has read my prediction; the region may be reused
+    return out
+
+
+def all_gather_rows_fused(x_local: torch.Tensor, ws: PeerWorkspace, name: str = "gather") -> torch.Tensor:
+    """x_local: [rows, C] (same shape on every rank) -> [rows * P, C], rank-major, by peer stores."""
+    rows, C = x_local.shape
+    full = ws.region(name, (rows * ws.world, C), x_local.dtype)
+    xc = x_local.contiguous()
+    rb = C * xc.element_size()
+    ws.barrier()  # nobody still reads the previous contents of this region
+    code = native.load().tfb_peer_push_rows(xc.data_ptr(), rb, ws.peer_table(name), ws.world, ws.rank * rows, rows, rb,
+                                            rb, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_peer_push_rows")
+    ws.barrier()
+    return full

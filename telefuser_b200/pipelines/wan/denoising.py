@@ -23,6 +23,13 @@ from telefuser_b200.parallel import mesh as pmesh
 from telefuser_b200.parallel import shard as pshard
 
 
+class _PeerPrediction:
+    """This rank's branch of a CFG-parallel pair; the partner's branch is read from its memory."""
+
+    def __init__(self, tensor: torch.Tensor) -> None:
+        self.tensor = tensor
+
+
 class WanDenoisingStage(BaseStage):
     def __init__(self, name: str, module_manager: Any, model_runtime_config: ModelRuntimeConfig, scheduler: Any,
                  dit: Any | None = None) -> None:  # fmt: skip
@@ -87,12 +94,25 @@ class WanDenoisingStage(BaseStage):
             mine = self.dit(latents, timestep, ctx, cond_flag=is_cond, **kw)
             if mine is None:  # not the last pipeline stage: nothing to combine here
                 return None, None
+            if self.mesh.fused and mine.is_cuda:
+                return _PeerPrediction(mine), None  # combined by peer loads inside the step kernel
             return pshard.cfg_parallel_unshard(mine, self.mesh)
         cond = self.dit(latents, timestep, prompt_emb_posi, cond_flag=True, **kw)
         if not use_cfg:
             return cond, None
         uncond = self.dit(latents, timestep, prompt_emb_nega, cond_flag=False, **kw)
         return cond, uncond
+
+    def guided_step(self, latents, cond, uncond, cfg_scale, dsigma):
+        """Guidance combine + flow-matching Euler update (one kernel; the CFG-parallel form reads the
+        partner rank's prediction over NVLink instead of all-gathering it first)."""
+        if isinstance(cond, _PeerPrediction):
+            from telefuser_b200.parallel.symm import cfg_combine_step_fused, get_workspace
+
+            pred = cond.tensor
+            ws = get_workspace(self.mesh.group("cfg"), pred.numel() * pred.element_size() + 4096)
+            return cfg_combine_step_fused(latents, pred, ws, cfg_scale, float(dsigma))
+        return TF.cfg_euler_step(latents, cond, uncond, cfg_scale, dsigma)
 
     # ---- the loop ---------------------------------------------------------------------
     @with_model_offload(["dit"])
@@ -118,10 +138,10 @@ class WanDenoisingStage(BaseStage):
             if pp:
                 src = self.mesh.ranks("pp")[-1]
                 if self.mesh.coord("pp") == self.mesh.size("pp") - 1:
-                    latents = TF.cfg_euler_step(latents, cond, uncond, cfg_scale, nxt - sigma)
+                    latents = self.guided_step(latents, cond, uncond, cfg_scale, nxt - sigma)
                 dist.broadcast(latents, src=src, group=self.mesh.group("pp"))
             else:
-                latents = TF.cfg_euler_step(latents, cond, uncond, cfg_scale, nxt - sigma)
+                latents = self.guided_step(latents, cond, uncond, cfg_scale, nxt - sigma)
             if self.step_callback is not None:
                 self.step_callback(i, latents)
         return latents

@@ -1,16 +1,58 @@
-"""Multi-GPU plumbing on real devices (NCCL): Ulysses and CFG-parallel denoising equal the single-GPU run."""
+"""Multi-GPU plumbing on real devices: Ulysses and CFG-parallel denoising equal the single-GPU run
+(peer-memory kernels by default, the NCCL path with TFB_FUSED_COLLECTIVES=0), the peer-memory
+paths equal the collective-library paths op by op, and a peer wait that nobody answers runs out
+with a status instead of hanging."""
+import ctypes
+
 import pytest
 import torch
 
 from telefuser_b200.testing.distributed_checks import spawn_tiny_wan_denoise, tiny_wan_denoise
 
-pytestmark = [pytest.mark.gpu, pytest.mark.multi_gpu]
+pytestmark = [pytest.mark.gpu]
+two_gpus = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@two_gpus
+@pytest.mark.multi_gpu
+@pytest.mark.parametrize("fused", ["1", "0"])
 @pytest.mark.parametrize("kw", [dict(sp_ulysses_degree=2), dict(cfg_degree=2)])
-def test_two_gpu_denoise_matches_single(kw):
+def test_two_gpu_denoise_matches_single(kw, fused, monkeypatch):
+    monkeypatch.setenv("TFB_FUSED_COLLECTIVES", fused)
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
     ref = tiny_wan_denoise(device="cuda:0", dtype=torch.bfloat16, preset="native-small")
     got = spawn_tiny_wan_denoise(2, backend="nccl", dtype=torch.bfloat16, preset="native-small", **kw)
     err = ((ref - got).norm() / ref.norm()).item()
     assert err < 2e-2, err
+
+
+@two_gpus
+@pytest.mark.multi_gpu
+def test_peer_memory_paths_match_collectives():
+    from telefuser_b200.testing.peer_checks import spawn
+
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    for errs in spawn(n):
+        assert errs["status"] == 0, errs
+        assert errs["ulysses"] <= 2e-2, errs  # bf16 outputs of two runs of the same kernel on the same data
+        assert errs["gather"] == 0.0, errs
+        if "cfg" in errs:
+            assert errs["cfg"] <= 1e-6, errs
+
+
+def test_peer_wait_runs_out_with_a_status():
+    """One GPU: the barrier waits for a second rank that does not exist. The wait is bounded (4 s), the
+    kernel returns, the context stays usable and the status word names the barrier's wait site."""
+    from telefuser_b200.ops import native
+
+    lib = native.load()
+    native.last_status()  # clear
+    flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
+    table = (ctypes.c_void_p * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+    assert lib.tfb_peer_barrier(table, 0, 2, 0, 1, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    status = native.last_status()
+    assert status & 0xFF == 1 and status >> 8 == 60, status  # TFB_ERR_TIMEOUT at site 60
+    assert flags[1][0].item() == 1  # the signal to the absent rank was still written
+    x = torch.ones(4, device="cuda") * 2  # context still answers
+    assert x.sum().item() == 8.0
