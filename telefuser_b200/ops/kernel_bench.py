@@ -70,10 +70,11 @@ def report(name: str, ms: float, flops: float = 0.0, bytes_: float = 0.0, **cfg)
     print(json.dumps(out), flush=True)
 
 
-def bench_attn(t: Timer, seq: int, heads: int, compare: bool) -> None:
+def bench_attn(t: Timer, seq: int, heads: int, compare: bool, variant: int = 0) -> None:
     q, k, v = (torch.randn(1, seq, heads, 128, device="cuda").bfloat16() for _ in range(3))
     flops = 4.0 * seq * seq * heads * 128
-    report("attn_fwd_tcgen05", t(lambda: TF.attention(q, k, v)), flops, seq=seq, heads=heads)
+    report("attn_fwd_tcgen05", t(lambda: TF.attention(q, k, v, variant=variant)), flops, seq=seq, heads=heads,
+           variant=variant)  # fmt: skip
     if compare:
         qt, kt, vt = (x.transpose(1, 2) for x in (q, k, v))
         fn = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt)  # noqa: E731
@@ -160,6 +161,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=75600)
     ap.add_argument("--dim", type=int, default=5120)
     ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--variant", type=int, default=0, help="attention kernel variant (0 = default)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--once", action="store_true", help="one launch per case, no flush, no comparison")
@@ -170,7 +172,7 @@ def main() -> None:
     t = Timer(a.warmup, a.iters, a.once)
     cmp_ = not (a.once or a.no_compare)
     if a.what in ("attn", "all"):
-        bench_attn(t, a.seq, a.heads, cmp_)
+        bench_attn(t, a.seq, a.heads, cmp_, a.variant)
     if a.what in ("gemm", "all"):
         bench_gemm(t, a.m, a.n, a.k, cmp_)
     if a.what in ("elementwise", "all"):
