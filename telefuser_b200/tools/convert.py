@@ -1,0 +1,237 @@
+"""Offline checkpoint converter / quantiser.
+
+    python -m telefuser_b200.tools.convert -s <ckpt file or dir> -o <out dir> [-o_n name]
+        [--direction forward|backward --model_type wan_dit] [--rule 'regex=>replacement' ...]
+        [--lora_path a.safetensors --lora_strength 1.0]
+        [--quantized --linear_dtype fp8|mxfp8 --quantize_modules attn ffn] [--save_by_block]
+
+* key mapping: built-in rule sets (diffusers -> native Wan DiT names, and back) plus ad-hoc regex rules
+* LoRA merge before any quantisation (same loader as run-time)
+* fp8: e4m3 weight + per-output-channel fp32 `weight_scale [out, 1]` (scale = row amax / 448) — the layout
+  the W8A8 linear consumes; mxfp8: e4m3 payload + UE8M0 scale per 32 input elements in `weight_sf`
+* output: one safetensors file, or one file per transformer block plus an index json
+Role parity: tools/convert/converter.py:32-937 (key mapping, quantize_model, load_loras, save by block).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+import shutil
+from collections import defaultdict
+
+import torch
+
+from telefuser_b200.utils.logging import logger
+from telefuser_b200.utils.model_weight import load_state_dict, save_state_dict
+
+FP8_MAX = 448.0
+
+
+def get_key_mapping_rules(direction: str, model_type: str) -> list[tuple[str, str]]:
+    """Regex rules; `forward` = other layout -> native names, `backward` = native -> other layout."""
+    if model_type == "wan_dit":
+        fwd = [
+            (r"^condition_embedder\.text_embedder\.linear_1\.", "text_embedding.0."),
+            (r"^condition_embedder\.text_embedder\.linear_2\.", "text_embedding.2."),
+            (r"^condition_embedder\.time_embedder\.linear_1\.", "time_embedding.0."),
+            (r"^condition_embedder\.time_embedder\.linear_2\.", "time_embedding.2."),
+            (r"^condition_embedder\.time_proj\.", "time_projection.1."),
+            (r"^blocks\.(\d+)\.attn1\.to_q\.", r"blocks.\1.self_attn.q."),
+            (r"^blocks\.(\d+)\.attn1\.to_k\.", r"blocks.\1.self_attn.k."),
+            (r"^blocks\.(\d+)\.attn1\.to_v\.", r"blocks.\1.self_attn.v."),
+            (r"^blocks\.(\d+)\.attn1\.to_out\.0\.", r"blocks.\1.self_attn.o."),
+            (r"^blocks\.(\d+)\.attn1\.norm_q\.", r"blocks.\1.self_attn.norm_q."),
+            (r"^blocks\.(\d+)\.attn1\.norm_k\.", r"blocks.\1.self_attn.norm_k."),
+            (r"^blocks\.(\d+)\.attn2\.to_q\.", r"blocks.\1.cross_attn.q."),
+            (r"^blocks\.(\d+)\.attn2\.to_k\.", r"blocks.\1.cross_attn.k."),
+            (r"^blocks\.(\d+)\.attn2\.to_v\.", r"blocks.\1.cross_attn.v."),
+            (r"^blocks\.(\d+)\.attn2\.to_out\.0\.", r"blocks.\1.cross_attn.o."),
+            (r"^blocks\.(\d+)\.attn2\.norm_q\.", r"blocks.\1.cross_attn.norm_q."),
+            (r"^blocks\.(\d+)\.attn2\.norm_k\.", r"blocks.\1.cross_attn.norm_k."),
+            (r"^blocks\.(\d+)\.ffn\.net\.0\.proj\.", r"blocks.\1.ffn.0."),
+            (r"^blocks\.(\d+)\.ffn\.net\.2\.", r"blocks.\1.ffn.2."),
+            (r"^blocks\.(\d+)\.norm2\.", r"blocks.\1.norm3."),
+            (r"^blocks\.(\d+)\.scale_shift_table$", r"blocks.\1.modulation"),
+            (r"^proj_out\.", "head.head."),
+            (r"^scale_shift_table$", "head.modulation"),
+        ]
+        bwd = [
+            (r"^text_embedding\.0\.", "condition_embedder.text_embedder.linear_1."),
+            (r"^text_embedding\.2\.", "condition_embedder.text_embedder.linear_2."),
+            (r"^time_embedding\.0\.", "condition_embedder.time_embedder.linear_1."),
+            (r"^time_embedding\.2\.", "condition_embedder.time_embedder.linear_2."),
+            (r"^time_projection\.1\.", "condition_embedder.time_proj."),
+            (r"^blocks\.(\d+)\.self_attn\.([qkv])\.", r"blocks.\1.attn1.to_\2."),
+            (r"^blocks\.(\d+)\.self_attn\.o\.", r"blocks.\1.attn1.to_out.0."),
+            (r"^blocks\.(\d+)\.self_attn\.norm_([qk])\.", r"blocks.\1.attn1.norm_\2."),
+            (r"^blocks\.(\d+)\.cross_attn\.([qkv])\.", r"blocks.\1.attn2.to_\2."),
+            (r"^blocks\.(\d+)\.cross_attn\.o\.", r"blocks.\1.attn2.to_out.0."),
+            (r"^blocks\.(\d+)\.cross_attn\.norm_([qk])\.", r"blocks.\1.attn2.norm_\2."),
+            (r"^blocks\.(\d+)\.ffn\.0\.", r"blocks.\1.ffn.net.0.proj."),
+            (r"^blocks\.(\d+)\.ffn\.2\.", r"blocks.\1.ffn.net.2."),
+            (r"^blocks\.(\d+)\.norm3\.", r"blocks.\1.norm2."),
+            (r"^blocks\.(\d+)\.modulation$", r"blocks.\1.scale_shift_table"),
+            (r"^head\.head\.", "proj_out."),
+            (r"^head\.modulation$", "scale_shift_table"),
+        ]
+        return fwd if direction == "forward" else bwd
+    if model_type in ("none", "", None):
+        return []
+    raise ValueError(f"no built-in key mapping for model type {model_type!r}")
+
+
+def apply_rules(sd: dict, rules: list[tuple[str, str]]) -> dict:
+    if not rules:
+        return dict(sd)
+    comp = [(re.compile(p), r) for p, r in rules]
+    out = {}
+    for k, v in sd.items():
+        nk = k
+        for pat, rep in comp:
+            nk2 = pat.sub(rep, nk)
+            if nk2 != nk:
+                nk = nk2
+                break
+        if nk in out:
+            raise ValueError(f"key mapping sends two keys to {nk!r}")
+        out[nk] = v
+    return out
+
+
+def quantize_fp8(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    scale = (w.float().abs().amax(dim=1, keepdim=True) / FP8_MAX).clamp_min(1e-12)
+    return (w.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), scale
+
+
+def quantize_mxfp8(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    from telefuser_b200.ops.functional import quant_mxfp8_reference
+
+    q, sf = quant_mxfp8_reference(w.float())
+    return q.view(torch.float8_e4m3fn).reshape(w.shape), sf.reshape(w.shape[0], -1)
+
+
+def quantize_model(sd: dict, linear_dtype: str = "fp8", quantize_modules=("attn", "ffn"), skip=("norm", "modulation",
+                   "embedding", "head", "time_"), min_dim: int = 64) -> tuple[dict, int]:  # fmt: skip
+    out, n = {}, 0
+    for k, v in sd.items():
+        is_target = (k.endswith(".weight") and v.dim() == 2 and min(v.shape) >= min_dim
+                     and any(m in k for m in quantize_modules) and not any(s in k for s in skip))  # fmt: skip
+        if not is_target or (linear_dtype == "mxfp8" and v.shape[1] % 32):
+            out[k] = v
+            continue
+        base = k[: -len(".weight")]
+        if linear_dtype == "fp8":
+            q, s = quantize_fp8(v)
+            out[k], out[base + ".weight_scale"] = q, s
+        elif linear_dtype == "mxfp8":
+            q, sf = quantize_mxfp8(v)
+            out[k], out[base + ".weight_sf"] = q, sf
+        else:
+            raise ValueError(f"unknown linear dtype {linear_dtype!r}")
+        n += 1
+    return out, n
+
+
+def save_by_block(sd: dict, out_dir: str, name: str) -> dict:
+    groups: dict[str, dict] = defaultdict(dict)
+    for k, v in sd.items():
+        m = re.match(r"^(?:.*\.)?blocks\.(\d+)\.", k)
+        groups[f"block_{int(m.group(1)):03d}" if m else "non_block"][k] = v
+    index = {"metadata": {"format": "pt"}, "weight_map": {}}
+    for g, part in sorted(groups.items()):
+        fn = f"{name}.{g}.safetensors"
+        save_state_dict(part, os.path.join(out_dir, fn))
+        index["weight_map"].update({k: fn for k in part})
+    with open(os.path.join(out_dir, f"{name}.safetensors.index.json"), "w") as f:
+        json.dump(index, f, indent=2)
+    return index
+
+
+def copy_non_weight_files(source_dir: str, target_dir: str) -> int:
+    n = 0
+    for root, _dirs, files in os.walk(source_dir):
+        for fn in files:
+            if fn.endswith((".safetensors", ".pth", ".pt", ".bin", ".ckpt")):
+                continue
+            rel = os.path.relpath(os.path.join(root, fn), source_dir)
+            dst = os.path.join(target_dir, rel)
+            os.makedirs(os.path.dirname(dst), exist_ok=True)
+            shutil.copy2(os.path.join(root, fn), dst)
+            n += 1
+    return n
+
+
+def convert_weights(args) -> dict:
+    sd = load_state_dict(args.source)
+    rules = get_key_mapping_rules(args.direction, args.model_type)
+    for r in args.rule or []:
+        pat, rep = r.split("=>", 1)
+        rules.append((pat, rep))
+    sd = apply_rules(sd, rules)
+    merged = 0
+    if args.lora_path:
+        from torch import nn
+
+        from telefuser_b200.utils.lora import LoRALoader
+
+        params = {k: nn.Parameter(v.float(), requires_grad=False) for k, v in sd.items() if v.is_floating_point()}
+
+        class _Flat(nn.Module):  # exposes the checkpoint's keys as parameter names to the LoRA loader
+            def named_parameters(self, *a, **kw):
+                return iter(params.items())
+
+            def named_buffers(self, *a, **kw):
+                return iter(())
+
+        for lp in args.lora_path:
+            merged += LoRALoader().apply_lora(_Flat(), lp, strength=args.lora_strength)["merged"]
+        for k, p in params.items():
+            sd[k] = p.data.to(sd[k].dtype)
+    nq = 0
+    if args.quantized:
+        sd, nq = quantize_model(sd, args.linear_dtype, tuple(args.quantize_modules))
+    if args.dtype:
+        dt = getattr(torch, args.dtype)
+        sd = {k: (v.to(dt) if v.is_floating_point() and v.dtype in (torch.float32, torch.float16, torch.bfloat16)
+                  and not k.endswith(("weight_scale", "weight_sf")) else v) for k, v in sd.items()}  # fmt: skip
+    os.makedirs(args.output, exist_ok=True)
+    if args.save_by_block:
+        save_by_block(sd, args.output, args.output_name)
+    else:
+        save_state_dict(sd, os.path.join(args.output, args.output_name + args.output_ext))
+    copied = 0
+    if args.copy_no_weight_files and os.path.isdir(args.source):
+        copied = copy_non_weight_files(args.source, args.output)
+    logger.info(f"converted {len(sd)} tensors ({nq} quantised, {merged} LoRA tensors merged, {copied} files copied)")
+    return {"tensors": len(sd), "quantized": nq, "lora_merged": merged, "copied": copied}
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(description="checkpoint converter / quantiser")
+    p.add_argument("-s", "--source", required=True)
+    p.add_argument("-o", "--output", required=True)
+    p.add_argument("-o_n", "--output_name", default="converted")
+    p.add_argument("-o_e", "--output_ext", default=".safetensors", choices=[".safetensors", ".pth"])
+    p.add_argument("-d", "--direction", default="forward", choices=["forward", "backward"])
+    p.add_argument("-t", "--model_type", default="none")
+    p.add_argument("--rule", action="append", help="extra regex rule 'pattern=>replacement'")
+    p.add_argument("--lora_path", nargs="*")
+    p.add_argument("--lora_strength", type=float, default=1.0)
+    p.add_argument("--quantized", action="store_true")
+    p.add_argument("--linear_dtype", default="fp8", choices=["fp8", "mxfp8"])
+    p.add_argument("--quantize_modules", nargs="*", default=["attn", "ffn"])
+    p.add_argument("--dtype", default=None, choices=[None, "bfloat16", "float16", "float32"])
+    p.add_argument("-b", "--save_by_block", action="store_true")
+    p.add_argument("--copy_no_weight_files", action="store_true")
+    return p
+
+
+def main(argv=None) -> dict:
+    return convert_weights(build_parser().parse_args(argv))
+
+
+if __name__ == "__main__":
+    main()
