@@ -341,3 +341,159 @@ extern "C" int tfb_moe_combine(const void* y, int hidden, const int* row_map, co
       static_cast<uint4*>(out));
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
+
+// =============================================================================================
+// Expert parallelism over peer-mapped memory: experts are split evenly over P ranks (rank o owns
+// experts [o*E_loc, (o+1)*E_loc)). Dispatch = the permute kernel storing token rows straight into
+// the owner's receive buffer; combine = the weighted sum loading expert outputs straight from the
+// owners' output buffers. No all-to-all, no staging copies.
+namespace tfb {
+
+struct MoePeers {
+  void* p[8];
+};
+
+// counts_all: int[P][E] (row s = histogram of rank s's tokens). One block.
+//   dst_base[e]   : first row, in the owner's receive buffer, for THIS rank's tokens of expert e
+//   tile_expert[m]: local expert id owning rows [m*align, (m+1)*align) of THIS rank's receive buffer, or -1
+__global__ void moe_ep_plan_kernel(const int* __restrict__ counts_all, int P, int E, int E_loc, int my_rank, int align,
+                                   int* __restrict__ dst_base, int* __restrict__ tile_expert, int max_tiles) {
+  __shared__ int seg_off[MOE_MAX_EXPERTS + 1];  // per owner: aligned start of each of its local experts
+  __shared__ int before_me[MOE_MAX_EXPERTS];    // rows of lower ranks inside the expert's segment
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int b = 0;
+    for (int s = 0; s < my_rank; ++s) b += counts_all[s * E + e];
+    before_me[e] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x < P) {  // thread o lays out owner o's buffer
+    const int o = threadIdx.x;
+    int acc = 0;
+    for (int l = 0; l < E_loc; ++l) {
+      const int e = o * E_loc + l;
+      int tot = 0;
+      for (int s = 0; s < P; ++s) tot += counts_all[s * E + e];
+      seg_off[e] = acc;
+      acc += (tot + align - 1) / align * align;
+    }
+    if (o == my_rank) seg_off[E] = acc;  // padded total of my own buffer
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) dst_base[e] = seg_off[e] + before_me[e];
+  const int base = my_rank * E_loc;
+  for (int m = threadIdx.x; m < max_tiles; m += blockDim.x) {
+    const int row = m * align;
+    int owner = -1;
+    if (row < seg_off[E]) {
+      int lo = 0, hi = E_loc - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (seg_off[base + mid] <= row) lo = mid; else hi = mid - 1;
+      }
+      owner = lo;
+    }
+    tile_expert[m] = owner;
+  }
+}
+
+// One warp per (token, k). row_map[i] = (owner << 26) | row.
+__global__ void moe_ep_dispatch_kernel(const uint4* __restrict__ x, int row_vecs, const int* __restrict__ ids,
+                                       const int* __restrict__ dst_base, int* __restrict__ cursor, long TK, int K,
+                                       int E_loc, MoePeers recv, int* __restrict__ row_map) {
+  const int lane = threadIdx.x & 31;
+  const long warp = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const long nwarps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  for (long i = warp; i < TK; i += nwarps) {
+    int pos = 0, owner = 0;
+    if (lane == 0) {
+      const int e = ids[i];
+      owner = e / E_loc;
+      pos = dst_base[e] + atomicAdd(&cursor[e], 1);
+      row_map[i] = (owner << 26) | pos;
+    }
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    owner = __shfl_sync(0xffffffffu, owner, 0);
+    const uint4* src = x + (i / K) * row_vecs;
+    uint4* dst = static_cast<uint4*>(recv.p[owner]) + static_cast<long>(pos) * row_vecs;
+    for (int c = lane; c < row_vecs; c += 32) dst[c] = src[c];
+  }
+}
+
+__global__ void moe_ep_combine_kernel(MoePeers ybuf, int row_vecs, const int* __restrict__ row_map,
+                                      const float* __restrict__ w, int T, int K, const uint4* __restrict__ residual,
+                                      uint4* __restrict__ out) {
+  const long total = static_cast<long>(T) * row_vecs;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long t = i / row_vecs;
+    const int c = static_cast<int>(i - t * row_vecs);
+    float acc[8];
+    if (residual) {
+      const uint4 r = residual[i];
+      const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(rp[k]);
+        acc[2 * k] = f.x, acc[2 * k + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    }
+    for (int k = 0; k < K; ++k) {
+      const float wk = w[t * K + k];
+      if (wk == 0.f) continue;
+      const int rm = row_map[t * K + k];
+      const uint4 v = static_cast<const uint4*>(ybuf.p[rm >> 26])[static_cast<long>(rm & 0x3ffffff) * row_vecs + c];
+      const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(vp[j]);
+        acc[2 * j] = fmaf(f.x, wk, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(f.y, wk, acc[2 * j + 1]);
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) op[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+    out[i] = o;
+  }
+}
+
+}  // namespace tfb
+
+extern "C" int tfb_moe_ep_plan(const int* counts_all, int P, int E, int my_rank, int align, int* dst_base,
+                               int* tile_expert, int max_tiles, void* stream) {
+  if (P < 1 || P > 8 || E < 1 || E > MOE_MAX_EXPERTS || E % P || my_rank < 0 || my_rank >= P || align < 1)
+    return TFB_ERR_BAD_SHAPE;
+  moe_ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts_all, P, E, E / P, my_rank, align, dst_base,
+                                                                     tile_expert, max_tiles);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+// recv: HOST array of P device pointers (every rank's receive buffer). cursor: int[E] scratch (zeroed here).
+extern "C" int tfb_moe_ep_dispatch(const void* x, int hidden, const int* ids, const int* dst_base, int* cursor, int E,
+                                   int P, long T, int K, void* const* recv, int* row_map, void* stream) {
+  if (T <= 0) return TFB_OK;
+  if (hidden % 8 || P < 1 || P > 8 || E % P || K < 1) return TFB_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MoePeers r;
+  for (int i = 0; i < 8; ++i) r.p[i] = i < P ? recv[i] : nullptr;
+  cudaMemsetAsync(cursor, 0, sizeof(int) * E, st);
+  moe_ep_dispatch_kernel<<<moe_grid(T * K * 32), 256, 0, st>>>(static_cast<const uint4*>(x), hidden / 8, ids, dst_base,
+                                                               cursor, T * K, K, E / P, r, row_map);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+// ybuf: HOST array of P device pointers (every rank's expert-output buffer).
+extern "C" int tfb_moe_ep_combine(void* const* ybuf, int P, int hidden, const int* row_map, const float* weights, int T,
+                                  int K, const void* residual, void* out, void* stream) {
+  if (T <= 0) return TFB_OK;
+  if (hidden % 8 || P < 1 || P > 8 || K < 1) return TFB_ERR_BAD_SHAPE;
+  MoePeers y;
+  for (int i = 0; i < 8; ++i) y.p[i] = i < P ? ybuf[i] : nullptr;
+  moe_ep_combine_kernel<<<moe_grid(static_cast<long>(T) * (hidden / 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      y, hidden / 8, row_map, weights, T, K, static_cast<const uint4*>(residual), static_cast<uint4*>(out));
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}

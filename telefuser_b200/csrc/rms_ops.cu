@@ -1,0 +1,213 @@
+// RMSNorm-based block glue of sandwich-norm DiTs (RMSNorm before and after every sub-layer, tanh gates):
+//   rmsnorm_modulate      : out = (w * x * rstd) * (1 + scale) + shift
+//   rmsnorm_gate_residual : out = res + tanh(gate) * (w * y * rstd)
+//   headnorm_rope         : per-head RMSNorm of q and k (weight [D]) + interleaved-pair RoPE, in place
+// Row kernels use one CTA of 256 threads per token row (C <= 8192); the head kernel one warp per
+// (token, head). bf16 activations, fp32 statistics, fp32 modulation / gate tables.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tfb_api.h"
+#include "tfb_common.cuh"
+
+namespace tfb {
+
+__device__ __forceinline__ void r_unpack8(const uint4& u, float (&f)[8]) {
+  f[0] = bf16_lo(u.x), f[1] = bf16_hi(u.x), f[2] = bf16_lo(u.y), f[3] = bf16_hi(u.y);
+  f[4] = bf16_lo(u.z), f[5] = bf16_hi(u.z), f[6] = bf16_lo(u.w), f[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ uint4 r_pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]), u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]), u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+__device__ __forceinline__ float r_block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ void load_f8(const float* p, float (&f)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+}
+
+// MODE 0: modulate (aux0 = shift, aux1 = scale; either may be null)
+// MODE 1: gated residual (res + tanh?(gate) * normed; aux0 = gate or null, res required)
+template <int NV, int MODE>
+__global__ void __launch_bounds__(256) rmsnorm_row_kernel(const __nv_bfloat16* __restrict__ x, long ldx,
+                                                          const __nv_bfloat16* __restrict__ res, long ldr,
+                                                          __nv_bfloat16* __restrict__ out, long ldo, int C, float eps,
+                                                          const float* __restrict__ w, const float* __restrict__ aux0,
+                                                          const float* __restrict__ aux1, long ldaux, int rows_per_aux,
+                                                          int tanh_gate) {
+  __shared__ float red[8];
+  const long row = blockIdx.x;
+  const int nvec = C >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      r_unpack8(xr[vi], v[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+  const float rstd = rsqrtf(r_block_sum(ss, red) / C + eps);
+  const long arow = (row / rows_per_aux) * ldaux;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      float wf[8], y[8];
+      if (w) {
+        load_f8(w + vi * 8, wf);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) wf[e] = 1.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = v[i][e] * rstd * wf[e];
+      if (MODE == 0) {
+        if (aux1) {
+          float sc[8];
+          load_f8(aux1 + arow + vi * 8, sc);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] *= 1.f + sc[e];
+        }
+        if (aux0) {
+          float sh[8];
+          load_f8(aux0 + arow + vi * 8, sh);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] += sh[e];
+        }
+      } else {
+        float r[8];
+        r_unpack8(reinterpret_cast<const uint4*>(res + row * ldr)[vi], r);
+        if (aux0) {
+          float g[8];
+          load_f8(aux0 + arow + vi * 8, g);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] = r[e] + (tanh_gate ? tanhf(g[e]) : g[e]) * y[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] += r[e];
+        }
+      }
+      reinterpret_cast<uint4*>(out + row * ldo)[vi] = r_pack8(y);
+    }
+  }
+}
+
+// One warp per (row, head, matrix); PL = D / 32 elements per lane (2, 4, 6 or 8), pairs stay in a lane.
+template <int PL>
+__global__ void headnorm_rope_kernel(__nv_bfloat16* __restrict__ x, long ldx, long mat_stride, int nmat, long rows,
+                                     int H, float eps, const float* __restrict__ w0, const float* __restrict__ w1,
+                                     const float* __restrict__ cs, const float* __restrict__ sn) {
+  constexpr int D = PL * 32;
+  const int lane = threadIdx.x & 31;
+  const long warp = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const long nwarps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  const long total = rows * H * nmat;
+  for (long i = warp; i < total; i += nwarps) {
+    const int mat = static_cast<int>(i % nmat);
+    const long rh = i / nmat;
+    const int h = static_cast<int>(rh % H);
+    const long row = rh / H;
+    __nv_bfloat16* p = x + row * ldx + mat * mat_stride + h * D + lane * PL;
+    float v[PL];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < PL; e += 2) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + e));
+      v[e] = f.x, v[e + 1] = f.y;
+      ss += f.x * f.x + f.y * f.y;
+    }
+    const float rstd = rsqrtf(warp_sum(ss) / D + eps);
+    const float* w = mat == 0 ? w0 : w1;
+#pragma unroll
+    for (int e = 0; e < PL; ++e) v[e] *= rstd * (w ? __ldg(w + lane * PL + e) : 1.f);
+    if (cs) {
+      const long t = row * (D / 2) + lane * (PL / 2);
+#pragma unroll
+      for (int e = 0; e < PL; e += 2) {
+        const float c = __ldg(cs + t + e / 2), s = __ldg(sn + t + e / 2);
+        const float a = v[e], b = v[e + 1];
+        v[e] = a * c - b * s;
+        v[e + 1] = a * s + b * c;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < PL; e += 2) *reinterpret_cast<__nv_bfloat162*>(p + e) = __floats2bfloat162_rn(v[e], v[e + 1]);
+  }
+}
+
+}  // namespace tfb
+
+using namespace tfb;
+
+template <int MODE>
+static int launch_rms_row(const void* x, long ldx, const void* res, long ldr, void* out, long ldo, int rows, int C,
+                          float eps, const float* w, const float* a0, const float* a1, long ldaux, int rows_per_aux,
+                          int tanh_gate, void* stream) {
+  if (rows <= 0) return TFB_OK;
+  if (C % 8 || C > 8192 || ldx % 8 || ldo % 8 || ldaux % 4 || (MODE == 1 && (!res || ldr % 8))) return TFB_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nv = (C / 8 + 255) / 256;
+  if (rows_per_aux <= 0) rows_per_aux = 1;
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* rp = static_cast<const __nv_bfloat16*>(res);
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+#define TFB_RMS_ROW(NV_)                                                                                         \
+  rmsnorm_row_kernel<NV_, MODE><<<rows, 256, 0, st>>>(xp, ldx, rp, ldr, op, ldo, C, eps, w, a0, a1, ldaux,         \
+                                                      rows_per_aux, tanh_gate)
+  switch (nv) {
+    case 1: TFB_RMS_ROW(1); break;
+    case 2: TFB_RMS_ROW(2); break;
+    case 3: TFB_RMS_ROW(3); break;
+    default: TFB_RMS_ROW(4); break;
+  }
+#undef TFB_RMS_ROW
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+extern "C" int tfb_rmsnorm_modulate(const void* x, long ldx, void* out, long ldo, int rows, int C, float eps,
+                                    const float* w, const float* shift, const float* scale, long ldmod,
+                                    int rows_per_mod, void* stream) {
+  return launch_rms_row<0>(x, ldx, nullptr, 0, out, ldo, rows, C, eps, w, shift, scale, ldmod, rows_per_mod, 0, stream);
+}
+
+extern "C" int tfb_rmsnorm_gate_residual(const void* y, long ldy, const void* res, long ldr, void* out, long ldo,
+                                         int rows, int C, float eps, const float* w, const float* gate, long ldg,
+                                         int rows_per_gate, int tanh_gate, void* stream) {
+  return launch_rms_row<1>(y, ldy, res, ldr, out, ldo, rows, C, eps, w, gate, nullptr, ldg, rows_per_gate, tanh_gate,
+                           stream);
+}
+
+extern "C" int tfb_headnorm_rope(void* x, long ldx, long mat_stride, int nmat, long rows, int H, int D, float eps,
+                                 const float* w0, const float* w1, const float* cos, const float* sin, void* stream) {
+  if (rows <= 0) return TFB_OK;
+  if (D % 64 || D > 256 || ldx % 2 || mat_stride % 2 || nmat < 1 || nmat > 2 || H < 1) return TFB_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long warps = rows * H * nmat;
+  long blocks = (warps + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  __nv_bfloat16* xp = static_cast<__nv_bfloat16*>(x);
+  switch (D / 32) {
+    case 2: headnorm_rope_kernel<2><<<blocks, 256, 0, st>>>(xp, ldx, mat_stride, nmat, rows, H, eps, w0, w1, cos, sin); break;
+    case 4: headnorm_rope_kernel<4><<<blocks, 256, 0, st>>>(xp, ldx, mat_stride, nmat, rows, H, eps, w0, w1, cos, sin); break;
+    case 6: headnorm_rope_kernel<6><<<blocks, 256, 0, st>>>(xp, ldx, mat_stride, nmat, rows, H, eps, w0, w1, cos, sin); break;
+    default: headnorm_rope_kernel<8><<<blocks, 256, 0, st>>>(xp, ldx, mat_stride, nmat, rows, H, eps, w0, w1, cos, sin); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}

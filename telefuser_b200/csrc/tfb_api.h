@@ -104,6 +104,19 @@ int tfb_moe_permute_static(const void* x, int hidden, const int* ids, const int*
 int tfb_moe_combine(const void* y, int hidden, const int* row_map, const float* weights, int T, int K,
                     const void* residual, void* out, void* stream);
 
+// ---- RMSNorm block glue of sandwich-norm DiTs (rms_ops.cu); norm weights and tables are fp32 ----
+// out = (w * x * rstd) * (1 + scale) + shift; w / shift / scale may be null; table row = row / rows_per_mod.
+int tfb_rmsnorm_modulate(const void* x, long ldx, void* out, long ldo, int rows, int C, float eps, const float* w,
+                         const float* shift, const float* scale, long ldmod, int rows_per_mod, void* stream);
+// out = res + g * (w * y * rstd), g = tanh(gate) if tanh_gate else gate (gate null: g = 1).
+int tfb_rmsnorm_gate_residual(const void* y, long ldy, const void* res, long ldr, void* out, long ldo, int rows, int C,
+                              float eps, const float* w, const float* gate, long ldg, int rows_per_gate,
+                              int tanh_gate, void* stream);
+// In place: per-head RMSNorm (weight fp32 [D], w0 for matrix 0, w1 for matrix 1) then interleaved-pair
+// RoPE with per-token cos/sin fp32 [rows, D/2] (null: no rotation). D in {64, 128, 192, 256}.
+int tfb_headnorm_rope(void* x, long ldx, long mat_stride, int nmat, long rows, int H, int D, float eps,
+                      const float* w0, const float* w1, const float* cos, const float* sin, void* stream);
+
 // ---- peer-mapped buffers (ipc.cu): allocate (zero-filled) + export a 64-byte IPC handle; map a peer's ----
 int tfb_ipc_alloc(long bytes, void** ptr, void* handle64);
 int tfb_ipc_open(const void* handle64, void** ptr);
@@ -127,6 +140,19 @@ int tfb_peer_push_rows(const void* src, long ld_bytes, void* const* dsts, int P,
 int tfb_attn_fwd_peer(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v, long ldv,
                       long bsv, void* const* peer_out, int n_peers, int rows_per_rank, int head_off, long ldo, long bso,
                       int B, int H, int Sq, int Skv, float scale, void* stream);
+
+// ---- expert parallelism over peer-mapped memory (moe.cu); rank o owns experts [o*E/P, (o+1)*E/P) ----
+// counts_all int32 [P, E] (row s = histogram of rank s) -> dst_base int32 [E] (first row of this rank's
+// tokens of expert e inside the owner's receive buffer) and tile_expert int32 [max_tiles] (local expert
+// id per 128-row tile of THIS rank's receive buffer, -1 past the end).
+int tfb_moe_ep_plan(const int* counts_all, int P, int E, int my_rank, int align, int* dst_base, int* tile_expert,
+                    int max_tiles, void* stream);
+// Token rows -> the owners' receive buffers by peer stores; row_map[t*K+k] = (owner << 26) | row.
+int tfb_moe_ep_dispatch(const void* x, int hidden, const int* ids, const int* dst_base, int* cursor, int E, int P,
+                        long T, int K, void* const* recv, int* row_map, void* stream);
+// out[t] = residual[t] (or 0) + sum_k weights[t,k] * ybuf[owner][row]   (peer loads, fp32 accumulate)
+int tfb_moe_ep_combine(void* const* ybuf, int P, int hidden, const int* row_map, const float* weights, int T, int K,
+                       const void* residual, void* out, void* stream);
 
 // ---- streaming / caching kernels (stream_ops.cu) ----
 // Rolling KV cache [B, kv_size, row_elems] bf16 (batch stride cache_bs elements): optional left shift

@@ -529,3 +529,105 @@ def frames_to_uint8(frames):
                                           native.stream_ptr())  # fmt: skip
     native.check(code, "tfb_frames_to_u8")
     return out
+
+
+# ---------------------------------------------------------------------------
+# RMSNorm block glue (sandwich-norm DiTs)
+# ---------------------------------------------------------------------------
+def _rms(x, w, eps):
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return y if w is None else y * w.float()
+
+
+def _table(t, rows):
+    """fp32 [B, S|1, C] (or [rows|1, C]) table -> (contiguous 2-D view, row stride, rows per table row)."""
+    t2 = t.float().reshape(-1, t.shape[-1]).contiguous()
+    return t2, t2.shape[-1], max(1, rows // t2.shape[0])
+
+
+def rmsnorm_modulate(x, weight=None, shift=None, scale=None, eps=1e-6):
+    """(w * rmsnorm(x)) * (1 + scale) + shift; x [..., C] bf16 on CUDA, fp32 weight / tables."""
+    if not _native(x) or x.dtype != torch.bfloat16 or x.shape[-1] % 8 or x.shape[-1] > 8192:
+        y = _rms(x, weight, eps)
+        if scale is not None:
+            y = y * (1.0 + scale.float())
+        if shift is not None:
+            y = y + shift.float()
+        return y.to(x.dtype)
+    C = x.shape[-1]
+    x2 = x.reshape(-1, C).contiguous()
+    rows = x2.shape[0]
+    out = torch.empty_like(x2)
+    w = None if weight is None else weight.float().contiguous()
+    sh = sc = None
+    ld, rpm = C, 1
+    if shift is not None:
+        sh, ld, rpm = _table(shift, rows)
+    if scale is not None:
+        sc, ld, rpm = _table(scale, rows)
+    code = native.load().tfb_rmsnorm_modulate(x2.data_ptr(), C, out.data_ptr(), C, rows, C, float(eps), native.ptr(w),
+                                              native.ptr(sh), native.ptr(sc), ld, rpm, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_rmsnorm_modulate")
+    return out.view(x.shape)
+
+
+def rmsnorm_gate_residual(res, y, weight=None, gate=None, eps=1e-6, tanh_gate=True):
+    """res + tanh(gate) * (w * rmsnorm(y))."""
+    if not _native(y) or y.dtype != torch.bfloat16 or res.dtype != torch.bfloat16 or y.shape[-1] % 8 or y.shape[-1] > 8192:
+        n = _rms(y, weight, eps)
+        if gate is not None:
+            n = (gate.float().tanh() if tanh_gate else gate.float()) * n
+        return (res.float() + n).to(res.dtype)
+    C = y.shape[-1]
+    y2, r2 = y.reshape(-1, C).contiguous(), res.reshape(-1, C).contiguous()
+    rows = y2.shape[0]
+    out = torch.empty_like(r2)
+    w = None if weight is None else weight.float().contiguous()
+    g, ld, rpg = None, C, 1
+    if gate is not None:
+        g, ld, rpg = _table(gate, rows)
+    code = native.load().tfb_rmsnorm_gate_residual(y2.data_ptr(), C, r2.data_ptr(), C, out.data_ptr(), C, rows, C,
+                                                   float(eps), native.ptr(w), native.ptr(g), ld, rpg, int(tanh_gate),
+                                                   native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_rmsnorm_gate_residual")
+    return out.view(res.shape)
+
+
+def headnorm_rope_(q, weight_q, cos=None, sin=None, eps=1e-6, k=None, weight_k=None):
+    """In place on q (and k): per-head RMSNorm over the last dim, then interleaved-pair RoPE.
+    q / k: [B, S, H, D] views (possibly slices of one fused buffer); cos / sin: fp32 [B*S, D/2]."""
+    B, S, H, D = q.shape
+
+    def ref(t, w):
+        y = _rms(t, w, eps)
+        if cos is not None:
+            y = rope_reference(y.reshape(1, B * S, H, D), cos, sin).reshape(B, S, H, D)
+        t.copy_(y.to(t.dtype))
+
+    ok = (_native(q) and q.dtype == torch.bfloat16 and D % 64 == 0 and D <= 256 and q.stride(-1) == 1
+          and q.stride(2) == D and (B == 1 or q.stride(0) == S * q.stride(1)))  # fmt: skip
+    if k is not None:
+        ok = ok and k.stride() == q.stride() and k.dtype == q.dtype
+    if not ok:
+        ref(q, weight_q)
+        if k is not None:
+            ref(k, weight_k)
+        return
+    nmat, stride = 1, 0
+    if k is not None:
+        delta = (k.data_ptr() - q.data_ptr()) // 2
+        if 0 < delta < q.stride(1):
+            nmat, stride = 2, delta
+    lib = native.load()
+    c = None if cos is None else cos.float().contiguous()
+    s = None if sin is None else sin.float().contiguous()
+    wq = None if weight_q is None else weight_q.float().contiguous()
+    wk = None if weight_k is None else weight_k.float().contiguous()
+    code = lib.tfb_headnorm_rope(q.data_ptr(), q.stride(1), stride, nmat, B * S, H, D, float(eps), native.ptr(wq),
+                                 native.ptr(wk), native.ptr(c), native.ptr(s), native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_headnorm_rope")
+    if k is not None and nmat == 1:
+        code = lib.tfb_headnorm_rope(k.data_ptr(), k.stride(1), 0, 1, B * S, H, D, float(eps), native.ptr(wk), None,
+                                     native.ptr(c), native.ptr(s), native.stream_ptr())  # fmt: skip
+        native.check(code, "tfb_headnorm_rope")

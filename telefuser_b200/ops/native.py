@@ -92,6 +92,16 @@ def _declare(lib) -> None:
         "tfb_plucker_fold": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
         "tfb_frames_to_u8": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "tfb_rmsnorm_modulate": [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_float, c_void_p, c_void_p,
+                                 c_void_p, c_long, c_int, c_void_p],
+        "tfb_rmsnorm_gate_residual": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_float,
+                                      c_void_p, c_void_p, c_long, c_int, c_int, c_void_p],
+        "tfb_headnorm_rope": [c_void_p, c_long, c_long, c_int, c_long, c_int, c_int, c_float, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p],
+        "tfb_moe_ep_plan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+        "tfb_moe_ep_dispatch": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_long, c_int, c_void_p,
+                                c_void_p, c_void_p],
+        "tfb_moe_ep_combine": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "tfb_peer_barrier": [c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tfb_ulysses_scatter": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p],
