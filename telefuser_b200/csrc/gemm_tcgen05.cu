@@ -31,6 +31,9 @@ struct GemmParams {
   // Grouped mode (mixture of experts): M tile m uses weight rows [tile_expert[m] * N, +N) of B, which
   // then has E * N rows; tiles whose entry is negative (padding past the last expert) are skipped.
   const int* tile_expert;
+  // FP8 (e4m3) operands: out = act((A @ B^T) * a_scale[row] * b_scale[col] + bias); null for bf16.
+  const float* a_scale;
+  const float* b_scale;
 };
 
 template <int BN>
@@ -45,12 +48,16 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BN>
+// FP8: operands are e4m3 bytes. A stage row is still 128 bytes (128 elements instead of 64), so the
+// shared-memory layout, descriptors and the K-step of 32 bytes are those of the bf16 kernel; only the
+// MMA kind (K = 32 per instruction), the element count per stage and the epilogue scales differ.
+template <int BN, bool FP8 = false>
 __global__ void __launch_bounds__(192, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int BKE = FP8 ? 2 * Cfg::BK : Cfg::BK;  // K elements per stage
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
@@ -87,7 +94,7 @@ __global__ void __launch_bounds__(192, 1)
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.m_tiles * p.n_tiles;
-  const int k_blocks = (p.K + Cfg::BK - 1) / Cfg::BK;
+  const int k_blocks = (p.K + BKE - 1) / BKE;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -114,15 +121,15 @@ __global__ void __launch_bounds__(192, 1)
           uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-          tma_load_2d(a_dst, &tmA, &full[s], kb * Cfg::BK, m_blk * Cfg::BM);
-          tma_load_2d(b_dst, &tmB, &full[s], kb * Cfg::BK, b_row);
+          tma_load_2d(a_dst, &tmA, &full[s], kb * BKE, m_blk * Cfg::BM);
+          tma_load_2d(b_dst, &tmB, &full[s], kb * BKE, b_row);
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    constexpr uint32_t idesc = make_idesc(128, BN, 1, 1, 0, 0);
+    constexpr uint32_t idesc = FP8 ? make_idesc(128, BN, 0, 0, 0, 0) : make_idesc(128, BN, 1, 1, 0, 0);
     uint32_t it = 0;
     uint32_t tile_iter = 0;
     bool ok = true;
@@ -152,7 +159,10 @@ __global__ void __launch_bounds__(192, 1)
           for (int kk = 0; kk < Cfg::BK / 16; ++kk) {
             const uint64_t ad = make_desc_k_sw128(a_addr + kk * 32);
             const uint64_t bd = make_desc_k_sw128(b_addr + kk * 32);
-            umma_f16_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+            if (FP8)
+              umma_f8_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+            else
+              umma_f16_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[s]);
           if (kb == k_blocks - 1) umma_commit(&tfull[acc]);
@@ -192,6 +202,11 @@ __global__ void __launch_bounds__(192, 1)
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
           const bool full_chunk = col0 + 32 <= p.N;
+          if (FP8) {
+            const float as = __ldg(p.a_scale + row);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= as * ((full_chunk || col0 + i < p.N) ? __ldg(p.b_scale + col0 + i) : 0.f);
+          }
           if (full_chunk) {
             if (p.bias) {
               const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
@@ -272,16 +287,16 @@ __global__ void __launch_bounds__(192, 1)
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
-template <int BN>
+template <int BN, bool FP8 = false>
 static int launch_gemm(const CUtensorMap& tmA, const void* B, int ldb, GemmParams p, cudaStream_t stream,
                        long b_rows = 0) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmB;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(b_rows > 0 ? b_rows : p.N)};
-    uint64_t str[1] = {static_cast<uint64_t>(ldb) * 2};
-    uint32_t box[2] = {64, static_cast<uint32_t>(BN)};
-    int e = make_tmap(&tmB, B, TM_BF16, 2, dims, str, box, TM_SW_128);
+    uint64_t str[1] = {static_cast<uint64_t>(ldb) * (FP8 ? 1 : 2)};
+    uint32_t box[2] = {FP8 ? 128u : 64u, static_cast<uint32_t>(BN)};
+    int e = make_tmap(&tmB, B, FP8 ? TM_U8 : TM_BF16, 2, dims, str, box, TM_SW_128);
     if (e) return e;
   }
   p.m_tiles = (p.M + 127) / 128;
@@ -291,12 +306,12 @@ static int launch_gemm(const CUtensorMap& tmA, const void* B, int ldb, GemmParam
   cudaGetDevice(&dev);
   dev &= 15;
   if (!attr_set[dev]) {
-    cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<BN, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     attr_set[dev] = true;
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_bf16_kernel<BN><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  gemm_bf16_kernel<BN, FP8><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 
@@ -328,6 +343,7 @@ extern "C" int tfb_gemm_bf16(const void* A, int lda, const void* B, int ldb, voi
   p.epi = epi;
   p.status = status_word();
   p.tile_expert = nullptr;
+  p.a_scale = p.b_scale = nullptr;
   CUtensorMap tmA;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
@@ -381,6 +397,7 @@ extern "C" int tfb_gemm_bf16_grouped(const void* A, int lda, const void* B, int 
   p.epi = epi;
   p.status = status_word();
   p.tile_expert = tile_expert;
+  p.a_scale = p.b_scale = nullptr;
   CUtensorMap tmA;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
@@ -394,4 +411,49 @@ extern "C" int tfb_gemm_bf16_grouped(const void* A, int lda, const void* B, int 
   if (N % 256 == 0) return launch_gemm<256>(tmA, B, ldb, p, st, b_rows);
   if (N % 128 == 0) return launch_gemm<128>(tmA, B, ldb, p, st, b_rows);
   return launch_gemm<64>(tmA, B, ldb, p, st, b_rows);
+}
+
+// W8A8 GEMM: A e4m3 [M, K] with one fp32 scale per row (per-token), B e4m3 [N, K] with one fp32 scale
+// per row (per-output-channel); out bf16 = epilogue((A @ B^T) * a_scale[m] * b_scale[n]).
+extern "C" int tfb_gemm_fp8(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K,
+                            const float* a_scale, const float* b_scale, const void* bias, int epi, const void* resid,
+                            int ldr, const float* gate, int ldg, int rows_per_gate, void* stream) {
+  using namespace tfb;
+  if (M <= 0 || N <= 0 || K <= 0 || !a_scale || !b_scale) return TFB_ERR_BAD_SHAPE;
+  if ((K % 16) || (lda % 16) || (ldb % 16) || (ldo % 8) || (N % 8)) return TFB_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return TFB_ERR_BAD_SHAPE;
+  if (resid && ((ldr % 8) || (reinterpret_cast<uintptr_t>(resid) & 15))) return TFB_ERR_BAD_SHAPE;
+  if (gate && ((ldg % 4) || (reinterpret_cast<uintptr_t>(gate) & 15))) return TFB_ERR_BAD_SHAPE;
+  if (bias && (reinterpret_cast<uintptr_t>(bias) & 15)) return TFB_ERR_BAD_SHAPE;
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.resid = static_cast<const __nv_bfloat16*>(resid);
+  p.ldr = ldr;
+  p.gate = gate;
+  p.ldg = ldg;
+  p.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1;
+  p.epi = epi;
+  p.status = status_word();
+  p.tile_expert = nullptr;
+  p.a_scale = a_scale;
+  p.b_scale = b_scale;
+  CUtensorMap tmA;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    uint64_t str[1] = {static_cast<uint64_t>(lda)};
+    uint32_t box[2] = {128, 128};
+    int e = make_tmap(&tmA, A, TM_U8, 2, dims, str, box, TM_SW_128);
+    if (e) return e;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long m_tiles = (M + 127) / 128;
+  if (N % 256 == 0 && m_tiles * (N / 256) >= sm_count()) return launch_gemm<256, true>(tmA, B, ldb, p, st);
+  if (N >= 128) return launch_gemm<128, true>(tmA, B, ldb, p, st);
+  return launch_gemm<64, true>(tmA, B, ldb, p, st);
 }

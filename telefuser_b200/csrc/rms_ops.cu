@@ -152,9 +152,57 @@ __global__ void headnorm_rope_kernel(__nv_bfloat16* __restrict__ x, long ldx, lo
   }
 }
 
+// Per-token FP8 quantisation for the W8A8 GEMM: q = e4m3(x / s), s = max(row amax / 448, 1e-12).
+// One CTA per row; the row is read twice (the second read hits L1/L2).
+__global__ void __launch_bounds__(256) quant_fp8_row_kernel(const __nv_bfloat16* __restrict__ x, long ldx,
+                                                            uint8_t* __restrict__ q, long ldq,
+                                                            float* __restrict__ scale, int C) {
+  __shared__ float red[8];
+  const long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
+  const int nvec = C >> 3;
+  float amax = 0.f;
+  for (int vi = threadIdx.x; vi < nvec; vi += 256) {
+    float f[8];
+    r_unpack8(xr[vi], f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+  }
+  amax = warp_max(amax);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  const float s = fmaxf(amax * (1.f / 448.f), 1e-12f);
+  const float inv = __fdiv_rn(1.f, s);
+  if (threadIdx.x == 0) scale[row] = s;
+  uint2* qr = reinterpret_cast<uint2*>(q + row * ldq);
+  for (int vi = threadIdx.x; vi < nvec; vi += 256) {
+    float f[8];
+    r_unpack8(xr[vi], f);
+    uint16_t h[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h[e]) : "f"(f[2 * e + 1] * inv), "f"(f[2 * e] * inv));
+    qr[vi] = make_uint2(static_cast<uint32_t>(h[0]) | (static_cast<uint32_t>(h[1]) << 16),
+                        static_cast<uint32_t>(h[2]) | (static_cast<uint32_t>(h[3]) << 16));
+  }
+}
+
 }  // namespace tfb
 
 using namespace tfb;
+
+extern "C" int tfb_quant_fp8_rowwise(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int C,
+                                     void* stream) {
+  if (rows <= 0) return TFB_OK;
+  if (C % 8 || ldx % 8 || ldq % 8) return TFB_ERR_BAD_SHAPE;
+  quant_fp8_row_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), ldq, scale, C);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
 
 template <int MODE>
 static int launch_rms_row(const void* x, long ldx, const void* res, long ldr, void* out, long ldo, int rows, int C,

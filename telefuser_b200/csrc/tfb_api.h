@@ -104,6 +104,15 @@ int tfb_moe_permute_static(const void* x, int hidden, const int* ids, const int*
 int tfb_moe_combine(const void* y, int hidden, const int* row_map, const float* weights, int T, int K,
                     const void* residual, void* out, void* stream);
 
+// ---- W8A8 FP8 linear: per-token activation scales x per-output-channel weight scales ----
+// out bf16 [M, N] = epilogue((A e4m3 [M,K] @ B e4m3 [N,K]^T) * a_scale[m] * b_scale[n]); same epilogue
+// options as tfb_gemm_bf16 (bias, GELU, gate, residual). K % 16 == 0.
+int tfb_gemm_fp8(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K,
+                 const float* a_scale, const float* b_scale, const void* bias, int epi, const void* resid, int ldr,
+                 const float* gate, int ldg, int rows_per_gate, void* stream);
+// x bf16 [rows, C] -> q e4m3 [rows, C] + scale fp32 [rows] (= max(amax/448, 1e-12)).
+int tfb_quant_fp8_rowwise(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int C, void* stream);
+
 // ---- RMSNorm block glue of sandwich-norm DiTs (rms_ops.cu); norm weights and tables are fp32 ----
 // out = (w * x * rstd) * (1 + scale) + shift; w / shift / scale may be null; table row = row / rows_per_mod.
 int tfb_rmsnorm_modulate(const void* x, long ldx, void* out, long ldo, int rows, int C, float eps, const float* w,

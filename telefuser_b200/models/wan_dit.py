@@ -142,9 +142,11 @@ def _fuse_linear_weights(linears: list[nn.Linear]):
         # Already row slices of one buffer (e.g. re-homed by the weight-sharding wrapper): view, no copy.
         W = torch.as_strided(w0.data, (sum(n), w0.shape[1]), (w0.shape[1], 1))
         b = torch.as_strided(linears[0].bias.data, (sum(n),), (1,)) if linears[0].bias is not None else None
-        return W, b
+        return _with_fused_scale(W, linears), b
     W = torch.empty(sum(n), w0.shape[1], dtype=w0.dtype, device=w0.device)
-    b = torch.empty(sum(n), dtype=w0.dtype, device=w0.device) if linears[0].bias is not None else None
+    b = None
+    if linears[0].bias is not None:
+        b = torch.empty(sum(n), dtype=linears[0].bias.dtype, device=w0.device)
     o = 0
     for lin, k in zip(linears, n):
         W[o : o + k].copy_(lin.weight.data)
@@ -153,7 +155,15 @@ def _fuse_linear_weights(linears: list[nn.Linear]):
             b[o : o + k].copy_(lin.bias.data)
             lin.bias.data = b[o : o + k]
         o += k
-    return W, b
+    return _with_fused_scale(W, linears), b
+
+
+def _with_fused_scale(W: torch.Tensor, linears: list[nn.Linear]) -> torch.Tensor:
+    """fp8 weights carry one scale per output channel (`tfb_scale`); the fused view gets their concatenation."""
+    scales = [getattr(lin.weight, "tfb_scale", None) for lin in linears]
+    if all(s is not None for s in scales):
+        W.tfb_scale = torch.cat([s.reshape(-1) for s in scales]).contiguous()
+    return W
 
 
 class WanSelfAttention(nn.Module):
@@ -443,6 +453,15 @@ class WanModel(BaseModel):
         if self.usp_flag:
             (x,) = pshard.sequence_parallel_unshard([x], [1], [seq_len])
         return self.unpatchify(x, grid)
+
+    def enable_quant(self, quant=None) -> int:
+        """W8A8 FP8 for the block projections (attention q/k/v/o and both FFN layers); embeddings, the
+        head and all norms / modulation tables stay in bf16 / fp32. Returns the number of layers converted."""
+        from telefuser_b200.ops.quant import quantize_model_fp8_
+
+        skip = tuple(getattr(quant, "skip_modules", None) or ("head", "time_embedding", "time_projection",
+                                                              "patch_embedding", "text_embedding", "img_emb"))  # fmt: skip
+        return quantize_model_fp8_(self, ("blocks.*",), skip)
 
     # ---- parallel plans --------------------------------------------------------
     def get_fsdp_module_names(self) -> list[str]:

@@ -53,6 +53,12 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
     x: [..., K] bf16; weight: [N, K]; gate: fp32 broadcastable over rows as
     [..., 1, N] (one gate row per leading batch entry) or per row [..., N].
     """
+    if weight.dtype == torch.float8_e4m3fn:
+        r = linear_fp8(x, weight, getattr(weight, "tfb_scale", None), bias, act, residual, gate)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
     if not _native(x) or x.dtype != torch.bfloat16:
         r = linear_reference(x, weight, bias, act, residual, gate)
         if out is not None:
@@ -98,6 +104,66 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
     if act not in (None, "gelu_tanh"):
         raise ValueError(f"unknown activation {act}")
     native.check(code, "tfb_gemm_bf16")
+    return out
+
+
+def quant_fp8_rowwise(x):
+    """x [..., C] -> (e4m3 [..., C], fp32 scale [..., 1]) with scale = row amax / 448 (floor 1e-12)."""
+    C = x.shape[-1]
+    if not _native(x) or x.dtype != torch.bfloat16 or C % 8:
+        s = (x.float().abs().amax(-1, keepdim=True) / 448.0).clamp_min(1e-12)
+        return (x.float() / s).clamp(-448, 448).to(torch.float8_e4m3fn), s
+    x2 = x.reshape(-1, C)
+    if x2.stride(-1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    q = torch.empty(x2.shape, device=x.device, dtype=torch.float8_e4m3fn)
+    s = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
+    code = native.load().tfb_quant_fp8_rowwise(x2.data_ptr(), x2.stride(0), q.data_ptr(), C, s.data_ptr(), x2.shape[0],
+                                               C, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_quant_fp8_rowwise")
+    return q.view(x.shape), s.view(*x.shape[:-1], 1)
+
+
+def linear_fp8(x, weight, weight_scale, bias=None, act=None, residual=None, gate=None):
+    """W8A8: weight e4m3 [N, K] with per-output-channel scale [N] or [N, 1]; activations are quantised
+    per token on the fly; fp32 accumulate; epilogue as `linear`."""
+    if weight_scale is None:
+        raise ValueError("an fp8 weight needs its per-channel scale (attribute `tfb_scale` or argument)")
+    ws = weight_scale.float().reshape(-1)
+    K, N = x.shape[-1], weight.shape[0]
+    if not _native(x) or x.dtype != torch.bfloat16 or K % 16 or N % 8:
+        q, s = quant_fp8_rowwise(x)
+        y = (q.float() @ weight.float().t()) * s.float() * ws
+        if bias is not None:
+            y = y + bias.float()
+        if act == "gelu_tanh":
+            y = F.gelu(y, approximate="tanh")
+        elif act is not None:
+            raise ValueError(f"unknown activation {act}")
+        if gate is not None:
+            y = y * gate.float()
+        if residual is not None:
+            y = y + residual.float()
+        return y.to(x.dtype)
+    q, s = quant_fp8_rowwise(x.reshape(-1, K))
+    M = q.shape[0]
+    ws = ws.contiguous()
+    out = torch.empty(*x.shape[:-1], N, device=x.device, dtype=torch.bfloat16)
+    res2 = None if residual is None else residual.reshape(-1, N).contiguous()
+    gate_ptr, ldg, rpg, g2 = None, 0, 1, None
+    if gate is not None:
+        g2 = gate.float().reshape(-1, N).contiguous()
+        gate_ptr, ldg, rpg = g2.data_ptr(), N, M // g2.shape[0]
+    if bias is not None and bias.dtype != torch.bfloat16:
+        bias = bias.to(torch.bfloat16)
+    if act not in (None, "gelu_tanh"):
+        raise ValueError(f"unknown activation {act}")
+    w = weight if weight.stride(-1) == 1 else weight.contiguous()
+    code = native.load().tfb_gemm_fp8(q.data_ptr(), K, w.data_ptr(), w.stride(0), out.data_ptr(), N, M, N, K,
+                                      s.data_ptr(), ws.data_ptr(), native.ptr(bias), 1 if act == "gelu_tanh" else 0,
+                                      native.ptr(res2), N if res2 is not None else 0, gate_ptr, ldg, rpg,
+                                      native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_gemm_fp8")
     return out
 
 

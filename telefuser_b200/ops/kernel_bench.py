@@ -88,6 +88,22 @@ def bench_gemm(t: Timer, m: int, n: int, k: int, compare: bool) -> None:
     flops = 2.0 * m * n * k
     report("gemm_bf16_tcgen05 (+bias, gelu)", t(lambda: TF.linear(a, w, bias, act="gelu_tanh")), flops, m=m, n=n, k=k)
     report("gemm_bf16_tcgen05 (+bias)", t(lambda: TF.linear(a, w, bias)), flops, m=m, n=n, k=k)
+    from telefuser_b200.ops.quant import quantize_weight_fp8
+
+    w8, ws = quantize_weight_fp8(w)
+    a8, as_ = TF.quant_fp8_rowwise(a)
+    report("quant_fp8_rowwise", t(lambda: TF.quant_fp8_rowwise(a)), bytes_=m * k * 3, m=m, k=k)
+    report("gemm_fp8_tcgen05 W8A8 (+bias, incl. activation quant)", t(lambda: TF.linear_fp8(a, w8, ws, bias)), flops,
+           m=m, n=n, k=k)  # fmt: skip
+    lib = TF.native.load()
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    wsf, asf = ws.reshape(-1).contiguous(), as_.reshape(-1).contiguous()
+
+    def gemm_only():
+        lib.tfb_gemm_fp8(a8.data_ptr(), k, w8.data_ptr(), k, out.data_ptr(), n, m, n, k, asf.data_ptr(), wsf.data_ptr(),
+                         bias.data_ptr(), 0, None, 0, None, 0, 1, TF.native.stream_ptr())
+
+    report("gemm_fp8_tcgen05 (GEMM only; fraction is of the bf16 peak)", t(gemm_only), flops, m=m, n=n, k=k)
     if compare:
         report("torch F.linear (cuBLAS)", t(lambda: torch.nn.functional.linear(a, w, bias)), flops, m=m, n=n, k=k)
 

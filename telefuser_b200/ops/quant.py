@@ -1,0 +1,93 @@
+"""Quantised linear layers: W8A8 FP8 (per-token activation scale x per-output-channel weight scale).
+
+Weights are stored as e4m3 `[out, in]` with `weight_scale [out, 1]` (fp32), the checkpoint layout the
+offline converter writes; activations are quantised per token on the fly by a row kernel and the product
+runs on the tcgen05 `kind::f8f6f4` GEMM with the scales applied in its epilogue (`ops.functional.linear`
+dispatches on the weight dtype, so model code does not change).
+`quantize_model_fp8_` converts the selected `nn.Linear` layers of a loaded bf16 model in place.
+Role parity: telefuser/ops/linear_fp8.py (`LinearFP8`), ops/fp8_gemm.py, `BaseModel.enable_quant`.
+"""
+
+from __future__ import annotations
+
+import fnmatch
+
+import torch
+from torch import nn
+
+from . import functional as TF
+
+FP8_MAX = 448.0
+
+
+def quantize_weight_fp8(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """[out, in] -> (e4m3 [out, in], fp32 scale [out, 1]); scale = row amax / 448."""
+    scale = (w.float().abs().amax(dim=1, keepdim=True) / FP8_MAX).clamp_min(1e-12)
+    return (w.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), scale
+
+
+class LinearFP8(nn.Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None) -> None:
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.zeros(out_features, in_features, dtype=torch.float8_e4m3fn, device=device),
+                                   requires_grad=False)  # fmt: skip
+        self.register_buffer("weight_scale", torch.ones(out_features, 1, dtype=torch.float32, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=torch.bfloat16, device=device)) if bias else None
+        self._sync()
+
+    def _sync(self) -> None:
+        self.weight.tfb_scale = self.weight_scale
+
+    @classmethod
+    def from_linear(cls, lin: nn.Linear) -> "LinearFP8":
+        m = cls(lin.in_features, lin.out_features, lin.bias is not None, lin.weight.device)
+        q, s = quantize_weight_fp8(lin.weight.data)
+        m.weight.data, m.weight_scale = q, s
+        if lin.bias is not None:
+            m.bias.data = lin.bias.data.to(torch.bfloat16)
+        m._sync()
+        return m
+
+    def _load_from_state_dict(self, *a, **kw):
+        super()._load_from_state_dict(*a, **kw)
+        self._sync()
+
+    def forward(self, x):
+        return TF.linear_fp8(x, self.weight, self.weight_scale, self.bias)
+
+
+def quantize_linear_fp8_(lin: nn.Linear) -> nn.Linear:
+    """In place: the module keeps its class (model code reads `.weight` / `.bias` directly) but its weight
+    becomes e4m3 and carries `tfb_scale`; a `weight_scale` buffer is registered for checkpoints."""
+    if lin.weight.dtype == torch.float8_e4m3fn:
+        return lin
+    q, s = quantize_weight_fp8(lin.weight.data)
+    lin.weight = nn.Parameter(q, requires_grad=False)
+    if "weight_scale" in lin._buffers:
+        lin.weight_scale = s
+    else:
+        lin.register_buffer("weight_scale", s)
+    lin.weight.tfb_scale = lin.weight_scale
+    return lin
+
+
+def quantize_model_fp8_(model: nn.Module, quantize_modules=("*attn*", "*ffn*"), skip_modules=("head", "time_embedding",
+                        "time_projection", "patch_embedding", "text_embedding", "img_emb"), min_features: int = 64) -> int:  # fmt: skip
+    """Quantises every `nn.Linear` whose qualified name matches one of `quantize_modules` (fnmatch) and
+    none of `skip_modules` (substring); returns the number of layers converted."""
+    n = 0
+    for name, m in model.named_modules():
+        if not isinstance(m, nn.Linear) or min(m.in_features, m.out_features) < min_features:
+            continue
+        if m.in_features % 16 or m.out_features % 8:
+            continue
+        if any(s in name for s in skip_modules) or not any(fnmatch.fnmatchcase(name, p) for p in quantize_modules):
+            continue
+        quantize_linear_fp8_(m)
+        n += 1
+    for m in model.modules():  # cached fused views must be rebuilt from the new weights
+        for attr in ("_qkv", "_kv", "_gu", "_fused"):
+            if hasattr(m, attr):
+                setattr(m, attr, None)
+    return n

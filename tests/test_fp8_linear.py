@@ -1,0 +1,90 @@
+"""W8A8 FP8 linear: quantisation helpers, in-place model conversion, and on GPUs the tcgen05 FP8 GEMM
+with all epilogue options against an fp32 evaluation of the same quantised operands."""
+
+import pytest
+import torch
+from torch import nn
+
+from telefuser_b200.ops import functional as TF
+from telefuser_b200.ops.quant import LinearFP8, quantize_linear_fp8_, quantize_weight_fp8
+from telefuser_b200.testing.distributed_checks import make_tiny_inputs, make_tiny_model
+
+
+def test_weight_and_row_quantisation_round_trip():
+    torch.manual_seed(0)
+    w = torch.randn(48, 64)
+    q, s = quantize_weight_fp8(w)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (48, 1)
+    assert (q.float() * s - w).abs().max() <= w.abs().max() * 0.07
+    x = torch.randn(5, 64)
+    xq, xs = TF.quant_fp8_rowwise(x)
+    assert xs.shape == (5, 1) and (xq.float() * xs - x).abs().max() <= x.abs().max() * 0.07
+    lin = nn.Linear(64, 48)
+    ref = lin(x)
+    m = LinearFP8.from_linear(lin)
+    assert (m(x) - ref).abs().max() <= 0.15 * ref.abs().max()
+    sd = m.state_dict()
+    assert set(sd) == {"weight", "weight_scale", "bias"}
+    m2 = LinearFP8(64, 48)
+    m2.load_state_dict(sd)
+    assert torch.equal(m2(x), m(x))
+    quantize_linear_fp8_(lin)
+    assert lin.weight.dtype == torch.float8_e4m3fn and torch.equal(lin.weight.tfb_scale, lin.weight_scale)
+    assert torch.allclose(TF.linear(x, lin.weight, lin.bias), m(x).to(x.dtype), atol=2e-3)  # m holds a bf16 bias
+
+
+def test_wan_enable_quant_stays_close_and_keeps_fused_views():
+    model = make_tiny_model()
+    latents, ctx, _ = make_tiny_inputs()
+    t = torch.tensor([500.0])
+    ref = model(latents, t, ctx)
+    n = model.enable_quant()
+    assert n == 2 * 10  # per block: 4 + 4 attention projections and 2 FFN layers
+    blk = model.blocks[0]
+    assert blk.ffn[0].weight.dtype == torch.float8_e4m3fn and model.head.head.weight.dtype == torch.float32
+    W, _ = blk.self_attn.fused_qkv()
+    assert W.dtype == torch.float8_e4m3fn and W.tfb_scale.shape == (3 * 128,)
+    out = model(latents, t, ctx)
+    assert torch.isfinite(out).all()
+    assert ((out - ref).norm() / ref.norm()).item() < 0.1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(300, 256, 512), (1024, 1536, 5120), (77, 72, 144)])
+def test_fp8_gemm_matches_fp32_product_of_the_quantised_operands(M, N, K):
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda") / K**0.5
+    bias = torch.randn(N, device="cuda").bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    gate = torch.randn(1, N, device="cuda")
+    q, ws = quantize_weight_fp8(w)
+    xq, xs = TF.quant_fp8_rowwise(x)
+    rq, rs = TF.quant_fp8_rowwise(x.float().cpu())
+    assert (xq.view(torch.uint8).cpu() != rq.view(torch.uint8)).float().mean() < 2e-3
+    assert torch.allclose(xs.cpu(), rs, rtol=1e-6, atol=0)
+    base = (xq.float() @ q.float().t()) * xs * ws.reshape(1, -1)
+    for kw in (dict(), dict(bias=bias), dict(bias=bias, act="gelu_tanh"), dict(bias=bias, residual=res, gate=gate)):
+        got = TF.linear_fp8(x, q, ws, **kw).float()
+        want = base.clone()
+        if "bias" in kw:
+            want = want + bias.float()
+        if kw.get("act"):
+            want = torch.nn.functional.gelu(want, approximate="tanh")
+        if "gate" in kw:
+            want = want * gate
+        if "residual" in kw:
+            want = want + res.float()
+        err = ((got - want).abs() / (1 + want.abs())).max().item()
+        assert err <= 1.5e-2, (kw.keys(), err)
+
+
+@pytest.mark.gpu
+def test_fp8_wan_block_on_gpu_tracks_bf16():
+    model = make_tiny_model(dtype=torch.bfloat16, preset="native-small").cuda()
+    latents, ctx, _ = make_tiny_inputs()
+    t = torch.tensor([500.0], device="cuda")
+    ref = model(latents.cuda().bfloat16(), t, ctx.cuda().bfloat16()).float()
+    assert model.enable_quant() == 20
+    out = model(latents.cuda().bfloat16(), t, ctx.cuda().bfloat16()).float()
+    assert ((out - ref).norm() / ref.norm()).item() < 0.1
