@@ -29,7 +29,9 @@ constexpr int A2_SMEM_BYTES = A2_BAR_OFF + 256 + 1024;
 
 // POLY: share of exp2 evaluated on the FMA pipe instead of MUFU (0 none, 1 a quarter, 2 half).
 // PEER: the epilogue stores each output row into the buffer of the rank that owns the token.
-template <int POLY, bool PEER = false>
+// SPARSE: block-sparse attention. Each CTA (256 query rows of one head) visits only the 128-key blocks
+//         listed for it in p.blk_idx (p.blk_cnt of them); everything else is the dense pipeline.
+template <int POLY, bool PEER = false, bool SPARSE = false>
 __global__ void __launch_bounds__(384, 1)
     attn2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -48,7 +50,9 @@ __global__ void __launch_bounds__(384, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int q_pair = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int n_kv = (p.Skv + ATT_BN - 1) / ATT_BN;
+  const long list_row = (static_cast<long>(b) * p.H + h) * gridDim.x + q_pair;
+  const int* blk_list = SPARSE ? p.blk_idx + list_row * p.max_blocks : nullptr;
+  const int n_kv = SPARSE ? __ldg(p.blk_cnt + list_row) : (p.Skv + ATT_BN - 1) / ATT_BN;
   AbortCtx ctx{abort_flag, p.status};
 
   if (threadIdx.x == 0) {
@@ -80,7 +84,7 @@ __global__ void __launch_bounds__(384, 1)
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 8) {
     // ------------------------------ TMA loader ------------------------------
-    if (lane == 0) {
+    if (lane == 0 && n_kv > 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
@@ -97,7 +101,7 @@ __global__ void __launch_bounds__(384, 1)
         if (!mbar_wait(&kv_empty[slot], ph ^ 1, ctx, 10)) break;
         uint8_t* dst = smem + A2_KV_OFF + slot * ATT_TILE_BYTES;
         const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
-        const int j = n >> 1;
+        const int j = SPARSE ? __ldg(blk_list + (n >> 1)) : (n >> 1);
         mbar_expect_tx(&kv_full[slot], ATT_TILE_BYTES);
         tma_load_3d(dst, tm, &kv_full[slot], h * ATT_D, j * ATT_BN, b);
         tma_load_3d(dst + ATT_BOX_BYTES, tm, &kv_full[slot], h * ATT_D + 64, j * ATT_BN, b);
@@ -129,7 +133,7 @@ __global__ void __launch_bounds__(384, 1)
         umma_f16_ts(o_tmem, p_tmem + kk * 8, make_desc_mn_sw128(v_addr + kk * 2048, ATT_BOX_BYTES), idesc_pv,
                     (j | kk) ? 1u : 0u);
     };
-    bool ok = mbar_wait_warp(&q_full[0], 0, ctx, 20) && mbar_wait_warp(&q_full[1], 0, ctx, 21) &&
+    bool ok = n_kv > 0 && mbar_wait_warp(&q_full[0], 0, ctx, 20) && mbar_wait_warp(&q_full[1], 0, ctx, 21) &&
               mbar_wait_warp(&kv_full[0], 0, ctx, 22);
     if (ok) {
       tc_fence_after();
@@ -192,7 +196,7 @@ __global__ void __launch_bounds__(384, 1)
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, s[c]);
       tmem_ld_wait();
-      const int kv_valid = p.Skv - j * ATT_BN;
+      const int kv_valid = p.Skv - (SPARSE ? __ldg(blk_list + j) : j) * ATT_BN;
       if (kv_valid < ATT_BN) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -270,6 +274,16 @@ __global__ void __launch_bounds__(384, 1)
       tc_fence_before();
       mbar_arrive(&p_ready[st]);
     }
+    if (SPARSE && n_kv == 0) {  // no key block listed for these rows: zero output, lse = -inf
+      const int grow = (q_pair * 2 + st) * ATT_BM + row;
+      if (grow < p.Sq) {
+        uint4* orow = reinterpret_cast<uint4*>(p.out + static_cast<long>(b) * p.bso + static_cast<long>(grow) * p.ldo +
+                                               h * ATT_D);
+        for (int i = 0; i < ATT_D / 8; ++i) orow[i] = make_uint4(0, 0, 0, 0);
+        if (p.lse) p.lse[(static_cast<long>(b) * p.H + h) * p.Sq + grow] = -INFINITY;
+      }
+      ok = false;
+    }
     if (ok) ok = mbar_wait_warp(&o_final[st], 0, ctx, 33);
     if (ok) {
       tc_fence_after();
@@ -343,8 +357,24 @@ static int launch_attn2_peer(const CUtensorMap& tq, const CUtensorMap& tk, const
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 
+static int launch_attn2_sparse(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                               int B, cudaStream_t st) {
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 15;
+  if (!attr_set[dev]) {
+    cudaFuncSetAttribute(attn2_fwd_kernel<0, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM_BYTES);
+    attr_set[dev] = true;
+  }
+  dim3 grid((p.Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), p.H, B);
+  attn2_fwd_kernel<0, false, true><<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
 int launch_attn2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
                  cudaStream_t st) {
+  if (p.blk_idx) return launch_attn2_sparse(tq, tk, tv, p, B, st);
   if (p.n_peers > 0) return launch_attn2_peer(tq, tk, tv, p, B, st);
   switch (p.poly) {
     case 0: return launch_attn2_impl<0>(tq, tk, tv, p, B, st);

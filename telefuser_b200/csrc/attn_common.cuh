@@ -19,6 +19,11 @@ struct AttnParams {
   // with plain peer stores. n_peers == 0: ordinary local output.
   __nv_bfloat16* peer_out[8];
   int n_peers, rows_per_rank, head_off;
+  // Block-sparse attention: for the CTA of (batch b, head h, query pair qp) the 128-key blocks to visit
+  // are blk_idx[((b*H + h)*n_qp + qp) * max_blocks + i], i < blk_cnt[(b*H + h)*n_qp + qp]; null = dense.
+  const int* blk_idx;
+  const int* blk_cnt;
+  int max_blocks;
 };
 
 constexpr int ATT_BM = 128, ATT_BN = 128, ATT_D = 128;

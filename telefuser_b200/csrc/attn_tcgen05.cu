@@ -404,9 +404,10 @@ __global__ void __launch_bounds__(128, 1)
 
 using namespace tfb;
 
-extern "C" int tfb_attn_fwd(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v,
-                            long ldv, long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq,
-                            int Skv, float scale, int variant, void* stream) {
+static int attn_fwd_impl(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v,
+                         long ldv, long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq, int Skv,
+                         float scale, int variant, const int* blk_idx, const int* blk_cnt, int max_blocks,
+                         void* stream) {
   if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0) return TFB_ERR_BAD_SHAPE;
   if ((ldq | ldk | ldv | ldo | bsq | bsk | bsv | bso) % 8) return TFB_ERR_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
@@ -431,10 +432,32 @@ extern "C" int tfb_attn_fwd(const void* q, long ldq, long bsq, const void* k, lo
   p.n_peers = 0;
   p.rows_per_rank = 1;
   p.head_off = 0;
+  p.blk_idx = blk_idx;
+  p.blk_cnt = blk_cnt;
+  p.max_blocks = max_blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (blk_idx) return launch_attn2(tq, tk, tv, p, B, st);
   if (variant == 1) return launch_attn<false>(tq, tk, tv, p, B, st);
   if (variant == 3) return launch_attn<true>(tq, tk, tv, p, B, st);
   return launch_attn2(tq, tk, tv, p, B, st);
+}
+
+extern "C" int tfb_attn_fwd(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v,
+                            long ldv, long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq,
+                            int Skv, float scale, int variant, void* stream) {
+  return attn_fwd_impl(q, ldq, bsq, k, ldk, bsk, v, ldv, bsv, out, ldo, bso, lse, B, H, Sq, Skv, scale, variant, nullptr,
+                       nullptr, 0, stream);
+}
+
+// Block-sparse attention: blk_idx int32 [B, H, ceil(Sq/256), max_blocks] lists the 128-key blocks every
+// 256-row query group attends to, blk_cnt int32 [B, H, ceil(Sq/256)] how many of them are valid.
+extern "C" int tfb_attn_fwd_sparse(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v,
+                                   long ldv, long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq,
+                                   int Skv, float scale, const int* blk_idx, const int* blk_cnt, int max_blocks,
+                                   void* stream) {
+  if (!blk_idx || !blk_cnt || max_blocks < 1) return TFB_ERR_BAD_SHAPE;
+  return attn_fwd_impl(q, ldq, bsq, k, ldk, bsk, v, ldv, bsv, out, ldo, bso, lse, B, H, Sq, Skv, scale, 0, blk_idx,
+                       blk_cnt, max_blocks, stream);
 }
 
 // Attention whose epilogue performs the sequence-parallel "gather heads" exchange: this rank holds
@@ -473,6 +496,9 @@ extern "C" int tfb_attn_fwd_peer(const void* q, long ldq, long bsq, const void* 
   p.n_peers = n_peers;
   p.rows_per_rank = rows_per_rank;
   p.head_off = head_off;
+  p.blk_idx = nullptr;
+  p.blk_cnt = nullptr;
+  p.max_blocks = 0;
   return launch_attn2(tq, tk, tv, p, B, static_cast<cudaStream_t>(stream));
 }
 

@@ -35,6 +35,13 @@ int tfb_attn_fwd(const void* q, long ldq, long bsq, const void* k, long ldk, lon
                  long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq, int Skv, float scale,
                  int variant, void* stream);
 
+// Block-sparse variant: blk_idx int32 [B, H, ceil(Sq/256), max_blocks] lists the 128-key blocks each
+// group of 256 query rows attends to (ascending), blk_cnt int32 [B, H, ceil(Sq/256)] how many are valid;
+// a group with no block gets zero output.
+int tfb_attn_fwd_sparse(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v, long ldv,
+                        long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq, int Skv, float scale,
+                        const int* blk_idx, const int* blk_cnt, int max_blocks, void* stream);
+
 // LayerNorm over the last dim (C), optional affine (bf16 w/b), then optional
 // modulation y = y * (1 + scale) + shift with fp32 scale/shift taken from row
 // (r / rows_per_mod) * ldmod of `shift` / `scale`.

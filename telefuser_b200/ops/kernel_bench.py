@@ -75,6 +75,17 @@ def bench_attn(t: Timer, seq: int, heads: int, compare: bool, variant: int = 0) 
     flops = 4.0 * seq * seq * heads * 128
     report("attn_fwd_tcgen05", t(lambda: TF.attention(q, k, v, variant=variant)), flops, seq=seq, heads=heads,
            variant=variant)  # fmt: skip
+    if variant == 0 and seq >= 8192:
+        from telefuser_b200.ops import sparse_attention as SA
+
+        frames = 16
+        mm = SA.RadialMaskMap(seq // frames * frames, frames)
+        mask = mm.query_block_mask(seq, 0.5, "cuda")
+        lists = SA.lists_from_mask(SA._broadcast_mask(mask, 1, heads))
+        dens = mask.float().mean().item()
+        report("attn_fwd_tcgen05 block-sparse (radial mask; FLOPs counted for visited blocks only)",
+               t(lambda: SA.block_sparse_attention(q, k, v, mask, lists)), flops * dens, seq=seq, heads=heads,
+               frames=frames, block_density=round(dens, 3))  # fmt: skip
     if compare:
         qt, kt, vt = (x.transpose(1, 2) for x in (q, k, v))
         fn = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt)  # noqa: E731

@@ -92,6 +92,9 @@ def _declare(lib) -> None:
         "tfb_plucker_fold": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
         "tfb_frames_to_u8": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "tfb_attn_fwd_sparse": [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p,
+                                c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
+                                c_void_p],
         "tfb_gemm_fp8": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                          c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "tfb_quant_fp8_rowwise": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
