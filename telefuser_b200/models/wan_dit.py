@@ -177,6 +177,7 @@ class WanSelfAttention(nn.Module):
         self.norm_q = RMSNormWeight(dim, eps)
         self.norm_k = RMSNormWeight(dim, eps)
         self._qkv = None
+        self.sparse_ctx = None  # (RadialMaskMap, decay factor, dense?) set by the model for every forward
 
     def fused_qkv(self):
         w = self.q.weight
@@ -197,6 +198,10 @@ class WanSelfAttention(nn.Module):
             from telefuser_b200.parallel.ring import long_context_attention
 
             o = long_context_attention(q, k, v)  # Ulysses, ring or both, by the mesh's SP degrees
+        elif self.sparse_ctx is not None and not self.sparse_ctx[2]:
+            from telefuser_b200.ops.sparse_attention import radial_attention
+
+            o = radial_attention(q, k, v, self.sparse_ctx[0], self.sparse_ctx[1])
         else:
             o = TF.attention(q, k, v)
         return o.reshape(B, S, C)
@@ -419,14 +424,37 @@ class WanModel(BaseModel):
 
     # ---- forward -------------------------------------------------------------
     @torch.no_grad()
+    def enable_radial_attention(self, dense_layers: int = 0, dense_timesteps: int = 40, decay_factor: float = 1.0):
+        """Radial block-sparse self-attention outside the dense warm-up layers / steps
+        (telefuser/models/wan_video_dit.py:975-1010)."""
+        from telefuser_b200.core.config import AttentionConfig
+
+        self.set_attention_config(AttentionConfig.radial_attention(dense_timesteps, dense_layers, decay_factor))
+
+    def _set_sparse_context(self, grid, numeral_timestep: int) -> None:
+        sc = getattr(self.attention_config, "sparse_config", None) if self.attention_config is not None else None
+        if sc is None or sc.sparse_impl != "radial" or self.usp_flag:
+            for blk in self.blocks:
+                blk.self_attn.sparse_ctx = None
+            return
+        from telefuser_b200.ops.sparse_attention import RadialMaskMap
+
+        f, h, w = grid
+        key = (f, h * w)
+        if getattr(self, "_radial_key", None) != key:
+            self._radial_map, self._radial_key = RadialMaskMap(f * h * w, f, "wan"), key
+        for i, blk in enumerate(self.blocks):
+            blk.self_attn.sparse_ctx = (self._radial_map, sc.decay_factor, sc.should_use_dense(numeral_timestep, i))
+
     def forward(self, x, timestep, context, clip_feature=None, cond_flag=True, add_condition=None,
-                freq_start_idx=0, freq_interval=1, **_unused):  # fmt: skip
+                freq_start_idx=0, freq_interval=1, numeral_timestep: int = 0, **_unused):  # fmt: skip
         """x: [B, C, F, H, W] latents; timestep: [B] or [B, S]; context: [B, L, text_dim]."""
         t, t_mod = self.time_embed(timestep.to(x.device), None if timestep.dim() == 1 else timestep.shape[1])
         context = self.embed_text(context)
         if self.has_image_input and clip_feature is not None:
             context = torch.cat([self.img_emb(clip_feature.to(self.dtype)), context], dim=1)
         x, grid = self.patchify(x)
+        self._set_sparse_context(grid, numeral_timestep)
         if add_condition is not None:
             x = x + add_condition
         seq_len = x.shape[1]

@@ -84,10 +84,12 @@ class WanDenoisingStage(BaseStage):
             self.dit.compile(self.model_runtime_config.compile_config)
 
     # ---- one guidance evaluation ---------------------------------------------------
-    def predict_noise_with_cfg(self, latents, timestep, prompt_emb_posi, prompt_emb_nega, clip_feature, cfg_scale):
-        """Returns (cond, uncond) predictions; `uncond` is None when guidance is off."""
+    def predict_noise_with_cfg(self, latents, timestep, prompt_emb_posi, prompt_emb_nega, clip_feature, cfg_scale,
+                               numeral_timestep: int = 0):  # fmt: skip
+        """Returns (cond, uncond) predictions; `uncond` is None when guidance is off.
+        `numeral_timestep` = denoising steps still to run after this one (selects dense / sparse attention)."""
         use_cfg = cfg_scale != 1.0 and prompt_emb_nega is not None
-        kw = dict(clip_feature=clip_feature)
+        kw = dict(clip_feature=clip_feature, numeral_timestep=numeral_timestep)
         if use_cfg and self.mesh.size("cfg") == 2:
             is_cond = self.mesh.coord("cfg") == 0
             ctx = prompt_emb_posi if is_cond else prompt_emb_nega
@@ -133,7 +135,7 @@ class WanDenoisingStage(BaseStage):
             x_in = latents if ref_latent is None else torch.cat([latents, ref_latent.to(latents)], dim=1)
             x_in = x_in.to(self.torch_dtype)
             cond, uncond = self.predict_noise_with_cfg(x_in, ts, prompt_emb_posi, prompt_emb_nega, clip_feature,
-                                                       cfg_scale)  # fmt: skip
+                                                       cfg_scale, len(timesteps) - i - 1)  # fmt: skip
             sigma, nxt = self.scheduler.sigma_pair(t)
             if pp:
                 src = self.mesh.ranks("pp")[-1]

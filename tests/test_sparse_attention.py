@@ -68,6 +68,22 @@ def test_topk_and_local_window_masks():
     assert pooled.shape == (1, 3, 1, 4) and torch.allclose(pooled, torch.ones_like(pooled))
 
 
+def test_wan_model_routes_to_radial_attention_outside_the_dense_steps():
+    from telefuser_b200.testing.distributed_checks import make_tiny_model
+
+    model = make_tiny_model()
+    x = torch.randn(1, 16, 4, 32, 32)  # 4 frames x 256 tokens
+    ctx, t = torch.randn(1, 8, 256), torch.tensor([500.0])
+    dense = model(x, t, ctx)
+    model.enable_radial_attention(dense_layers=1, dense_timesteps=2, decay_factor=0.5)
+    late = model(x, t, ctx, numeral_timestep=0)  # inside the dense steps
+    assert torch.equal(late, dense)
+    assert [b.self_attn.sparse_ctx[2] for b in model.blocks] == [True, True]
+    early = model(x, t, ctx, numeral_timestep=5)
+    assert [b.self_attn.sparse_ctx[2] for b in model.blocks] == [True, False]  # layer 0 stays dense
+    assert torch.isfinite(early).all() and early.shape == dense.shape
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("Sq,Skv,H", [(1024, 1024, 2), (777, 1300, 3)])
 def test_sparse_kernel_matches_masked_reference(Sq, Skv, H):
