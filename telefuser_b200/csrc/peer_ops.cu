@@ -101,6 +101,67 @@ __global__ void peer_push_rows_kernel(const uint4* __restrict__ src, long ld_vec
   }
 }
 
+// Second half of GEMM -> reduce-scatter / all-reduce: sums the P partial slabs that the GEMM epilogues of
+// all ranks stored into this rank's buffer (fp32 accumulation), applies bias / gate / residual once, and
+// writes the rows to n_dst destinations (1 = local reduce-scatter result, P = every peer's full output).
+struct SlabReduceArgs {
+  const uint4* slabs;  // [P, rows, ld_vec]
+  long ld_vec, slab_vecs;
+  const __nv_bfloat16* bias;
+  const uint4* resid;
+  long ldr_vec;
+  const float* gate;  // row r reads gate[((gate_row0 + r) / rows_per_gate) * ldg + col]
+  long ldg;
+  long gate_row0;
+  int rows_per_gate;
+  PeerPtrs dst;
+  int n_dst;
+  long ldd_vec, dst_row0;
+};
+
+__global__ void slab_reduce_kernel(SlabReduceArgs a, int P, long rows, int row_vecs) {
+  const long total = rows * row_vecs;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = i / row_vecs;
+    const int c = static_cast<int>(i - r * row_vecs);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < P; ++p) {
+      const uint4 v = a.slabs[p * a.slab_vecs + r * a.ld_vec + c];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += bf16_lo(w[e]);
+        acc[2 * e + 1] += bf16_hi(w[e]);
+      }
+    }
+    if (a.bias) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += __bfloat162float(a.bias[c * 8 + e]);
+    }
+    if (a.gate) {
+      const float* g = a.gate + ((a.gate_row0 + r) / a.rows_per_gate) * a.ldg + c * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= g[e];
+    }
+    if (a.resid) {
+      const uint4 v = a.resid[r * a.ldr_vec + c];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += bf16_lo(w[e]);
+        acc[2 * e + 1] += bf16_hi(w[e]);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    for (int d = 0; d < a.n_dst; ++d) static_cast<uint4*>(a.dst.p[d])[(a.dst_row0 + r) * a.ldd_vec + c] = o;
+  }
+}
+
 static inline int peer_grid(long items, int per_block = 256, int max_blocks = 148 * 8) {
   long b = (items + per_block - 1) / per_block;
   return static_cast<int>(b < 1 ? 1 : (b > max_blocks ? max_blocks : b));
@@ -148,5 +209,33 @@ extern "C" int tfb_peer_push_rows(const void* src, long ld, void* const* dsts, i
   for (int r = 0; r < PEER_MAX; ++r) d.p[r] = r < P ? dsts[r] : nullptr;
   peer_push_rows_kernel<<<peer_grid(rows * (row_elems_bytes / 16)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), ld / 16, d, P, row0, rows, row_elems_bytes / 16, dst_ld_bytes / 16);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+// slabs: local bf16 [P, rows, ld]; out row r = resid[r] + gate[(gate_row0 + r) / rows_per_gate] * (sum_p slabs[p][r] + bias),
+// stored at row dst_row0 + r of each of the n_dst destinations (HOST array of device pointers, leading dim ldd).
+extern "C" int tfb_slab_reduce(const void* slabs, int P, long rows, int N, long ld, const void* bias, const void* resid,
+                               long ldr, const float* gate, long ldg, int rows_per_gate, long gate_row0,
+                               void* const* dsts, int n_dst, long ldd, long dst_row0, void* stream) {
+  if (P < 1 || P > PEER_MAX || n_dst < 1 || n_dst > PEER_MAX || rows < 0 || N % 8 || ld % 8 || ldd % 8) return TFB_ERR_BAD_SHAPE;
+  if (resid && ldr % 8) return TFB_ERR_BAD_SHAPE;
+  if (gate && (ldg % 4 || rows_per_gate < 1)) return TFB_ERR_BAD_SHAPE;
+  if (rows == 0) return TFB_OK;
+  SlabReduceArgs a;
+  a.slabs = static_cast<const uint4*>(slabs);
+  a.ld_vec = ld / 8;
+  a.slab_vecs = rows * (ld / 8);
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.resid = static_cast<const uint4*>(resid);
+  a.ldr_vec = ldr / 8;
+  a.gate = gate;
+  a.ldg = ldg;
+  a.gate_row0 = gate_row0;
+  a.rows_per_gate = rows_per_gate > 0 ? rows_per_gate : 1;
+  for (int r = 0; r < PEER_MAX; ++r) a.dst.p[r] = r < n_dst ? dsts[r] : nullptr;
+  a.n_dst = n_dst;
+  a.ldd_vec = ldd / 8;
+  a.dst_row0 = dst_row0;
+  slab_reduce_kernel<<<peer_grid(rows * (N / 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, P, rows, N / 8);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }

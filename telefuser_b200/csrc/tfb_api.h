@@ -151,6 +151,19 @@ int tfb_ulysses_scatter(void* const* srcs, const long* lds, const long* bss, voi
 // rows [row0, row0+rows) of every rank's buffer dsts[r] <- src (byte strides; row bytes % 16 == 0).
 int tfb_peer_push_rows(const void* src, long ld_bytes, void* const* dsts, int P, long row0, long rows,
                        int row_bytes, long dst_ld_bytes, void* stream);
+// GEMM -> reduce-scatter: epilogue tiles of row segment s go to rank s's slab buffer peer_out[s]
+// ([n_seg, seg_rows, ldo] bf16) at slab `rank`; every rank then sums its slabs with tfb_slab_reduce.
+int tfb_gemm_bf16_rs(const void* A, int lda, const void* B, int ldb, void* const* peer_out, int ldo, int n_seg,
+                     int rank, int seg_rows, int N, int K, const void* bias, void* stream);
+// all-gather -> GEMM: n_copiers CTAs pull the row shards peer_a[s] ([seg_rows, K] contiguous) into the local
+// a_gather while the other CTAs multiply the shards that have landed. sync: 16 ints of local scratch.
+int tfb_gemm_bf16_ag(void* const* peer_a, void* a_gather, int* sync, int n_copiers, const void* B, int ldb, void* out,
+                     int ldo, int n_seg, int rank, int seg_rows, int N, int K, const void* bias, int epi, void* stream);
+// out row r = resid[r] + gate[(gate_row0 + r) / rows_per_gate] * (sum_p slabs[p][r] + bias) at row dst_row0 + r of
+// each of the n_dst destinations (1: local result of a reduce-scatter; P peers: all-reduce).
+int tfb_slab_reduce(const void* slabs, int P, long rows, int N, long ld, const void* bias, const void* resid, long ldr,
+                    const float* gate, long ldg, int rows_per_gate, long gate_row0, void* const* dsts, int n_dst,
+                    long ldd, long dst_row0, void* stream);
 // Attention over this rank's head slice whose epilogue stores each output row into the buffer of the
 // rank that owns the token (see attn_tcgen05.cu).
 int tfb_attn_fwd_peer(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v, long ldv,

@@ -278,8 +278,19 @@ class WanBlock(nn.Module):
         h = self.norm2(x, shift_mlp, scale_mlp)
         h = TF.linear(h, self.ffn[0].weight, self.ffn[0].bias, act="gelu_tanh")
         if getattr(self, "tp_size", 1) > 1:  # FFN split over TP ranks: partial sums meet before the gate
+            from telefuser_b200.parallel import mesh as pmesh
             from telefuser_b200.parallel.tp import all_reduce_sum
 
+            B, S, C = x.shape
+            if pmesh.get_mesh().fused and x.is_cuda and B == 1 and S % self.tp_size == 0:
+                # row-parallel GEMM whose epilogue scatters the partial tiles to the row owners over NVLink
+                from telefuser_b200.parallel.symm import get_workspace
+                from telefuser_b200.parallel.tp_fused import gemm_all_reduce
+
+                ws = get_workspace(self.tp_group, 2 * S * C * 2 + (1 << 20))
+                y = gemm_all_reduce(h.reshape(S, -1), self.ffn[2].weight, self.ffn[2].bias, residual=x.reshape(S, C),
+                                    gate=gate_mlp.reshape(-1, C), group=self.tp_group, ws=ws)  # fmt: skip
+                return y.view(B, S, C)
             y = all_reduce_sum(TF.linear(h, self.ffn[2].weight, self.ffn[2].bias), self.tp_group)
             return TF.gated_residual(x, y, gate_mlp)
         x = TF.linear(h, self.ffn[2].weight, self.ffn[2].bias, residual=x, gate=gate_mlp)

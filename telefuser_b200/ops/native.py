@@ -112,6 +112,12 @@ def _declare(lib) -> None:
         "tfb_ulysses_scatter": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p],
         "tfb_peer_push_rows": [c_void_p, c_long, c_void_p, c_int, c_long, c_long, c_int, c_long, c_void_p],
+        "tfb_gemm_bf16_rs": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p, c_void_p],
+        "tfb_gemm_bf16_ag": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_void_p, c_int, c_void_p],
+        "tfb_slab_reduce": [c_void_p, c_int, c_long, c_int, c_long, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int,
+                            c_long, c_void_p, c_int, c_long, c_long, c_void_p],
         "tfb_attn_fwd_peer": [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p,
                               c_int, c_int, c_int, c_long, c_long, c_int, c_int, c_int, c_int, c_float, c_void_p],
     }  # fmt: skip

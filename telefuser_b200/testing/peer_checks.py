@@ -19,6 +19,40 @@ from telefuser_b200.ops import native
 from telefuser_b200.parallel import symm, ulysses
 
 
+def tp_fused_errors(group, dev, ws, M: int = 1400, K: int = 1024, N: int = 768, rounds: int = 2) -> dict:
+    """Relative errors of the fused tensor-parallel linears (peer workspace `ws`, or None for the collective
+    composition) against the unsharded fp32 product; every rank builds the same full operands."""
+    from telefuser_b200.parallel import tp_fused
+
+    rank, P = dist.get_rank(group), dist.get_world_size(group)
+    out = {"tp_rs": 0.0, "tp_ar": 0.0, "tp_ag": 0.0}
+    dt = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()  # noqa: E731
+    for it in range(rounds):
+        g = torch.Generator().manual_seed(300 + it)
+        x = (torch.randn(M, K, generator=g) / 4).to(dt)
+        w = (torch.randn(N, K, generator=g) / K**0.5).to(dt)
+        bias = torch.randn(N, generator=g).to(dt)
+        res = torch.randn(M, N, generator=g).to(dt)
+        gate = torch.randn(1, N, generator=g)
+        full = res.float() + gate * (x.float() @ w.float().t() + bias.float())
+        kc, seg = K // P, M // P
+        xs, wsh = x[:, rank * kc : (rank + 1) * kc].to(dev), w[:, rank * kc : (rank + 1) * kc].to(dev)
+        b = bias.to(dev) if rank == 0 else None
+        mine = slice(rank * seg, (rank + 1) * seg)
+        got = tp_fused.gemm_reduce_scatter(xs, wsh, b, res[mine].to(dev), gate.to(dev), group, ws)
+        out["tp_rs"] = max(out["tp_rs"], rel(got.cpu(), full[mine]))
+        got = tp_fused.gemm_all_reduce(xs, wsh, b, res.to(dev), gate.to(dev), group, ws)
+        out["tp_ar"] = max(out["tp_ar"], rel(got.cpu(), full))
+        nc = N // P  # column-parallel weight shard on row-sharded activations
+        want = torch.nn.functional.gelu(x.float() @ w[rank * nc : (rank + 1) * nc].float().t() + bias[rank * nc : (rank + 1) * nc].float(),
+                                        approximate="tanh")  # fmt: skip
+        got = tp_fused.all_gather_gemm(x[mine].to(dev), w[rank * nc : (rank + 1) * nc].to(dev), bias[rank * nc : (rank + 1) * nc].to(dev),
+                                       "gelu_tanh", group, ws, n_copiers=4)  # fmt: skip
+        out["tp_ag"] = max(out["tp_ag"], rel(got.cpu(), want))
+    return out
+
+
 def rank_main(rank: int, world_size: int, port: int, out_path: str, seq: int = 512, heads: int = 8, layers: int = 3):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world_size), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                       NCCL_NVLS_ENABLE="0")  # fmt: skip
@@ -30,7 +64,7 @@ def rank_main(rank: int, world_size: int, port: int, out_path: str, seq: int = 5
         group = dist.group.WORLD
         P, D, B = world_size, 128, 1
         S_loc = seq // P
-        ws = symm.PeerWorkspace(group, 4 * (B * S_loc * heads * D * 2 + 256) + (8 << 20))
+        ws = symm.PeerWorkspace(group, 4 * (B * S_loc * heads * D * 2 + 256) + (32 << 20))
         worst = 0.0
         for layer in range(layers):
             g = torch.Generator(device="cpu").manual_seed(100 + layer)
@@ -62,6 +96,7 @@ def rank_main(rank: int, world_size: int, port: int, out_path: str, seq: int = 5
                 got = symm.cfg_combine_step_fused(lat, preds[rank], ws, 5.0, -0.02)
                 worst = max(worst, (got - want).abs().max().item())
             errs["cfg"] = worst
+        errs.update(tp_fused_errors(group, dev, ws))
         torch.cuda.synchronize()
         errs["status"] = native.last_status()
         gathered = [None] * world_size

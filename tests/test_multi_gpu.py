@@ -38,6 +38,8 @@ def test_peer_memory_paths_match_collectives():
         assert errs["gather"] == 0.0, errs
         if "cfg" in errs:
             assert errs["cfg"] <= 1e-6, errs
+        for key in ("tp_rs", "tp_ar", "tp_ag"):  # fused GEMM + collective against the unsharded fp32 product
+            assert errs[key] <= 1e-2, errs
 
 
 def test_peer_wait_runs_out_with_a_status():

@@ -88,3 +88,26 @@ def test_tensor_parallel_text_encoder():
         mp.spawn(_tp_encoder_rank, nprocs=2, join=True, args=(2, find_free_port(), path))
         full, sharded = torch.load(path)
     assert (full - sharded).abs().max().item() <= 1e-5
+
+
+def _tp_fused_rank(rank, world, port, path):
+    from telefuser_b200.testing.peer_checks import tp_fused_errors
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        errs = tp_fused_errors(dist.group.WORLD, torch.device("cpu"), None, M=64, K=32, N=24, rounds=1)
+        if rank == 0:
+            torch.save(errs, path)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_linears_compose_collectives_without_a_peer_workspace():
+    from telefuser_b200.utils.system import find_free_port
+
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "errs.pt")
+        mp.spawn(_tp_fused_rank, nprocs=2, join=True, args=(2, find_free_port(), path))
+        errs = torch.load(path)
+    assert max(errs.values()) <= 1e-5, errs
