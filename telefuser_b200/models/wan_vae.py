@@ -104,13 +104,14 @@ class Upsample(nn.Upsample):
 
 
 class Resample(nn.Module):
-    def __init__(self, dim: int, mode: str):
+    def __init__(self, dim: int, mode: str, keep_width: bool = False):
         assert mode in ("none", "upsample2d", "upsample3d", "downsample2d", "downsample3d")
         super().__init__()
         self.dim, self.mode = dim, mode
         if mode in ("upsample2d", "upsample3d"):
+            # the 16-channel VAE halves the width in the upsampling conv, the 48-channel one keeps it
             self.resample = nn.Sequential(Upsample(scale_factor=(2.0, 2.0), mode="nearest-exact"),
-                                          nn.Conv2d(dim, dim // 2, 3, padding=1))  # fmt: skip
+                                          nn.Conv2d(dim, dim if keep_width else dim // 2, 3, padding=1))  # fmt: skip
             if mode == "upsample3d":
                 self.time_conv = CausalConv3d(dim, dim * 2, (3, 1, 1), padding=(1, 0, 0))
         elif mode in ("downsample2d", "downsample3d"):
@@ -434,14 +435,16 @@ class WanVideoVAE(BaseModel):
 
     def tiled_decode(self, latents, tile_size=(34, 34), tile_stride=(18, 16)):
         t_out = (latents.shape[2] - 1) * 4 + 1
-        out = self._tiled(latents, tile_size, tile_stride, lambda z: self.model.decode(z, self.scale), 8.0, 3, t_out)
+        f = float(self.upsampling_factor)
+        out = self._tiled(latents, tile_size, tile_stride, lambda z: self.model.decode(z, self.scale), f, 3, t_out)
         return out.clamp_(-1, 1).to(latents.dtype)
 
     def tiled_encode(self, videos, tile_size=(34, 34), tile_stride=(18, 16)):
-        ts = (tile_size[0] * 8, tile_size[1] * 8)
-        st = (tile_stride[0] * 8, tile_stride[1] * 8)
+        f = self.upsampling_factor
+        ts = (tile_size[0] * f, tile_size[1] * f)
+        st = (tile_stride[0] * f, tile_stride[1] * f)
         t_out = (videos.shape[2] - 1) // 4 + 1
-        out = self._tiled(videos, ts, st, lambda v: self.model.encode(v, self.scale), 1 / 8.0, self.z_dim, t_out)
+        out = self._tiled(videos, ts, st, lambda v: self.model.encode(v, self.scale), 1.0 / f, self.z_dim, t_out)
         return out.to(videos.dtype)
 
     # ---- 2-D domain decomposition -----------------------------------------------------
@@ -459,19 +462,20 @@ class WanVideoVAE(BaseModel):
         h1, w1 = min(H, h0 + hs), min(W, w0 + ws)
         a0, b0 = max(0, h0 - halo), max(0, w0 - halo)
         a1, b1 = min(H, h1 + halo), min(W, w1 + halo)
+        f = self.upsampling_factor
         tile = self.model.decode(latents[:, :, :, a0:a1, b0:b1], self.scale)
-        tile = tile[:, :, :, (h0 - a0) * 8 : (h0 - a0) * 8 + (h1 - h0) * 8, (w0 - b0) * 8 : (w0 - b0) * 8 + (w1 - w0) * 8]
+        tile = tile[:, :, :, (h0 - a0) * f : (h0 - a0) * f + (h1 - h0) * f, (w0 - b0) * f : (w0 - b0) * f + (w1 - w0) * f]
         if world == 1:
             return tile.clamp_(-1, 1)
-        padded = torch.zeros(B, 3, tile.shape[2], hs * 8, ws * 8, device=tile.device, dtype=tile.dtype)
+        padded = torch.zeros(B, 3, tile.shape[2], hs * f, ws * f, device=tile.device, dtype=tile.dtype)
         padded[:, :, :, : tile.shape[3], : tile.shape[4]] = tile
         parts = [torch.empty_like(padded) for _ in range(world)]
         dist.all_gather(parts, padded.contiguous())
-        out = torch.zeros(B, 3, tile.shape[2], rows * hs * 8, cols * ws * 8, device=tile.device, dtype=tile.dtype)
+        out = torch.zeros(B, 3, tile.shape[2], rows * hs * f, cols * ws * f, device=tile.device, dtype=tile.dtype)
         for k, part in enumerate(parts):
             rr, cc = divmod(k, cols)
-            out[:, :, :, rr * hs * 8 : (rr + 1) * hs * 8, cc * ws * 8 : (cc + 1) * ws * 8] = part
-        return out[:, :, :, : H * 8, : W * 8].clamp_(-1, 1)
+            out[:, :, :, rr * hs * f : (rr + 1) * hs * f, cc * ws * f : (cc + 1) * ws * f] = part
+        return out[:, :, :, : H * f, : W * f].clamp_(-1, 1)
 
     # ---- streaming --------------------------------------------------------------------
     def new_stream(self, kind: str) -> VAEStreamState:
