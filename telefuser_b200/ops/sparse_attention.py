@@ -259,3 +259,47 @@ def local_window_block_mask(grid: tuple[int, int, int], window: tuple[int, int, 
         klo, khi = span(coord, size, BK)
         mask &= (klo[None, :] <= qhi[:, None] + win) & (khi[None, :] >= qlo[:, None] - win)
     return mask
+
+
+# ---------------------------------------------------------------------------
+# 3-D chunked top-k block-sparse attention (LongCat-Video refinement)
+# ---------------------------------------------------------------------------
+def to_3d_blocks(x: torch.Tensor, grid, chunk) -> torch.Tensor:
+    """[B, T*H*W, heads, D] in grid order -> the same tokens ordered chunk by chunk (chunks of t x h x w tokens)."""
+    B, _, Hh, D = x.shape
+    (T, H, W), (t, h, w) = grid, chunk
+    x = x.view(B, T // t, t, H // h, h, W // w, w, Hh, D).permute(0, 1, 3, 5, 2, 4, 6, 7, 8)
+    return x.reshape(B, T * H * W, Hh, D)
+
+
+def from_3d_blocks(x: torch.Tensor, grid, chunk) -> torch.Tensor:
+    B, _, Hh, D = x.shape
+    (T, H, W), (t, h, w) = grid, chunk
+    x = x.view(B, T // t, H // h, W // w, t, h, w, Hh, D).permute(0, 1, 4, 2, 5, 3, 6, 7, 8)
+    return x.reshape(B, T * H * W, Hh, D)
+
+
+def bsa_3d_attention(q, k, v, latent_shape_q, latent_shape_k=None, sparsity: float = 0.9375, chunk_3d_shape_q=(4, 4, 4),
+                     chunk_3d_shape_k=(4, 4, 4)):  # fmt: skip
+    """q, k, v: [B, S, H, D] in (T, H, W) order. Tokens are regrouped into 3-D chunks; every query chunk keeps the
+    `(1 - sparsity)` fraction of key chunks with the largest mean-pooled q.k score. On GPUs with chunks of 64 or
+    128 tokens the kernel's 256 x 128 blocks receive the union of the masks of the chunks they contain."""
+    latent_shape_k = latent_shape_k or latent_shape_q
+    cq, ck = math.prod(chunk_3d_shape_q), math.prod(chunk_3d_shape_k)
+    qb, kb, vb = to_3d_blocks(q, latent_shape_q, chunk_3d_shape_q), to_3d_blocks(k, latent_shape_k, chunk_3d_shape_k), \
+        to_3d_blocks(v, latent_shape_k, chunk_3d_shape_k)  # fmt: skip
+    qm = mean_pool_blocks(qb, cq).float().permute(0, 2, 1, 3)  # [B, H, nQ, D]
+    km = mean_pool_blocks(kb, ck).float().permute(0, 2, 1, 3)
+    score = qm @ km.transpose(-1, -2)
+    keep = max(1, int((1 - sparsity) * score.shape[-1]))
+    mask = torch.zeros_like(score, dtype=torch.bool).scatter_(3, torch.topk(score, keep, dim=-1).indices, True)
+    if _native(q) and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and BQ % cq == 0 and BK % ck == 0 \
+            and q.shape[1] % BQ == 0 and k.shape[1] % BK == 0:  # fmt: skip
+        m = mask.view(*mask.shape[:2], mask.shape[2] // (BQ // cq), BQ // cq, mask.shape[3] // (BK // ck), BK // ck)
+        out = block_sparse_attention(qb, kb, vb, m.any(dim=(3, 5)))
+    else:
+        tok = mask.repeat_interleave(cq, dim=2).repeat_interleave(ck, dim=3)
+        s = (qb.float().permute(0, 2, 1, 3) @ kb.float().permute(0, 2, 3, 1)) / math.sqrt(q.shape[-1])
+        p = torch.softmax(s.masked_fill(~tok, float("-inf")), dim=-1)
+        out = (p @ vb.float().permute(0, 2, 1, 3)).permute(0, 2, 1, 3).to(q.dtype)
+    return from_3d_blocks(out, latent_shape_q, chunk_3d_shape_q)
