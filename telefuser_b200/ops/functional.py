@@ -59,15 +59,17 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
             out.copy_(r)
             return out
         return r
-    if not _native(x) or x.dtype != torch.bfloat16:
+    K = x.shape[-1]
+    N = weight.shape[0]
+    # The tensor-core kernel moves 16-byte rows: widths that are not multiples of 8 elements (toy configurations)
+    # take the fp32 evaluation.
+    if not _native(x) or x.dtype != torch.bfloat16 or K % 8 or N % 8:
         r = linear_reference(x, weight, bias, act, residual, gate)
         if out is not None:
             out.copy_(r)
             return out
         return r
     lib = native.load()
-    K = x.shape[-1]
-    N = weight.shape[0]
     x2 = x.reshape(-1, K)
     if x2.stride(-1) != 1:
         x2 = x2.contiguous()
