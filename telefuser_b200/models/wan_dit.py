@@ -287,7 +287,7 @@ class WanBlock(nn.Module):
                 from telefuser_b200.parallel.symm import get_workspace
                 from telefuser_b200.parallel.tp_fused import gemm_all_reduce
 
-                ws = get_workspace(self.tp_group, 2 * S * C * 2 + (1 << 20))
+                ws = get_workspace(self.tp_group, 2 * S * C * 2 + (1 << 20), tag="tp")
                 y = gemm_all_reduce(h.reshape(S, -1), self.ffn[2].weight, self.ffn[2].bias, residual=x.reshape(S, C),
                                     gate=gate_mlp.reshape(-1, C), group=self.tp_group, ws=ws)  # fmt: skip
                 return y.view(B, S, C)

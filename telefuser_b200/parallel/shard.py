@@ -54,6 +54,15 @@ def sequence_parallel_unshard(tensors, seq_dims, seq_lens, mesh: ParallelMesh | 
     out = []
     for t, d, n in zip(tensors, seq_dims, seq_lens):
         t = t.contiguous()
+        if mesh.fused and t.is_cuda and d == 1 and t.dim() == 3 and t.shape[0] == 1 and (t.shape[2] * t.element_size()) % 16 == 0:
+            # every rank stores its rows straight into all ranks' full buffer over NVLink (no gather list, no cat)
+            from .symm import all_gather_rows_fused, get_workspace
+
+            rows, width = t.shape[1], t.shape[2]
+            ws = get_workspace(group, P * rows * width * t.element_size() + 4096, tag="sp_unshard")
+            full = all_gather_rows_fused(t[0], ws, name=f"sp_unshard_{width}")
+            out.append(full[:n].clone().unsqueeze(0))
+            continue
         parts = [torch.empty_like(t) for _ in range(P)]
         dist.all_gather(parts, t, group=group)
         out.append(torch.cat(parts, dim=d).narrow(d, 0, n))

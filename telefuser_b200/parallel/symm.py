@@ -116,9 +116,10 @@ class PeerWorkspace:
 _WORKSPACES: dict = {}
 
 
-def get_workspace(group, nbytes: int) -> PeerWorkspace:
-    """One workspace per process group, grown by re-creation when a larger one is asked for."""
-    key = id(group)
+def get_workspace(group, nbytes: int, tag: str = "") -> PeerWorkspace:
+    """One workspace per (process group, tag), grown by re-creation when a larger one is asked for. Callers whose
+    regions must not compete for space (attention slabs, tensor-parallel slabs, the output gather) use own tags."""
+    key = (id(group), tag)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.flag_off < nbytes:
         if ws is not None:

@@ -121,3 +121,43 @@ def test_ti2v_keeps_the_reference_frame_and_marks_it_clean():
     assert torch.equal(both[0, :, :1], ref) and torch.equal(both[0, :, -1:], end)
     plain = stage.process(latents, 4, None, None, ctx, neg, 5.0, 5.0)
     assert torch.allclose(plain, tiny_wan_denoise(steps=4), atol=1e-5)
+
+
+def test_async_pipeline_emits_stage_events(tmp_path):
+    import asyncio
+
+    from telefuser_b200.core.module_manager import ModuleManager
+    from telefuser_b200.models.wan_vae import WanVideoVAE
+    from telefuser_b200.pipelines.wan.async_wan22_video import AsyncWan22VideoPipeline, AsyncWan22VideoPipelineConfig
+
+    torch.manual_seed(0)
+    mm = ModuleManager(torch_dtype=torch.float32, device="cpu")
+    mm.add_module(make_tiny_model(), "wan_video_dit")
+    mm.add_module(make_tiny_model(seed=3), "wan_video_dit")
+    mm.add_module(WanVideoVAE(z_dim=16, dim=8).eval(), "wan_video_vae")
+    rc = lambda: ModelRuntimeConfig(torch_dtype=torch.float32, device_type="cpu")  # noqa: E731
+
+    class Text:
+        def process(self, prompts):
+            return [torch.randn(1, 8, 256) for _ in prompts]
+
+    pipe = AsyncWan22VideoPipeline(device="cpu", torch_dtype=torch.float32)
+    pipe.init(mm, AsyncWan22VideoPipelineConfig(vae_config=rc(), dit_high_config=rc(), dit_low_config=rc(), text_encoding_config=rc(),
+                                                name="unit", output_root=str(tmp_path)), text_stage=Text())  # fmt: skip
+
+    async def run(**kw):
+        events = []
+        async for e in pipe.agenerate(request_id="r1", prompt="x", height=64, width=64, num_frames=5, num_inference_steps=2,
+                                      file_ext=".frames", **kw):  # fmt: skip
+            events.append(e)
+        await pipe.astop()
+        return events
+
+    events = asyncio.run(run())
+    assert [e["type"] for e in events] == ["stage_end"] * 5 + ["final"]
+    assert [e["stage"]["name"] for e in events[:5]] == ["text_encoding", "vae_encode", "denoise", "vae_decode", "artifact_save"]
+    assert all(e["v"] == "teleai.v2.event.v1" and e["seq"] == i + 1 for i, e in enumerate(events))
+    art = events[-1]["payload"]["artifacts"][0]
+    assert art["num_frames"] == 5 and art["height"] == 64 and events[-1]["payload"]["params_snapshot"]["num_frames"] == 5
+    bad = asyncio.run(run(cfg_scale_high="not a number"))
+    assert bad[-1]["type"] == "error" and bad[-1]["error"]["stage"]["name"] in ("text_encoding", "denoise")
