@@ -148,7 +148,7 @@ def apply_rotary_emb(x, freqs_cis, rope_type: LTXRopeType = LTXRopeType.INTERLEA
         a, b = x.unflatten(-1, (-1, 2)).unbind(-1)
         rot = torch.stack((-b, a), dim=-1).flatten(-2)
         return x * cos + rot * sin
-    B, H, T, _ = cos.shape  # split halves per head: x [B, T, H*D]
+    (_, H, T, _), B = cos.shape, x.shape[0]  # split halves per head: x [B, T, H*D]; tables may have batch 1
     xh = x.reshape(B, T, H, -1).transpose(1, 2)
     first, second = xh.unflatten(-1, (2, -1)).unbind(-2)
     out = torch.stack([first * cos - second * sin, second * cos + first * sin], dim=-2).flatten(-2)
