@@ -1,4 +1,4 @@
-from .pipeline import HunyuanVideo15Pipeline, HunyuanVideo15PipelineConfig, HunyuanVideoDenoisingStage, HunyuanVideoSRDenoisingStage
+from .pipeline import HunyuanTextEncodingStage, HunyuanVideo15Pipeline, HunyuanVideo15PipelineConfig, HunyuanVideoDenoisingStage, HunyuanVideoSRDenoisingStage
 
-__all__ = ["HunyuanVideo15Pipeline", "HunyuanVideo15PipelineConfig", "HunyuanVideoDenoisingStage",
+__all__ = ["HunyuanTextEncodingStage", "HunyuanVideo15Pipeline", "HunyuanVideo15PipelineConfig", "HunyuanVideoDenoisingStage",
            "HunyuanVideoSRDenoisingStage"]  # fmt: skip

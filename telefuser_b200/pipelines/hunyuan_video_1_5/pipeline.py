@@ -157,16 +157,17 @@ class HunyuanVideo15Pipeline(BasePipeline):
     def __init__(self, device="cuda", torch_dtype=torch.bfloat16) -> None:
         super().__init__(device=device, torch_dtype=torch_dtype)
         self.height_division_factor = self.width_division_factor = 16
-        self.text_stage = self.vision_stage = self.vae = self.sr_stage = None
+        self.text_stage = self.vision_stage = self.vae = self.sr_stage = self.upsampler = None
 
     def _get_stages(self) -> list:
         return [s for s in (self.denoise_stage, self.sr_stage) if s is not None]
 
-    def init(self, module_manager, config: HunyuanVideo15PipelineConfig, text_stage=None, vision_stage=None, vae=None):
+    def init(self, module_manager, config: HunyuanVideo15PipelineConfig, text_stage=None, vision_stage=None, vae=None, upsampler=None):
         from telefuser_b200.worker.parallel_worker import ParallelWorker
 
         self.config = config
         self.text_stage, self.vision_stage, self.vae = text_stage, vision_stage, vae
+        self.upsampler = upsampler if upsampler is not None else module_manager.fetch_module("upsampler")
         self.denoise_stage = HunyuanVideoDenoisingStage("denoise", module_manager, config.dit_config,
                                                         FlowMatchDiscreteScheduler(shift=config.sigma_shift),
                                                         use_meanflow=config.use_meanflow)  # fmt: skip
@@ -192,7 +193,8 @@ class HunyuanVideo15Pipeline(BasePipeline):
         task = "i2v" if (input_image is not None or image_latents is not None) else "t2v"
         if input_image is not None and image_latents is None:
             img = input_image if isinstance(input_image, torch.Tensor) else self.preprocess_image(input_image, height, width)
-            image_latents = self.vae.encode(img.unsqueeze(2).to(self.device, self.torch_dtype))
+            frame = img.unsqueeze(2).to(self.device, self.torch_dtype)
+            image_latents = self.vae.encode_latents(frame) if hasattr(self.vae, "encode_latents") else self.vae.encode(frame)
             if vision_states is None and self.vision_stage is not None:
                 vision_states = self.vision_stage(img)
         shape = (1, latent_channels, (num_frames - 1) // 4 + 1, height // spatial_factor, width // spatial_factor)
@@ -209,7 +211,32 @@ class HunyuanVideo15Pipeline(BasePipeline):
             hi = self.generate_noise((1, latent_channels, shape[2], sh // spatial_factor, sw // spatial_factor),
                                      seed=None if seed is None else seed + 1, device="cpu").to(self.device)  # fmt: skip
             cond = None if image_latents is None else F.interpolate(image_latents.float(), size=(1, *hi.shape[3:]), mode="trilinear")
+            if self.upsampler is not None:  # learned refinement of the bilinearly resized low-resolution latents
+                from telefuser_b200.models.hunyuan_video_vae import resize_latents
+
+                up_dtype = next(self.upsampler.parameters()).dtype
+                out = self.upsampler(resize_latents(out.to(up_dtype), tuple(hi.shape[3:]))).to(out.dtype)
             out = self.sr_stage.process(hi, out, sr_num_inference_steps, cfg_scale=1.0, image_cond=cond, seed=seed, **kw)
         if return_latents or self.vae is None:
             return out
+        if hasattr(self.vae, "decode_latents"):
+            return self.tensor2video(self.vae.decode_latents(out.to(self.torch_dtype))[0])
         return self.tensor2video(self.vae.decode(out.to(self.torch_dtype))[0])
+
+
+class HunyuanTextEncodingStage:
+    """Prompt list -> list of dicts (text_states, mask, byt5_text_states, byt5_text_mask) from the LLM and glyph encoders."""
+
+    def __init__(self, text_encoder, byt5_encoder=None, data_type: str = "video") -> None:
+        self.text_encoder, self.byt5_encoder, self.data_type = text_encoder, byt5_encoder, data_type
+
+    @torch.no_grad()
+    def __call__(self, prompts: list) -> list:
+        out = []
+        for p in prompts:
+            enc = self.text_encoder(p, data_type=self.data_type)
+            item = {"text_states": enc.hidden_state, "mask": enc.attention_mask}
+            if self.byt5_encoder is not None:
+                item.update(self.byt5_encoder(p))
+            out.append(item)
+        return out

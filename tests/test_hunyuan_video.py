@@ -91,3 +91,27 @@ def test_gpu_bf16_forward_tracks_cpu_fp32():
     got = gpu_m(x.cuda().bfloat16(), t.cuda(), txt.cuda().bfloat16(), vision_states=vis.cuda().bfloat16(), mask_type="i2v").float().cpu()
     err = ((got - ref).norm() / ref.norm()).item()
     assert err < 3e-2, err
+
+
+def test_pipeline_with_vae_upsampler_and_text_stage():
+    from types import SimpleNamespace
+
+    from telefuser_b200.models.hunyuan_video_vae import HunyuanVideoVAE, SRTo720pUpsampler
+    from telefuser_b200.pipelines.hunyuan_video_1_5 import HunyuanTextEncodingStage
+
+    torch.manual_seed(0)
+    vae = HunyuanVideoVAE(latent_channels=4, block_out_channels=(16, 32, 64, 64), layers_per_block=1, ffactor_spatial=8, ffactor_temporal=4,
+                          sample_size=64).float().eval()  # fmt: skip
+    up = SRTo720pUpsampler(in_channels=4, out_channels=4, hidden_channels=8, num_blocks=1, global_residual=True).float().eval()
+    llm = lambda p, data_type="video": SimpleNamespace(hidden_state=torch.randn(1, 6, 24), attention_mask=torch.ones(1, 6, dtype=torch.long))  # noqa: E731
+    glyph = lambda p: {"byt5_text_states": torch.zeros(1, 5, 16), "byt5_text_mask": torch.zeros(1, 5, dtype=torch.long)}  # noqa: E731
+    mm = ModuleManager(torch_dtype=torch.float32, device="cpu")
+    mm.add_module(small(), "hunyuan_video_dit")
+    mm.add_module(small(extra_cond=5), "hunyuan_video_sr_dit")
+    rc = lambda: ModelRuntimeConfig(device_type="cpu", torch_dtype=torch.float32)  # noqa: E731
+    pipe = HunyuanVideo15Pipeline(device="cpu", torch_dtype=torch.float32)
+    pipe.init(mm, HunyuanVideo15PipelineConfig(dit_config=rc(), sr_dit_config=rc(), vae_config=rc(), text_encoding_config=rc()),
+              text_stage=HunyuanTextEncodingStage(llm, glyph), vae=vae, upsampler=up)  # fmt: skip
+    frames = pipe("a fox", input_image=torch.rand(1, 3, 32, 32) * 2 - 1, seed=0, height=32, width=32, num_frames=5, num_inference_steps=2,
+                  cfg_scale=2.0, latent_channels=4, spatial_factor=8, enable_sr=True, sr_height=64, sr_width=64, sr_num_inference_steps=2)  # fmt: skip
+    assert len(frames) == 5 and frames[0].size == (64, 64)
