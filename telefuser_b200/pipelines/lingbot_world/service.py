@@ -1,0 +1,322 @@
+"""Interactive LingBot-World session service: keyboard / pose control in, video chunks out.
+
+Implements the bidirectional streaming-service interface (`start / stop / create_session / push_chunk /
+pull_chunks / close_session`) on top of the pipeline's streaming runtime. Each session owns a worker thread
+that, chunk by chunk, snapshots the held direction keys (or takes an explicit pose chunk pushed by the client),
+integrates the camera pose over the chunk's latent frames, builds the control tensor, feeds the runtime while it
+has input capacity and forwards decoded frames to a bounded output queue (oldest frame chunks are dropped when a
+slow client falls behind; status and terminal messages are never dropped). An optional HUD draws the held keys
+into the frames.
+Role parity: telefuser/pipelines/lingbot_world_fast/service.py:71-1207.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import base64
+import io
+import queue
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any, AsyncGenerator
+
+import numpy as np
+import torch
+
+from telefuser_b200.utils.logging import logger
+
+from .control import KEY_MOVES, KEY_TURNS, integrate_keys
+
+DIRECTION_KEYS = {"forward": "w", "backward": "s", "left": "a", "right": "d", "up": "e", "down": "q", "turn_left": "j", "turn_right": "l",
+                  "look_up": "i", "look_down": "k"}  # fmt: skip
+_VALID_KEYS = set(KEY_MOVES) | set(KEY_TURNS)
+
+
+@dataclass
+class LingBotWorldFastSessionConfig:
+    prompt: str = ""
+    height: int = 480
+    width: int = 832
+    seed: int = 0
+    fps: int = 16
+    max_duration_seconds: float = 10.0
+    move_step: float = 0.05
+    turn_step_deg: float = 1.5
+    hud: bool = False
+    output_queue_size: int = 8
+
+
+@dataclass
+class LingBotWorldFastSessionState:
+    session_id: str
+    config: LingBotWorldFastSessionConfig
+    generation: Any
+    stream: Any
+    outputs: "queue.Queue[dict]"
+    lock: threading.Lock = field(default_factory=threading.Lock)
+    held_keys: set = field(default_factory=set)
+    explicit_chunks: list = field(default_factory=list)
+    pose: torch.Tensor = field(default_factory=lambda: torch.eye(4))
+    stop_event: threading.Event = field(default_factory=threading.Event)
+    worker: threading.Thread | None = None
+    dropped_chunks: int = 0
+    submitted: int = 0
+    emitted: int = 0
+    created_at: float = field(default_factory=time.time)
+    finished: bool = False
+
+
+def frame_num_for_duration(max_duration_seconds: float, fps: int, chunk_size: int) -> int:
+    """Largest 4n+1 frame count within the duration whose latent frames are a whole number of chunks (at least one)."""
+    latent = max(1, int(max_duration_seconds * fps) // 4 + 1)
+    latent = max(chunk_size, latent // chunk_size * chunk_size)
+    return (latent - 1) * 4 + 1
+
+
+def load_image(config: dict):
+    """`image` (PIL / array / tensor), `image_path`, or `image_data_url` (data:image/...;base64,...) -> PIL image or tensor."""
+    from PIL import Image
+
+    if config.get("image") is not None:
+        return config["image"]
+    if config.get("image_path"):
+        return Image.open(config["image_path"]).convert("RGB")
+    url = config.get("image_data_url")
+    if url:
+        if not url.startswith("data:image/") or ";base64," not in url:
+            raise ValueError("image_data_url must be a base64 data URL of an image")
+        return Image.open(io.BytesIO(base64.b64decode(url.split(";base64,", 1)[1]))).convert("RGB")
+    raise ValueError("a session needs an image, image_path or image_data_url")
+
+
+def keys_from_chunk(chunk: dict) -> set | None:
+    """Held-key snapshot carried by a control message, or None when the message is not a snapshot."""
+    if "keys" in chunk:
+        keys = {str(k).lower() for k in chunk["keys"]}
+    elif "directions" in chunk:
+        keys = {DIRECTION_KEYS[d] for d in chunk["directions"] if d in DIRECTION_KEYS}
+    else:
+        return None
+    return keys & _VALID_KEYS
+
+
+def overlay_control_hud(frames: np.ndarray, keys) -> np.ndarray:
+    """Draws one small square per movement key in the lower-left corner (filled when held). frames: [T, H, W, 3] uint8."""
+    out = frames.copy()
+    _, h, w, _ = out.shape
+    cell = max(4, min(h, w) // 24)
+    layout = {"w": (1, 0), "a": (0, 1), "s": (1, 1), "d": (2, 1), "j": (4, 1), "l": (6, 1), "i": (5, 0), "k": (5, 1), "q": (0, 0), "e": (2, 0)}
+    keys = set(keys or ())
+    for key, (cx, cy) in layout.items():
+        x0, y0 = cell + cx * (cell + 2), h - 3 * cell - 2 + cy * (cell + 2)
+        if x0 + cell > w or y0 + cell > h or y0 < 0:
+            continue
+        out[:, y0 : y0 + cell, x0 : x0 + cell] = (255, 255, 255) if key in keys else (40, 40, 40)
+    return out
+
+
+class LingBotWorldFastService:
+    def __init__(self, pipeline, default_config: LingBotWorldFastSessionConfig | None = None, warmup: bool = False) -> None:
+        self.pipeline, self.default_config, self._warmup = pipeline, default_config or LingBotWorldFastSessionConfig(), warmup
+        self._sessions: dict[str, LingBotWorldFastSessionState] = {}
+        self._lock = threading.Lock()
+        self._started = False
+
+    # ---- lifecycle ------------------------------------------------------------------------------
+    def start(self) -> None:
+        if self._started:
+            return
+        if self._warmup:
+            self.pipeline.warmup(self.default_config.height, self.default_config.width)
+        self._started = True
+
+    def stop(self) -> None:
+        for sid in list(self._sessions):
+            self.close_session(sid, timeout=10.0)
+        self._started = False
+
+    def has_session(self, session_id: str) -> bool:
+        return session_id in self._sessions
+
+    def _state(self, session_id: str) -> LingBotWorldFastSessionState:
+        state = self._sessions.get(session_id)
+        if state is None:
+            raise KeyError(f"unknown session {session_id!r}")
+        return state
+
+    def create_session(self, config: dict) -> str:
+        known = LingBotWorldFastSessionConfig.__dataclass_fields__
+        cfg = LingBotWorldFastSessionConfig(**{**self.default_config.__dict__, **{k: v for k, v in config.items() if k in known}})
+        for name in ("fps", "max_duration_seconds", "move_step", "turn_step_deg"):
+            if not float(getattr(cfg, name)) > 0:
+                raise ValueError(f"{name} must be positive")
+        chunk_size = self.pipeline.config.chunk_size
+        frames = frame_num_for_duration(cfg.max_duration_seconds, cfg.fps, chunk_size)
+        generation = self.pipeline._create_initialized_session(cfg.prompt, load_image(config), frames, cfg.height, cfg.width, cfg.seed,
+                                                               prompt_emb=config.get("prompt_emb"))  # fmt: skip
+        stream = self.pipeline.runtime.create_session(generation)
+        sid = config.get("session_id") or uuid.uuid4().hex
+        state = LingBotWorldFastSessionState(sid, cfg, generation, stream, queue.Queue())
+        state.explicit_chunks = list(config.get("controls", []))  # pose chunks known up front, used before any key snapshot
+        with self._lock:
+            if sid in self._sessions:
+                raise ValueError(f"session {sid!r} already exists")
+            self._sessions[sid] = state
+        self._enqueue(state, {"type": "status", "stage": "created", "session_id": sid, "frames": frames, "chunks": generation.chunk_count,
+                              "chunk_size": chunk_size, "height": cfg.height, "width": cfg.width, "fps": cfg.fps})  # fmt: skip
+        state.worker = threading.Thread(target=self._worker_loop, args=(state,), name=f"lingbot-session-{sid[:8]}", daemon=True)
+        state.worker.start()
+        return sid
+
+    # ---- client -> service ---------------------------------------------------------------------
+    def push_chunk(self, session_id: str, chunk: dict) -> None:
+        state = self._state(session_id)
+        kind = chunk.get("type", "control")
+        with state.lock:
+            if kind == "stop":
+                state.stop_event.set()
+            elif kind == "key_down" and str(chunk.get("key", "")).lower() in _VALID_KEYS:
+                state.held_keys.add(str(chunk["key"]).lower())
+            elif kind == "key_up":
+                state.held_keys.discard(str(chunk.get("key", "")).lower())
+            elif "poses" in chunk or "control_tensor" in chunk:
+                state.explicit_chunks.append(chunk)  # used for the next chunk instead of the key snapshot
+            else:
+                keys = keys_from_chunk(chunk)
+                if keys is None and chunk.get("direction") in DIRECTION_KEYS:
+                    keys = {DIRECTION_KEYS[chunk["direction"]]}
+                if keys is not None:
+                    state.held_keys = keys
+
+    # ---- service -> client ---------------------------------------------------------------------
+    @staticmethod
+    def _enqueue(state: LingBotWorldFastSessionState, payload: dict) -> None:
+        """Frame chunks beyond the queue bound push out the oldest queued frame chunk; other messages always fit."""
+        q = state.outputs
+        if payload.get("type") == "frames":
+            with state.lock:
+                queued = [p for p in list(q.queue) if p.get("type") == "frames"]
+                if len(queued) >= state.config.output_queue_size:
+                    with q.mutex:
+                        for i, p in enumerate(q.queue):
+                            if p.get("type") == "frames":
+                                del q.queue[i]
+                                state.dropped_chunks += 1
+                                break
+        q.put(payload)
+
+    async def pull_chunks(self, session_id: str) -> AsyncGenerator[dict, None]:
+        state = self._state(session_id)
+        loop = asyncio.get_running_loop()
+        while True:
+            try:
+                item = state.outputs.get_nowait()
+            except queue.Empty:
+                if state.finished and state.outputs.empty():
+                    return
+                await asyncio.sleep(0.005) if loop else None
+                continue
+            yield item
+            if item.get("type") in ("done", "error"):
+                return
+
+    def drain(self, session_id: str, timeout: float = 60.0) -> list:
+        """Blocking variant of `pull_chunks` for synchronous callers: every message up to the terminal one."""
+        state, out, deadline = self._state(session_id), [], time.time() + timeout
+        while time.time() < deadline:
+            try:
+                item = state.outputs.get(timeout=0.05)
+            except queue.Empty:
+                if state.finished:
+                    break
+                continue
+            out.append(item)
+            if item.get("type") in ("done", "error"):
+                break
+        return out
+
+    # ---- per-session worker -------------------------------------------------------------------
+    def _next_control(self, state: LingBotWorldFastSessionState, chunk_index: int):
+        """(control tensor, key list) for chunk `chunk_index`: an explicit pose chunk if one is pending, else the held keys."""
+        builder, cs = state.generation.control_builder, state.generation.chunk_size
+        with state.lock:
+            explicit = state.explicit_chunks.pop(0) if state.explicit_chunks else None
+            keys = sorted(state.held_keys)
+        if explicit is not None:
+            if "poses" in explicit:
+                state.pose = torch.as_tensor(np.asarray(explicit["poses"]), dtype=torch.float32)[-1].cpu()
+            return builder.build(explicit), None
+        steps = (cs - 1 if chunk_index == 0 else cs) * 4
+        path = integrate_keys(state.pose, keys, steps, state.config.move_step, state.config.turn_step_deg) if steps else torch.zeros(0, 4, 4)
+        latent = path[3::4]
+        poses = torch.cat([state.pose[None], latent]) if chunk_index == 0 else latent
+        if len(path):
+            state.pose = path[-1]
+        return builder.build({"poses": poses, "relative": True}), keys
+
+    def _worker_loop(self, state: LingBotWorldFastSessionState) -> None:
+        runtime, stream, total = self.pipeline.runtime, state.stream, state.generation.chunk_count
+        pending: dict[int, list | None] = {}
+        cancelled = False
+        try:
+            self._enqueue(state, {"type": "status", "stage": "running", "session_id": state.session_id})
+            while state.emitted < total:
+                if state.stop_event.is_set():
+                    cancelled = True
+                    break
+                progressed = False
+                if state.submitted < total and runtime.can_submit_chunk(stream):
+                    control, keys = self._next_control(state, state.submitted)
+                    if runtime.try_submit_chunk(stream, state.submitted, control):
+                        pending[state.submitted] = keys
+                        state.submitted += 1
+                        progressed = True
+                for idx, frames in runtime.poll_frames(stream):
+                    self._emit_frames(state, idx, frames, pending.pop(idx, None))
+                    progressed = True
+                err = runtime.error(stream)
+                if err is not None:
+                    raise RuntimeError(f"streaming runtime failed: {err}")
+                if not progressed:
+                    time.sleep(0.001)
+            metrics = {}
+            try:
+                metrics = runtime.metrics(stream)
+            except Exception:  # noqa: BLE001 - metrics are best effort
+                pass
+            self._enqueue(state, {"type": "done", "session_id": state.session_id, "cancelled": cancelled, "chunks": state.emitted,
+                                  "dropped_chunks": state.dropped_chunks, "metrics": metrics})  # fmt: skip
+        except Exception as exc:  # noqa: BLE001 - reported to the client, then the session ends
+            logger.error(f"LingBot session {state.session_id} failed: {exc}")
+            cancelled = True
+            self._enqueue(state, {"type": "error", "session_id": state.session_id, "message": str(exc)})
+        finally:
+            try:
+                self.pipeline.release_session(stream, cancel=cancelled or state.emitted < total)
+            except Exception as exc:  # noqa: BLE001
+                logger.warning(f"release of LingBot session {state.session_id} failed: {exc}")
+            state.finished = True
+
+    def _emit_frames(self, state: LingBotWorldFastSessionState, idx: int, frames: torch.Tensor, keys) -> None:
+        """frames: [B, 3, T, H, W] in [-1, 1] -> uint8 [T, H, W, 3] with the HUD drawn in when enabled."""
+        from telefuser_b200.ops.functional import frames_to_uint8
+
+        arr = frames_to_uint8(frames[0] if frames.dim() == 5 else frames)
+        arr = arr.cpu().numpy() if isinstance(arr, torch.Tensor) else np.asarray(arr)
+        if state.config.hud:
+            arr = overlay_control_hud(arr, keys)
+        state.emitted += 1
+        self._enqueue(state, {"type": "frames", "session_id": state.session_id, "chunk_index": idx, "frames": arr, "controls": keys,
+                              "fps": state.config.fps, "elapsed_s": time.time() - state.created_at})  # fmt: skip
+
+    def close_session(self, session_id: str, timeout: float | None = None) -> None:
+        state = self._sessions.get(session_id)
+        if state is None:
+            return
+        state.stop_event.set()
+        if state.worker is not None and state.worker is not threading.current_thread():
+            state.worker.join(timeout if timeout is not None else 30.0)
+        with self._lock:
+            self._sessions.pop(session_id, None)

@@ -69,3 +69,58 @@ def test_control_builder_and_key_integration():
     assert one.shape == (1, 384, 2, 4, 6) and torch.isfinite(one).all()
     moved = integrate_keys(torch.eye(4), ["w"], 3)
     assert moved[-1, 2, 3] > moved[0, 2, 3] > 0
+
+
+def test_interactive_service_session():
+    import asyncio
+
+    import numpy as np
+
+    from telefuser_b200.pipelines.lingbot_world.service import (LingBotWorldFastService, LingBotWorldFastSessionConfig,
+                                                                  frame_num_for_duration, keys_from_chunk, load_image,
+                                                                  overlay_control_hud)
+
+    assert frame_num_for_duration(1.0, 16, 2) == 13 and frame_num_for_duration(0.1, 16, 2) == 5 and frame_num_for_duration(2.0, 16, 3) == 33
+    assert keys_from_chunk({"keys": ["W", "x", "j"]}) == {"w", "j"} and keys_from_chunk({"directions": ["left", "nope"]}) == {"a"}
+    assert keys_from_chunk({"type": "ping"}) is None
+    hud = overlay_control_hud(np.zeros((2, 48, 64, 3), np.uint8), ["w"])
+    assert hud.max() == 255 and (hud == 40).any() and hud.shape == (2, 48, 64, 3)
+    import pytest
+    with pytest.raises(ValueError):
+        load_image({"image_data_url": "http://x"})
+    pipe = tiny_pipeline()
+    svc = LingBotWorldFastService(pipe, LingBotWorldFastSessionConfig(height=32, width=32, fps=16, max_duration_seconds=2.0, hud=True))
+    svc.start()
+    emb, img = torch.randn(1, 8, 32), torch.rand(3, 32, 32) * 2 - 1
+    sid = svc.create_session({"image": img, "prompt_emb": emb, "seed": 1})
+    assert svc.has_session(sid)
+    svc.push_chunk(sid, {"type": "key_down", "key": "w"})
+    svc.push_chunk(sid, {"keys": ["w", "l"]})
+
+    async def collect():
+        return [m async for m in svc.pull_chunks(sid)]
+
+    msgs = asyncio.run(collect())
+    kinds = [m["type"] for m in msgs]
+    assert kinds[0] == "status" and kinds[-1] == "done" and kinds.count("frames") == 4  # 2 s at 16 fps -> 29 frames -> 4 chunks
+    frames = [m for m in msgs if m["type"] == "frames"]
+    assert [m["chunk_index"] for m in frames] == [0, 1, 2, 3] and frames[0]["frames"].shape == (5, 32, 32, 3) and frames[1]["frames"].shape == (8, 32, 32, 3)
+    assert frames[0]["frames"].dtype == np.uint8 and msgs[-1]["chunks"] == 4 and not msgs[-1]["cancelled"]
+    svc.close_session(sid)
+    assert not svc.has_session(sid)
+    # explicit pose chunks and an early stop
+    poses = random_walk_trajectory(2, seed=3)
+    sid2 = svc.create_session({"image": img, "prompt_emb": emb, "seed": 1, "max_duration_seconds": 3.0, "hud": False,
+                               "controls": [{"poses": poses, "relative": True}]})
+    first = None
+    for _ in range(2000):
+        got = svc.drain(sid2, timeout=0.05)
+        first = next((m for m in got if m["type"] == "frames"), first)
+        if first is not None:
+            break
+    assert first is not None and first["controls"] is None
+    svc.push_chunk(sid2, {"type": "stop"})
+    tail = svc.drain(sid2, timeout=30.0)
+    assert tail[-1]["type"] == "done" and tail[-1]["cancelled"]
+    svc.stop()
+    pipe.close()
