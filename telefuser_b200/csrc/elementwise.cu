@@ -424,3 +424,47 @@ extern "C" int tfb_quant_mxfp8(const void* x, long ldx, void* q, void* sf, int r
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), rows, C);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
+
+// ---------------------------------------------------------------------------
+// NF4 weights -> bf16. A code is a 4-bit index into 16 fixed levels (quantiles of a standard normal scaled to [-1, 1]);
+// every `block` consecutive values share one fp32 absmax. Two codes per byte, the first in the high nibble.
+// ---------------------------------------------------------------------------
+__constant__ float kNF4Levels[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                     -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                     0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                                     0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+
+__global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ absmax,
+                                                          __nv_bfloat16* __restrict__ out, long n_vec, int block) {
+  __shared__ float lv[16];
+  if (threadIdx.x < 16) lv[threadIdx.x] = kNF4Levels[threadIdx.x];
+  __syncthreads();
+  // one vector = 8 bytes = 16 values, which never straddles a block (block is a multiple of 16)
+  for (long i = blockIdx.x * 256L + threadIdx.x; i < n_vec; i += static_cast<long>(gridDim.x) * 256L) {
+    const uint2 raw = reinterpret_cast<const uint2*>(packed)[i];
+    const float s = absmax[(i * 16) / block];
+    const uint32_t w[2] = {raw.x, raw.y};
+    uint32_t o[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const uint32_t byte = (w[h] >> (8 * b)) & 0xffu;
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lv[byte >> 4] * s, lv[byte & 15u] * s);
+        o[h * 4 + b] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + i * 16);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+extern "C" int tfb_nf4_dequant(const void* packed, const float* absmax, void* out, long numel, int block, void* stream) {
+  if (numel <= 0 || (numel & 15) || block < 16 || (block & 15)) return TFB_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(packed) & 7) || (reinterpret_cast<uintptr_t>(out) & 15)) return TFB_ERR_BAD_SHAPE;
+  const long n_vec = numel >> 4;
+  nf4_dequant_kernel<<<grid_for(n_vec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(packed), absmax, static_cast<__nv_bfloat16*>(out), n_vec, block);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}

@@ -73,6 +73,8 @@ int tfb_cfg_euler_step(const float* x, const void* cond, const void* uncond, int
 // Per-row MXFP8 quantisation: e4m3 payload + UE8M0 scale per 32 elements.
 //   x: bf16 [rows, C];  q: uint8 [rows, C];  sf: uint8 [rows, C/32] (row-major)
 int tfb_quant_mxfp8(const void* x, long ldx, void* q, void* sf, int rows, int C, void* stream);
+// NF4 codes (two per byte, first in the high nibble) with one fp32 absmax per `block` values -> bf16; numel % 16 == 0.
+int tfb_nf4_dequant(const void* packed, const float* absmax, void* out, long numel, int block, void* stream);
 
 // Grouped bf16 GEMM for expert layers. A: [M, K] token rows sorted by expert, each expert's segment
 // starting on a multiple of 128 rows (M = padded row count, multiple of 128); B: [E*N, K]; M tile m

@@ -590,9 +590,21 @@ class LTXVideoTransformer(BaseModel):
         return ["velocity_model.transformer_blocks"]
 
     def enable_quant(self, quant=None) -> int:
+        """`quant`: a QuantConfig, a QuantType or a name. NF4 packs the block linears to 4.5 bits per weight (the 22B
+        model then fits one GPU several times over); anything else selects W8A8 FP8."""
+        kind = getattr(quant, "quant_type", quant)
+        name = str(getattr(kind, "name", kind)).lower()
+        include = getattr(quant, "quantize_modules", None)
+        exclude = tuple(getattr(quant, "skip_modules", None) or ()) + ("to_gate_logits",)
+        if name.endswith("nf4"):
+            from telefuser_b200.ops.nf4 import quantize_model_nf4_
+
+            self.quant_type = kind
+            return quantize_model_nf4_(self.velocity_model.transformer_blocks, include, exclude)
         from telefuser_b200.ops.quant import quantize_model_fp8_
 
-        return quantize_model_fp8_(self, ("velocity_model.transformer_blocks.*",), ("to_gate_logits",))
+        self.quant_type = kind
+        return quantize_model_fp8_(self, ("velocity_model.transformer_blocks.*",), exclude)
 
     def forward(self, video: Modality | None, audio: Modality | None = None, perturbations=None, x0: bool = False):
         if x0:

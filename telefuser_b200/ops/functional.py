@@ -59,6 +59,10 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
             out.copy_(r)
             return out
         return r
+    if weight.dtype == torch.uint8 and hasattr(weight, "tfb_nf4_absmax"):
+        from telefuser_b200.ops.nf4 import expand_nf4_weight
+
+        weight = expand_nf4_weight(weight, x.dtype)  # packed 4-bit codes -> [N, K] in a shared scratch buffer
     K = x.shape[-1]
     N = weight.shape[0]
     # The tensor-core kernel moves 16-byte rows: widths that are not multiples of 8 elements (toy configurations)

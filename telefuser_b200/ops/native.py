@@ -98,6 +98,7 @@ def _declare(lib) -> None:
         "tfb_gemm_fp8": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                          c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "tfb_quant_fp8_rowwise": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
+        "tfb_nf4_dequant": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "tfb_rmsnorm_modulate": [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_float, c_void_p, c_void_p,
                                  c_void_p, c_long, c_int, c_void_p],
         "tfb_rmsnorm_gate_residual": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_float,
