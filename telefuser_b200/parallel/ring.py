@@ -3,8 +3,8 @@
 Ring: every rank keeps its query shard and the K,V shards travel round the ring; step r attends to
 the shard that started r ranks upstream while the next shard is already in flight (`isend`/`irecv`
 into the other half of a double buffer); partial results are merged by log-sum-exp. Non-causal, so
-the visiting order does not matter. This is the collective-library path and the oracle for the fused
-peer-memory ring kernel.
+the visiting order does not matter. This is the collective-library path and the oracle for the fused form
+(`symm.ring_attention_fused`: one peer-store all-gather of K / V overlapped with the local attention).
 USP: all-to-all over the Ulysses group (sequence -> heads) inside each ring group, ring attention
 over the ring group, inverse all-to-all.
 Role parity: telefuser/distributed/ring.py:61-214, ops/attention/attention_impl.py:319-558.
@@ -27,11 +27,21 @@ def _group_info(group):
     return dist.get_rank(group), dist.get_world_size(group), dist.get_process_group_ranks(group)
 
 
-def ring_attention(q, k, v, group=None, scale=None, return_lse: bool = False):
-    """q, k, v: [B, S_local, H, D] shards of one sequence over `group` -> [B, S_local, H, D]."""
+def _fused_ok(q, k, fused: bool) -> bool:
+    return fused and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and q.shape[0] == 1 and k.shape[0] == 1
+
+
+def ring_attention(q, k, v, group=None, scale=None, return_lse: bool = False, fused: bool = False):
+    """q, k, v: [B, S_local, H, D] shards of one sequence over `group` -> [B, S_local, H, D].
+    `fused`: exchange K / V by peer stores overlapped with the local attention instead of NCCL ring steps."""
     rank, P, ranks = _group_info(group)
     if P == 1:
         return TF.attention(q, k, v, scale, return_lse)
+    if _fused_ok(q, k, fused):
+        from .symm import get_workspace, ring_attention_fused, ring_workspace_bytes
+
+        ws = get_workspace(group, ring_workspace_bytes(k.shape[1], k.shape[2], k.shape[3], P), tag="ring")
+        return ring_attention_fused(q, k, v, ws, scale, return_lse)
     nxt, prv = ranks[(rank + 1) % P], ranks[(rank - 1) % P]
     cur = torch.stack([k, v]).contiguous()  # one message per step
     other = torch.empty_like(cur)
@@ -49,12 +59,12 @@ def ring_attention(q, k, v, group=None, scale=None, return_lse: bool = False):
     return (out, lse) if return_lse else out
 
 
-def usp_attention(q, k, v, ulysses_group=None, ring_group=None, scale=None):
+def usp_attention(q, k, v, ulysses_group=None, ring_group=None, scale=None, fused: bool = False):
     """Sequence sharded over ring x Ulysses; heads are exchanged inside the Ulysses group first."""
     hq = ulysses.scatter_heads(q, ulysses_group, async_op=True)
     hk = ulysses.scatter_heads(k, ulysses_group, async_op=True)
     hv = ulysses.scatter_heads(v, ulysses_group, async_op=True)
-    o = ring_attention(hq.wait(), hk.wait(), hv.wait(), ring_group, scale)
+    o = ring_attention(hq.wait(), hk.wait(), hv.wait(), ring_group, scale, fused=fused)
     return ulysses.gather_heads(o, ulysses_group)
 
 
@@ -77,7 +87,7 @@ def long_context_attention(q, k, v, scale=None, mesh=None, strategy: str | None 
         hv = ulysses.scatter_heads(v, g, async_op=True)
         return ulysses.gather_heads(TF.attention(hq.wait(), hk.wait(), hv.wait(), scale), g)
     if strategy == "ring":
-        return ring_attention(q, k, v, mesh.group("ring"), scale)
+        return ring_attention(q, k, v, mesh.group("ring"), scale, fused=mesh.fused)
     if strategy == "usp":
-        return usp_attention(q, k, v, mesh.group("ulysses"), mesh.group("ring"), scale)
+        return usp_attention(q, k, v, mesh.group("ulysses"), mesh.group("ring"), scale, fused=mesh.fused)
     raise ValueError(f"unknown attention strategy {strategy!r}")

@@ -203,3 +203,65 @@ def all_gather_rows_fused(x_local: torch.Tensor, ws: PeerWorkspace, name: str = 
     native.check(code, "tfb_peer_push_rows")
     ws.barrier()
     return full
+
+
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = str(device)
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
+def ring_workspace_bytes(S_local: int, H: int, D: int, world: int, itemsize: int = 2) -> int:
+    return 2 * (world * S_local * H * D * itemsize + 256) + 4096
+
+
+def ring_attention_fused(q, k, v, ws: PeerWorkspace, scale: float | None = None, return_lse: bool = False):
+    """Context-parallel attention over `ws.group` with the K / V exchange done by peer stores.
+
+    q, k, v: [1, S_local, H, 128] bf16 shards of one sequence. On a side stream one kernel pushes this rank's K and
+    V rows into every peer's gather buffer (each shard crosses NVLink once and is then read from local memory),
+    bracketed by flag barriers; meanwhile the main stream attends to the local shard. The remote shards form at
+    most two contiguous runs in rank order; each is attended with one kernel launch and merged by log-sum-exp.
+    All ranks hold all keys afterwards, so there are no ring steps: on an NVSwitch fabric every peer is one hop.
+    """
+    from telefuser_b200.ops import functional as TF
+
+    B, S, H, D = q.shape
+    if B != 1 or k.shape != v.shape or k.shape[0] != 1:
+        raise ValueError("ring_attention_fused takes one sequence per call (batch 1)")
+    P, rank, C = ws.world, ws.rank, H * D
+    Sk = k.shape[1]
+    kbuf = ws.region("ring_k", (P * Sk, C), k.dtype)
+    vbuf = ws.region("ring_v", (P * Sk, C), v.dtype)
+    lib, rb = native.load(), C * k.element_size()
+
+    def rows(t):
+        t2 = t.reshape(Sk, C) if t.is_contiguous() else t[0].reshape(Sk, C)
+        if t2.stride(1) != 1 or (t2.stride(0) * t2.element_size()) % 16:
+            t2 = t2.contiguous()
+        return t2, t2.stride(0) * t2.element_size()
+
+    (k2, ldk), (v2, ldv) = rows(k), rows(v)
+    main, side = torch.cuda.current_stream(q.device), _side_stream(q.device)
+    side.wait_stream(main)  # K / V are produced on the main stream; its earlier reads of the buffers are done too
+    with torch.cuda.stream(side):
+        ws.barrier(1)  # every rank is past its reads of the previous contents
+        for src, ld, name in ((k2, ldk, "ring_k"), (v2, ldv, "ring_v")):
+            code = lib.tfb_peer_push_rows(src.data_ptr(), ld, ws.peer_table(name), P, rank * Sk, Sk, rb, rb, native.stream_ptr())
+            native.check(code, "tfb_peer_push_rows")
+        ws.barrier(1)  # every shard has landed everywhere
+    k2.record_stream(side)
+    v2.record_stream(side)
+    o, lse = TF.attention(q, k, v, scale, return_lse=True)  # local shard, overlaps the exchange
+    main.wait_stream(side)
+    for lo, hi in ((0, rank), (rank + 1, P)):
+        if hi > lo:
+            kk = kbuf[lo * Sk : hi * Sk].view(1, (hi - lo) * Sk, H, D)
+            vv = vbuf[lo * Sk : hi * Sk].view(1, (hi - lo) * Sk, H, D)
+            o2, lse2 = TF.attention(q, kk, vv, scale, return_lse=True)
+            o, lse = TF.merge_attn_states(o, lse, o2, lse2)
+    return (o, lse) if return_lse else o

@@ -85,6 +85,23 @@ def rank_main(rank: int, world_size: int, port: int, out_path: str, seq: int = 5
             got = symm.all_gather_rows_fused(x, ws)
             worst = max(worst, (got.float() - torch.cat(parts).float()).abs().max().item())
         errs["gather"] = worst
+        # context-parallel attention: K / V exchanged by peer stores vs the NCCL ring and vs attention over the full sequence
+        from telefuser_b200.parallel import ring
+
+        rws = symm.PeerWorkspace(group, symm.ring_workspace_bytes(S_loc, heads, D, P))
+        worst = 0.0
+        for it in range(2):  # twice: the gather buffers are reused
+            g = torch.Generator(device="cpu").manual_seed(200 + it)
+            qkv = torch.randn(B, seq, 3 * heads * D, generator=g).bfloat16()
+            mine = qkv[:, rank * S_loc : (rank + 1) * S_loc].to(dev)
+            q, k, v = (mine[..., i * heads * D : (i + 1) * heads * D].unflatten(-1, (heads, D)) for i in range(3))
+            got = symm.ring_attention_fused(q, k, v, rws)
+            want = ring.ring_attention(q.contiguous(), k.contiguous(), v.contiguous(), group)
+            full_k, full_v = (qkv[..., i * heads * D : (i + 1) * heads * D].unflatten(-1, (heads, D)).to(dev) for i in (1, 2))
+            oracle = TF.attention(q.contiguous(), full_k.contiguous(), full_v.contiguous())
+            worst = max(worst, (got.float() - want.float()).abs().max().item(), (got.float() - oracle.float()).abs().max().item())
+        errs["ring"] = worst
+        rws.close()
         if world_size == 2:
             torch.manual_seed(7)
             lat = torch.randn(1, 16, 3, 8, 8, device=dev)

@@ -1,0 +1,54 @@
+"""Checkpoint viewer and the communication check tool (CPU / gloo forms)."""
+
+import json
+import os
+import subprocess
+import sys
+
+import torch
+from safetensors.torch import save_file
+
+from telefuser_b200.tools import comm_test, weight_viewer
+from telefuser_b200.utils.system import find_free_port
+
+
+def test_weight_viewer_tree_merge_and_export(tmp_path, capsys):
+    sd1 = {f"blocks.{i}.attn.q.weight": torch.zeros(8, 8, dtype=torch.bfloat16) for i in range(3)}
+    sd1.update({f"blocks.{i}.attn.q.bias": torch.zeros(8, dtype=torch.bfloat16) for i in range(3)})
+    sd2 = {"blocks.3.attn.q.weight": torch.zeros(8, 4), "head.weight": torch.zeros(4, 8), "patch.proj.weight": torch.zeros(2, 3, 1, 2, 2)}
+    save_file(sd1, str(tmp_path / "m-00001-of-00002.safetensors"))
+    save_file(sd2, str(tmp_path / "m-00002-of-00002.safetensors"))
+    assert [os.path.basename(f) for f in weight_viewer.expand_file_pattern(str(tmp_path / "m-*.safetensors"))] == [
+        "m-00001-of-00002.safetensors", "m-00002-of-00002.safetensors"]  # fmt: skip
+    v = weight_viewer.WeightViewer().load_weights(str(tmp_path / "m-*.safetensors"))
+    s = v.get_summary()
+    assert s["files"] == 2 and s["tensors"] == 9 and s["parameters"] == 3 * 72 + 32 + 32 + 24
+    assert s["dtypes"]["BF16"] == 216 and s["bytes"] == 216 * 2 + 88 * 4 and s["top_level"]["blocks"] == 248
+    assert set(s["fingerprint"]) >= {"keys", "keys_and_shapes", "registered_as"} and s["fingerprint"]["registered_as"] is None
+    lines = v.render(max_depth=5)
+    assert any("0..2 (x3, identical)" in line for line in lines) and any(line.strip().startswith("3/") for line in lines)
+    assert len(v.render(merge_similar=False)) > len(lines) and len(v.render(max_depth=1)) == 3
+    assert weight_viewer.WeightViewer.format_number(1_500_000) == "1.50M"
+    torch.save({"state_dict": {"a": {"w": torch.zeros(2, 2)}}}, tmp_path / "x.pt")
+    assert weight_viewer.read_torch_checkpoint(str(tmp_path / "x.pt")) == {"a.w": ("float32", (2, 2))}
+    assert weight_viewer.main([str(tmp_path / "m-*.safetensors"), "--quiet", "--export", str(tmp_path / "o.json")]) == 0
+    assert "9 tensors" in capsys.readouterr().out and json.load(open(tmp_path / "o.json"))["tensors"]["head.weight"]["shape"] == [4, 8]
+
+
+def test_comm_test_single_process_and_gloo(tmp_path):
+    env = comm_test.environment()
+    assert env["torch"] == torch.__version__ and isinstance(env["devices"], list)
+    r = comm_test.host_device_bandwidth(torch.device("cpu"), 1, warmup=1, iters=2)
+    assert r["h2d_gbs"] > 0 and r["d2h_gbs"] > 0
+    text = comm_test.format_report({"environment": env, "world": 1, "host_device": [r]})
+    assert "host<->device" in text
+    out = tmp_path / "report.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(find_free_port()), "-m", "telefuser_b200.tools.comm_test", "--backend", "gloo", "--sizes-mb", "1",
+           "--iters", "2", "--json", str(out)]  # fmt: skip
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env={**os.environ, "OMP_NUM_THREADS": "1"})
+    assert res.returncode == 0, res.stderr[-2000:]
+    rep = json.load(open(out))
+    col = rep["collectives"][0]
+    assert rep["world"] == 2 and col["world"] == 2 and {"all_reduce", "all_gather", "send_recv_ring"} <= set(col)
+    assert col["all_reduce"]["bus_gbs"] > 0 and abs(col["all_reduce"]["bus_gbs"] / col["all_reduce"]["alg_gbs"] - 1.0) < 1e-6  # 2(P-1)/P = 1 at P = 2
