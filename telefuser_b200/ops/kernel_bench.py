@@ -136,6 +136,13 @@ def bench_elementwise(t: Timer, rows: int, dim: int) -> None:
     report("rmsnorm_rope (q and k)", t(lambda: TF.rmsnorm_rope_(q, w, heads, cos, sin, 1e-6, x2=k, weight2=w)),
            bytes_=4 * nb + 2 * rows * 64 * 4, rows=rows, dim=dim)  # fmt: skip
     report("quant_mxfp8", t(lambda: TF.quant_mxfp8(x)), bytes_=nb + nb // 2 + nb // 64, rows=rows, dim=dim)
+    from telefuser_b200.ops import nf4
+
+    wq = torch.randint(0, 256, (4 * dim * dim // 2,), device="cuda", dtype=torch.uint8)  # a [4 dim, dim] MLP weight, packed
+    am = torch.rand(4 * dim * dim // 64, device="cuda")
+    wout = torch.empty(4 * dim, dim, device="cuda", dtype=torch.bfloat16)
+    report("nf4_dequant", t(lambda: nf4.dequantize_nf4(wq, am, wout.shape, out=wout)), bytes_=wq.numel() + am.numel() * 4 + wout.numel() * 2,
+           n=4 * dim, k=dim)  # fmt: skip
     lat = torch.randn(1, 16, 21, 90, 160, device="cuda")
     c, u = torch.randn_like(lat).bfloat16(), torch.randn_like(lat).bfloat16()
     report("cfg_euler_step", t(lambda: TF.cfg_euler_step(lat, c, u, 5.0, -0.02)), bytes_=lat.numel() * (4 + 2 + 2 + 4))
