@@ -325,8 +325,9 @@ class BasicAVTransformerBlock(nn.Module):
                  rope_type: LTXRopeType = LTXRopeType.INTERLEAVED, norm_eps: float = 1e-6) -> None:  # fmt: skip
         super().__init__()
         self.idx, self.norm_eps = idx, norm_eps
-        att = lambda c, ctx=None, h=None, d=None: Attention(c.dim if ctx != "q_audio" else audio.dim, ctx if isinstance(ctx, int) else None,  # noqa: E731
-                                                            h or c.heads, d or c.d_head, norm_eps, rope_type, c.apply_gated_attention)  # fmt: skip
+        def att(c: TransformerConfig, context_dim: int | None = None) -> Attention:
+            return Attention(c.dim, context_dim, c.heads, c.d_head, norm_eps, rope_type, c.apply_gated_attention)
+
         if video is not None:
             self.attn1 = att(video)
             self.attn2 = att(video, video.context_dim)
