@@ -362,6 +362,21 @@ class DitDenoisingStage(BaseStage):
         self.flow_match_scheduler = FlowMatchScheduler(template="LTX.2")
         self.video_patchifier, self.audio_patchifier = VideoLatentPatchifier(1), AudioPatchifier(1)
         self.forward_calls = 0
+        self._lora_applied = False
+
+    def _maybe_apply_loras(self) -> None:
+        """Merges the stage's configured LoRA files into the velocity model once (stage 2 usually carries the distilled LoRA)."""
+        if self._lora_applied:
+            return
+        self._lora_applied = True
+        configs = getattr(self.model_runtime_config, "lora_configs", None) or []
+        if not configs:
+            return
+        from telefuser_b200.utils.lora import LoRALoader
+
+        target, loader = getattr(self.dit, "velocity_model", self.dit), LoRALoader()
+        for cfg in configs:
+            loader.apply_lora(target, cfg.path, strength=cfg.strength)
 
     def _x0(self, video: Modality, audio: Modality, perturbations=None):
         self.forward_calls += 1
@@ -474,6 +489,7 @@ class DitDenoisingStage(BaseStage):
                 video_noise: torch.Tensor, audio_noise: torch.Tensor, initial_video_latent=None, initial_audio_latent=None, sigmas=None,
                 noise_scale: float = 1.0, simple_denoise: bool = False):  # fmt: skip
         """-> (video LatentState [B, 128, F, H, W], audio LatentState [B, 8, T, 16]) after the last step."""
+        self._maybe_apply_loras()
         sigmas, timesteps = self._prepare_schedule(num_inference_steps, sigmas, initial_video_latent)
         fn = self._build_denoise_fn(positive_context, negative_context, video_guider_params, audio_guider_params, simple_denoise)
         vs, as_, vtools, atools = self._create_initial_states(height, width, num_frames, frame_rate, conditionings,
