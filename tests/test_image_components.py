@@ -60,3 +60,37 @@ def test_prompt_encoders_tiny():
     sd, _ = q.state_dict_converter().from_official({"visual.a": 1, "model.layers.0.w": 2, "lm_head.weight": 3})
     assert sorted(sd) == ["lm_head.weight", "model.language_model.layers.0.w", "model.visual.a"]
     assert set(sd) <= {k.split(".weight")[0] + ".weight" if k.endswith(".weight") else k for k in sd}
+
+
+def test_qwen_image_text_stage_packing():
+    from types import SimpleNamespace
+
+    from telefuser_b200.pipelines.qwen_image.text_encoding import (GENERATE_DROP, GENERATE_TEMPLATE, QwenImageTextEncodingStage,
+                                                                    pack_valid_tokens)
+
+    hidden = torch.arange(2 * 6 * 2, dtype=torch.float32).view(2, 6, 2)
+    mask = torch.tensor([[1, 1, 1, 1, 1, 0], [1, 1, 1, 0, 0, 0]])
+    emb, m = pack_valid_tokens(hidden, mask, drop=2)
+    assert emb.shape == (2, 3, 2) and m.tolist() == [[1, 1, 1], [1, 0, 0]] and torch.equal(emb[0], hidden[0, 2:5]) and bool((emb[1, 1:] == 0).all())
+    assert pack_valid_tokens(hidden, mask, 2, max_len=2)[0].shape == (2, 2, 2)
+
+    class Tok:
+        def __call__(self, texts, max_length=None, padding=True, truncation=True, return_tensors="pt"):
+            rows = [[ord(c) % 50 + 1 for c in t] for t in texts]
+            n = max(len(r) for r in rows)
+            ids = torch.tensor([r + [0] * (n - len(r)) for r in rows])
+            return {"input_ids": ids, "attention_mask": (ids > 0).long()}
+
+    encoder = lambda input_ids, attention_mask, output_hidden_states=True, **kw: (None, input_ids[..., None].float().repeat(1, 1, 4))  # noqa: E731
+    stage = QwenImageTextEncodingStage(encoder, Tok(), device="cpu", torch_dtype=torch.float32)
+    emb, m = stage(["a cat", "a much longer prompt"])
+    base = len(GENERATE_TEMPLATE.format("")) - GENERATE_DROP
+    assert emb.shape == (2, base + 20, 4) and m.sum(dim=1).tolist() == [base + 5, base + 20]
+    pos, pm, neg, nm = stage.process("x", "y", num_images_per_prompt=2)
+    assert pos.shape[0] == 2 and neg.shape == pos.shape and torch.equal(pm, nm)
+    proc = lambda text, images, padding=True, return_tensors="pt": SimpleNamespace(  # noqa: E731
+        to=lambda dev: SimpleNamespace(input_ids=torch.ones(1, 70, dtype=torch.long), attention_mask=torch.ones(1, 70, dtype=torch.long),
+                                       pixel_values=torch.zeros(4, 8), image_grid_thw=torch.tensor([[1, 2, 2]])), text=text)  # fmt: skip
+    stage.processor = proc
+    e2, m2 = stage("make it blue", images=[torch.zeros(3, 8, 8)])
+    assert e2.shape == (1, 6, 4) and int(m2.sum()) == 6  # 70 valid tokens minus the 64 template tokens
