@@ -354,7 +354,7 @@ def _skip(kind: PerturbationType, blocks) -> Perturbation:
 
 class DitDenoisingStage(BaseStage):
     def __init__(self, name: str, module_manager: Any, config: ModelRuntimeConfig, model_name: str = "ltx_dit", scheduler=None,
-                 dit=None) -> None:  # fmt: skip
+                 dit=None, batched_guidance: bool = False) -> None:  # fmt: skip
         super().__init__(name, config)
         self.dit = dit if dit is not None else module_manager.fetch_module(model_name)
         self.model_names = ["dit"]
@@ -363,6 +363,8 @@ class DitDenoisingStage(BaseStage):
         self.video_patchifier, self.audio_patchifier = VideoLatentPatchifier(1), AudioPatchifier(1)
         self.forward_calls = 0
         self._lora_applied = False
+        # run the guidance passes of a step (prompt, negative prompt, perturbed, modality-isolated) as one batch of up to four
+        self.batched_guidance = batched_guidance
 
     def _maybe_apply_loras(self) -> None:
         """Merges the stage's configured LoRA files into the velocity model once (stage 2 usually carries the distilled LoRA)."""
@@ -397,6 +399,14 @@ class DitDenoisingStage(BaseStage):
                         positions=state.positions, context=context, enabled=enabled, context_mask=None,
                         attention_mask=state.attention_mask)  # fmt: skip
 
+    @staticmethod
+    def _stack(m: Modality, contexts: list) -> Modality:
+        """One sample -> a batch with one entry per context (same latents, positions and timesteps)."""
+        n = len(contexts)
+        rep = lambda t: None if t is None else t.repeat(n, *([1] * (t.dim() - 1)))  # noqa: E731
+        return Modality(latent=rep(m.latent), sigma=m.sigma.reshape(-1)[:1].expand(n), timesteps=rep(m.timesteps), positions=rep(m.positions),
+                        context=torch.cat(contexts, dim=0), enabled=m.enabled, context_mask=None, attention_mask=rep(m.attention_mask))  # fmt: skip
+
     def _build_denoise_fn(self, positive_context, negative_context, video_params: MultiModalGuiderParams,
                           audio_params: MultiModalGuiderParams, simple_denoise: bool):  # fmt: skip
         pos_v, pos_a = resolve_context(positive_context)
@@ -413,6 +423,23 @@ class DitDenoisingStage(BaseStage):
                 return last[0], last[1]
             sigma = sigmas[i]
             video, audio = self._modality(vs, pos_v, sigma, not skip_v), self._modality(as_, pos_a, sigma, not skip_a)
+            if self.batched_guidance and vs.latent.shape[0] == 1 and not (skip_v or skip_a):
+                passes = [("cond", pos_v, pos_a, PerturbationConfig.empty())]
+                if vg.do_unconditional_generation() or ag.do_unconditional_generation():
+                    passes.append(("neg", pos_v if neg_v is None else neg_v, pos_a if neg_a is None else neg_a, PerturbationConfig.empty()))
+                if vg.do_perturbed_generation() or ag.do_perturbed_generation():
+                    items = ([_skip(P.SKIP_VIDEO_SELF_ATTN, video_params.stg_blocks)] if vg.do_perturbed_generation() else []) + (
+                        [_skip(P.SKIP_AUDIO_SELF_ATTN, audio_params.stg_blocks)] if ag.do_perturbed_generation() else [])  # fmt: skip
+                    passes.append(("ptb", pos_v, pos_a, PerturbationConfig(items)))
+                if vg.do_isolated_modality_generation() or ag.do_isolated_modality_generation():
+                    passes.append(("mod", pos_v, pos_a, PerturbationConfig([_skip(P.SKIP_A2V_CROSS_ATTN, None), _skip(P.SKIP_V2A_CROSS_ATTN, None)])))
+                out_v, out_a = self._x0(self._stack(video, [p[1] for p in passes]), self._stack(audio, [p[2] for p in passes]),
+                                        BatchedPerturbationConfig([p[3] for p in passes]))  # fmt: skip
+                got = {p[0]: (out_v[i : i + 1], out_a[i : i + 1]) for i, p in enumerate(passes)}
+                zero = (0.0, 0.0)
+                last[0] = vg.calculate(got["cond"][0], got.get("neg", zero)[0], got.get("ptb", zero)[0], got.get("mod", zero)[0])
+                last[1] = ag.calculate(got["cond"][1], got.get("neg", zero)[1], got.get("ptb", zero)[1], got.get("mod", zero)[1])
+                return last[0], last[1]
             cond_v, cond_a = self._x0(video, audio)
             neg = ptb = mod = (0.0, 0.0)
             if vg.do_unconditional_generation() or ag.do_unconditional_generation():

@@ -49,6 +49,7 @@ class LTXVideoPipelineConfig:
     enable_vae_parallel: bool = False
     enable_vae_ray: bool = False
     stage2_lora_strength: float = 1.0
+    batched_guidance: bool = True  # the up-to-four guidance passes of a stage-1 step run as one batch
 
 
 class LTX23VideoPipeline(BasePipeline):
@@ -77,7 +78,7 @@ class LTX23VideoPipeline(BasePipeline):
         self.module_manager, self.config = module_manager, config
         self.vae_stage = VAEStage("vae", module_manager, config.vae_config)
         self.stage1_denoise_stage = DitDenoisingStage("stage1_denoise", module_manager, config.dit_stage1_config, "ltx_dit",
-                                                      self._scheduler(config.sample_solver))  # fmt: skip
+                                                      self._scheduler(config.sample_solver), batched_guidance=config.batched_guidance)  # fmt: skip
         self.stage2_denoise_stage = DitDenoisingStage("stage2_denoise", module_manager, config.dit_stage2_config, "ltx_dit",
                                                       self._scheduler(config.sample_solver))  # fmt: skip
         self.upsampler_stage = UpsamplerStage("upsampler", module_manager, config.upsampler_config)

@@ -251,7 +251,7 @@ def test_two_stage_pipeline_end_to_end():
                              tiled=False, video_stg_blocks=[0], audio_stg_blocks=[0])  # fmt: skip
     assert len(frames) == 9 and frames[0].size == (128, 128) and rate == 24000
     assert wav.shape == (2, (9 * 4 - 3) * 8) and bool(torch.isfinite(wav).all())
-    assert pipe.stage1_denoise_stage.forward_calls == 8 and pipe.stage2_denoise_stage.forward_calls == 3
+    assert pipe.stage1_denoise_stage.forward_calls == 2 and pipe.stage2_denoise_stage.forward_calls == 3  # four guidance passes per batched call
     lat_v, lat_a = pipe("a tiny test", seed=3, height=128, width=128, num_frames=9, num_inference_steps=1, video_cfg_scale=1.0,
                         audio_cfg_scale=1.0, video_stg_scale=0.0, audio_stg_scale=0.0, video_modality_scale=1.0, audio_modality_scale=1.0,
                         return_latents=True)  # fmt: skip
@@ -262,3 +262,20 @@ def test_two_stage_pipeline_end_to_end():
     packed = cond.encode_image(img, 64, 64, frame_idx=8, strength=0.8)
     assert packed.shape == (1, 129, 2, 2, 2) and torch.allclose(packed[:, 0, 1], torch.tensor(0.2)) and bool((packed[:, 0, 0] == 1).all())
     assert cond.encode_image(None, 64, 64) is None and cond.encode_image(img, 64, 64, strength=0.0) is None
+
+
+def test_batched_guidance_equals_sequential_passes():
+    ctx = (torch.randn(1, 8, 32), torch.randn(1, 8, 16))
+    neg = (torch.randn(1, 8, 32), torch.randn(1, 8, 16))
+    nv, na = torch.randn(1, 8, 128), torch.randn(1, 9, 128)
+    full = DD.MultiModalGuiderParams(cfg_scale=3.0, stg_scale=1.0, stg_blocks=[1], rescale_scale=0.7, modality_scale=3.0)
+    kw = dict(height=64, width=64, num_frames=9, frame_rate=24.0, conditionings=None, positive_context=ctx, negative_context=neg,
+              num_inference_steps=2, video_guider_params=full, audio_guider_params=full, video_noise=nv, audio_noise=na)  # fmt: skip
+    outs = []
+    for batched in (False, True):
+        stage = DD.DitDenoisingStage("denoise", None, ModelRuntimeConfig(device_type="cpu", torch_dtype=torch.float32), dit=_dit(), batched_guidance=batched)
+        stage.onload_models_flag = True
+        outs.append(stage.process(**kw))
+        assert stage.forward_calls == (2 if batched else 8)
+    (v0, a0), (v1, a1) = outs
+    assert torch.allclose(v0.latent, v1.latent, atol=2e-5) and torch.allclose(a0.latent, a1.latent, atol=2e-5)
