@@ -134,3 +134,24 @@ def test_gpu_bf16_matches_fp32():
     for o, r in ((out_v, ref_v), (out_a, ref_a)):
         err = (o.float().cpu() - r).abs().max().item()
         assert err < 0.04 * max(1.0, r.abs().max().item()), err
+
+
+@pytest.mark.gpu
+def test_gpu_batched_passes_with_perturbations():
+    """Batch of two with different prompts and perturbations (the batched-guidance form) on the native kernels."""
+    P, T = M.Perturbation, M.PerturbationType
+    ptb = lambda: M.BatchedPerturbationConfig([M.PerturbationConfig.empty(),  # noqa: E731
+                                               M.PerturbationConfig([P(T.SKIP_VIDEO_SELF_ATTN, [1]), P(T.SKIP_A2V_CROSS_ATTN, None), P(T.SKIP_AUDIO_SELF_ATTN, [0])])])
+    m = _model()
+    v, a = _inputs(B=2, grid=(4, 6, 8), Ta=40)
+    v = M.Modality(**{**v.__dict__, "context_mask": None})
+    ref_v, ref_a = m(v, a, ptb())
+    mg = _model().to("cuda", torch.bfloat16)
+    vg, ag = _inputs(B=2, grid=(4, 6, 8), Ta=40, device="cuda", dtype=torch.bfloat16)
+    vg = M.Modality(**{**vg.__dict__, "context_mask": None})
+    out_v, out_a = mg(vg, ag, ptb())
+    for o, r in ((out_v, ref_v), (out_a, ref_a)):
+        err = (o.float().cpu() - r).abs().max().item()
+        assert err < 0.04 * max(1.0, r.abs().max().item()), err
+    x0_v, _ = mg(vg, ag, ptb(), x0=True)
+    assert x0_v.shape == vg.latent.shape and bool(torch.isfinite(x0_v.float()).all())
