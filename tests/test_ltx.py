@@ -153,5 +153,5 @@ def test_gpu_batched_passes_with_perturbations():
     for o, r in ((out_v, ref_v), (out_a, ref_a)):
         err = (o.float().cpu() - r).abs().max().item()
         assert err < 0.04 * max(1.0, r.abs().max().item()), err
-    x0_v, _ = mg(vg, ag, ptb(), x0=True)
+    x0_v, _ = M.X0Model(mg)(vg, ag, ptb())
     assert x0_v.shape == vg.latent.shape and bool(torch.isfinite(x0_v.float()).all())
