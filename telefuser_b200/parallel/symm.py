@@ -258,10 +258,20 @@ def ring_attention_fused(q, k, v, ws: PeerWorkspace, scale: float | None = None,
     v2.record_stream(side)
     o, lse = TF.attention(q, k, v, scale, return_lse=True)  # local shard, overlaps the exchange
     main.wait_stream(side)
+    o, lse = attend_remote_runs(q, o, lse, kbuf, vbuf, rank, P, Sk, scale)
+    return (o, lse) if return_lse else o
+
+
+def attend_remote_runs(q, o, lse, kbuf, vbuf, rank: int, P: int, Sk: int, scale=None):
+    """Merges into (o, lse) the attention of `q` over the other ranks' shards held rank-major in kbuf / vbuf [P * Sk, H * D]:
+    the rows before and after this rank's own shard are two contiguous runs, one kernel launch each."""
+    from telefuser_b200.ops import functional as TF
+
+    H, D = q.shape[2], q.shape[3]
     for lo, hi in ((0, rank), (rank + 1, P)):
         if hi > lo:
             kk = kbuf[lo * Sk : hi * Sk].view(1, (hi - lo) * Sk, H, D)
             vv = vbuf[lo * Sk : hi * Sk].view(1, (hi - lo) * Sk, H, D)
             o2, lse2 = TF.attention(q, kk, vv, scale, return_lse=True)
             o, lse = TF.merge_attn_states(o, lse, o2, lse2)
-    return (o, lse) if return_lse else o
+    return o, lse

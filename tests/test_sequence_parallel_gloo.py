@@ -111,3 +111,34 @@ def test_tensor_parallel_linears_compose_collectives_without_a_peer_workspace():
         mp.spawn(_tp_fused_rank, nprocs=2, join=True, args=(2, find_free_port(), path))
         errs = torch.load(path)
     assert max(errs.values()) <= 1e-5, errs
+
+
+def _remote_runs_case(device, dtype, D, tol):
+    import torch
+
+    from telefuser_b200.ops import functional as TF
+    from telefuser_b200.parallel.symm import attend_remote_runs
+
+    torch.manual_seed(0)
+    P, Sk, H = 4, 64, 2
+    k_full, v_full = (torch.randn(P * Sk, H * D, device=device, dtype=dtype) for _ in range(2))
+    for rank in range(P):
+        q = torch.randn(1, 48, H, D, device=device, dtype=dtype)
+        own = slice(rank * Sk, (rank + 1) * Sk)
+        o, lse = TF.attention(q, k_full[own].view(1, Sk, H, D), v_full[own].view(1, Sk, H, D), return_lse=True)
+        o, lse = attend_remote_runs(q, o, lse, k_full, v_full, rank, P, Sk)
+        want = TF.attention(q, k_full.view(1, P * Sk, H, D), v_full.view(1, P * Sk, H, D))
+        assert (o.float() - want.float()).abs().max() < tol, rank
+
+
+def test_context_parallel_remote_runs_cover_every_rank_position():
+    import torch
+
+    _remote_runs_case("cpu", torch.float32, 16, 1e-5)
+
+
+@pytest.mark.gpu
+def test_context_parallel_remote_runs_gpu():
+    import torch
+
+    _remote_runs_case("cuda", torch.bfloat16, 128, 2e-2)
