@@ -109,6 +109,34 @@ class BaseStage(ABC):
     def parallel_models(self) -> None:
         """Called once in every worker rank after the process group is up. Override."""
 
+    # ---- device health ---------------------------------------------------------
+    def configure_device_waits(self) -> None:
+        """Bounds every wait of a kernel on another rank by the parallel configuration's timeout."""
+        if self.device.type != "cuda":
+            return
+        from telefuser_b200.ops import native
+
+        cfg = self.model_runtime_config.parallel_config
+        limit_s = min(float(getattr(cfg, "device_wait_timeout", 30.0)), float(cfg.timeout))
+        native.set_peer_wait_ms(int(max(0.1, min(600.0, limit_s)) * 1000))
+
+    def check_device_waits(self, final: bool = False) -> None:
+        """Surfaces an expired bounded wait of a device kernel (a peer that stopped answering, a lost copy) as
+        `DeviceWaitTimeout`, so that the worker rank reports a failure instead of returning data computed from
+        stale buffers. Inside a loop (`final=False`) nothing blocks: the word posted after the previous step is
+        read and a new copy is enqueued behind the work issued so far. `final=True` synchronises; it belongs
+        where the caller reads the result anyway."""
+        if self.device.type != "cuda":
+            return
+        from telefuser_b200.ops import native
+
+        what = f"stage {self.name!r}"
+        if final:
+            native.finish_status(what)
+        else:
+            native.poll_status(what)
+            native.post_status()
+
     def setup_feature_cache(self, model, cache_config: FeatureCacheConfig, num_inference_steps: int,
                             init_step: int = 0) -> None:  # fmt: skip
         from telefuser_b200.feature_cache import create_feature_cache

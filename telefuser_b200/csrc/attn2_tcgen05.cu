@@ -329,14 +329,8 @@ __global__ void __launch_bounds__(384, 1)
 template <int POLY>
 static int launch_attn2_impl(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
                              int B, cudaStream_t st) {
-  static bool attr_set[16] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  dev &= 15;
-  if (!attr_set[dev]) {
-    cudaFuncSetAttribute(attn2_fwd_kernel<POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM_BYTES);
-    attr_set[dev] = true;
-  }
+  static bool attr_set[TFB_MAX_DEVICES] = {false};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&attn2_fwd_kernel<POLY>), A2_SMEM_BYTES, attr_set)) return rc;
   dim3 grid((p.Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), p.H, B);
   attn2_fwd_kernel<POLY><<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
@@ -344,14 +338,8 @@ static int launch_attn2_impl(const CUtensorMap& tq, const CUtensorMap& tk, const
 
 static int launch_attn2_peer(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
                              int B, cudaStream_t st) {
-  static bool attr_set[16] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  dev &= 15;
-  if (!attr_set[dev]) {
-    cudaFuncSetAttribute(attn2_fwd_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM_BYTES);
-    attr_set[dev] = true;
-  }
+  static bool attr_set[TFB_MAX_DEVICES] = {false};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&attn2_fwd_kernel<0, true>), A2_SMEM_BYTES, attr_set)) return rc;
   dim3 grid((p.Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), p.H, B);
   attn2_fwd_kernel<0, true><<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
@@ -359,14 +347,8 @@ static int launch_attn2_peer(const CUtensorMap& tq, const CUtensorMap& tk, const
 
 static int launch_attn2_sparse(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
                                int B, cudaStream_t st) {
-  static bool attr_set[16] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  dev &= 15;
-  if (!attr_set[dev]) {
-    cudaFuncSetAttribute(attn2_fwd_kernel<0, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM_BYTES);
-    attr_set[dev] = true;
-  }
+  static bool attr_set[TFB_MAX_DEVICES] = {false};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&attn2_fwd_kernel<0, false, true>), A2_SMEM_BYTES, attr_set)) return rc;
   dim3 grid((p.Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), p.H, B);
   attn2_fwd_kernel<0, false, true><<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;

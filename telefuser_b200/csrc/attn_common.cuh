@@ -24,6 +24,8 @@ struct AttnParams {
   const int* blk_idx;
   const int* blk_cnt;
   int max_blocks;
+  int head_dim;  // 64 or 128
+  int causal;    // key j visible to query row i when j <= i + (Skv - Sq)
 };
 
 constexpr int ATT_BM = 128, ATT_BN = 128, ATT_D = 128;
@@ -31,15 +33,18 @@ constexpr int ATT_TILE_BYTES = 128 * 128 * 2;  // 32 KB: two 16 KB boxes of [128
 constexpr int ATT_BOX_BYTES = 16384;
 constexpr float ATT_RESCALE_THRESHOLD = 8.0f;
 
-// 3-D tensor map over [B][S][H*128] bf16 with a [1][128][64] box and 128B swizzle.
-inline int make_qkv_tmap(CUtensorMap* m, const void* base, long ld, long bs, int B, int S, int H) {
-  uint64_t dims[3] = {static_cast<uint64_t>(H) * ATT_D, static_cast<uint64_t>(S), static_cast<uint64_t>(B)};
+// 3-D tensor map over [B][S][H*head_dim] bf16 with a [1][128][64] box and 128B swizzle.
+inline int make_qkv_tmap(CUtensorMap* m, const void* base, long ld, long bs, int B, int S, int H, int head_dim = ATT_D) {
+  uint64_t dims[3] = {static_cast<uint64_t>(H) * head_dim, static_cast<uint64_t>(S), static_cast<uint64_t>(B)};
   uint64_t str[2] = {static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(bs) * 2};
   uint32_t box[3] = {64, 128, 1};
   return make_tmap(m, base, TM_BF16, 3, dims, str, box, TM_SW_128);
 }
 
-// Two-query-tile kernel (attn2_tcgen05.cu).
+// Two query tiles per CTA, each row split over two threads (attn_fwd_split.cu).
+int launch_attn_split(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
+                      cudaStream_t st);
+// Two query tiles per CTA, one thread per row (attn2_tcgen05.cu): head_dim 128, no causal mask.
 int launch_attn2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
                  cudaStream_t st);
 

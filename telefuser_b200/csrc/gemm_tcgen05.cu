@@ -472,15 +472,8 @@ static int launch_gemm(const CUtensorMap& tmA, const void* B, int ldb, GemmParam
   }
   p.m_tiles = DIST ? p.n_seg * p.seg_tiles : (p.M + 127) / 128;
   p.n_tiles = (p.N + BN - 1) / BN;
-  static bool attr_set[16] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  dev &= 15;
-  if (!attr_set[dev]) {
-    cudaFuncSetAttribute(gemm_bf16_kernel<BN, FP8, DIST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         Cfg::SMEM_BYTES);
-    attr_set[dev] = true;
-  }
+  static bool attr_set[TFB_MAX_DEVICES] = {false};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_bf16_kernel<BN, FP8, DIST>), Cfg::SMEM_BYTES, attr_set)) return rc;
   const int tiles = p.m_tiles * p.n_tiles;
   const int copiers = DIST ? p.n_copiers : 0;
   const int compute = tiles < sm_count() - copiers ? tiles : sm_count() - copiers;

@@ -177,21 +177,27 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int align
 }
 
 // One warp per (token, k): claims a slot in its expert's segment and copies the token row.
-// `cursor` (int[E]) is scratch and must be zero on entry.
+// `cursor` (int[E]) is scratch and must be zero on entry. An expert id outside [0, E) claims nothing: its
+// row_map entry becomes -1 (skipped by the combine) and the status word records a bad-shape error.
 __global__ void moe_permute_kernel(const uint4* __restrict__ x, int row_vecs, const int* __restrict__ ids,
-                                   const int* __restrict__ offsets, int* __restrict__ cursor, long TK, int K,
-                                   uint4* __restrict__ xp, int* __restrict__ row_map) {
+                                   const int* __restrict__ offsets, int* __restrict__ cursor, long TK, int K, int E,
+                                   uint4* __restrict__ xp, int* __restrict__ row_map, int* status) {
   const int lane = threadIdx.x & 31;
   const long warp = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
   const long nwarps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
   for (long i = warp; i < TK; i += nwarps) {
-    int pos = 0;
+    int pos = -1;
     if (lane == 0) {
       const int e = ids[i];
-      pos = offsets[e] + atomicAdd(&cursor[e], 1);
+      if (e >= 0 && e < E) {
+        pos = offsets[e] + atomicAdd(&cursor[e], 1);
+      } else if (status) {
+        atomicCAS(status, 0, TFB_ERR_BAD_SHAPE | (70 << 8));
+      }
       row_map[i] = pos;
     }
     pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (pos < 0) continue;
     const uint4* src = x + (i / K) * row_vecs;
     uint4* dst = xp + static_cast<long>(pos) * row_vecs;
     for (int c = lane; c < row_vecs; c += 32) dst[c] = src[c];
@@ -223,7 +229,9 @@ __global__ void moe_combine_kernel(const uint4* __restrict__ y, int row_vecs, co
     }
     for (int k = 0; k < K; ++k) {
       const float wk = w[t * K + k];
-      const uint4 v = y[static_cast<long>(row_map[t * K + k]) * row_vecs + c];
+      const int src_row = row_map[t * K + k];
+      if (src_row < 0) continue;  // an expert id that the permute refused
+      const uint4 v = y[static_cast<long>(src_row) * row_vecs + c];
       const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -290,7 +298,8 @@ extern "C" int tfb_moe_permute(const void* x, int hidden, const int* ids, const 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaMemsetAsync(cursor, 0, sizeof(int) * E, st);
   moe_permute_kernel<<<moe_grid(T * K * 32), 256, 0, st>>>(static_cast<const uint4*>(x), hidden / 8, ids, offsets,
-                                                           cursor, T * K, K, static_cast<uint4*>(x_perm), row_map);
+                                                           cursor, T * K, K, E, static_cast<uint4*>(x_perm), row_map,
+                                                           status_word());
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 
@@ -328,7 +337,8 @@ extern "C" int tfb_moe_permute_static(const void* x, int hidden, const int* ids,
   // The first E cursors must be zero when the kernel starts: cleared here, in stream order.
   if (cudaMemsetAsync(cursor, 0, sizeof(int) * E, st) != cudaSuccess) return TFB_ERR_LAUNCH;
   moe_permute_kernel<<<moe_grid(T * K * 32), 256, 0, st>>>(static_cast<const uint4*>(x), hidden / 8, ids, offsets,
-                                                           cursor, T * K, K, static_cast<uint4*>(x_perm), row_map);
+                                                           cursor, T * K, K, E, static_cast<uint4*>(x_perm), row_map,
+                                                           status_word());
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 

@@ -16,7 +16,6 @@
 namespace tfb {
 
 constexpr int PEER_MAX = 8;
-constexpr unsigned long long PEER_WAIT_NS = 4000000000ull;  // 4 s
 
 struct PeerPtrs {
   void* p[PEER_MAX];
@@ -40,7 +39,8 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 
 // flags[r] is rank r's flag array (int[PEER_MAX] per slot). Thread t < n: tells rank t that this
 // rank reached `epoch`, then waits until rank t told us the same.
-__global__ void peer_barrier_kernel(PeerPtrs flags, int my_rank, int n, int slot, int epoch, int* status) {
+__global__ void peer_barrier_kernel(PeerPtrs flags, int my_rank, int n, int slot, int epoch, int* status,
+                                    unsigned long long wait_ns) {
   const int t = threadIdx.x;
   if (t < n) {
     __threadfence_system();
@@ -48,7 +48,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int my_rank, int n, int slot
     const int* mine = static_cast<const int*>(flags.p[my_rank]) + slot * PEER_MAX + t;
     const unsigned long long t0 = globaltimer_ns();
     while (ld_acquire_sys(mine) < epoch) {
-      if (globaltimer_ns() - t0 > PEER_WAIT_NS) {
+      if (globaltimer_ns() - t0 > wait_ns) {
         if (status) atomicCAS(status, 0, TFB_ERR_TIMEOUT | (60 << 8));
         break;
       }
@@ -176,7 +176,8 @@ extern "C" int tfb_peer_barrier(void* const* flags, int my_rank, int n, int slot
   if (n < 1 || n > PEER_MAX || my_rank < 0 || my_rank >= n || slot < 0 || epoch < 1) return TFB_ERR_BAD_SHAPE;
   PeerPtrs f;
   for (int i = 0; i < PEER_MAX; ++i) f.p[i] = i < n ? flags[i] : nullptr;
-  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, my_rank, n, slot, epoch, status_word());
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, my_rank, n, slot, epoch, status_word(),
+                                                                       peer_wait_ns());
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 

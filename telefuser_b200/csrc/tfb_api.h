@@ -13,8 +13,14 @@ enum { TFB_EPI_NONE = 0, TFB_EPI_GELU = 1 };
 
 int tfb_abi_version();
 int tfb_sm_count();
-// Reads and clears the per-device status word written by bounded waits.
+// Reads and clears the per-device status word written by bounded waits (synchronises the device).
 int tfb_last_status();
+// Non-blocking form for serving loops: tfb_status_post enqueues a copy of the status word into pinned host
+// memory on `stream`; tfb_status_peek returns the last copy that has landed, without touching the device.
+int tfb_status_post(void* stream);
+int tfb_status_peek();
+// Upper bound of every wait on another rank (flag barriers), in milliseconds; 4000 by default.
+int tfb_set_peer_wait_ms(int ms);
 
 // out[M,N] = resid + gate * act(A[M,K] @ B[N,K]^T + bias)   (bf16 in/out, fp32 accumulate)
 //   bias  : bf16 [N] or null
@@ -25,22 +31,23 @@ int tfb_gemm_bf16(const void* A, int lda, const void* B, int ldb, void* out, int
                   const void* bias, int epi, const void* resid, int ldr, const float* gate, int ldg,
                   int rows_per_gate, int force_bn, void* stream);
 
-// Flash attention forward, bf16, head_dim 128 (tcgen05 + TMEM).
-//   q   : [B, Sq, H, 128] with row stride ldq (elements between tokens), batch stride bsq
-//   k,v : [B, Skv, H, 128] likewise
-//   out : [B, Sq, H, 128] bf16, row stride ldo
+// Flash attention forward, bf16, head_dim D = 64 or 128 (tcgen05 + TMEM).
+//   q   : [B, Sq, H, D] with row stride ldq (elements between tokens), batch stride bsq
+//   k,v : [B, Skv, H, D] likewise
+//   out : [B, Sq, H, D] bf16, row stride ldo
 //   lse : optional fp32 [B, H, Sq] (natural log), or null
-//   variant: 0 = default
+//   causal: key j is visible to query row i when j <= i + (Skv - Sq); needs Skv >= Sq
+//   variant: 0 = default; see attn_host.cu for the benchmark selectors
 int tfb_attn_fwd(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v, long ldv,
-                 long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq, int Skv, float scale,
-                 int variant, void* stream);
+                 long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq, int Skv, int D, int causal,
+                 float scale, int variant, void* stream);
 
 // Block-sparse variant: blk_idx int32 [B, H, ceil(Sq/256), max_blocks] lists the 128-key blocks each
 // group of 256 query rows attends to (ascending), blk_cnt int32 [B, H, ceil(Sq/256)] how many are valid;
 // a group with no block gets zero output.
 int tfb_attn_fwd_sparse(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v, long ldv,
                         long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq, int Skv, float scale,
-                        const int* blk_idx, const int* blk_cnt, int max_blocks, void* stream);
+                        const int* blk_idx, const int* blk_cnt, int max_blocks, int variant, void* stream);
 
 // LayerNorm over the last dim (C), optional affine (bf16 w/b), then optional
 // modulation y = y * (1 + scale) + shift with fp32 scale/shift taken from row
@@ -167,10 +174,10 @@ int tfb_slab_reduce(const void* slabs, int P, long rows, int N, long ld, const v
                     const float* gate, long ldg, int rows_per_gate, long gate_row0, void* const* dsts, int n_dst,
                     long ldd, long dst_row0, void* stream);
 // Attention over this rank's head slice whose epilogue stores each output row into the buffer of the
-// rank that owns the token (see attn_tcgen05.cu).
+// rank that owns the token (see attn_host.cu).
 int tfb_attn_fwd_peer(const void* q, long ldq, long bsq, const void* k, long ldk, long bsk, const void* v, long ldv,
                       long bsv, void* const* peer_out, int n_peers, int rows_per_rank, int head_off, long ldo, long bso,
-                      int B, int H, int Sq, int Skv, float scale, void* stream);
+                      int B, int H, int Sq, int Skv, float scale, int variant, void* stream);
 
 // ---- expert parallelism over peer-mapped memory (moe.cu); rank o owns experts [o*E/P, (o+1)*E/P) ----
 // counts_all int32 [P, E] (row s = histogram of rank s) -> dst_base int32 [E] (first row of this rank's
@@ -210,11 +217,6 @@ int tfb_plucker_fold(const float* c2w, const float* ks, const float* extra, int 
                      int w, int c1, int c2, int only_d, void* stream);
 // frames [3, T, H, W] (fp32 or bf16) in [-1, 1] -> uint8 [T, H, W, 3].  W % 4 == 0.
 int tfb_frames_to_u8(const void* frames, int is_bf16, void* out, int T, int H, int W, void* stream);
-
-// Descriptor self-test: one CTA computes D[128,N] = A[128,K] @ B^T with the
-// operand modes used by the attention kernel. mode 0: A,B K-major from smem;
-// mode 1: B MN-major from smem (B given as [K,N]); mode 2: A from TMEM.
-int tfb_umma_probe(const void* A, const void* B, float* D, int N, int K, int mode, void* stream);
 
 #ifdef __cplusplus
 }

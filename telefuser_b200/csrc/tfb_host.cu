@@ -1,6 +1,7 @@
 // Host utilities: tensor maps via the driver entry point, SM count, status word.
 #include "tfb_host.h"
 
+#include <atomic>
 #include <mutex>
 
 #include "tfb_common.cuh"
@@ -58,11 +59,27 @@ int make_tmap(CUtensorMap* out, const void* base, int dtype, int rank, const uin
   return r == CUDA_SUCCESS ? TFB_OK : TFB_ERR_TMAP;
 }
 
-int sm_count() {
-  static int cached[16] = {0};
+int device_slot() {
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 16) dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TFB_MAX_DEVICES) return -1;
+  return dev;
+}
+
+int ensure_dynamic_smem(const void* func, int bytes, bool* done_per_device) {
+  const int dev = device_slot();
+  if (dev < 0) return TFB_ERR_TOO_LARGE;
+  if (!done_per_device[dev]) {
+    if (cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+      return TFB_ERR_LAUNCH;
+    done_per_device[dev] = true;
+  }
+  return TFB_OK;
+}
+
+int sm_count() {
+  static int cached[TFB_MAX_DEVICES] = {0};
+  int dev = device_slot();
+  if (dev < 0) return 148;
   if (cached[dev] == 0) {
     int n = 0;
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
@@ -71,12 +88,30 @@ int sm_count() {
   return cached[dev];
 }
 
-int* status_word() {
-  static int* words[16] = {nullptr};
+static std::atomic<unsigned long long> g_peer_wait_ns{4000000000ull};
+
+unsigned long long peer_wait_ns() { return g_peer_wait_ns.load(std::memory_order_relaxed); }
+
+// Pinned host copy of the status word per device: filled by stream-ordered copies (tfb_status_post) and read
+// without touching the device (tfb_status_peek).
+static volatile int* host_status_copy(int dev) {
+  static int* copies[TFB_MAX_DEVICES] = {nullptr};
   static std::mutex mu;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 16) dev = 0;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!copies[dev]) {
+    int* p = nullptr;
+    if (cudaHostAlloc(&p, sizeof(int), cudaHostAllocDefault) != cudaSuccess) return nullptr;
+    *p = 0;
+    copies[dev] = p;
+  }
+  return copies[dev];
+}
+
+int* status_word() {
+  static int* words[TFB_MAX_DEVICES] = {nullptr};
+  static std::mutex mu;
+  const int dev = device_slot();
+  if (dev < 0) return nullptr;
   std::lock_guard<std::mutex> lk(mu);
   if (!words[dev]) {
     int* p = nullptr;
@@ -97,7 +132,39 @@ extern "C" int tfb_last_status() {
   int v = 0;
   if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return tfb::TFB_ERR_LAUNCH;
   if (v != 0) cudaMemset(p, 0, sizeof(int));
+  const int dev = tfb::device_slot();
+  volatile int* h = dev >= 0 ? tfb::host_status_copy(dev) : nullptr;
+  if (h) *h = 0;
   return v;
+}
+
+// Enqueues a copy of the status word into pinned host memory on `stream` (no synchronisation). The value
+// becomes visible to tfb_status_peek() once the stream has reached this point.
+extern "C" int tfb_status_post(void* stream) {
+  int* p = tfb::status_word();
+  const int dev = tfb::device_slot();
+  if (!p || dev < 0) return tfb::TFB_ERR_LAUNCH;
+  volatile int* h = tfb::host_status_copy(dev);
+  if (!h) return tfb::TFB_ERR_LAUNCH;
+  return cudaMemcpyAsync(const_cast<int*>(h), p, sizeof(int), cudaMemcpyDeviceToHost,
+                         static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? tfb::TFB_OK
+             : tfb::TFB_ERR_LAUNCH;
+}
+
+// Last posted value of the status word of the current device; never blocks, never touches the device.
+extern "C" int tfb_status_peek() {
+  const int dev = tfb::device_slot();
+  if (dev < 0) return 0;
+  volatile int* h = tfb::host_status_copy(dev);
+  return h ? *h : 0;
+}
+
+// Upper bound of every wait on a peer (flag barrier, gathered-segment wait), in milliseconds (100 .. 600000).
+extern "C" int tfb_set_peer_wait_ms(int ms) {
+  if (ms < 100 || ms > 600000) return tfb::TFB_ERR_BAD_SHAPE;
+  tfb::g_peer_wait_ns.store(static_cast<unsigned long long>(ms) * 1000000ull, std::memory_order_relaxed);
+  return tfb::TFB_OK;
 }
 
 extern "C" int tfb_sm_count() { return tfb::sm_count(); }

@@ -160,7 +160,7 @@ def _fuse_linear_weights(linears: list[nn.Linear]):
 
 def _with_fused_scale(W: torch.Tensor, linears: list[nn.Linear]) -> torch.Tensor:
     """fp8 weights carry one scale per output channel (`tfb_scale`); the fused view gets their concatenation."""
-    scales = [getattr(lin.weight, "tfb_scale", None) for lin in linears]
+    scales = [TF.fp8_weight_scale(lin.weight) for lin in linears]
     if all(s is not None for s in scales):
         W.tfb_scale = torch.cat([s.reshape(-1) for s in scales]).contiguous()
     return W

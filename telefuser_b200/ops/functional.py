@@ -54,7 +54,7 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
     [..., 1, N] (one gate row per leading batch entry) or per row [..., N].
     """
     if weight.dtype == torch.float8_e4m3fn:
-        r = linear_fp8(x, weight, getattr(weight, "tfb_scale", None), bias, act, residual, gate)
+        r = linear_fp8(x, weight, fp8_weight_scale(weight), bias, act, residual, gate)
         if out is not None:
             out.copy_(r)
             return out
@@ -102,6 +102,7 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
         gate = g2  # keep alive
     if bias is not None and bias.dtype != torch.bfloat16:
         bias = bias.to(torch.bfloat16)
+    native.same_device(x2, weight, bias, res2)
     code = lib.tfb_gemm_bf16(
         x2.data_ptr(), x2.stride(0), weight.data_ptr(), weight.stride(0), out2.data_ptr(), out2.stride(0),
         M, N, K, native.ptr(bias), 1 if act == "gelu_tanh" else 0,
@@ -130,12 +131,25 @@ def quant_fp8_rowwise(x):
     return q.view(x.shape), s.view(*x.shape[:-1], 1)
 
 
+def fp8_weight_scale(weight):
+    """Per-output-channel scale tagged on an e4m3 weight (`tfb_scale`), on the weight's own device.
+
+    The tag is set when a layer is quantised. `Module.to()` moves the parameter's storage but keeps the Python
+    object, so after a move the tag still points at the old device; it is re-homed here (and cached back) so that
+    the GEMM never receives an address of another device."""
+    s = getattr(weight, "tfb_scale", None)
+    if s is not None and s.device != weight.device:
+        s = s.to(device=weight.device, dtype=torch.float32)
+        weight.tfb_scale = s
+    return s
+
+
 def linear_fp8(x, weight, weight_scale, bias=None, act=None, residual=None, gate=None):
     """W8A8: weight e4m3 [N, K] with per-output-channel scale [N] or [N, 1]; activations are quantised
     per token on the fly; fp32 accumulate; epilogue as `linear`."""
     if weight_scale is None:
         raise ValueError("an fp8 weight needs its per-channel scale (attribute `tfb_scale` or argument)")
-    ws = weight_scale.float().reshape(-1)
+    ws = weight_scale.to(device=x.device, dtype=torch.float32).reshape(-1)
     K, N = x.shape[-1], weight.shape[0]
     if not _native(x) or x.dtype != torch.bfloat16 or K % 16 or N % 8:
         q, s = quant_fp8_rowwise(x)
@@ -165,6 +179,7 @@ def linear_fp8(x, weight, weight_scale, bias=None, act=None, residual=None, gate
     if act not in (None, "gelu_tanh"):
         raise ValueError(f"unknown activation {act}")
     w = weight if weight.stride(-1) == 1 else weight.contiguous()
+    native.same_device(x, w, ws, bias, res2, g2)
     code = native.load().tfb_gemm_fp8(q.data_ptr(), K, w.data_ptr(), w.stride(0), out.data_ptr(), N, M, N, K,
                                       s.data_ptr(), ws.data_ptr(), native.ptr(bias), 1 if act == "gelu_tanh" else 0,
                                       native.ptr(res2), N if res2 is not None else 0, gate_ptr, ldg, rpg,
@@ -298,42 +313,84 @@ def rmsnorm_rope_(x, weight, num_heads, cos=None, sin=None, eps=1e-6, x2=None, w
 # ---------------------------------------------------------------------------
 # Attention
 # ---------------------------------------------------------------------------
-def attention_reference(q, k, v, scale=None, return_lse=False):
-    """q: [B, Sq, H, D], k/v: [B, Skv, H, D] -> [B, Sq, H, D] (fp32 softmax)."""
+def attention_reference(q, k, v, scale=None, return_lse=False, causal=False, mask=None, q_block: int | None = None):
+    """q: [B, Sq, H, D], k/v: [B, Skv, H, D] -> [B, Sq, H, D] (fp32 softmax).
+
+    `causal`: key j is visible to query i when j <= i + (Skv - Sq). `mask`: boolean, broadcastable to
+    [B, H, Sq, Skv], True = visible. `q_block` bounds the score matrix held at once to [B, H, q_block, Skv]."""
     D = q.shape[-1]
+    Sq, Skv = q.shape[1], k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
-    s = (qf @ kf.transpose(-1, -2)) * scale
-    o = (torch.softmax(s, dim=-1) @ vf).permute(0, 2, 1, 3).to(q.dtype)
+    kf, vf = (t.float().permute(0, 2, 1, 3) for t in (k, v))
+    outs, lses = [], []
+    step = q_block or Sq
+    for s0 in range(0, Sq, step):
+        s1 = min(Sq, s0 + step)
+        qf = q[:, s0:s1].float().permute(0, 2, 1, 3)
+        s = (qf @ kf.transpose(-1, -2)) * scale
+        if causal:
+            rows = torch.arange(s0, s1, device=q.device).unsqueeze(1) + (Skv - Sq)
+            s = s.masked_fill(torch.arange(Skv, device=q.device).unsqueeze(0) > rows, float("-inf"))
+        if mask is not None:
+            m = mask if mask.dim() < 2 or mask.shape[-2] == 1 else mask[..., s0:s1, :]
+            s = s.masked_fill(~m, float("-inf"))
+        outs.append((torch.softmax(s, dim=-1) @ vf).permute(0, 2, 1, 3).to(q.dtype))
+        if return_lse:
+            lses.append(torch.logsumexp(s, dim=-1))
+    o = outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
     if return_lse:
-        return o, torch.logsumexp(s, dim=-1)
+        return o, (lses[0] if len(lses) == 1 else torch.cat(lses, dim=-1))
     return o
 
 
-def attention(q, k, v, scale=None, return_lse=False, variant=0):
-    """Dense non-causal attention, layout BSHD. Native kernel: head_dim 128, bf16."""
-    if not _native(q) or q.dtype != torch.bfloat16 or q.shape[-1] != 128:
-        return attention_reference(q, k, v, scale, return_lse)
-    lib = native.load()
-    B, Sq, H, D = q.shape
-    Skv = k.shape[1]
+def _pad_head_dim(t, D_to):
+    return F.pad(t, (0, D_to - t.shape[-1]))
+
+
+def attention(q, k, v, scale=None, return_lse=False, variant=0, causal=False, mask=None):
+    """Attention, layout BSHD: q [B, Sq, H, D], k / v [B, Skv, H, D] -> [B, Sq, H, D].
+
+    CUDA bf16 / fp16 inputs with D <= 128 run on the tcgen05 kernel (head dims other than 64 / 128 are zero-padded
+    to the next of the two, fp16 is computed in bf16); `causal` is handled inside the kernel. A general boolean
+    `mask` (True = visible) and head dims above 128 take the fp32 evaluation in query blocks, so that no
+    [Sq, Skv] score matrix is ever held for the whole sequence. CPU tensors always take the fp32 evaluation."""
+    D = q.shape[-1]
+    if not _native(q) or q.dtype not in (torch.bfloat16, torch.float16) or D > 128 or mask is not None or D % 8 \
+            or (causal and k.shape[1] < q.shape[1]):  # fmt: skip
+        blk = None
+        if q.is_cuda and q.shape[1] * k.shape[1] > (1 << 24):
+            blk = max(128, (1 << 24) // k.shape[1])
+        return attention_reference(q, k, v, scale, return_lse, causal, mask, blk)
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    in_dtype = q.dtype
+    if in_dtype != torch.bfloat16:
+        q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    Dk = 64 if D <= 64 else 128
+    if Dk != D:
+        q, k, v = _pad_head_dim(q, Dk), _pad_head_dim(k, Dk), _pad_head_dim(v, Dk)
+    lib = native.load()
+    B, Sq, H, _ = q.shape
+    Skv = k.shape[1]
 
     def prep(t):
         S = t.shape[1]
-        if t.stride(-1) != 1 or t.stride(2) != D or (B > 1 and t.stride(0) % 8) or t.stride(1) % 8:
+        if t.stride(-1) != 1 or t.stride(2) != Dk or (B > 1 and t.stride(0) % 8) or t.stride(1) % 8:
             t = t.contiguous()
         return t, t.stride(1), (t.stride(0) if B > 1 else S * t.stride(1))
 
     q, ldq, bsq = prep(q)
     k, ldk, bsk = prep(k)
     v, ldv, bsv = prep(v)
-    out = torch.empty(B, Sq, H, D, device=q.device, dtype=torch.bfloat16)
+    out = torch.empty(B, Sq, H, Dk, device=q.device, dtype=torch.bfloat16)
     lse = torch.empty(B, H, Sq, device=q.device, dtype=torch.float32) if return_lse else None
     code = lib.tfb_attn_fwd(
-        q.data_ptr(), ldq, bsq, k.data_ptr(), ldk, bsk, v.data_ptr(), ldv, bsv, out.data_ptr(), H * D, Sq * H * D,
-        native.ptr(lse), B, H, Sq, Skv, scale, variant, native.stream_ptr())  # fmt: skip
+        q.data_ptr(), ldq, bsq, k.data_ptr(), ldk, bsk, v.data_ptr(), ldv, bsv, out.data_ptr(), H * Dk, Sq * H * Dk,
+        native.ptr(lse), B, H, Sq, Skv, Dk, int(bool(causal)), scale, variant, native.stream_ptr())  # fmt: skip
     native.check(code, "tfb_attn_fwd")
+    if Dk != D:
+        out = out[..., :D]
+    if in_dtype != torch.bfloat16:
+        out = out.to(in_dtype)
     return (out, lse) if return_lse else out
 
 

@@ -45,8 +45,13 @@ def _declare(lib) -> None:
     lib.tfb_attn_fwd.restype = c_int
     lib.tfb_attn_fwd.argtypes = [
         c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_long,
-        c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+        c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
     ]  # fmt: skip
+    lib.tfb_status_post.restype = c_int
+    lib.tfb_status_post.argtypes = [c_void_p]
+    lib.tfb_status_peek.restype = c_int
+    lib.tfb_set_peer_wait_ms.restype = c_int
+    lib.tfb_set_peer_wait_ms.argtypes = [c_int]
     lib.tfb_layernorm_modulate.restype = c_int
     lib.tfb_layernorm_modulate.argtypes = [
         c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_float, c_void_p, c_void_p,
@@ -69,8 +74,6 @@ def _declare(lib) -> None:
     ]
     lib.tfb_quant_mxfp8.restype = c_int
     lib.tfb_quant_mxfp8.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_void_p]
-    lib.tfb_umma_probe.restype = c_int
-    lib.tfb_umma_probe.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     table = {
         "tfb_gemm_bf16_grouped": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                   c_void_p, c_int, c_void_p],
@@ -94,7 +97,7 @@ def _declare(lib) -> None:
         "tfb_frames_to_u8": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
         "tfb_attn_fwd_sparse": [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p,
                                 c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
-                                c_void_p],
+                                c_int, c_void_p],
         "tfb_gemm_fp8": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                          c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "tfb_quant_fp8_rowwise": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
@@ -120,7 +123,7 @@ def _declare(lib) -> None:
         "tfb_slab_reduce": [c_void_p, c_int, c_long, c_int, c_long, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int,
                             c_long, c_void_p, c_int, c_long, c_long, c_void_p],
         "tfb_attn_fwd_peer": [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p,
-                              c_int, c_int, c_int, c_long, c_long, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                              c_int, c_int, c_int, c_long, c_long, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     }  # fmt: skip
     for name, args in table.items():
         fn = getattr(lib, name)
@@ -185,5 +188,47 @@ def last_status() -> int:
     return int(load().tfb_last_status())
 
 
+class DeviceWaitTimeout(NativeLibraryError):
+    """A bounded wait inside a kernel (on a peer's flag, an mbarrier, a gathered segment) ran out: the data the
+    following kernels consumed may be stale, so the result of the current call must be discarded."""
+
+
+def post_status() -> None:
+    """Enqueues, on the current stream, a copy of the status word to pinned host memory (no synchronisation)."""
+    check(load().tfb_status_post(stream_ptr()), "tfb_status_post")
+
+
+def poll_status(what: str = "device kernels") -> None:
+    """Raises `DeviceWaitTimeout` when the last posted status word that has reached the host is non-zero.
+    Never blocks: a word posted after work still in flight is seen by a later poll."""
+    code = int(load().tfb_status_peek())
+    if code:
+        last_status()  # clear, so that a restarted worker does not trip over the same record
+        raise DeviceWaitTimeout(f"{what}: a bounded device wait expired (site {code >> 8}, kind {code & 0xff})")
+
+
+def finish_status(what: str = "device kernels") -> None:
+    """Synchronising check for the end of a call whose result is about to be read anyway."""
+    code = last_status()
+    if code:
+        raise DeviceWaitTimeout(f"{what}: a bounded device wait expired (site {code >> 8}, kind {code & 0xff})")
+
+
+def set_peer_wait_ms(ms: int) -> None:
+    check(load().tfb_set_peer_wait_ms(int(ms)), "tfb_set_peer_wait_ms")
+
+
 def ptr(t: torch.Tensor | None) -> int | None:
-    return None if t is None else t.data_ptr()
+    """Device address of an optional operand. A host tensor is refused: a kernel given a host address faults."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise NativeLibraryError(f"a native kernel was handed a {t.device} tensor of shape {tuple(t.shape)}")
+    return t.data_ptr()
+
+
+def same_device(ref: torch.Tensor, *others: torch.Tensor | None) -> None:
+    """Raises when an operand lives on another device than `ref` (a module moved after its tensors were tagged)."""
+    for t in others:
+        if t is not None and t.device != ref.device:
+            raise NativeLibraryError(f"operand on {t.device}, expected {ref.device} (shape {tuple(t.shape)})")

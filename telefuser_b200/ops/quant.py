@@ -26,7 +26,30 @@ def quantize_weight_fp8(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return (w.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), scale
 
 
-class LinearFP8(nn.Module):
+class _ScaleTagged:
+    """Keeps `weight.tfb_scale` (what `ops.functional.linear` reads) pointing at the module's live
+    `weight_scale` buffer. `Module.to()` / `.cuda()` / `.cpu()` replace the buffer object but keep the
+    Parameter object, deep copies and unpickling rebuild the Parameter without its attributes: after each of
+    those the tag is set again, so the GEMM never sees a scale left behind on another device."""
+
+    def _sync(self) -> None:
+        self.weight.tfb_scale = self.weight_scale
+
+    def _load_from_state_dict(self, *a, **kw):
+        super()._load_from_state_dict(*a, **kw)
+        self._sync()
+
+    def _apply(self, fn, recurse=True):
+        r = super()._apply(fn, recurse)
+        self._sync()
+        return r
+
+    def __setstate__(self, state):
+        super().__setstate__(state)
+        self._sync()
+
+
+class LinearFP8(_ScaleTagged, nn.Module):
     def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None) -> None:
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
@@ -35,9 +58,6 @@ class LinearFP8(nn.Module):
         self.register_buffer("weight_scale", torch.ones(out_features, 1, dtype=torch.float32, device=device))
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=torch.bfloat16, device=device)) if bias else None
         self._sync()
-
-    def _sync(self) -> None:
-        self.weight.tfb_scale = self.weight_scale
 
     @classmethod
     def from_linear(cls, lin: nn.Linear) -> "LinearFP8":
@@ -49,17 +69,21 @@ class LinearFP8(nn.Module):
         m._sync()
         return m
 
-    def _load_from_state_dict(self, *a, **kw):
-        super()._load_from_state_dict(*a, **kw)
-        self._sync()
+    def forward(self, x):
+        return TF.linear_fp8(x, self.weight, self.weight_scale, self.bias)
+
+
+class QuantizedLinear(_ScaleTagged, nn.Linear):
+    """What an `nn.Linear` becomes when it is quantised in place: still an `nn.Linear` for model code that reads
+    `.weight` / `.bias` and calls the functional linear, plus the bookkeeping of `_ScaleTagged`."""
 
     def forward(self, x):
         return TF.linear_fp8(x, self.weight, self.weight_scale, self.bias)
 
 
 def quantize_linear_fp8_(lin: nn.Linear) -> nn.Linear:
-    """In place: the module keeps its class (model code reads `.weight` / `.bias` directly) but its weight
-    becomes e4m3 and carries `tfb_scale`; a `weight_scale` buffer is registered for checkpoints."""
+    """In place: the module stays an `nn.Linear` (its class becomes `QuantizedLinear`), its weight becomes e4m3
+    and carries `tfb_scale`; a `weight_scale` buffer is registered for checkpoints."""
     if lin.weight.dtype == torch.float8_e4m3fn:
         return lin
     q, s = quantize_weight_fp8(lin.weight.data)
@@ -68,6 +92,8 @@ def quantize_linear_fp8_(lin: nn.Linear) -> nn.Linear:
         lin.weight_scale = s
     else:
         lin.register_buffer("weight_scale", s)
+    if type(lin) is nn.Linear:
+        lin.__class__ = QuantizedLinear
     lin.weight.tfb_scale = lin.weight_scale
     return lin
 

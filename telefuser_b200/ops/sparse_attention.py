@@ -90,7 +90,7 @@ def block_sparse_attention(q, k, v, mask=None, lists=None, scale=None):
     idx, cnt = idx.contiguous(), cnt.contiguous()
     code = native.load().tfb_attn_fwd_sparse(q.data_ptr(), ldq, bsq, k.data_ptr(), ldk, bsk, v.data_ptr(), ldv, bsv,
                                              out.data_ptr(), H * D, Sq * H * D, None, B, H, Sq, Skv, scale,
-                                             idx.data_ptr(), cnt.data_ptr(), idx.shape[-1], native.stream_ptr())  # fmt: skip
+                                             idx.data_ptr(), cnt.data_ptr(), idx.shape[-1], 0, native.stream_ptr())  # fmt: skip
     native.check(code, "tfb_attn_fwd_sparse")
     return out
 

@@ -69,24 +69,34 @@ class PeerWorkspace:
         self.flag_off = self.nbytes - FLAG_BYTES
         self._flag_table = (ctypes.c_void_p * self.world)(*[p + self.flag_off for p in self.ptrs])
         self._epoch = 0
-        self._regions: dict[str, tuple[int, tuple, torch.dtype]] = {}
+        self._regions: dict[str, tuple[int, tuple, torch.dtype, int]] = {}  # offset, shape, dtype, reserved bytes
         self._cursor = 0
         dist.barrier(group=group)  # every mapping exists before anyone stores
 
     # ---- regions ------------------------------------------------------------------
     def region(self, name: str, shape, dtype=torch.bfloat16) -> torch.Tensor:
-        """This rank's view of a named region (allocated on first use; same order on every rank)."""
+        """This rank's view of a named region (carved on first use; same call order on every rank).
+
+        A name that recurs with another shape or dtype (a request at another resolution, frame count or batch)
+        keeps its place when the new extent fits the bytes reserved for it. Otherwise the whole table is carved
+        anew from offset 0: every earlier view of this workspace is then invalid, which is safe because the
+        callers' barriers order each reuse and a shape only changes between requests."""
         shape = tuple(int(s) for s in shape)
         n = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
         hit = self._regions.get(name)
         if hit is not None and (hit[1] != shape or hit[2] != dtype):
-            raise ValueError(f"region {name!r} exists with another shape")
+            if n <= hit[3]:
+                hit = self._regions[name] = (hit[0], shape, dtype, hit[3])
+            else:
+                self._regions.clear()
+                self._cursor = 0
+                hit = None
         if hit is None:
             off = self._cursor
             if off + n > self.flag_off:
                 raise MemoryError(f"peer workspace of {self.flag_off} bytes cannot hold region {name!r} ({n} bytes)")
             self._cursor = -(-(off + n) // 256) * 256
-            hit = self._regions[name] = (off, shape, dtype)
+            hit = self._regions[name] = (off, shape, dtype, self._cursor - off)
         off = hit[0]
         return self.local[off : off + n].view(dtype).view(shape)
 
@@ -116,15 +126,32 @@ class PeerWorkspace:
 _WORKSPACES: dict = {}
 
 
+_RESERVED: dict = {}
+
+
+def reserve_workspace(group, nbytes: int, tag: str = "") -> None:
+    """Declares the largest request a session will make (e.g. the full rolling window of a streaming session), so
+    that the workspace is created once at that size instead of being re-created as requests grow."""
+    key = (id(group), tag)
+    _RESERVED[key] = max(int(nbytes), _RESERVED.get(key, 0))
+
+
 def get_workspace(group, nbytes: int, tag: str = "") -> PeerWorkspace:
-    """One workspace per (process group, tag), grown by re-creation when a larger one is asked for. Callers whose
-    regions must not compete for space (attention slabs, tensor-parallel slabs, the output gather) use own tags."""
+    """One workspace per (process group, tag). It is created at the larger of the request, the reserved size and
+    `TFB_PEER_WORKSPACE_MB`; a later, larger request re-creates it with a quarter of headroom (a collective
+    operation: free, allocate, exchange handles), smaller or differently shaped requests re-carve it in place.
+    Callers whose regions must not compete for space (attention slabs, tensor-parallel slabs, the output gather)
+    use own tags."""
+    import os
+
     key = (id(group), tag)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.flag_off < nbytes:
+        want = max(int(nbytes), _RESERVED.get(key, 0), int(os.environ.get("TFB_PEER_WORKSPACE_MB", "0")) << 20)
         if ws is not None:
             ws.close()
-        ws = _WORKSPACES[key] = PeerWorkspace(group, nbytes)
+            want = max(want, int(nbytes * 1.25))
+        ws = _WORKSPACES[key] = PeerWorkspace(group, want)
     return ws
 
 
@@ -167,7 +194,7 @@ def ulysses_attention_fused(q, k, v, ws: PeerWorkspace, scale: float | None = No
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     code = lib.tfb_attn_fwd_peer(sq.data_ptr(), Hp * D, St * Hp * D, sk.data_ptr(), Hp * D, St * Hp * D, sv.data_ptr(),
                                  Hp * D, St * Hp * D, ws.peer_table("ulysses_o"), P, S, r * Hp, H * D, S * H * D, B, Hp,
-                                 St, St, scale, st)  # fmt: skip
+                                 St, St, scale, 0, st)  # fmt: skip
     native.check(code, "tfb_attn_fwd_peer")
     ws.barrier()  # every peer has stored its heads of my tokens; slabs may be overwritten again
     return out

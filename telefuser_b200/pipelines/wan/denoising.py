@@ -63,6 +63,7 @@ class WanDenoisingStage(BaseStage):
     def parallel_models(self) -> None:
         cfg = self.model_runtime_config.parallel_config
         self.mesh = pmesh.create_device_mesh_from_config(cfg)
+        self.configure_device_waits()
         self.dit.device_mesh = self.mesh
         self.dit.set_attention_config(self.model_runtime_config.attention_config)
         if cfg.sp_degree > 1:
@@ -146,6 +147,8 @@ class WanDenoisingStage(BaseStage):
                 latents = self.guided_step(latents, cond, uncond, cfg_scale, nxt - sigma)
             if self.step_callback is not None:
                 self.step_callback(i, latents)
+            self.check_device_waits()  # non-blocking: sees the word posted one step ago
+        self.check_device_waits(final=True)
         return latents
 
 

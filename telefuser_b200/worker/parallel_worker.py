@@ -93,6 +93,8 @@ def _worker_loop(rank: int, stage, world_size: int, port: int, device_type: str,
 
         profiler.mark_as_worker_process()
         stage.device = device
+        if hasattr(stage, "configure_device_waits"):
+            stage.configure_device_waits()
         if world_size > 1:
             stage.parallel_models()
         queue_out.put(("ready", rank, None))
@@ -103,6 +105,8 @@ def _worker_loop(rank: int, stage, world_size: int, port: int, device_type: str,
             args, kwargs = to_device(args, device), to_device(kwargs, device)
             with torch.no_grad():
                 result = getattr(stage, name)(*args, **kwargs)
+            if hasattr(stage, "check_device_waits"):
+                stage.check_device_waits(final=True)  # an expired wait on a peer fails the call on this rank
             if empty_cache_each_call and device.type == "cuda":
                 torch.cuda.empty_cache()
             # every rank acknowledges every call, so a failure on any rank is seen by the parent

@@ -88,3 +88,52 @@ def test_fp8_wan_block_on_gpu_tracks_bf16():
     assert model.enable_quant() == 20
     out = model(latents.cuda().bfloat16(), t, ctx.cuda().bfloat16()).float()
     assert ((out - ref).norm() / ref.norm()).item() < 0.1
+
+
+def test_scale_follows_the_module_across_moves_copies_and_pickling():
+    import copy
+    import io
+
+    def round_trip(m):
+        buf = io.BytesIO()
+        torch.save(m, buf)
+        buf.seek(0)
+        return torch.load(buf, weights_only=False)
+
+    torch.manual_seed(0)
+    x = torch.randn(5, 64)
+    for make in (lambda: quantize_linear_fp8_(nn.Linear(64, 48)), lambda: LinearFP8.from_linear(nn.Linear(64, 48))):
+        lin = make()
+        want = TF.linear(x, lin.weight, lin.bias)
+        old = lin.weight_scale
+        lin._apply(lambda t: t.clone())  # what .to() / .cuda() do: new buffer object, same Parameter object
+        assert lin.weight_scale is not old and lin.weight.tfb_scale is lin.weight_scale
+        assert TF.fp8_weight_scale(lin.weight) is lin.weight_scale
+        for other in (copy.deepcopy(lin), round_trip(lin)):
+            assert other.weight.tfb_scale is other.weight_scale
+            assert torch.equal(TF.linear(x, other.weight, other.bias), want)
+    model = make_tiny_model()
+    model.enable_quant()
+    model._apply(lambda t: t.clone())
+    blk = model.blocks[0]
+    W, _ = blk.self_attn.fused_qkv()
+    live = torch.cat([m.weight_scale.reshape(-1) for m in (blk.self_attn.q, blk.self_attn.k, blk.self_attn.v)])
+    assert torch.equal(W.tfb_scale, live)
+    assert all(m.weight.tfb_scale is m.weight_scale for m in (blk.self_attn.q, blk.ffn[0]))
+
+
+@pytest.mark.gpu
+def test_model_quantised_on_the_host_then_moved_runs_on_the_device():
+    torch.manual_seed(0)
+    lin = nn.Linear(256, 128).bfloat16()
+    x = torch.randn(64, 256).bfloat16()
+    ref = lin(x).float()
+    quantize_linear_fp8_(lin)
+    lin.cuda()
+    assert lin.weight.tfb_scale.is_cuda and lin.weight.tfb_scale is lin.weight_scale
+    got = TF.linear(x.cuda(), lin.weight, lin.bias).float().cpu()
+    assert ((got - ref).norm() / ref.norm()).item() < 0.06
+    from telefuser_b200.ops import native
+
+    with pytest.raises(native.NativeLibraryError):
+        TF.linear_fp8(x.cuda(), lin.weight, lin.weight_scale, lin.bias.cpu())

@@ -79,3 +79,53 @@ def test_static_permute_rejects_more_experts_than_its_scratch_holds(capfd):
     assert code == 5  # TFB_ERR_TOO_LARGE: nothing was launched
     assert "static scratch limit of 1024" in capfd.readouterr().err
     torch.cuda.synchronize()
+
+
+def test_static_permute_at_its_limit_and_with_stale_cursors_beyond_e():
+    """E = 1024 exactly (the whole scratch array), then E = 96 right after a call with E = 512: the cursors of
+    experts 96..511 keep the counts of the earlier call, which no in-range id of the later call can touch."""
+    dev = torch.device("cuda:0")
+    static, _, plan = _symbols()
+    stream = torch.cuda.current_stream().cuda_stream
+    hidden, K = 64, 2
+    for seed, (E, T) in enumerate(((1024, 1500), (512, 900), (96, 333))):
+        x, ids, counts = _case(10 + seed, T, K, E, hidden, dev)
+        rows = -(-(T * K + E * 127) // 128) * 128
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        tiles = torch.empty(rows // 128, dtype=torch.int32, device=dev)
+        assert plan(counts.data_ptr(), E, 128, offsets.data_ptr(), tiles.data_ptr(), rows // 128, stream) == 0
+        xp = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=dev)
+        row_map = torch.empty(T * K, dtype=torch.int32, device=dev)
+        assert static(x.data_ptr(), hidden, ids.data_ptr(), offsets.data_ptr(), E, T, K, xp.data_ptr(),
+                      row_map.data_ptr(), stream) == 0  # fmt: skip
+        torch.cuda.synchronize()
+        assert torch.equal(xp[row_map.long()], x.repeat_interleave(K, dim=0)), E
+        flat = ids.reshape(-1).long()
+        assert ((row_map >= offsets[flat]) & (row_map < offsets[flat] + counts[flat])).all(), E
+        assert row_map.unique().numel() == T * K, E
+
+
+def test_an_expert_id_outside_the_range_is_skipped_and_reported():
+    dev = torch.device("cuda:0")
+    static, _, plan = _symbols()
+    stream = torch.cuda.current_stream().cuda_stream
+    E, T, K, hidden = 8, 16, 1, 64
+    x, ids, _ = _case(3, T, K, E, hidden, dev)
+    ids[5, 0] = 300  # inside the static array but not an expert of this call
+    ids[9, 0] = -2
+    valid = (ids.reshape(-1) >= 0) & (ids.reshape(-1) < E)
+    counts = torch.bincount(ids.reshape(-1)[valid].long(), minlength=E).to(torch.int32)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    tiles = torch.empty(16, dtype=torch.int32, device=dev)
+    assert plan(counts.data_ptr(), E, 128, offsets.data_ptr(), tiles.data_ptr(), 16, stream) == 0
+    xp = torch.zeros(16 * 128, hidden, dtype=torch.bfloat16, device=dev)
+    row_map = torch.empty(T, dtype=torch.int32, device=dev)
+    native.last_status()
+    assert static(x.data_ptr(), hidden, ids.data_ptr(), offsets.data_ptr(), E, T, K, xp.data_ptr(), row_map.data_ptr(),
+                  stream) == 0  # fmt: skip
+    torch.cuda.synchronize()
+    status = native.last_status()
+    assert status & 0xFF == 2 and status >> 8 == 70, status  # TFB_ERR_BAD_SHAPE at the permute's check
+    assert row_map[5].item() == -1 and row_map[9].item() == -1
+    keep = valid.nonzero().reshape(-1)
+    assert torch.equal(xp[row_map[keep].long()], x[keep])
