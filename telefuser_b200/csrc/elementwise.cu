@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(256) cfg_euler_kernel(const float* __restrict_
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ldx,
                                                           uint8_t* __restrict__ q, uint8_t* __restrict__ sf, long rows,
-                                                          int C) {
+                                                          int C, int tiled) {
   const int vec_per_row = C >> 3;
   const long total = rows * vec_per_row;
   const long total_pad = (total + 31) & ~31L;  // whole warps stay in the loop for the shuffles
@@ -320,7 +320,16 @@ __global__ void __launch_bounds__(256) quant_mxfp8_kernel(const __nv_bfloat16* _
     }
     if (!valid) continue;
     reinterpret_cast<uint2*>(q + row * static_cast<long>(C))[vi] = make_uint2(packed[0], packed[1]);
-    if ((vi & 3) == 0) sf[row * (C >> 5) + (vi >> 2)] = static_cast<uint8_t>(ebits);
+    if ((vi & 3) == 0) {
+      const int blk = vi >> 2;  // index of the 32-element block in the row
+      if (tiled) {
+        // Order read by the block-scaled MMA (gemm_mxfp8.cu): 512-byte tiles of 128 rows x 4 blocks.
+        const long tile = (row >> 7) * (C >> 7) + (blk >> 2);
+        sf[tile * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (blk & 3)] = static_cast<uint8_t>(ebits);
+      } else {
+        sf[row * (C >> 5) + blk] = static_cast<uint8_t>(ebits);
+      }
+    }
   }
 }
 
@@ -414,14 +423,16 @@ extern "C" int tfb_cfg_euler_step(const float* x, const void* cond, const void* 
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 
-extern "C" int tfb_quant_mxfp8(const void* x, long ldx, void* q, void* sf, int rows, int C, void* stream) {
+// tiled = 0: sf is [rows, C/32]; tiled = 1: sf is [ceil(rows/128)][C/128][512] in the order the block-scaled
+// MMA reads (C a multiple of 128; bytes of rows past `rows` are left as they are).
+extern "C" int tfb_quant_mxfp8(const void* x, long ldx, void* q, void* sf, int rows, int C, int tiled, void* stream) {
   if (rows <= 0) return TFB_OK;
-  if (C % 32 || ldx % 8) return TFB_ERR_BAD_SHAPE;
+  if (C % 32 || ldx % 8 || (tiled && C % 128)) return TFB_ERR_BAD_SHAPE;
   const long nvec = static_cast<long>(rows) * (C / 8);
   // Blocks must cover whole groups of 4 lanes: total is a multiple of 4 and
   // the grid-stride step (gridDim*256) keeps lane groups aligned.
   quant_mxfp8_kernel<<<grid_for(nvec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), rows, C);
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), rows, C, tiled);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 

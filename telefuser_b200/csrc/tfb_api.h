@@ -78,8 +78,17 @@ int tfb_cfg_euler_step(const float* x, const void* cond, const void* uncond, int
                        float dsigma, float* x_out, float* v_out, long n, void* stream);
 
 // Per-row MXFP8 quantisation: e4m3 payload + UE8M0 scale per 32 elements.
-//   x: bf16 [rows, C];  q: uint8 [rows, C];  sf: uint8 [rows, C/32] (row-major)
-int tfb_quant_mxfp8(const void* x, long ldx, void* q, void* sf, int rows, int C, void* stream);
+//   x: bf16 [rows, C];  q: uint8 [rows, C];  sf: uint8 [rows, C/32] (row-major, tiled = 0) or the tiled order
+//   of tfb_gemm_mxfp8 (tiled = 1, C a multiple of 128, buffer of ceil(rows/128) * (C/128) * 512 bytes)
+int tfb_quant_mxfp8(const void* x, long ldx, void* q, void* sf, int rows, int C, int tiled, void* stream);
+
+// Block-scaled MXFP8 GEMM: out[M,N] = resid + gate * act(deq(A) @ deq(B)^T + bias), A [M,K] / B [N,K] e4m3 bytes
+// (row strides lda / ldb in bytes, K a multiple of 128), sfa / sfb their UE8M0 scales per 32 K-elements in 512-byte
+// tiles: rows [128*i, +128) x k-blocks [4*j, +4) at ((i * K/128) + j) * 512, row r / block b at
+// (r%32)*16 + (r/32)*4 + b. The scale buffers cover whole 128-row tiles. Epilogue arguments as tfb_gemm_bf16.
+int tfb_gemm_mxfp8(const void* A, int lda, const void* sfa, const void* B, int ldb, const void* sfb, void* out,
+                   int ldo, int M, int N, int K, const void* bias, int epi, const void* resid, int ldr,
+                   const float* gate, int ldg, int rows_per_gate, void* stream);
 // NF4 codes (two per byte, first in the high nibble) with one fp32 absmax per `block` values -> bf16; numel % 16 == 0.
 int tfb_nf4_dequant(const void* packed, const float* absmax, void* out, long numel, int block, void* stream);
 

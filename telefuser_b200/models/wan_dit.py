@@ -160,6 +160,17 @@ def _fuse_linear_weights(linears: list[nn.Linear]):
 
 def _with_fused_scale(W: torch.Tensor, linears: list[nn.Linear]) -> torch.Tensor:
     """fp8 weights carry one scale per output channel (`tfb_scale`); the fused view gets their concatenation."""
+    mx = [getattr(lin.weight, "tfb_mx_sf", None) for lin in linears]
+    if all(s is not None for s in mx):
+        # block-scaled weights: the scale tiles cover 128 output rows each, so they concatenate tile-wise when
+        # every part is a whole number of tiles, and through the row-major form otherwise
+        mx = [s.to(W.device) for s in mx]
+        if all(lin.weight.shape[0] % 128 == 0 for lin in linears):
+            W.tfb_mx_sf = torch.cat(mx, dim=0).contiguous()
+        else:
+            rows = [TF.mx_untile_scales(s, lin.weight.shape[0]) for s, lin in zip(mx, linears)]
+            W.tfb_mx_sf = TF.mx_tile_scales(torch.cat(rows, dim=0))
+        return W
     scales = [TF.fp8_weight_scale(lin.weight) for lin in linears]
     if all(s is not None for s in scales):
         W.tfb_scale = torch.cat([s.reshape(-1) for s in scales]).contiguous()
@@ -494,13 +505,17 @@ class WanModel(BaseModel):
         return self.unpatchify(x, grid)
 
     def enable_quant(self, quant=None) -> int:
-        """W8A8 FP8 for the block projections (attention q/k/v/o and both FFN layers); embeddings, the
+        """W8A8 for the block projections (attention q/k/v/o and both FFN layers): block-scaled MXFP8 when the
+        configuration says `QuantType.MXFP8` (or "mxfp8"), per-token x per-channel FP8 otherwise; embeddings, the
         head and all norms / modulation tables stay in bf16 / fp32. Returns the number of layers converted."""
+        from telefuser_b200.core.config import QuantType
         from telefuser_b200.ops.quant import quantize_model_fp8_
 
         skip = tuple(getattr(quant, "skip_modules", None) or ("head", "time_embedding", "time_projection",
                                                               "patch_embedding", "text_embedding", "img_emb"))  # fmt: skip
-        return quantize_model_fp8_(self, ("blocks.*",), skip)
+        kind = getattr(quant, "quant_type", quant)
+        mx = kind is QuantType.MXFP8 or (isinstance(kind, str) and kind.lower() == "mxfp8")
+        return quantize_model_fp8_(self, ("blocks.*",), skip, block_scaled=mx)
 
     # ---- parallel plans --------------------------------------------------------
     def get_fsdp_module_names(self) -> list[str]:

@@ -54,7 +54,13 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
     [..., 1, N] (one gate row per leading batch entry) or per row [..., N].
     """
     if weight.dtype == torch.float8_e4m3fn:
-        r = linear_fp8(x, weight, fp8_weight_scale(weight), bias, act, residual, gate)
+        mx_sf = getattr(weight, "tfb_mx_sf", None)
+        if mx_sf is not None:
+            if mx_sf.device != weight.device:  # the module was moved after quantisation
+                mx_sf = weight.tfb_mx_sf = mx_sf.to(weight.device)
+            r = linear_mxfp8(x, weight, mx_sf, bias, act, residual, gate)
+        else:
+            r = linear_fp8(x, weight, fp8_weight_scale(weight), bias, act, residual, gate)
         if out is not None:
             out.copy_(r)
             return out
@@ -537,18 +543,93 @@ def dequant_mxfp8(q, sf):
     return (v * torch.exp2(sf.float() - 127)[..., None]).reshape(-1, C)
 
 
-def quant_mxfp8(x):
-    if not _native(x) or x.dtype != torch.bfloat16:
-        return quant_mxfp8_reference(x)
-    lib = native.load()
+def mx_tile_scales(sf: torch.Tensor) -> torch.Tensor:
+    """Row-major UE8M0 scales [rows, C/32] (C a multiple of 128) -> the tiled order of the block-scaled GEMM:
+    uint8 [ceil(rows/128), C/128, 512], row r / block b of a tile at (r%32)*16 + (r/32)*4 + b. Rows of padding
+    get the exponent 0 (scale 2^-127)."""
+    rows, nb = sf.shape
+    if nb % 4:
+        raise ValueError("the tiled scale layout needs a multiple of 128 columns")
+    mt = -(-rows // 128)
+    full = torch.zeros(mt * 128, nb, dtype=torch.uint8, device=sf.device)
+    full[:rows] = sf
+    # [mt, r/32 (4), r%32 (32), kb, b (4)] -> [mt, kb, r%32, r/32, b]
+    return full.view(mt, 4, 32, nb // 4, 4).permute(0, 3, 2, 1, 4).contiguous().view(mt, nb // 4, 512)
+
+
+def mx_untile_scales(tiled: torch.Tensor, rows: int) -> torch.Tensor:
+    mt, kb, _ = tiled.shape
+    return tiled.view(mt, kb, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(mt * 128, kb * 4)[:rows].contiguous()
+
+
+def quant_mxfp8(x, tiled: bool = False):
+    """x [..., C] -> (e4m3 payload uint8 [rows, C], UE8M0 scales). `tiled=False`: scales [rows, C/32];
+    `tiled=True`: the order read by the block-scaled GEMM (`mx_tile_scales`), written directly by the kernel."""
     C = x.shape[-1]
-    x2 = x.reshape(-1, C).contiguous()
-    q = torch.empty(x2.shape, device=x.device, dtype=torch.uint8)
-    sf = torch.empty(x2.shape[0], C // 32, device=x.device, dtype=torch.uint8)
-    code = lib.tfb_quant_mxfp8(x2.data_ptr(), x2.stride(0), q.data_ptr(), sf.data_ptr(), x2.shape[0], C,
+    if not _native(x) or x.dtype != torch.bfloat16:
+        q, sf = quant_mxfp8_reference(x)
+        return (q, mx_tile_scales(sf)) if tiled else (q, sf)
+    lib = native.load()
+    x2 = x.reshape(-1, C)
+    if x2.stride(-1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    q = torch.empty(rows, C, device=x.device, dtype=torch.uint8)
+    if tiled:
+        sf = torch.zeros(-(-rows // 128), C // 128, 512, device=x.device, dtype=torch.uint8)
+    else:
+        sf = torch.empty(rows, C // 32, device=x.device, dtype=torch.uint8)
+    code = lib.tfb_quant_mxfp8(x2.data_ptr(), x2.stride(0), q.data_ptr(), sf.data_ptr(), rows, C, int(tiled),
                                native.stream_ptr())  # fmt: skip
     native.check(code, "tfb_quant_mxfp8")
     return q, sf
+
+
+def quantize_weight_mxfp8(w: torch.Tensor):
+    """[N, K] (K a multiple of 128) -> (e4m3 [N, K], tiled UE8M0 scales uint8 [ceil(N/128), K/128, 512])."""
+    q, sf = quant_mxfp8_reference(w) if not (w.is_cuda and w.dtype == torch.bfloat16) else quant_mxfp8(w)
+    return q.view(torch.float8_e4m3fn).reshape(w.shape), mx_tile_scales(sf.reshape(w.shape[0], -1))
+
+
+def linear_mxfp8(x, weight, weight_sf, bias=None, act=None, residual=None, gate=None):
+    """Block-scaled W8A8: weight e4m3 [N, K] with tiled UE8M0 scales per 32 K-elements (`quantize_weight_mxfp8`);
+    activations are quantised to the same format on the fly (one scale per token and 32 channels) and both scalings
+    happen inside the tensor core. Epilogue as `linear`."""
+    K, N = x.shape[-1], weight.shape[0]
+    if act not in (None, "gelu_tanh"):
+        raise ValueError(f"unknown activation {act}")
+    if not _native(x) or x.dtype != torch.bfloat16 or K % 128 or N % 8:
+        xq, xsf = quant_mxfp8_reference(x)
+        wsf = mx_untile_scales(weight_sf, N)
+        y = dequant_mxfp8(xq, xsf) @ dequant_mxfp8(weight.view(torch.uint8).reshape(N, K), wsf).t()
+        y = y.reshape(*x.shape[:-1], N)
+        if bias is not None:
+            y = y + bias.float()
+        if act == "gelu_tanh":
+            y = F.gelu(y, approximate="tanh")
+        if gate is not None:
+            y = y * gate.float()
+        if residual is not None:
+            y = y + residual.float()
+        return y.to(x.dtype)
+    q, sf = quant_mxfp8(x.reshape(-1, K), tiled=True)
+    M = q.shape[0]
+    out = torch.empty(*x.shape[:-1], N, device=x.device, dtype=torch.bfloat16)
+    res2 = None if residual is None else residual.reshape(-1, N).contiguous()
+    gate_ptr, ldg, rpg, g2 = None, 0, 1, None
+    if gate is not None:
+        g2 = gate.float().reshape(-1, N).contiguous()
+        gate_ptr, ldg, rpg = g2.data_ptr(), N, M // g2.shape[0]
+    if bias is not None and bias.dtype != torch.bfloat16:
+        bias = bias.to(torch.bfloat16)
+    w = weight if weight.stride(-1) == 1 else weight.contiguous()
+    native.same_device(x, w, weight_sf, bias, res2, g2)
+    code = native.load().tfb_gemm_mxfp8(q.data_ptr(), K, sf.data_ptr(), w.data_ptr(), w.stride(0), weight_sf.data_ptr(),
+                                        out.data_ptr(), N, M, N, K, native.ptr(bias), 1 if act == "gelu_tanh" else 0,
+                                        native.ptr(res2), N if res2 is not None else 0, gate_ptr, ldg, rpg,
+                                        native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_gemm_mxfp8")
+    return out
 
 
 # ---------------------------------------------------------------------------

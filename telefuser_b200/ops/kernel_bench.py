@@ -70,11 +70,16 @@ def report(name: str, ms: float, flops: float = 0.0, bytes_: float = 0.0, **cfg)
     print(json.dumps(out), flush=True)
 
 
-def bench_attn(t: Timer, seq: int, heads: int, compare: bool, variant: int = 0) -> None:
-    q, k, v = (torch.randn(1, seq, heads, 128, device="cuda").bfloat16() for _ in range(3))
-    flops = 4.0 * seq * seq * heads * 128
-    report("attn_fwd_tcgen05", t(lambda: TF.attention(q, k, v, variant=variant)), flops, seq=seq, heads=heads,
-           variant=variant)  # fmt: skip
+def bench_attn(t: Timer, seq: int, heads: int, compare: bool, variant: int = 0, head_dim: int = 128,
+               causal: bool = False) -> None:  # fmt: skip
+    q, k, v = (torch.randn(1, seq, heads, head_dim, device="cuda").bfloat16() for _ in range(3))
+    flops = 4.0 * seq * seq * heads * head_dim * (0.5 if causal else 1.0)
+    variants = [variant] if variant >= 0 else [30, 31, 32, 20, 21, 22]  # -1: every kernel form and exp2 share
+    for vr in variants:
+        report("attn_fwd_tcgen05", t(lambda: TF.attention(q, k, v, variant=vr, causal=causal)), flops, seq=seq,
+               heads=heads, head_dim=head_dim, causal=causal, variant=vr)  # fmt: skip
+    if head_dim != 128 or causal:
+        return
     if variant == 0 and seq >= 8192:
         from telefuser_b200.ops import sparse_attention as SA
 
@@ -195,7 +200,9 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=75600)
     ap.add_argument("--dim", type=int, default=5120)
     ap.add_argument("--tokens", type=int, default=16384)
-    ap.add_argument("--variant", type=int, default=0, help="attention kernel variant (0 = default)")
+    ap.add_argument("--variant", type=int, default=0, help="attention kernel variant (0 = default, -1 = all forms)")
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--causal", action="store_true")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--once", action="store_true", help="one launch per case, no flush, no comparison")
@@ -206,7 +213,7 @@ def main() -> None:
     t = Timer(a.warmup, a.iters, a.once)
     cmp_ = not (a.once or a.no_compare)
     if a.what in ("attn", "all"):
-        bench_attn(t, a.seq, a.heads, cmp_, a.variant)
+        bench_attn(t, a.seq, a.heads, cmp_, a.variant, a.head_dim, a.causal)
     if a.what in ("gemm", "all"):
         bench_gemm(t, a.m, a.n, a.k, cmp_)
     if a.what in ("elementwise", "all"):

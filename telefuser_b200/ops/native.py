@@ -73,7 +73,7 @@ def _declare(lib) -> None:
         c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p, c_long, c_void_p,
     ]
     lib.tfb_quant_mxfp8.restype = c_int
-    lib.tfb_quant_mxfp8.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.tfb_quant_mxfp8.argtypes = [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     table = {
         "tfb_gemm_bf16_grouped": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                   c_void_p, c_int, c_void_p],
@@ -100,6 +100,8 @@ def _declare(lib) -> None:
                                 c_int, c_void_p],
         "tfb_gemm_fp8": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                          c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+        "tfb_gemm_mxfp8": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                           c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "tfb_quant_fp8_rowwise": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "tfb_nf4_dequant": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "tfb_rmsnorm_modulate": [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_float, c_void_p, c_void_p,

@@ -33,7 +33,10 @@ class _ScaleTagged:
     those the tag is set again, so the GEMM never sees a scale left behind on another device."""
 
     def _sync(self) -> None:
-        self.weight.tfb_scale = self.weight_scale
+        if "weight_scale" in self._buffers:
+            self.weight.tfb_scale = self.weight_scale
+        if "weight_scale_mx" in self._buffers:
+            self.weight.tfb_mx_sf = self.weight_scale_mx
 
     def _load_from_state_dict(self, *a, **kw):
         super()._load_from_state_dict(*a, **kw)
@@ -98,10 +101,37 @@ def quantize_linear_fp8_(lin: nn.Linear) -> nn.Linear:
     return lin
 
 
+class QuantizedLinearMX(_ScaleTagged, nn.Linear):
+    """An `nn.Linear` quantised in place to block-scaled MXFP8: e4m3 weight plus one UE8M0 scale per 32 input
+    channels, kept in the tile order the tensor core reads (buffer `weight_scale_mx`, tag `weight.tfb_mx_sf`)."""
+
+    def forward(self, x):
+        return TF.linear_mxfp8(x, self.weight, self.weight_scale_mx, self.bias)
+
+
+def quantize_linear_mxfp8_(lin: nn.Linear) -> nn.Linear:
+    """In place, block-scaled MXFP8 (needs in_features to be a multiple of 128)."""
+    if lin.weight.dtype == torch.float8_e4m3fn:
+        return lin
+    q, sf = TF.quantize_weight_mxfp8(lin.weight.data)
+    lin.weight = nn.Parameter(q, requires_grad=False)
+    if "weight_scale_mx" in lin._buffers:
+        lin.weight_scale_mx = sf
+    else:
+        lin.register_buffer("weight_scale_mx", sf)
+    if type(lin) is nn.Linear:
+        lin.__class__ = QuantizedLinearMX
+    lin.weight.tfb_mx_sf = lin.weight_scale_mx
+    return lin
+
+
 def quantize_model_fp8_(model: nn.Module, quantize_modules=("*attn*", "*ffn*"), skip_modules=("head", "time_embedding",
-                        "time_projection", "patch_embedding", "text_embedding", "img_emb"), min_features: int = 64) -> int:  # fmt: skip
+                        "time_projection", "patch_embedding", "text_embedding", "img_emb"), min_features: int = 64,
+                        block_scaled: bool = False) -> int:  # fmt: skip
     """Quantises every `nn.Linear` whose qualified name matches one of `quantize_modules` (fnmatch) and
-    none of `skip_modules` (substring); returns the number of layers converted."""
+    none of `skip_modules` (substring); returns the number of layers converted. `block_scaled=True` selects
+    MXFP8 (a scale per 32 input channels) for layers whose input width is a multiple of 128; the others, and
+    everything when it is False, get per-channel FP8."""
     n = 0
     for name, m in model.named_modules():
         if not isinstance(m, nn.Linear) or min(m.in_features, m.out_features) < min_features:
@@ -110,7 +140,10 @@ def quantize_model_fp8_(model: nn.Module, quantize_modules=("*attn*", "*ffn*"), 
             continue
         if any(s in name for s in skip_modules) or not any(fnmatch.fnmatchcase(name, p) for p in quantize_modules):
             continue
-        quantize_linear_fp8_(m)
+        if block_scaled and m.in_features % 128 == 0:
+            quantize_linear_mxfp8_(m)
+        else:
+            quantize_linear_fp8_(m)
         n += 1
     for m in model.modules():  # cached fused views must be rebuilt from the new weights
         for attr in ("_qkv", "_kv", "_gu", "_fused"):

@@ -46,6 +46,19 @@ class StreamingActorFailedError(RuntimeError):
     """The actor stopped for good; every session that uses it fails."""
 
 
+def _positive(owner: str, **limits: int) -> None:
+    """Every keyword is a capacity / concurrency limit of `owner` and has to be 1 or more."""
+    for field_name, value in limits.items():
+        if int(value) < 1:
+            raise ValueError(f"{owner}: {field_name}={value!r} is not a positive count")
+
+
+def _freeze(obj, **collections) -> None:
+    """Stores normalised immutable collections on a frozen dataclass instance."""
+    for field_name, value in collections.items():
+        object.__setattr__(obj, field_name, value)
+
+
 @dataclass(frozen=True)
 class StreamingTaskKey:
     session_id: str
@@ -72,20 +85,21 @@ class StreamingStageSpec:
     resource_group: str | None = None
 
     def __post_init__(self) -> None:
-        object.__setattr__(self, "consumes", frozenset(self.consumes))
-        object.__setattr__(self, "produces", frozenset(self.produces))
-        if not self.stage_id or not self.consumes or not self.produces:
-            raise ValueError("A stage requires a non-empty ID, at least one input, and at least one output")
-        if self.resource_group == "":
-            raise ValueError("resource_group must be non-empty when provided")
-        if self.max_in_flight_per_session < 1:
-            raise ValueError("max_in_flight_per_session must be at least one")
-        if self.max_in_flight_global < 1:
-            raise ValueError("max_in_flight_global must be at least one")
-        if self.max_in_flight_per_session > self.max_in_flight_global:
-            raise ValueError("max_in_flight_per_session cannot exceed max_in_flight_global")
-        if self.ordering == StageOrdering.PER_SESSION_STRICT and self.max_in_flight_per_session != 1:
-            raise ValueError("PER_SESSION_STRICT stages require max_in_flight_per_session=1")
+        _freeze(self, consumes=frozenset(self.consumes), produces=frozenset(self.produces))
+        label = f"stage {self.stage_id!r}"
+        missing = [what for what, have in (("an id", self.stage_id), ("an input artifact", self.consumes),
+                                           ("an output artifact", self.produces)) if not have]  # fmt: skip
+        if missing:
+            raise ValueError(f"{label} lacks {' and '.join(missing)}")
+        if self.resource_group is not None and not self.resource_group:
+            raise ValueError(f"{label}: an empty string does not name a resource group (use None for no group)")
+        _positive(label, max_in_flight_per_session=self.max_in_flight_per_session,
+                  max_in_flight_global=self.max_in_flight_global)  # fmt: skip
+        per_session, overall = self.max_in_flight_per_session, self.max_in_flight_global
+        if per_session > overall:
+            raise ValueError(f"{label}: {per_session} chunks in flight per session cannot fit the overall limit {overall}")
+        if self.ordering is StageOrdering.PER_SESSION_STRICT and per_session > 1:
+            raise ValueError(f"{label}: strict per-session ordering runs one chunk of a session at a time, not {per_session}")
 
 
 @dataclass(frozen=True)
@@ -95,9 +109,8 @@ class StreamingResourceGroupSpec:
 
     def __post_init__(self) -> None:
         if not self.name:
-            raise ValueError("A resource group requires a non-empty name")
-        if self.max_concurrency < 1:
-            raise ValueError("max_concurrency must be at least one")
+            raise ValueError("a resource group is looked up by name; it cannot be empty")
+        _positive(f"resource group {self.name!r}", max_concurrency=self.max_concurrency)
 
 
 @dataclass(frozen=True)
@@ -108,10 +121,9 @@ class StreamingEdgeSpec:
     capacity_per_session: int = 1
 
     def __post_init__(self) -> None:
-        if not self.artifact or not self.target_stage:
-            raise ValueError("An edge requires artifact and target_stage")
-        if self.capacity_per_session < 1:
-            raise ValueError("capacity_per_session must be at least one")
+        if not (self.artifact and self.target_stage):
+            raise ValueError(f"edge {self.artifact!r} -> {self.target_stage!r}: both the artifact and the consuming stage must be named")
+        _positive(f"edge {self.artifact!r} -> {self.target_stage!r}", capacity_per_session=self.capacity_per_session)
 
 
 @dataclass(frozen=True)
@@ -123,12 +135,9 @@ class StreamingPipelineSpec:
     resource_groups: tuple = ()
 
     def __post_init__(self) -> None:
-        object.__setattr__(self, "stages", tuple(self.stages))
-        object.__setattr__(self, "edges", tuple(self.edges))
-        object.__setattr__(self, "output_artifacts", frozenset(self.output_artifacts))
-        object.__setattr__(self, "resource_groups", tuple(self.resource_groups))
-        if self.output_capacity_per_session < 1:
-            raise ValueError("output_capacity_per_session must be at least one")
+        _freeze(self, stages=tuple(self.stages), edges=tuple(self.edges),
+                output_artifacts=frozenset(self.output_artifacts), resource_groups=tuple(self.resource_groups))  # fmt: skip
+        _positive("pipeline", output_capacity_per_session=self.output_capacity_per_session)
 
 
 @dataclass(frozen=True)

@@ -227,6 +227,54 @@ class Flux2KleinPipeline(BasePipeline):
         if config.enable_denoising_parallel:
             self.denoise_stage = ParallelWorker(self.denoise_stage)
 
+    @classmethod
+    def from_pretrained(cls, model_id_or_path: str, device="cuda", torch_dtype=torch.bfloat16, cache_dir=None,
+                        attention_config=None, parallel_devices=None, cfg_degree=None, sp_ulysses_degree=None,
+                        quant_config=None, **kwargs):  # fmt: skip
+        """FLUX.2 [klein] from a diffusers-layout folder or hub id: `transformer/`, `vae/` (2-D KL autoencoder),
+        `text_encoder/` (a Qwen3 causal LM, loaded through transformers) and `tokenizer/`.
+        Loader of telefuser/pipelines/flux2_klein/pipeline.py:286."""
+        from telefuser_b200.core.module_manager import ModuleManager
+        from telefuser_b200.models.autoencoder_kl import AutoencoderKL
+        from telefuser_b200.models.flux2_dit import Flux2DiT
+        from telefuser_b200.utils.hf import resolve_hf_path
+        from telefuser_b200.utils.hf_model_analyzer import HFModelAnalyzer
+
+        root = resolve_hf_path(model_id_or_path, cache_dir)
+        found = HFModelAnalyzer(root)
+        dit_path, vae_path = found.get_transformer_path(), found.get_vae_path()
+        if not dit_path:
+            raise FileNotFoundError(f"{root} has no transformer weights; found {sorted(found.analyze())}")
+        mm = ModuleManager(torch_dtype=torch_dtype, device=str(device))
+        mm.load_model(dit_path, model_class=Flux2DiT, name="flux2_dit", model_resource="diffusers", quant_config=quant_config)
+        if vae_path:
+            mm.load_model(vae_path, model_class=AutoencoderKL, name="vae", model_resource="diffusers")
+        enc_dir, tok_dir = found.component_folder("text_encoder"), found.get_tokenizer_path()
+        if enc_dir and tok_dir:
+            from transformers import AutoModelForCausalLM, AutoTokenizer
+
+            mm.load_from_huggingface(enc_dir, "text_encoder", AutoModelForCausalLM, torch_dtype=torch_dtype, device=device)
+            mm.add_module(AutoTokenizer.from_pretrained(tok_dir), "tokenizer", path=tok_dir)
+        config = Flux2KleinPipelineConfig()
+        for c in (config.dit_config, config.text_encoding_config, config.vae_config):
+            c.torch_dtype, c.device_type = torch_dtype, torch.device(device).type
+            c.device_id = torch.device(device).index or 0
+        if attention_config is not None:
+            config.dit_config.attention_config = attention_config
+        if parallel_devices and len(parallel_devices) > 1:
+            n = len(parallel_devices)
+            pc = config.dit_config.parallel_config
+            pc.device_ids = list(parallel_devices)
+            pc.cfg_degree = cfg_degree or 1
+            pc.sp_ulysses_degree = sp_ulysses_degree or n // pc.cfg_degree
+            config.enable_denoising_parallel = True
+        for k, v in kwargs.items():
+            if hasattr(config, k):
+                setattr(config, k, v)
+        pipe = cls(device=device, torch_dtype=torch_dtype)
+        pipe.init(mm, config)
+        return pipe
+
     @staticmethod
     def check_resize_height_width(height: int, width: int) -> tuple[int, int]:
         return (height + 15) // 16 * 16, (width + 15) // 16 * 16

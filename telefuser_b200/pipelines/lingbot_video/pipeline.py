@@ -233,6 +233,59 @@ class LingBotVideoPipeline(BasePipeline):
             self.vae_stage = VAEStage("vae", module_manager, config.vae_config)
             self.vae_stage.onload_models_flag = True
 
+    @classmethod
+    def from_pretrained(cls, model_id_or_path: str, device="cuda", torch_dtype=torch.bfloat16, cache_dir=None,
+                        parallel_devices=None, cfg_degree=None, sp_ulysses_degree=None, expert_parallel: bool = False,
+                        quant_config=None, **kwargs):  # fmt: skip
+        """LingBot-Video (dense or MoE, told apart by the checkpoint keys) from a model folder or hub id:
+        `transformer/`, `vae/` (Wan 16-channel VAE) and `text_encoder/` + `processor/` (Qwen3-VL, loaded through
+        transformers). Keyword arguments that name a field of `LingBotVideoPipelineConfig` set it."""
+        import os
+
+        from telefuser_b200.core.module_manager import ModuleManager
+        from telefuser_b200.models.wan_vae import WanVideoVAE
+        from telefuser_b200.utils.hf import resolve_hf_path
+        from telefuser_b200.utils.hf_model_analyzer import HFModelAnalyzer
+
+        from .text_encoding import LingBotVideoTextEncodingStage
+
+        root = resolve_hf_path(model_id_or_path, cache_dir)
+        found = HFModelAnalyzer(root)
+        dit_path = found.get_transformer_path()
+        if not dit_path:
+            raise FileNotFoundError(f"{root} has no transformer weights; found {sorted(found.analyze())}")
+        mm = ModuleManager(torch_dtype=torch_dtype, device=str(device))
+        if not mm.load_model(dit_path, quant_config=quant_config):  # the registry tells dense from MoE by the keys
+            raise ValueError(f"{dit_path}: not a LingBot-Video transformer checkpoint")
+        if found.get_vae_path():
+            mm.load_model(found.get_vae_path(), model_class=WanVideoVAE, name="wan_video_vae")
+        config = LingBotVideoPipelineConfig(**{k: v for k, v in kwargs.items() if k in LingBotVideoPipelineConfig.__dataclass_fields__})
+        for c in (config.dit_config, config.vae_config):
+            c.torch_dtype, c.device_type = torch_dtype, torch.device(device).type
+            c.device_id = torch.device(device).index or 0
+        if parallel_devices and len(parallel_devices) > 1:
+            n = len(parallel_devices)
+            pc = config.dit_config.parallel_config
+            pc.device_ids = list(parallel_devices)
+            pc.cfg_degree = cfg_degree or (2 if n % 2 == 0 else 1)
+            pc.sp_ulysses_degree = sp_ulysses_degree or n // pc.cfg_degree
+            if expert_parallel:
+                pc.ep_degree = n
+            config.enable_denoising_parallel = True
+            config.enable_expert_parallel = expert_parallel
+        text_stage = None
+        enc_dir = found.component_folder("text_encoder")
+        proc_dir = found.component_folder("processor") or os.path.join(root, "processor")
+        if enc_dir and os.path.isdir(proc_dir):
+            from transformers import AutoModelForImageTextToText, AutoProcessor
+
+            mm.load_from_huggingface(enc_dir, "text_encoder", AutoModelForImageTextToText, torch_dtype=torch_dtype, device=device)
+            mm.add_module(AutoProcessor.from_pretrained(proc_dir), "processor", path=proc_dir)
+            text_stage = LingBotVideoTextEncodingStage("text_encoding", mm, config.dit_config)
+        pipe = cls(device=device, torch_dtype=torch_dtype)
+        pipe.init(mm, config, text_stage=text_stage)
+        return pipe
+
     def _encode_text(self, caption: str):
         if self.text_stage is None:
             raise RuntimeError("no text stage configured: pass prompt embeddings to generate()")

@@ -113,6 +113,67 @@ class QwenImagePipeline(BasePipeline):
         if config.enable_denoising_parallel:
             self.denoising_stage = ParallelWorker(self.denoising_stage)
 
+    @classmethod
+    def from_pretrained(cls, model_id_or_path: str, device="cuda", torch_dtype=torch.bfloat16, cache_dir=None,
+                        attention_config=None, parallel_devices=None, cfg_degree=None, sp_ulysses_degree=None,
+                        quant_config=None, **kwargs):  # fmt: skip
+        """Qwen-Image from a diffusers-layout folder or hub id: `transformer/` (sharded DiT), `vae/`,
+        `text_encoder/` (Qwen2.5-VL) and `tokenizer/` (+ `processor/` for the edit models). The text stage and the
+        image VAE are built here, so the returned pipeline takes plain prompts.
+        Loader of telefuser/pipelines/qwen_image/qwen_image.py:194."""
+        from telefuser_b200.core.module_manager import ModuleManager
+        from telefuser_b200.models.hf_text_encoders import QwenImageTextEncoder
+        from telefuser_b200.models.qwen_image_dit import QwenImageDiT
+        from telefuser_b200.models.qwen_image_vae import QwenImageVAE
+        from telefuser_b200.utils.hf import resolve_hf_path
+        from telefuser_b200.utils.hf_model_analyzer import HFModelAnalyzer
+
+        from .text_encoding import QwenImageTextEncodingStage
+
+        root = resolve_hf_path(model_id_or_path, cache_dir)
+        found = HFModelAnalyzer(root)
+        need = {"transformer": found.get_transformer_path(), "vae": found.get_vae_path(),
+                "text_encoder": found.get_text_encoder_path(), "tokenizer": found.get_tokenizer_path()}  # fmt: skip
+        missing = [k for k, v in need.items() if not v]
+        if missing:
+            raise FileNotFoundError(f"{root} lacks {', '.join(missing)}; found {sorted(found.analyze())}")
+        mm = ModuleManager(torch_dtype=torch_dtype, device=str(device))
+        mm.load_model(need["transformer"], model_class=QwenImageDiT, name="qwen_image_dit", model_resource="diffusers",
+                      quant_config=quant_config)  # fmt: skip
+        mm.load_model(need["vae"], model_class=QwenImageVAE, name="qwen_image_vae", model_resource="diffusers")
+        mm.load_model(need["text_encoder"], model_class=QwenImageTextEncoder, name="qwen_image_text_encoder",
+                      model_resource="diffusers")  # fmt: skip
+        from transformers import AutoProcessor, AutoTokenizer
+
+        tokenizer = AutoTokenizer.from_pretrained(need["tokenizer"])
+        proc_dir = found.component_folder("processor") or (root + "/processor")
+        import os
+
+        processor = AutoProcessor.from_pretrained(proc_dir) if os.path.isdir(proc_dir) else None
+        config = QwenImagePipelineConfig()
+        for c in (config.dit_config, config.text_encoding_config, config.vae_config):
+            c.torch_dtype, c.device_type = torch_dtype, torch.device(device).type
+            c.device_id = torch.device(device).index or 0
+        if attention_config is not None:
+            config.dit_config.attention_config = attention_config
+        if parallel_devices and len(parallel_devices) > 1:
+            n = len(parallel_devices)
+            pc = config.dit_config.parallel_config
+            pc.device_ids = list(parallel_devices)
+            pc.cfg_degree = cfg_degree or (2 if n % 2 == 0 else 1)
+            pc.sp_ulysses_degree = sp_ulysses_degree or n // pc.cfg_degree
+            config.enable_denoising_parallel = True
+        for k, v in kwargs.items():
+            if hasattr(config, k):
+                setattr(config, k, v)
+        text_stage = QwenImageTextEncodingStage(mm.fetch_module("qwen_image_text_encoder"), tokenizer, processor, device,
+                                                torch_dtype)  # fmt: skip
+        pipe = cls(device=device, torch_dtype=torch_dtype)
+        pipe.init(mm, config, text_stage=lambda prompt, images=None: (
+            text_stage.encode_prompt(prompt) if images is None else text_stage.encode_prompt_with_image(prompt, images)),
+            vae=mm.fetch_module("qwen_image_vae"))  # fmt: skip
+        return pipe
+
     @staticmethod
     def check_resize_height_width(height: int, width: int) -> tuple[int, int]:
         return (height + 15) // 16 * 16, (width + 15) // 16 * 16

@@ -46,6 +46,54 @@ def _round_frames(num_frames: int) -> int:
     return num_frames
 
 
+def _load_wan_components(model_id_or_path, torch_dtype, offload, *, experts: int, vae_class, vae_name: str, cache_dir=None):
+    """Resolves a Wan2.2 model folder (official or diffusers layout) and loads its DiT(s), VAE and UMT5 encoder
+    into a ModuleManager. Returns (module manager, tokenizer folder or None)."""
+    from telefuser_b200.models.umt5 import WanTextEncoder
+    from telefuser_b200.models.wan_dit import WanModel
+    from telefuser_b200.utils.hf import resolve_hf_path
+    from telefuser_b200.utils.hf_model_analyzer import HFModelAnalyzer
+
+    root = resolve_hf_path(model_id_or_path, cache_dir)
+    found = HFModelAnalyzer(root)
+    comps = found.analyze()
+    dits = [found.get_transformer_path()] + ([found.get_transformer_2_path()] if experts == 2 else [])
+    missing = [n for n, v in (("a DiT", dits[0]), ("the second (low-noise) DiT", dits[-1]), ("a VAE", found.get_vae_path()),
+                              ("a text encoder", found.get_text_encoder_path())) if not v]  # fmt: skip
+    if missing:
+        raise FileNotFoundError(f"{root} lacks {', '.join(missing)}; found {sorted(comps)}")
+    mm = ModuleManager(torch_dtype=torch_dtype, device="cpu" if offload else None)
+    for role, path in zip(("transformer", "transformer_2"), dits):  # high-noise expert first
+        diffusers = (comps[role].class_name or "").endswith("Transformer3DModel")
+        mm.load_model(path, model_class=WanModel, name="wan_video_dit", model_resource="diffusers" if diffusers else "official")
+    mm.load_model(found.get_vae_path(), model_class=vae_class, name=vae_name)
+    mm.load_model(found.get_text_encoder_path(), model_class=WanTextEncoder, name="wan_video_text_encoder")
+    logger.info(f"loaded {root}:\n{found.describe()}")
+    return mm, found.get_tokenizer_path()
+
+
+def _text_stage(mm, config, tokenizer_dir):
+    """A diffusers folder keeps the tokenizer in its own sub-folder; the official layout keeps it beside the
+    encoder file (`google/umt5-xxl`), which the stage finds by itself."""
+    if tokenizer_dir is None:
+        return None
+    from telefuser_b200.models.umt5 import HuggingfaceTokenizer
+
+    return TextEncodingStage("text_encoding", mm, config, tokenizer=HuggingfaceTokenizer(tokenizer_dir, 512, "whitespace"))
+
+
+def _apply_parallel(configs, parallel_devices, sp_ulysses_degree, cfg_degree) -> bool:
+    if not parallel_devices or len(parallel_devices) < 2:
+        return False
+    n = len(parallel_devices)
+    cfg_degree = cfg_degree or (2 if n % 2 == 0 and n >= 4 else 1)
+    for c in configs:
+        c.parallel_config.device_ids = list(parallel_devices)
+        c.parallel_config.cfg_degree = cfg_degree
+        c.parallel_config.sp_ulysses_degree = sp_ulysses_degree or n // cfg_degree
+    return True
+
+
 @dataclass
 class Wan22VideoPipelineConfig:
     vae_config: ModelRuntimeConfig = field(default_factory=ModelRuntimeConfig)
@@ -119,6 +167,37 @@ class Wan22VideoPipeline(BasePipeline):
             return out, payload
         return out
 
+    @classmethod
+    def from_pretrained(cls, model_id_or_path: str, device="cuda", torch_dtype=torch.bfloat16, cache_dir=None,
+                        attention_config=None, parallel_devices=None, sample_solver="euler", offload_type=None,
+                        enable_metrics=False, sp_ulysses_degree=None, cfg_degree=None, **kwargs):  # fmt: skip
+        """Wan2.2 A14B from a model folder or hub id: `high_noise_model/` + `low_noise_model/` (official) or
+        `transformer/` + `transformer_2/` (diffusers), the 16-channel VAE and the UMT5 encoder. Keyword arguments
+        that name a field of `Wan22VideoPipelineConfig` set it. Loader of telefuser/pipelines/wan_video/wan22_video.py:220."""
+        from telefuser_b200.core.config import WeightOffloadType
+        from telefuser_b200.models.wan_vae import WanVideoVAE
+
+        offload = offload_type not in (None, WeightOffloadType.NO_CPU_OFFLOAD)
+        mm, tokenizer_dir = _load_wan_components(model_id_or_path, torch_dtype, offload, experts=2, vae_class=WanVideoVAE,
+                                                 vae_name="wan_video_vae", cache_dir=cache_dir)  # fmt: skip
+        config = Wan22VideoPipelineConfig(sample_solver=sample_solver, enable_metrics=enable_metrics)
+        runtime = (config.vae_config, config.dit_high_config, config.dit_low_config, config.text_encoding_config)
+        for c in runtime:
+            c.torch_dtype, c.device_type = torch_dtype, torch.device(device).type
+            c.device_id = torch.device(device).index or 0
+            if offload:
+                c.offload_config.offload_type = offload_type
+        if attention_config is not None:
+            config.dit_high_config.attention_config = config.dit_low_config.attention_config = attention_config
+        config.enable_denoising_parallel = _apply_parallel((config.dit_high_config, config.dit_low_config), parallel_devices,
+                                                           sp_ulysses_degree, cfg_degree)  # fmt: skip
+        for k, v in kwargs.items():
+            if hasattr(config, k):
+                setattr(config, k, v)
+        pipe = cls(device=device, torch_dtype=torch_dtype)
+        pipe.init(mm, config, text_stage=_text_stage(mm, config.text_encoding_config, tokenizer_dir))
+        return pipe
+
     def close(self) -> None:
         for st in (getattr(self, "denoise_stage", None), getattr(self, "vae_stage", None)):
             if isinstance(st, ParallelWorker):
@@ -186,6 +265,34 @@ class Wan22TI2VPipeline(BasePipeline):
                                   posi, nega, cfg_scale, sigma_shift)()  # fmt: skip
         frames = auto_async_call(self.vae_stage.process, "decode_video", latents, **tiler)()
         return frames if output_type == "pt" else self.tensor2video(frames[0])
+
+    @classmethod
+    def from_pretrained(cls, model_id_or_path: str, device="cuda", torch_dtype=torch.bfloat16, cache_dir=None,
+                        attention_config=None, parallel_devices=None, sample_solver="euler", offload_type=None,
+                        enable_metrics=False, sp_ulysses_degree=None, cfg_degree=None, **kwargs):  # fmt: skip
+        """Wan2.2 TI2V 5B from a model folder or hub id: one DiT, the 48-channel VAE (`Wan2.2_VAE.pth` or `vae/`)
+        and the UMT5 encoder. Loader of telefuser/pipelines/wan_video/wan22_ti2v.py:276."""
+        from telefuser_b200.core.config import WeightOffloadType
+        from telefuser_b200.models.wan22_vae import Wan22VideoVAE
+
+        offload = offload_type not in (None, WeightOffloadType.NO_CPU_OFFLOAD)
+        mm, tokenizer_dir = _load_wan_components(model_id_or_path, torch_dtype, offload, experts=1, vae_class=Wan22VideoVAE,
+                                                 vae_name="wan22_video_vae", cache_dir=cache_dir)  # fmt: skip
+        config = Wan22TI2VPipelineConfig(sample_solver=sample_solver, enable_metrics=enable_metrics)
+        for c in (config.vae_config, config.dit_config, config.text_encoding_config):
+            c.torch_dtype, c.device_type = torch_dtype, torch.device(device).type
+            c.device_id = torch.device(device).index or 0
+            if offload:
+                c.offload_config.offload_type = offload_type
+        if attention_config is not None:
+            config.dit_config.attention_config = attention_config
+        config.enable_denoising_parallel = _apply_parallel((config.dit_config,), parallel_devices, sp_ulysses_degree, cfg_degree)
+        for k, v in kwargs.items():
+            if hasattr(config, k):
+                setattr(config, k, v)
+        pipe = cls(device=device, torch_dtype=torch_dtype)
+        pipe.init(mm, config, text_stage=_text_stage(mm, config.text_encoding_config, tokenizer_dir))
+        return pipe
 
     def close(self) -> None:
         for st in (getattr(self, "denoise_stage", None), getattr(self, "vae_stage", None)):

@@ -1,7 +1,7 @@
 """Micro-benchmarks of the peer-memory (fused) collectives against their NCCL compositions.
 
 Run under `python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P
--m telefuser_b200.parallel.bench_fused [--seq 75600 --heads 40 --dim 5120 --ffn 13824]`. Every case is timed on
+-m telefuser_b200.tools.bench_fused [--seq 75600 --heads 40 --dim 5120 --ffn 13824]`. Every case is timed on
 the device with CUDA events after warm-up, an L2 flush between iterations, and the maximum over ranks is
 reported; rank 0 prints one JSON line per case with both times, the bytes this rank must move over NVLink, and the
 fraction of the measured per-direction link bandwidth (770 GB/s) or of the measured GEMM peak that the fused

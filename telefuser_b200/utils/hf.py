@@ -1,5 +1,5 @@
-"""Hugging Face helpers: id-vs-path test, snapshot resolution, component discovery in a model folder.
-Role parity: telefuser/utils/hf_model_utils.py:21-209 and hf_model_analyzer.py:28-382 (condensed)."""
+"""Hugging Face helpers: id-vs-path test, snapshot resolution, task detection of a model folder. Component discovery
+is in `hf_model_analyzer`. Role parity: telefuser/utils/hf_model_utils.py:21-209."""
 
 from __future__ import annotations
 
@@ -48,22 +48,10 @@ def detect_model_task(root: str) -> str:
     return "i2v" if "i2v" in os.path.basename(root).lower() else "t2v"
 
 
-class HFModelAnalyzer:
-    """Lists the components (transformer / vae / text_encoder / image_encoder / tokenizer) of a model folder."""
+def __getattr__(name: str):
+    # `HFModelAnalyzer` lives in `hf_model_analyzer` (which imports this module for the task detection).
+    if name in ("HFModelAnalyzer", "ModelComponentInfo", "discover_model_components"):
+        from . import hf_model_analyzer
 
-    COMPONENTS = ("transformer", "transformer_2", "vae", "text_encoder", "image_encoder", "tokenizer", "scheduler")
-
-    def __init__(self, root: str):
-        self.root = root
-
-    def analyze(self) -> dict:
-        out = {"root": self.root, "task": detect_model_task(self.root), "components": {}}
-        idx = os.path.join(self.root, "model_index.json")
-        if os.path.isfile(idx):
-            out["model_index"] = json.load(open(idx))
-        for c in self.COMPONENTS:
-            p = get_component_path(self.root, c)
-            if p:
-                out["components"][c] = p
-        out["files"] = sorted(f for f in os.listdir(self.root) if f.endswith((".safetensors", ".pth", ".bin")))
-        return out
+        return getattr(hf_model_analyzer, name)
+    raise AttributeError(name)

@@ -137,3 +137,62 @@ def test_model_quantised_on_the_host_then_moved_runs_on_the_device():
 
     with pytest.raises(native.NativeLibraryError):
         TF.linear_fp8(x.cuda(), lin.weight, lin.weight_scale, lin.bias.cpu())
+
+
+def test_mxfp8_linear_reference_path_and_model_conversion():
+    torch.manual_seed(0)
+    x, w = torch.randn(70, 256), torch.randn(64, 256)
+    wq, wsf = TF.quantize_weight_mxfp8(w)
+    assert wq.dtype == torch.float8_e4m3fn and wsf.shape == (1, 2, 512) and wsf.dtype == torch.uint8
+    want = x @ w.t()
+    assert ((TF.linear_mxfp8(x, wq, wsf) - want).norm() / want.norm()).item() < 0.05
+    sf = torch.randint(0, 255, (300, 8), dtype=torch.uint8)
+    tiled = TF.mx_tile_scales(sf)
+    assert torch.equal(TF.mx_untile_scales(tiled, 300), sf)
+    r, b = 137, 5  # row 137, 32-element block 5: tile (1, 1), inside it (r%32)*16 + (r/32)*4 + b%4
+    assert tiled.view(-1)[((r >> 7) * 2 + (b >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (b & 3)] == sf[r, b]
+
+    model = make_tiny_model()
+    latents, ctx, _ = make_tiny_inputs()
+    t = torch.tensor([500.0])
+    ref = model(latents, t, ctx)
+    assert model.enable_quant("mxfp8") == 20
+    blk = model.blocks[0]
+    assert blk.ffn[0].weight.tfb_mx_sf is blk.ffn[0].weight_scale_mx
+    W, _ = blk.self_attn.fused_qkv()
+    assert W.dtype == torch.float8_e4m3fn and W.tfb_mx_sf.shape == (3, 1, 512)
+    out = model(latents, t, ctx)
+    assert ((out - ref).norm() / ref.norm()).item() < 0.1
+    model._apply(lambda t_: t_.clone())
+    assert blk.ffn[0].weight.tfb_mx_sf is blk.ffn[0].weight_scale_mx
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 200, 512), (1024, 1536, 5120), (77, 72, 128)])
+def test_mxfp8_gemm_matches_fp32_product_of_the_dequantised_operands(M, N, K):
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 4).bfloat16()
+    w = (torch.randn(N, K, device="cuda") / K**0.5).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    gate = torch.randn(1, N, device="cuda")
+    wq, wsf = TF.quantize_weight_mxfp8(w)
+    xq, xsf_t = TF.quant_mxfp8(x, tiled=True)
+    xq_r, xsf_r = TF.quant_mxfp8(x)
+    assert torch.equal(xq, xq_r) and torch.equal(TF.mx_untile_scales(xsf_t, M), xsf_r)  # tiled order written right
+    base = TF.dequant_mxfp8(xq, xsf_r) @ TF.dequant_mxfp8(wq.view(torch.uint8), TF.mx_untile_scales(wsf, N)).t()
+    for kw in (dict(), dict(bias=bias), dict(bias=bias, act="gelu_tanh"), dict(bias=bias, residual=res, gate=gate)):
+        got = TF.linear_mxfp8(x, wq, wsf, **kw).float()
+        want = base.clone()
+        if "bias" in kw:
+            want = want + bias.float()
+        if kw.get("act"):
+            want = torch.nn.functional.gelu(want, approximate="tanh")
+        if "gate" in kw:
+            want = want * gate
+        if "residual" in kw:
+            want = want + res.float()
+        err = ((got - want).abs() / (1 + want.abs())).max().item()
+        assert err <= 1.5e-2, (kw.keys(), err)
+    full = (x.float() @ w.float().t())
+    assert ((TF.linear_mxfp8(x, wq, wsf).float() - full).norm() / full.norm()).item() < 0.05

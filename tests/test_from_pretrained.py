@@ -1,0 +1,96 @@
+"""`from_pretrained` of the Wan2.2 pipelines: component discovery in both folder layouts, expert order, module names
+and runtime configuration. Checkpoint reading is replaced by tiny random models (the loaders' file handling is
+covered by tests/test_module_manager.py and tests/test_hf_model_analyzer.py)."""
+
+import json
+
+import pytest
+import torch
+
+from telefuser_b200.core.module_manager import ModuleManager
+from telefuser_b200.models.wan_dit import WanModel
+from telefuser_b200.pipelines.wan import wan22_video as W
+from telefuser_b200.testing.synthetic import HashTokenizer
+
+
+def _touch(path):
+    path.parent.mkdir(parents=True, exist_ok=True)
+    path.write_bytes(b"\0" * 8)
+
+
+class _TinyVAE(torch.nn.Module):
+    z_dim, upsampling_factor = 48, 16
+
+
+class _TinyText(torch.nn.Module):
+    def forward(self, ids, mask):
+        return torch.zeros(ids.shape[0], ids.shape[1], 64)
+
+
+@pytest.fixture
+def fake_loading(monkeypatch):
+    calls = []
+
+    def load_model(self, file_path, device=None, torch_dtype=None, low_cpu_mem_usage=False, name=None, model_class=None,
+                   model_resource="official", converter_kwargs=None, quant_config=None):  # fmt: skip
+        calls.append((name, model_class.__name__, model_resource, file_path))
+        if model_class is WanModel:
+            module = WanModel(dim=64, ffn_dim=128, num_heads=2, num_layers=1, text_dim=64)
+        elif "VAE" in model_class.__name__:
+            module = _TinyVAE()
+        else:
+            module = _TinyText()
+        self.add_module(module, name, path=file_path)
+        return True
+
+    monkeypatch.setattr(ModuleManager, "load_model", load_model)
+    monkeypatch.setattr("telefuser_b200.models.umt5.HuggingfaceTokenizer", lambda *a, **k: HashTokenizer(4096, 32))
+    return calls
+
+
+def test_wan22_a14b_official_layout(tmp_path, fake_loading):
+    root = tmp_path / "Wan2.2-T2V-A14B"
+    for expert in ("high_noise_model", "low_noise_model"):
+        for i in (1, 2):
+            _touch(root / expert / f"diffusion_pytorch_model-0000{i}-of-00002.safetensors")
+        (root / expert / "config.json").write_text(json.dumps({"_class_name": "WanModel"}))
+    _touch(root / "models_t5_umt5-xxl-enc-bf16.pth")
+    _touch(root / "Wan2.1_VAE.pth")
+    pipe = W.Wan22VideoPipeline.from_pretrained(str(root), device="cpu", torch_dtype=torch.float32, sample_solver="mix-euler",
+                                                parallel_devices=[0, 1, 2, 3], enable_vfi=False)  # fmt: skip
+    names = [(n, c, r) for n, c, r, _ in fake_loading]
+    assert names == [("wan_video_dit", "WanModel", "official"), ("wan_video_dit", "WanModel", "official"),
+                     ("wan_video_vae", "WanVideoVAE", "official"), ("wan_video_text_encoder", "WanTextEncoder", "official")]
+    assert "high_noise_model" in fake_loading[0][3][0] and "low_noise_model" in fake_loading[1][3][0]  # high-noise expert first
+    assert len(fake_loading[0][3]) == 2
+    cfg = pipe.config
+    assert cfg.sample_solver == "mix-euler" and cfg.enable_denoising_parallel
+    pc = cfg.dit_high_config.parallel_config
+    assert (pc.cfg_degree, pc.sp_ulysses_degree, pc.device_ids) == (2, 2, [0, 1, 2, 3])
+    pipe.close()
+
+
+def test_wan22_ti2v_diffusers_layout_and_missing_parts(tmp_path, fake_loading):
+    root = tmp_path / "Wan2.2-TI2V-5B-Diffusers"
+    (root).mkdir()
+    (root / "model_index.json").write_text(json.dumps({
+        "transformer": ["diffusers", "WanTransformer3DModel"], "vae": ["diffusers", "AutoencoderKLWan"],
+        "text_encoder": ["transformers", "UMT5EncoderModel"], "tokenizer": ["transformers", "T5TokenizerFast"]}))
+    _touch(root / "transformer" / "diffusion_pytorch_model.safetensors")
+    _touch(root / "vae" / "diffusion_pytorch_model.safetensors")
+    _touch(root / "text_encoder" / "model.safetensors")
+    (root / "tokenizer").mkdir()
+    (root / "tokenizer" / "tokenizer_config.json").write_text("{}")
+    pipe = W.Wan22TI2VPipeline.from_pretrained(str(root), device="cpu", torch_dtype=torch.float32)
+    assert [(n, c, r) for n, c, r, _ in fake_loading] == [
+        ("wan_video_dit", "WanModel", "diffusers"), ("wan22_video_vae", "Wan22VideoVAE", "official"),
+        ("wan_video_text_encoder", "WanTextEncoder", "official")]
+    assert pipe.z_dim == 48 and not pipe.config.enable_denoising_parallel
+    assert isinstance(pipe.text_encoding_stage.tokenizer, HashTokenizer)  # built from the `tokenizer/` folder
+    (root / "vae" / "diffusion_pytorch_model.safetensors").unlink()
+    with pytest.raises(FileNotFoundError, match="a VAE"):
+        W.Wan22TI2VPipeline.from_pretrained(str(root), device="cpu")
+    with pytest.raises(FileNotFoundError, match="low-noise"):
+        (root / "vae").rmdir()
+        _touch(root / "vae" / "diffusion_pytorch_model.safetensors")
+        W.Wan22VideoPipeline.from_pretrained(str(root), device="cpu")

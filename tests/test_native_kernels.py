@@ -51,17 +51,79 @@ def test_gemm_per_row_gate_and_batched():
                TF.linear_reference(x, w, None, residual=res, gate=gate_tok)) < 6e-3
 
 
+@pytest.mark.parametrize("variant", [0, 21])  # two threads per query row (default) / one thread per row
 @pytest.mark.parametrize("B,Sq,Skv,H", [(1, 128, 128, 1), (1, 256, 384, 2), (2, 300, 500, 3), (1, 1000, 77, 2),
                                          (1, 515, 1029, 2), (1, 4096, 4096, 4)])
-def test_attention(B, Sq, Skv, H):
+def test_attention(B, Sq, Skv, H, variant):
     torch.manual_seed(0)
     q = torch.randn(B, Sq, H, 128, device="cuda").bfloat16()
     k = torch.randn(B, Skv, H, 128, device="cuda").bfloat16()
     v = torch.randn(B, Skv, H, 128, device="cuda").bfloat16()
-    got, lse = TF.attention(q, k, v, return_lse=True)
+    got, lse = TF.attention(q, k, v, return_lse=True, variant=variant)
     ref, lse_ref = TF.attention_reference(q, k, v, return_lse=True)
     assert rel(got, ref) < 1e-2
     assert rel(lse, lse_ref) < 1e-4
+    again = TF.attention(q, k, v, variant=variant)
+    assert torch.equal(got, again)  # no atomics, fixed order: bitwise reproducible
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("B,Sq,Skv,H", [(1, 256, 256, 2), (2, 300, 300, 3), (1, 200, 777, 2), (1, 1031, 1031, 1)])
+def test_attention_causal_and_head_dim_64(B, Sq, Skv, H, D):
+    torch.manual_seed(0)
+    q = torch.randn(B, Sq, H, D, device="cuda").bfloat16()
+    k = torch.randn(B, Skv, H, D, device="cuda").bfloat16()
+    v = torch.randn(B, Skv, H, D, device="cuda").bfloat16()
+    for causal in (False, True):
+        got, lse = TF.attention(q, k, v, return_lse=True, causal=causal)
+        ref, lse_ref = TF.attention_reference(q, k, v, return_lse=True, causal=causal)
+        assert rel(got, ref) < 1e-2, (causal, D)
+        assert rel(lse, lse_ref) < 1e-4, (causal, D)
+
+
+@pytest.mark.parametrize("D,dtype", [(80, torch.bfloat16), (40, torch.float16), (96, torch.bfloat16)])
+def test_attention_pads_other_head_dims(D, dtype):
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(2, 257, 4, D, device="cuda").to(dtype) for _ in range(3))
+    launches = TF.native.launch_count()
+    got = TF.attention(q, k, v)
+    assert TF.native.launch_count() == launches + 1 and got.dtype == dtype and got.shape == q.shape
+    assert rel(got, TF.attention_reference(q, k, v)) < 1e-2
+
+
+def test_attention_masked_and_wide_heads_take_the_blocked_fp32_path():
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, 300, 2, 384, device="cuda").bfloat16() for _ in range(3))
+    want = TF.attention_reference(q, k, v)
+    assert rel(TF.attention(q, k, v), want) < 1e-6
+    assert rel(TF.attention_reference(q, k, v, q_block=64), want) < 1e-6
+    q, k, v = (torch.randn(2, 100, 2, 64, device="cuda").bfloat16() for _ in range(3))
+    mask = torch.rand(2, 1, 100, 100, device="cuda") > 0.3
+    mask[..., 0] = True
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) / 8
+    want = torch.einsum("bhqk,bkhd->bqhd", s.masked_fill(~mask, float("-inf")).softmax(-1), v.float())
+    assert rel(TF.attention(q, k, v, mask=mask), want) < 1e-2
+    assert rel(TF.attention_reference(q, k, v, mask=mask, q_block=32), want) < 1e-2
+
+
+def test_attention_long_sequence_and_layer_like_magnitudes():
+    """32k keys with inputs shaped like a DiT layer's: RMS-normed, RoPE-rotated q / k with a learned gain and a few
+    outlier channels, so the running maximum moves and the lazy rescale fires many times over 256 key tiles."""
+    torch.manual_seed(0)
+    S, H = 32768, 2
+    q = torch.randn(1, S, H, 128, device="cuda")
+    k = torch.randn(1, S, H, 128, device="cuda")
+    gain = 1 + 0.5 * torch.randn(128, device="cuda").abs()
+    gain[::17] *= 4
+    ramp = torch.linspace(0.2, 3.0, S, device="cuda").reshape(1, S, 1, 1)  # later keys score higher
+    q = (q / q.pow(2).mean(-1, keepdim=True).sqrt() * gain).bfloat16()
+    k = (k / k.pow(2).mean(-1, keepdim=True).sqrt() * gain * ramp).bfloat16()
+    v = torch.randn(1, S, H, 128, device="cuda").bfloat16()
+    for variant in (0, 21):
+        got, lse = TF.attention(q[:, :2048], k, v, return_lse=True, variant=variant)
+        ref, lse_ref = TF.attention_reference(q[:, :2048], k, v, return_lse=True)
+        assert rel(got, ref) < 1.5e-2, variant
+        assert rel(lse, lse_ref) < 1e-4, variant
 
 
 def test_attention_strided_fused_qkv_and_peaked_scores():

@@ -72,3 +72,43 @@ def test_unipc_add_noise_and_timesteps():
     sig = s.sigmas[s.index_for_timestep(t[0])]
     assert abs(float(sig) - float(s.sigmas[358])) < 2e-3
     assert torch.allclose(s.add_noise(x, n, t), (1 - sig) * x)
+
+
+def _reference_flow_match():
+    """The reference's scheduler file, loaded by path (its package `__init__` needs packages that are not installed)."""
+    import importlib.util
+    from pathlib import Path
+
+    import pytest
+
+    path = Path(__file__).resolve().parents[1] / "baseline" / "_ref" / "telefuser" / "schedulers" / "flow_match.py"
+    if not path.is_file():
+        pytest.skip("the reference tree is not installed")
+    spec = importlib.util.spec_from_file_location("telefuser_ref_flow_match_for_tests", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.FlowMatchScheduler
+
+
+def test_every_template_equals_the_reference_schedule():
+    Ref = _reference_flow_match()
+    cases = [("Wan", {"shift": 5.0}), ("Wan", {"shift": 3.0, "denoising_strength": 0.6}), ("FLUX.1", {}),
+             ("FLUX.1", {"shift": 2.0}), ("Qwen-Image", {"dynamic_shift_len": 4096}),
+             ("Qwen-Image", {"dynamic_shift_len": 1024, "denoising_strength": 0.8}), ("FLUX.2", {"dynamic_shift_len": 4096}),
+             ("Z-Image", {}), ("Z-Image", {"shift": 6.0}), ("LTX.2", {})]  # fmt: skip
+    torch.manual_seed(0)
+    for name, kw in cases:
+        for steps in (4, 20):
+            try:
+                want = Ref(name)
+                want.set_timesteps(steps, **kw)
+            except TypeError:
+                continue  # the reference's template does not take this keyword
+            got = FlowMatchScheduler(name)
+            got.set_timesteps(steps, **kw)
+            assert torch.equal(got.sigmas.float(), want.sigmas.float()), (name, kw, steps)
+            assert torch.equal(got.timesteps.float(), want.timesteps.float()), (name, kw, steps)
+            x, v = torch.randn(2, 5), torch.randn(2, 5)
+            for i in (0, steps // 2, steps - 1):
+                a, b = got.step(v, got.timesteps[i], x), want.step(v, want.timesteps[i], x)
+                assert torch.allclose(a, b, atol=1e-6, rtol=0), (name, kw, steps, i)
