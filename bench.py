@@ -4,16 +4,27 @@
 
 A *step* is one full denoising step of the 50-step sampler: conditional and
 unconditional DiT forward (40 blocks, dim 5120) + classifier-free guidance (5.0)
-+ flow-matching Euler update. `value` is the whole-video time: 50 x the measured
-step time plus the measured one-off stages (listed in `config`). Weights are
-random-init bf16 tensors of the 14B architecture; text embeddings and noise
++ flow-matching Euler update. `value` is the time of the denoising loop of one
+video: 50 x the measured step time. The one-off stages of the public pipeline
+call (UMT5-XXL prompt encoding of the two prompts, 720p VAE decode of the
+81 frames) are measured once each, on rank 0, after the timed region, and
+reported beside it as `pipeline` (their sum with `value` is the time of
+`pipeline(prompt, num_frames=81, height=720, width=1280)`). Weights are
+random-init bf16 tensors of the real architectures; text embeddings and noise
 latents are synthetic tensors of the real shapes.
 
-Layouts: 1 GPU plain; 2 GPUs CFG-parallel; 4 GPUs CFG2 x Ulysses2; 8 GPUs
-CFG2 x Ulysses4 (strong scaling: one video, more GPUs).
+Layouts (`--layout`, default by GPU count): 1 GPU plain; 2 GPUs CFG-parallel;
+4 GPUs CFG2 x Ulysses2; 8 GPUs CFG2 x Ulysses4 (strong scaling: one video, more
+GPUs). Others are spelled from `cfg2`, `u<N>` (Ulysses), `r<N>` (ring / context
+parallel), `tp<N>` (tensor-parallel FFN): `u8`, `r8`, `u4r2`, `tp8`, `cfg2u4`.
+`--quant fp8|mxfp8` runs the block projections in W8A8 (per-channel FP8 or
+block-scaled MXFP8); such a line says so in `dtype` and is not the bf16 headline.
 
 `--impl reference` runs the unmodified reference package installed under
-baseline/_ref through its own stage API on the same shapes.
+baseline/_ref through its own stage API on the same shapes, with the fastest
+attention setting among those it ships that work on this machine
+(`--ref-attn auto` times TORCH_SDPA, TORCH_CUDNN and FLASH_ATTN_2 on one layer's
+attention call and keeps the winner; the table is printed in `ref_attention`).
 """
 
 from __future__ import annotations
@@ -52,15 +63,30 @@ def parse_args():
     ap.add_argument("--height", type=int, default=720)
     ap.add_argument("--width", type=int, default=1280)
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (pinned host <-> device) measurement")
+    ap.add_argument("--layout", default="auto", help="auto | single | cfg2 | u8 | r8 | u4r2 | tp8 | cfg2u4 | ...")
+    ap.add_argument("--quant", default="none", choices=["none", "fp8", "mxfp8"])
+    ap.add_argument("--ref-attn", default="auto", choices=["auto", "sdpa", "cudnn", "fa2"])
+    ap.add_argument("--no-pipeline-stages", action="store_true", help="skip the text-encode / VAE-decode timings")
     return ap.parse_args()
 
 
-def layout_for(n: int) -> dict:
-    if n == 1:
-        return dict(cfg_degree=1, sp_ulysses_degree=1, name="single")
-    if n == 2:
-        return dict(cfg_degree=2, sp_ulysses_degree=1, name="cfg2")
-    return dict(cfg_degree=2, sp_ulysses_degree=n // 2, name=f"cfg2xulysses{n // 2}")
+def layout_for(n: int, spec: str = "auto") -> dict:
+    """Parallel degrees for `n` GPUs. `spec` is a concatenation of cfg2 / u<N> / r<N> / tp<N> whose product is n."""
+    import re
+
+    if spec in ("auto", ""):
+        spec = {1: "single", 2: "cfg2"}.get(n, f"cfg2xulysses{n // 2}")
+    out = dict(cfg_degree=1, sp_ulysses_degree=1, sp_ring_degree=1, tp_degree=1, name=spec)
+    if spec != "single":
+        keys = {"cfg": "cfg_degree", "u": "sp_ulysses_degree", "ulysses": "sp_ulysses_degree", "r": "sp_ring_degree",
+                "ring": "sp_ring_degree", "tp": "tp_degree", "x": None}  # fmt: skip
+        for word, num in re.findall(r"(cfg|ulysses|ring|tp|u|r|x)(\d*)", spec.lower()):
+            if keys[word] is not None:
+                out[keys[word]] = int(num or 1)
+    prod = out["cfg_degree"] * out["sp_ulysses_degree"] * out["sp_ring_degree"] * out["tp_degree"]
+    if prod != n:
+        raise SystemExit(f"layout {spec!r} needs {prod} GPUs, --gpus says {n}")
+    return out
 
 
 class ClockSampler:
@@ -179,8 +205,13 @@ def build_ours(args, layout, world, local):
     model = model.to_empty(device="cuda").to(torch.bfloat16)
     random_init_(model)
     model.eval()
+    if args.quant != "none":
+        n_q = model.enable_quant("mxfp8" if args.quant == "mxfp8" else "fp8")
+        if local == 0:
+            print(f"[bench] {n_q} linear layers quantised to {args.quant}", file=sys.stderr)
     pc = ParallelConfig(device_ids=list(range(world)) if world > 1 else None, cfg_degree=layout["cfg_degree"],
-                        sp_ulysses_degree=layout["sp_ulysses_degree"])  # fmt: skip
+                        sp_ulysses_degree=layout["sp_ulysses_degree"], sp_ring_degree=layout["sp_ring_degree"],
+                        tp_degree=layout["tp_degree"])  # fmt: skip
     cfg = ModelRuntimeConfig(torch_dtype=torch.bfloat16, parallel_config=pc, device_type="cuda", device_id=local)
     stage = WanDenoisingStage("dit_denoise", None, cfg, FlowMatchScheduler("Wan"), dit=model)
     if world > 1:
@@ -190,7 +221,38 @@ def build_ours(args, layout, world, local):
     def run(latents, steps, posi, nega):
         return stage.process(latents, steps, None, posi, nega, None, CFG_SCALE, SIGMA_SHIFT)
 
-    return run, native
+    return run, native, {}
+
+
+def pick_reference_attention(args, AttentionConfig, AttnImplType, attention, heads: int, tokens: int) -> tuple:
+    """Times one layer's self-attention call of the real shape through the reference's own `attention()` for each
+    stock setting that works here; returns (winning AttnImplType, {name: ms or reason})."""
+    names = {"sdpa": "TORCH_SDPA", "cudnn": "TORCH_CUDNN", "fa2": "FLASH_ATTN_2"}
+    todo = list(names) if args.ref_attn == "auto" else [args.ref_attn]
+    q, k, v = (torch.randn(1, tokens, heads, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    table, best = {}, (None, float("inf"))
+    for key in todo:
+        impl = getattr(AttnImplType, names[key])
+        cfg = AttentionConfig.dense_attention(impl)
+        try:
+            for _ in range(2):
+                attention(q, k, v, attention_config=cfg, input_layout="BSND", output_layout="BSND")
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                attention(q, k, v, attention_config=cfg, input_layout="BSND", output_layout="BSND")
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 3
+            table[names[key]] = round(ms, 3)
+            if ms < best[1]:
+                best = (impl, ms)
+        except Exception as e:  # noqa: BLE001 - a setting that does not run on this machine is skipped
+            table[names[key]] = f"failed: {type(e).__name__}: {e}"[:160]
+    if best[0] is None:
+        best = (AttnImplType.TORCH_SDPA, float("nan"))
+    return best[0], table
 
 
 def build_reference(args, layout, world, local):
@@ -199,10 +261,15 @@ def build_reference(args, layout, world, local):
         raise RuntimeError("reference is not installed under baseline/_ref")
     sys.path.insert(0, ref_root)
     os.environ.setdefault("TELEFUSER_LOG_LEVEL", "WARNING")
-    from telefuser.core.config import ModelRuntimeConfig, ParallelConfig
+    from telefuser.core.config import AttentionConfig, AttnImplType, ModelRuntimeConfig, ParallelConfig
     from telefuser.core.module_manager import ModuleManager
     from telefuser.models.wan_video_dit import WanModel
+    from telefuser.ops.attention.attention_impl import attention as ref_attention
     from telefuser.pipelines.wan_video.single_dit_denoising import SingleDitDenoisingStage
+
+    if args.quant != "none":
+        raise RuntimeError("the reference's quantised linears need its tf_kernel extension or vLLM kernels, neither of "
+                           "which can be built offline here")  # fmt: skip
 
     # The reference's `telefuser.schedulers` package imports its UniPC scheduler, which needs
     # `diffusers` (not installable offline). Its flow-matching scheduler file has no such
@@ -231,9 +298,16 @@ def build_reference(args, layout, world, local):
     mm = ModuleManager(torch_dtype=torch.bfloat16, device="cuda")
     mm.add_module(model, "wan_video_dit")
     pc = ParallelConfig(device_ids=list(range(world)) if world > 1 else None, cfg_degree=layout["cfg_degree"],
-                        sp_ulysses_degree=layout["sp_ulysses_degree"])  # fmt: skip
-    cfg = ModelRuntimeConfig(torch_dtype=torch.bfloat16, parallel_config=pc, device_type="cuda", device_id=local)
+                        sp_ulysses_degree=layout["sp_ulysses_degree"], sp_ring_degree=layout["sp_ring_degree"],
+                        tp_degree=layout["tp_degree"])  # fmt: skip
+    sp = layout["sp_ulysses_degree"]
+    tokens = ((args.frames - 1) // 4 + 1) * (args.height // 16) * (args.width // 16)
+    impl, table = pick_reference_attention(args, AttentionConfig, AttnImplType, ref_attention, m["num_heads"] // sp, tokens)
+    cfg = ModelRuntimeConfig(torch_dtype=torch.bfloat16, parallel_config=pc, device_type="cuda", device_id=local,
+                             attention_config=AttentionConfig.dense_attention(impl))  # fmt: skip
     stage = SingleDitDenoisingStage("dit_denoise", mm, cfg, FlowMatchScheduler("Wan"))
+    if hasattr(model, "set_attention_config"):
+        model.set_attention_config(cfg.attention_config)
     if world > 1:
         stage.parallel_models()
     stage.onload_models_flag = True
@@ -241,7 +315,57 @@ def build_reference(args, layout, world, local):
     def run(latents, steps, posi, nega):
         return stage.process(latents.to(torch.bfloat16), steps, None, posi, nega, None, CFG_SCALE, SIGMA_SHIFT)
 
-    return run, None
+    return run, None, {"ref_attn_impl": impl.name, "ref_attention_ms": table}
+
+
+def time_pipeline_stages(args) -> dict:
+    """The one-off stages of the public pipeline call at the headline shape, each timed once after one warm-up:
+    UMT5-XXL encoding of the positive and the negative prompt (512 tokens each) and the VAE decode of the
+    [1, 16, 21, 90, 160] latents to 81 frames of 720 x 1280. Random-init weights of the real architectures."""
+    out: dict = {}
+    lat = torch.randn(1, 16, (args.frames - 1) // 4 + 1, args.height // 8, args.width // 8, device="cuda")
+    ids = torch.randint(1, 30000, (1, 512), device="cuda")
+    mask = torch.ones(1, 512, dtype=torch.long, device="cuda")
+
+    def timed(fn, warm: int = 1):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3
+
+    if args.impl == "reference":
+        from telefuser.models.wan_video_text_encoder import WanTextEncoder
+        from telefuser.models.wan_video_vae import WanVideoVAE
+    else:
+        from telefuser_b200.models.umt5 import WanTextEncoder
+        from telefuser_b200.models.wan_vae import WanVideoVAE
+    try:
+        with torch.device("meta"):
+            te = WanTextEncoder()
+        te = te.to_empty(device="cuda").to(torch.bfloat16).eval()
+        random_init_(te, seed=5)
+        with torch.no_grad():
+            out["text_encode_s"] = round(timed(lambda: (te(ids, mask), te(ids, mask))), 4)
+        del te
+    except Exception as e:  # noqa: BLE001
+        out["text_encode_s"], out["text_encode_error"] = None, f"{type(e).__name__}: {e}"[:200]
+    torch.cuda.empty_cache()
+    try:
+        vae = WanVideoVAE().to("cuda").to(torch.bfloat16).eval()
+        random_init_(vae, seed=6)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        with torch.no_grad():
+            out["vae_decode_s"] = round(timed(lambda: vae.decode(lat.to(torch.bfloat16), device=dev)), 4)
+        del vae
+    except Exception as e:  # noqa: BLE001
+        out["vae_decode_s"], out["vae_decode_error"] = None, f"{type(e).__name__}: {e}"[:200]
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -252,9 +376,9 @@ def main():
             return
         raise SystemExit("bench.py needs a CUDA device")
     rank, world, local = dist_setup(args.gpus)
-    layout = layout_for(world)
+    layout = layout_for(world, args.layout)
     try:
-        run, native = (build_reference if args.impl == "reference" else build_ours)(args, layout, world, local)
+        run, native, extra = (build_reference if args.impl == "reference" else build_ours)(args, layout, world, local)
     except Exception as e:  # noqa: BLE001 - report why the arm cannot run
         if args.impl == "reference":
             if rank == 0:
@@ -305,14 +429,25 @@ def main():
                "h2d_bytes_per_step": lat_h.numel() * 4 + posi_h.numel() * 2 + nega_h.numel() * 2,
                "d2h_bytes_per_step": res_h.numel() * 4}  # fmt: skip
 
+    stages = None
+    if rank == 0 and not args.no_pipeline_stages:
+        stages = time_pipeline_stages(args)
+    barrier_sync(world)
+
     if rank == 0:
         value = ms_step * SAMPLER_STEPS / 1e3
+        if stages is not None:
+            parts = [stages.get("text_encode_s"), stages.get("vae_decode_s")]
+            stages["denoise_loop_s"] = value
+            stages["total_s"] = None if None in parts else round(value + sum(parts), 3)
+            stages["what"] = "text encode (2 prompts) + 50-step denoising loop + VAE decode = pipeline(prompt, 81, 720, 1280)"
         line = {
             "metric": "wan2.1_t2v_14b_81f_720p_seconds_per_video" if args.model.endswith("14b") else
                       f"{args.model}_seconds_per_video",  # fmt: skip
             "value": value, "unit": "s/video", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (random-init weights, N(0,1) latents and text embeddings)",
+            "dtype": "bf16" if args.quant == "none" else f"bf16 activations, {args.quant} W8A8 block projections",
+            "data": "synthetic (random-init weights, N(0,1) latents and text embeddings)",
             "impl": args.impl, "finite_output": finite,
             "config": {"model": args.model, "global_batch": 1, "seq_len": tokens, "frames": args.frames,
                        "height": args.height, "width": args.width, "sampler_steps": SAMPLER_STEPS,
@@ -320,8 +455,10 @@ def main():
                        "step": "cond+uncond DiT forward + guidance + Euler update",
                        "value_formula": "50 * ms_per_step / 1000 (DiT denoising loop; text encoder and VAE decode not in value)",
                        "l2": "activations per step (>700 MB per tensor) exceed the 126 MB L2; no flush needed"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "pipeline": stages, **extra,
         }  # fmt: skip
+        if args.quant != "none":
+            line["metric"] += f"_{args.quant}"
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

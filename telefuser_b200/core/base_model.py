@@ -99,10 +99,32 @@ class BaseModel(nn.Module):
         enable_sequential_cpu_offload(self, device, **kwargs)
 
     def compile(self, config: CompileConfig | None = None, **kwargs):  # noqa: A003 - mirrors nn.Module.compile
-        """Enables CUDA-graph capture of the block loop (there is no tracing compiler here)."""
+        """Switches the forward to CUDA-graph replay (there is no tracing compiler here): from the next call on,
+        `__call__` goes through a `GraphRunner` whenever `graph_capturable()` says the call can be captured."""
         if config is None or config.enabled:
+            from .cuda_graph import GraphRunner
+
             self.graph_capture = True
+            self._graph_runner = GraphRunner(lambda *a, **k: nn.Module.__call__(self, *a, **k),
+                                             warmup=int(kwargs.get("warmup", 2)))  # fmt: skip
+        else:
+            self.graph_capture, self._graph_runner = False, None
         return self
+
+    def graph_capturable(self) -> bool:
+        """A forward can be replayed from a graph when nothing in it depends on the host between calls: no
+        layer-wise offload (host-driven copies), no pipeline-parallel send / receive, no sequence-parallel exchange
+        (peer barriers pair up with other ranks' launches) and no feature cache (it decides per step on the host)."""
+        from telefuser_b200.feature_cache.base import NoOpCache
+
+        return not (self.async_offload_flag or self.pp_flag or self.usp_flag or self.fsdp_flag
+                    or not isinstance(self.feature_cache, NoOpCache))  # fmt: skip
+
+    def __call__(self, *args, **kwargs):
+        runner = getattr(self, "_graph_runner", None)
+        if runner is not None and self.graph_capture and self.graph_capturable():
+            return runner(*args, **kwargs)
+        return super().__call__(*args, **kwargs)
 
     def mark_compile_static(self, *args, **kwargs) -> None:
         return None

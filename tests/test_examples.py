@@ -63,3 +63,32 @@ def test_streaming_example_serves_a_session_with_random_weights(monkeypatch):
         inner.close_session(sid)
     finally:
         inner.stop()
+
+
+def _run_regression(*extra):
+    import json
+    import subprocess
+    import sys
+
+    cmd = [sys.executable, str(EXAMPLES / "run_examples.py"), *extra]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+    reports = [json.loads(line) for line in res.stdout.splitlines() if line.startswith("{")]
+    return res, reports
+
+
+def test_regression_runner_on_the_oracle_path(tmp_path):
+    """CPU: both runs take the fp32 evaluation, so the videos agree exactly and the stored baseline is matched."""
+    res, reports = _run_regression("--only", "wan21_t2v", "--device", "cpu")
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert reports[0]["passed"] and reports[0]["ssim"] == 1.0 and reports[0]["baseline_drift"] <= 5e-3
+
+
+@pytest.mark.gpu
+def test_regression_runner_bf16_kernels_against_the_fp32_oracle():
+    """GPU: the whole pipelines (text encoder -> denoising -> VAE decode; streaming runtime) in bf16 on the native
+    kernels against their fp32 evaluation from the same seed: PSNR >= 25 dB, SSIM >= 0.85, no NaN, native launches."""
+    res, reports = _run_regression("--device", "cuda:0")
+    assert len(reports) == 2, res.stdout + res.stderr
+    for rep in reports:
+        assert rep["passed"], rep
+        assert rep["native_launches"] > 0 and rep["psnr_db"] >= 25.0
