@@ -57,6 +57,30 @@ class LingBotCacheState:
     def nbytes(self) -> int:
         return sum(c.nbytes() for c in self.kv)
 
+    def snapshot(self, to_cpu: bool = True) -> dict:
+        """Everything a later `restore` needs to continue the session: the filled part of every rolling K/V buffer
+        with its cursors. The text K/V caches are derived from the prompt embedding on the next call, so they are
+        not stored."""
+        def keep(t):
+            return t.detach().to("cpu", copy=True) if to_cpu else t.detach().clone()
+
+        return {"frame_tokens": self.frame_tokens,
+                "kv": [{"k": keep(c.k[:, : c.local_end]), "v": keep(c.v[:, : c.local_end]), "global_end": c.global_end,
+                        "local_end": c.local_end} for c in self.kv]}  # fmt: skip
+
+    def restore(self, snap: dict) -> None:
+        if len(snap["kv"]) != len(self.kv) or snap["frame_tokens"] != self.frame_tokens:
+            raise ValueError("the snapshot was taken from a session of another model or resolution")
+        for c, s in zip(self.kv, snap["kv"]):
+            n = s["local_end"]
+            if n > c.kv_size or s["k"].shape[2:] != c.k.shape[2:]:
+                raise ValueError("the snapshot does not fit this session's K/V buffers")
+            c.k[:, :n].copy_(s["k"])
+            c.v[:, :n].copy_(s["v"])
+            c.global_end, c.local_end = s["global_end"], n
+        for c in self.cross:
+            c.k = c.v = None
+
 
 class CausalSelfAttention(nn.Module):
     def __init__(self, dim, num_heads, local_attn_size=-1, sink_size=0, qk_norm=True, eps=1e-6):

@@ -150,3 +150,85 @@ def quantize_model_fp8_(model: nn.Module, quantize_modules=("*attn*", "*ffn*"), 
             if hasattr(m, attr):
                 setattr(m, attr, None)
     return n
+
+
+# ---------------------------------------------------------------------------------------------------
+# quantised side-car checkpoints
+# ---------------------------------------------------------------------------------------------------
+SIDECAR_FORMAT = "telefuser_b200.quantized_linears.v1"
+
+
+def quantized_state(model: nn.Module) -> dict:
+    """Tensors of the quantised linears only, keyed like a state dict: `<name>.weight` (e4m3 bytes as uint8),
+    `<name>.weight_scale` (fp32 per output channel) or `<name>.weight_scale_mx` (tiled UE8M0 bytes)."""
+    out: dict = {}
+    for name, m in model.named_modules():
+        w = getattr(m, "weight", None)
+        if not isinstance(m, (nn.Linear, LinearFP8)) or w is None or w.dtype != torch.float8_e4m3fn:
+            continue
+        out[f"{name}.weight"] = w.data.view(torch.uint8).cpu()
+        for buf in ("weight_scale", "weight_scale_mx"):
+            if buf in m._buffers:
+                out[f"{name}.{buf}"] = m._buffers[buf].cpu()
+    return out
+
+
+def save_quantized_sidecar(model: nn.Module, path: str) -> int:
+    """Writes the quantised linears of `model` next to its bf16 checkpoint (safetensors), so that a later start
+    loads the 8-bit weights and their scales as they are instead of quantising again. Returns the layer count."""
+    from safetensors.torch import save_file
+
+    state = quantized_state(model)
+    layers = sum(1 for k in state if k.endswith(".weight"))
+    kinds = {"mxfp8" if any(k.endswith("weight_scale_mx") for k in state) else "fp8"} if state else set()
+    save_file({k: v.contiguous() for k, v in state.items()}, path,
+              metadata={"format": SIDECAR_FORMAT, "layers": str(layers), "kind": ",".join(sorted(kinds))})  # fmt: skip
+    return layers
+
+
+def load_quantized_sidecar(model: nn.Module, path: str, strict: bool = True) -> int:
+    """Turns the linears named in the side-car into their quantised form in place (class swap as
+    `quantize_linear_*_`, weights and scales taken from the file). Returns the number of layers converted."""
+    from safetensors import safe_open
+
+    with safe_open(path, framework="pt") as f:
+        meta = f.metadata() or {}
+        if meta.get("format") != SIDECAR_FORMAT:
+            raise ValueError(f"{path} is not a quantised side-car (format {meta.get('format')!r})")
+        state = {k: f.get_tensor(k) for k in f.keys()}
+    modules = dict(model.named_modules())
+    n = 0
+    for key in [k for k in state if k.endswith(".weight")]:
+        name = key[: -len(".weight")]
+        m = modules.get(name)
+        if m is None or not isinstance(m, (nn.Linear, LinearFP8)):
+            if strict:
+                raise KeyError(f"the side-car names {name!r}, which is not a linear layer of this model")
+            continue
+        dev = m.weight.device
+        w8 = state[key]
+        if tuple(w8.shape) != tuple(m.weight.shape):
+            raise ValueError(f"{name}: side-car weight {tuple(w8.shape)} vs layer {tuple(m.weight.shape)}")
+        m.weight = nn.Parameter(w8.view(torch.float8_e4m3fn).to(dev), requires_grad=False)
+        mx = state.get(f"{name}.weight_scale_mx")
+        per_channel = state.get(f"{name}.weight_scale")
+        for buf, val in (("weight_scale_mx", mx), ("weight_scale", per_channel)):
+            if val is None:
+                m._buffers.pop(buf, None)
+            elif buf in m._buffers:
+                m._buffers[buf] = val.to(dev)
+            else:
+                m.register_buffer(buf, val.to(dev))
+        if mx is None and per_channel is None:
+            raise ValueError(f"{name}: the side-car holds no scale for this layer")
+        if type(m) is nn.Linear:
+            m.__class__ = QuantizedLinearMX if mx is not None else QuantizedLinear
+        if hasattr(m.weight, "tfb_scale") and per_channel is None:
+            del m.weight.tfb_scale
+        m._sync()
+        n += 1
+    for m in model.modules():  # fused views cached from the bf16 weights are stale now
+        for attr in ("_qkv", "_kv", "_gu", "_fused"):
+            if hasattr(m, attr):
+                setattr(m, attr, None)
+    return n

@@ -103,6 +103,28 @@ class LingBotWorldFastDenoisingStage(BaseStage):
     def cache_bytes(self, cache_handle: int) -> int:
         return self._caches[cache_handle].model_cache.nbytes()
 
+    # ---- snapshot / resume ------------------------------------------------------------------
+    def snapshot_cache(self, cache_handle: int) -> dict:
+        """Session state of this stage as CPU tensors and plain values (picklable): the K/V history of every block,
+        both random generators and the chunk counter. With `restore_cache` on a fresh stage (after a worker
+        restart, or on another replica) the session continues with the same chunks it would have produced."""
+        st = self._state(cache_handle)
+        return {"chunks_done": st.chunks_done, "noise_shape": list(st.noise_shape), "timesteps": st.timesteps.cpu(),
+                "generator": st.generator.get_state(), "noise_generator": st.noise_generator.get_state(),
+                "model_cache": st.model_cache.snapshot()}  # fmt: skip
+
+    def restore_cache(self, cache_handle: int, snap: dict) -> bool:
+        """The handle must have been registered by `initialize_cache` with the session's shapes."""
+        st = self._state(cache_handle)
+        if tuple(snap["noise_shape"]) != tuple(st.noise_shape):
+            raise ValueError("the snapshot belongs to a session of another resolution or chunk size")
+        st.model_cache.restore(snap["model_cache"])
+        st.generator.set_state(torch.as_tensor(snap["generator"], dtype=torch.uint8))
+        st.noise_generator.set_state(torch.as_tensor(snap["noise_generator"], dtype=torch.uint8))
+        st.timesteps = snap["timesteps"].to(st.timesteps.device)
+        st.chunks_done = int(snap["chunks_done"])
+        return True
+
     def _state(self, cache_handle: int) -> DenoisingCacheState:
         try:
             return self._caches[cache_handle]

@@ -95,3 +95,47 @@ if __name__ == "__main__":
     ref = tiny_wan_denoise()
     got = spawn_tiny_wan_denoise(2, sp_ulysses_degree=2)
     print("single vs ulysses-2 max abs diff:", (ref - got).abs().max().item())
+
+
+# ---------------------------------------------------------------------------------------------------
+# VAE spatial parallelism (tile round-robin with all-reduce, 2-D domain decomposition with all-gather)
+# ---------------------------------------------------------------------------------------------------
+def _tiny_vae(seed: int = 0):
+    from telefuser_b200.models.wan_vae import WanVideoVAE
+    from telefuser_b200.testing.synthetic import random_init_
+
+    torch.manual_seed(seed)
+    return random_init_(WanVideoVAE(dim=8).float(), seed, std=0.05).eval()
+
+
+def vae_parallel_outputs(parallelism: int = 1) -> dict:
+    """Tiled decode / encode and the 2-D split decode of a tiny VAE on fixed inputs; under a process group every rank
+    computes its share and the collectives assemble the full result on every rank."""
+    vae = _tiny_vae()
+    vae.parallelism = parallelism
+    g = torch.Generator().manual_seed(1)
+    latents = torch.randn(1, 16, 2, 12, 10, generator=g)
+    video = torch.rand(1, 3, 5, 64, 48, generator=g) * 2 - 1
+    with torch.no_grad():
+        return {"tiled_decode": vae.tiled_decode(latents, tile_size=(8, 6), tile_stride=(4, 4)),
+                "tiled_encode": vae.tiled_encode(video, tile_size=(6, 4), tile_stride=(2, 2)),
+                "dist_2d": vae.decode_dist_2d(latents, halo=12),
+                "plain": vae.model.decode(latents, vae.scale).clamp(-1, 1)}  # fmt: skip
+
+
+def _vae_rank_main(rank: int, world_size: int, port: int, out_dir: str) -> None:
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world_size))
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world_size)
+    try:
+        torch.save(vae_parallel_outputs(world_size), os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def spawn_vae_parallel(world_size: int) -> list[dict]:
+    from telefuser_b200.utils.system import find_free_port
+
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_vae_rank_main, nprocs=world_size, join=True, args=(world_size, find_free_port(), d))
+        return [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(world_size)]

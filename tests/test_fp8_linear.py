@@ -196,3 +196,28 @@ def test_mxfp8_gemm_matches_fp32_product_of_the_dequantised_operands(M, N, K):
         assert err <= 1.5e-2, (kw.keys(), err)
     full = (x.float() @ w.float().t())
     assert ((TF.linear_mxfp8(x, wq, wsf).float() - full).norm() / full.norm()).item() < 0.05
+
+
+@pytest.mark.parametrize("kind", ["fp8", "mxfp8"])
+def test_quantised_sidecar_round_trip(tmp_path, kind):
+    from telefuser_b200.ops.quant import load_quantized_sidecar, save_quantized_sidecar
+
+    latents, ctx, _ = make_tiny_inputs()
+    t = torch.tensor([500.0])
+    model = make_tiny_model()
+    model.enable_quant(kind)
+    want = model(latents, t, ctx)
+    path = str(tmp_path / "dit.quant.safetensors")
+    assert save_quantized_sidecar(model, path) == 20
+    fresh = make_tiny_model()  # same seed: identical bf16 weights, not quantised
+    assert fresh.blocks[0].ffn[0].weight.dtype != torch.float8_e4m3fn
+    assert load_quantized_sidecar(fresh, path) == 20
+    lin = fresh.blocks[0].ffn[0]
+    assert lin.weight.dtype == torch.float8_e4m3fn
+    assert (lin.weight.tfb_mx_sf is lin.weight_scale_mx) if kind == "mxfp8" else (lin.weight.tfb_scale is lin.weight_scale)
+    assert torch.equal(fresh(latents, t, ctx), want)  # no second quantisation: bit-identical weights and scales
+    with pytest.raises(ValueError, match="not a quantised side-car"):
+        from safetensors.torch import save_file
+
+        save_file({"x": torch.zeros(1)}, str(tmp_path / "other.safetensors"))
+        load_quantized_sidecar(fresh, str(tmp_path / "other.safetensors"))

@@ -1,5 +1,6 @@
 """LingBot-World streaming pipeline on CPU with tiny random-init models: chunks flow through the
 encode -> denoise -> decode actor graph in order, the rolling cache evicts, sessions are isolated."""
+import pytest
 import torch
 
 from telefuser_b200.cache.rolling_kv import RollingKVCache
@@ -123,4 +124,36 @@ def test_interactive_service_session():
     tail = svc.drain(sid2, timeout=30.0)
     assert tail[-1]["type"] == "done" and tail[-1]["cancelled"]
     svc.stop()
+    pipe.close()
+
+
+def test_denoising_session_snapshot_resumes_with_identical_chunks():
+    """Two chunks, snapshot, two more chunks; a fresh stage restored from the snapshot produces the same last two
+    chunks (K/V history, both generators and the chunk counter are carried over)."""
+    import pickle
+
+    pipe = tiny_pipeline()
+    stage = pipe.denoise_stage
+    emb = torch.randn(1, 8, 32)
+    g = torch.Generator().manual_seed(0)
+    conds = [torch.randn(1, 20, 2, 4, 4, generator=g) for _ in range(4)]
+    frame_tokens, kv = 4, 4 * 3
+    init = lambda st, h: st.initialize_cache(h, 1, kv, 8, 10.0, 11, 12, (1, 16, 2, 4, 4), (0, 500), frame_tokens)  # noqa: E731
+    step = lambda st, h, i: st.denoise_and_update_cache(h, conds[i], emb, None, i * 2 * frame_tokens, kv)  # noqa: E731
+    init(stage, 1)
+    first = [step(stage, 1, i) for i in range(2)]
+    snap = pickle.loads(pickle.dumps(stage.snapshot_cache(1)))  # what a worker restart would ship
+    assert snap["chunks_done"] == 2 and snap["model_cache"]["kv"][0]["local_end"] > 0
+    want = [step(stage, 1, i) for i in (2, 3)]
+
+    other = tiny_pipeline().denoise_stage  # same seed: same weights
+    init(other, 7)
+    assert other.restore_cache(7, snap)
+    got = [step(other, 7, i) for i in (2, 3)]
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    assert other._state(7).chunks_done == 4 and torch.isfinite(first[0]).all()
+    bad = dict(snap, noise_shape=[1, 16, 2, 8, 8])
+    with pytest.raises(ValueError, match="another resolution"):
+        other.restore_cache(7, bad)
     pipe.close()

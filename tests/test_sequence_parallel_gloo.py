@@ -142,3 +142,20 @@ def test_context_parallel_remote_runs_gpu():
     import torch
 
     _remote_runs_case("cuda", torch.bfloat16, 128, 2e-2)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_vae_spatial_parallelism_matches_the_single_process_result(world):
+    """Tile round-robin + all-reduce (`_tiled`) and the 2-D domain split + all-gather (`decode_dist_2d`) under a
+    process group: every rank ends with the full tensor, equal to what one process computes."""
+    from telefuser_b200.testing.distributed_checks import spawn_vae_parallel, vae_parallel_outputs
+
+    want = vae_parallel_outputs(1)
+    # a halo as large as the latent makes every rank's tile see the whole input: the split decode is then exact
+    assert (want["dist_2d"] - want["plain"]).abs().max() <= 1e-5
+    outs = spawn_vae_parallel(world)
+    assert len(outs) == world
+    for rank, got in enumerate(outs):
+        for key in ("tiled_decode", "tiled_encode", "dist_2d"):
+            assert got[key].shape == want[key].shape, (rank, key)
+            assert (got[key] - want[key]).abs().max() <= 2e-5, (rank, key, world)
