@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -27,6 +28,8 @@ import torch.distributed as dist
 from telefuser_b200.ops import native
 
 FLAG_BYTES = 4096
+CANARY_BYTES = 256
+CANARY_PATTERN = 0x5A
 
 
 class _DevMem:
@@ -71,6 +74,8 @@ class PeerWorkspace:
         self._epoch = 0
         self._regions: dict[str, tuple[int, tuple, torch.dtype, int]] = {}  # offset, shape, dtype, reserved bytes
         self._cursor = 0
+        self.canaries = os.environ.get("TFB_PEER_CANARY") == "1"
+        self._canaries: dict[str, tuple[int, int]] = {}
         dist.barrier(group=group)  # every mapping exists before anyone stores
 
     # ---- regions ------------------------------------------------------------------
@@ -89,16 +94,32 @@ class PeerWorkspace:
                 hit = self._regions[name] = (hit[0], shape, dtype, hit[3])
             else:
                 self._regions.clear()
+                self._canaries.clear()
                 self._cursor = 0
                 hit = None
         if hit is None:
             off = self._cursor
-            if off + n > self.flag_off:
+            gap = CANARY_BYTES if self.canaries else 0
+            if off + n + gap > self.flag_off:
                 raise MemoryError(f"peer workspace of {self.flag_off} bytes cannot hold region {name!r} ({n} bytes)")
-            self._cursor = -(-(off + n) // 256) * 256
-            hit = self._regions[name] = (off, shape, dtype, self._cursor - off)
+            end = -(-(off + n) // 256) * 256
+            if gap:  # a strip of a known pattern behind the region: peers that store past their slab land here
+                self.local[end : end + gap].fill_(CANARY_PATTERN)
+                self._canaries[name] = (end, gap)
+            self._cursor = end + gap
+            hit = self._regions[name] = (off, shape, dtype, end - off)
         off = hit[0]
         return self.local[off : off + n].view(dtype).view(shape)
+
+    def check_canaries(self) -> None:
+        """With `TFB_PEER_CANARY=1` every region is followed by a strip of a fixed byte pattern; raises when a
+        peer (or this rank) stored past the end of a region. Synchronises the device: for tests and debugging."""
+        for name, (off, n) in getattr(self, "_canaries", {}).items():
+            strip = self.local[off : off + n]
+            bad = (strip != CANARY_PATTERN).nonzero()
+            if bad.numel():
+                raise AssertionError(f"peer region {name!r}: {bad.numel()} bytes behind its end were overwritten "
+                                     f"(first at +{int(bad[0])})")  # fmt: skip
 
     def peer_ptr(self, rank: int, name: str) -> int:
         return self.ptrs[rank] + self._regions[name][0]

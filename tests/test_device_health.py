@@ -20,6 +20,7 @@ def _fake_workspace(nbytes: int) -> symm.PeerWorkspace:
     ws.local = torch.zeros(ws.nbytes, dtype=torch.uint8)
     ws.ptrs = [1 << 20, 2 << 20]
     ws._regions, ws._cursor = {}, 0
+    ws.canaries, ws._canaries = False, {}
     return ws
 
 
@@ -106,3 +107,17 @@ def test_a_stage_fails_loudly_when_a_peer_wait_runs_out():
         assert (torch.ones(4, device="cuda") * 2).sum().item() == 8.0  # the context still answers
     finally:
         native.set_peer_wait_ms(4000)
+
+
+def test_canary_strips_behind_peer_regions():
+    ws = _fake_workspace(64 * 1024)
+    ws.canaries = True
+    a = ws.region("slab_a", (100,), torch.uint8)  # 100 bytes -> strip starts at the next 256-byte boundary
+    b = ws.region("slab_b", (1, 64, 2, 32))
+    assert ws.peer_ptr(0, "slab_b") - ws.peer_ptr(0, "slab_a") == 256 + symm.CANARY_BYTES
+    a.fill_(1)
+    b.fill_(1.0)
+    ws.check_canaries()  # writes inside the regions leave the strips alone
+    ws.local[256 + 5] = 0  # what a store past the end of slab_a would do
+    with pytest.raises(AssertionError, match="slab_a.*first at \\+5"):
+        ws.check_canaries()
