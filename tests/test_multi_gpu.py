@@ -59,3 +59,29 @@ def test_peer_wait_runs_out_with_a_status():
     assert flags[1][0].item() == 1  # the signal to the absent rank was still written
     x = torch.ones(4, device="cuda") * 2  # context still answers
     assert x.sum().item() == 8.0
+
+
+def _run_suite(n: int, backend: str, tmp_path, timeout: int = 1500):
+    import json
+    import subprocess
+    import sys
+
+    from telefuser_b200.utils.system import find_free_port
+
+    out = tmp_path / f"suite_{n}.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(find_free_port()), "-m", "telefuser_b200.testing.multi_gpu_suite", "--backend", backend,
+           "--out", str(out)]  # fmt: skip
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    assert out.is_file(), res.stdout[-3000:] + res.stderr[-3000:]
+    return res.returncode, json.loads(out.read_text())
+
+
+@two_gpus
+@pytest.mark.multi_gpu
+def test_every_multi_gpu_path_on_all_visible_gpus(tmp_path):
+    """All layouts (CFG x Ulysses, Ulysses, ring, Ulysses x ring, TP, PP x Ulysses, sharded weights), the peer-memory
+    kernels against collectives and oracles, expert parallelism and the VAE split, on 2, 4 or 8 ranks in one launch."""
+    n = max(k for k in (2, 4, 8) if k <= torch.cuda.device_count())
+    code, rep = _run_suite(n, "nccl", tmp_path)
+    assert code == 0 and rep["passed"], rep["failures"]

@@ -159,3 +159,21 @@ def test_vae_spatial_parallelism_matches_the_single_process_result(world):
         for key in ("tiled_decode", "tiled_encode", "dist_2d"):
             assert got[key].shape == want[key].shape, (rank, key)
             assert (got[key] - want[key]).abs().max() <= 2e-5, (rank, key, world)
+
+
+def test_multi_gpu_suite_host_logic_on_two_cpu_ranks(tmp_path):
+    """The layout sweep and the VAE split of the multi-GPU verification program, on gloo ranks."""
+    import json
+    import subprocess
+    import sys
+
+    from telefuser_b200.utils.system import find_free_port
+
+    out = tmp_path / "suite.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(find_free_port()), "-m", "telefuser_b200.testing.multi_gpu_suite", "--backend", "gloo",
+           "--out", str(out)]  # fmt: skip
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    rep = json.loads(out.read_text())
+    assert rep["passed"] and {"cfg2/collectives", "u2/collectives", "r2/collectives", "tp2/collectives"} <= set(rep["rank0"]["layouts"])
