@@ -65,6 +65,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (pinned host <-> device) measurement")
     ap.add_argument("--layout", default="auto", help="auto | single | cfg2 | u8 | r8 | u4r2 | tp8 | cfg2u4 | ...")
     ap.add_argument("--quant", default="none", choices=["none", "fp8", "mxfp8"])
+    ap.add_argument("--attn", default="bf16", choices=["bf16", "int8"], help="int8: Q.K^T scores on int8 operands")
     ap.add_argument("--ref-attn", default="auto", choices=["auto", "sdpa", "cudnn", "fa2"])
     ap.add_argument("--no-pipeline-stages", action="store_true", help="skip the text-encode / VAE-decode timings")
     return ap.parse_args()
@@ -213,6 +214,10 @@ def build_ours(args, layout, world, local):
                         sp_ulysses_degree=layout["sp_ulysses_degree"], sp_ring_degree=layout["sp_ring_degree"],
                         tp_degree=layout["tp_degree"])  # fmt: skip
     cfg = ModelRuntimeConfig(torch_dtype=torch.bfloat16, parallel_config=pc, device_type="cuda", device_id=local)
+    if args.attn == "int8":
+        from telefuser_b200.core.config import AttentionConfig, AttnImplType
+
+        cfg.attention_config = AttentionConfig(attn_impl=AttnImplType.TCGEN05_Q8)
     stage = WanDenoisingStage("dit_denoise", None, cfg, FlowMatchScheduler("Wan"), dit=model)
     if world > 1:
         stage.parallel_models()
@@ -267,6 +272,9 @@ def build_reference(args, layout, world, local):
     from telefuser.ops.attention.attention_impl import attention as ref_attention
     from telefuser.pipelines.wan_video.single_dit_denoising import SingleDitDenoisingStage
 
+    if args.attn != "bf16":
+        raise RuntimeError("the reference's SageAttention kernels come from its tf_kernel extension, which cannot be built "
+                           "offline here")  # fmt: skip
     if args.quant != "none":
         raise RuntimeError("the reference's quantised linears need its tf_kernel extension or vLLM kernels, neither of "
                            "which can be built offline here")  # fmt: skip
@@ -446,7 +454,8 @@ def main():
                       f"{args.model}_seconds_per_video",  # fmt: skip
             "value": value, "unit": "s/video", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16" if args.quant == "none" else f"bf16 activations, {args.quant} W8A8 block projections",
+            "dtype": ("bf16" if args.quant == "none" else f"bf16 activations, {args.quant} W8A8 block projections")
+                     + ("" if args.attn == "bf16" else ", int8 attention scores"),  # fmt: skip
             "data": "synthetic (random-init weights, N(0,1) latents and text embeddings)",
             "impl": args.impl, "finite_output": finite,
             "config": {"model": args.model, "global_batch": 1, "seq_len": tokens, "frames": args.frames,
@@ -459,6 +468,8 @@ def main():
         }  # fmt: skip
         if args.quant != "none":
             line["metric"] += f"_{args.quant}"
+        if args.attn != "bf16":
+            line["metric"] += f"_attn_{args.attn}"
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

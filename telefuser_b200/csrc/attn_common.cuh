@@ -26,12 +26,24 @@ struct AttnParams {
   int max_blocks;
   int head_dim;  // 64 or 128
   int causal;    // key j visible to query row i when j <= i + (Skv - Sq)
+  // Int8 scores: q / k operands are int8, q_scale fp32 [B, H, Sq] (one per query token and head) and k_scale
+  // fp32 [B, H] (one per head) restore their magnitudes; both null for bf16 operands.
+  const float* q_scale;
+  const float* k_scale;
 };
 
 constexpr int ATT_BM = 128, ATT_BN = 128, ATT_D = 128;
 constexpr int ATT_TILE_BYTES = 128 * 128 * 2;  // 32 KB: two 16 KB boxes of [128 rows][64 cols]
 constexpr int ATT_BOX_BYTES = 16384;
 constexpr float ATT_RESCALE_THRESHOLD = 8.0f;
+
+// 3-D tensor map over [B][S][H*128] int8 with a [1][128][128] box and 128B swizzle (ld / bs in elements = bytes).
+inline int make_qk8_tmap(CUtensorMap* m, const void* base, long ld, long bs, int B, int S, int H) {
+  uint64_t dims[3] = {static_cast<uint64_t>(H) * 128, static_cast<uint64_t>(S), static_cast<uint64_t>(B)};
+  uint64_t str[2] = {static_cast<uint64_t>(ld), static_cast<uint64_t>(bs)};
+  uint32_t box[3] = {128, 128, 1};
+  return make_tmap(m, base, TM_U8, 3, dims, str, box, TM_SW_128);
+}
 
 // 3-D tensor map over [B][S][H*head_dim] bf16 with a [1][128][64] box and 128B swizzle.
 inline int make_qkv_tmap(CUtensorMap* m, const void* base, long ld, long bs, int B, int S, int H, int head_dim = ATT_D) {

@@ -1,5 +1,6 @@
 // Flash-attention forward for sm_100a with every query row shared by two threads
-// (bf16, head_dim 64 or 128, optional causal mask, optional peer-store epilogue, optional block sparsity).
+// (bf16, head_dim 64 or 128, optional causal mask, optional peer-store epilogue, optional block sparsity;
+// optionally Q.K^T on int8 operands with per-token / per-head scales, P.V staying in bf16).
 //
 // One CTA owns 256 query rows of one (batch, head) as two independent 128-row tiles that share every
 // K/V tile. 640 threads:
@@ -26,10 +27,14 @@
 
 namespace tfb {
 
-template <int HD>
+// QK8: Q and K arrive as int8 (one 16 KB box of [128 rows][128 bytes] per tile), S = Q.K^T is accumulated in
+// int32 by `tcgen05.mma.kind::i8` and scaled per row in the softmax; V and P stay bf16.
+template <int HD, bool QK8 = false>
 struct SplitCfg {
-  static constexpr int TILE_BYTES = 128 * HD * 2;  // one 128-row tile of Q, K or V
-  static constexpr int BOXES = HD / 64;            // 16 KB boxes of [128 rows][64 columns] per tile
+  static constexpr int TILE_BYTES = 128 * HD * 2;  // one 128-row bf16 tile of Q, K or V (a ring slot)
+  static constexpr int QK_TILE_BYTES = QK8 ? 128 * HD : TILE_BYTES;  // bytes of a Q or K tile
+  static constexpr int BOXES = HD / 64;            // 16 KB boxes of [128 rows][64 columns] per bf16 tile
+  static constexpr int QK_BOXES = QK8 ? 1 : BOXES;
   static constexpr int KV_SLOTS = 4;
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = 2 * TILE_BYTES;
@@ -40,11 +45,12 @@ struct SplitCfg {
   static constexpr int OC = HD / 2;        // accumulator columns per thread
 };
 
-template <int HD, int POLY, bool PEER, bool SPARSE, bool CAUSAL>
+template <int HD, int POLY, bool PEER, bool SPARSE, bool CAUSAL, bool QK8 = false>
 __global__ void __launch_bounds__(640, 1)
     attn_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
-  using C = SplitCfg<HD>;
+  using C = SplitCfg<HD, QK8>;
+  static_assert(!QK8 || HD == 128, "the int8 score path is built for head_dim 128");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* mx_buf = reinterpret_cast<float*>(smem + C::MX_OFF);
@@ -107,9 +113,9 @@ __global__ void __launch_bounds__(640, 1)
         for (int st = 0; st < 2; ++st) {
           uint8_t* qd = smem + C::Q_OFF + st * C::TILE_BYTES;
           const int q0 = (q_pair * 2 + st) * ATT_BM;
-          mbar_expect_tx(&q_full[st], C::TILE_BYTES);
+          mbar_expect_tx(&q_full[st], C::QK_TILE_BYTES);
 #pragma unroll
-          for (int x = 0; x < C::BOXES; ++x)
+          for (int x = 0; x < C::QK_BOXES; ++x)
             tma_load_3d(qd + x * ATT_BOX_BYTES, &tmQ, &q_full[st], h * HD + x * 64, q0, b);
         }
         for (int n = 0; n < 2 * n_kv; ++n) {
@@ -119,27 +125,39 @@ __global__ void __launch_bounds__(640, 1)
           uint8_t* dst = smem + C::KV_OFF + slot * C::TILE_BYTES;
           const CUtensorMap* tm = (n & 1) ? &tmV : &tmK;
           const int j = SPARSE ? __ldg(blk_list + (n >> 1)) : (n >> 1);
-          mbar_expect_tx(&kv_full[slot], C::TILE_BYTES);
+          if (QK8 && !(n & 1)) {  // int8 K: one box of 128 bytes per row
+            mbar_expect_tx(&kv_full[slot], C::QK_TILE_BYTES);
+            tma_load_3d(dst, tm, &kv_full[slot], h * HD, j * ATT_BN, b);
+          } else {
+            mbar_expect_tx(&kv_full[slot], C::TILE_BYTES);
 #pragma unroll
-          for (int x = 0; x < C::BOXES; ++x)
-            tma_load_3d(dst + x * ATT_BOX_BYTES, tm, &kv_full[slot], h * HD + x * 64, j * ATT_BN, b);
+            for (int x = 0; x < C::BOXES; ++x)
+              tma_load_3d(dst + x * ATT_BOX_BYTES, tm, &kv_full[slot], h * HD + x * 64, j * ATT_BN, b);
+          }
         }
       }
       __syncwarp();
     } else if (warp == 17) {
       // ------------------------------ MMA issuer ------------------------------
-      constexpr uint32_t idesc_qk = make_idesc(128, 128, 1, 1, 0, 0);
+      constexpr uint32_t idesc_qk = QK8 ? make_idesc_i8(128, 128) : make_idesc(128, 128, 1, 1, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(128, HD, 1, 1, 0, 1);  // B (= V) is MN-major
       auto slot_addr = [&](int n) { return smem_u32(smem + C::KV_OFF + (n & (C::KV_SLOTS - 1)) * C::TILE_BYTES); };
       auto issue_qk = [&](int st, int j) {
         const uint32_t q_addr = smem_u32(smem + C::Q_OFF + st * C::TILE_BYTES);
         const uint32_t k_addr = slot_addr(2 * j);
         const uint32_t d_tmem = tmem_base + st * 128;
+        if (QK8) {  // 32 int8 elements (32 bytes of the 128-byte row) per instruction
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * ATT_BOX_BYTES + (kk & 3) * 32;
-          umma_f16_ss(d_tmem, make_desc_k_sw128(q_addr + off), make_desc_k_sw128(k_addr + off), idesc_qk,
-                      kk ? 1u : 0u);
+          for (int kk = 0; kk < HD / 32; ++kk)
+            umma_i8_ss(d_tmem, make_desc_k_sw128(q_addr + kk * 32), make_desc_k_sw128(k_addr + kk * 32), idesc_qk,
+                       kk ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * ATT_BOX_BYTES + (kk & 3) * 32;
+            umma_f16_ss(d_tmem, make_desc_k_sw128(q_addr + off), make_desc_k_sw128(k_addr + off), idesc_qk,
+                        kk ? 1u : 0u);
+          }
         }
       };
       auto issue_pv = [&](int st, int j) {
@@ -210,6 +228,12 @@ __global__ void __launch_bounds__(640, 1)
     float* mx_other = mx_buf + ((st * 2 + (half ^ 1)) * 128 + row);
     constexpr int MX_PARITY_STRIDE = 2 * 2 * 128;
     float m_used = -INFINITY, l = 0.f;
+    // Score scale of this row in the log2 domain. Int8 scores carry the row's Q scale and the head's K scale.
+    float row_scale = p.scale_log2;
+    if (QK8) {
+      const long bh = static_cast<long>(b) * p.H + h;
+      row_scale *= __ldg(p.k_scale + bh) * (grow < p.Sq ? __ldg(p.q_scale + bh * p.Sq + grow) : 0.f);
+    }
     bool ok = true;
     int j = 0;
     for (; j < n_kv; ++j) {
@@ -222,6 +246,22 @@ __global__ void __launch_bounds__(640, 1)
       tmem_ld_32x32(tmem_s, s[0]);
       tmem_ld_32x32(tmem_s + 32, s[1]);
       tmem_ld_wait();
+      if (QK8) {
+        // int32 -> fp32 without the conversion pipe: |s| <= 128 * 127^2 < 2^22, so adding the bit pattern of
+        // 1.5 * 2^23 gives the float 1.5 * 2^23 + s exactly, and the subtraction is exact too.
+        const uint64_t neg_magic2 = f2_pack(-12582912.f, -12582912.f);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const uint64_t f2 = f2_add(f2_pack(__uint_as_float(s[c][i] + 0x4B400000u), __uint_as_float(s[c][i + 1] + 0x4B400000u)),
+                                       neg_magic2);
+            float lo, hi;
+            f2_unpack(f2, lo, hi);
+            s[c][i] = __float_as_uint(lo);
+            s[c][i + 1] = __float_as_uint(hi);
+          }
+      }
       const int key0 = (SPARSE ? __ldg(blk_list + j) : j) * ATT_BN + half * 64;  // key index of my first column
       int kv_valid = p.Skv - key0;
       if (CAUSAL) kv_valid = min(kv_valid, grow + causal_off - key0 + 1);
@@ -256,7 +296,7 @@ __global__ void __launch_bounds__(640, 1)
       tc_fence_after();
       const float mx = fmaxf(mx_part, mx_other[(j & 1) * MX_PARITY_STRIDE]);
       // A fully masked row keeps m at a finite floor so that exp2(-inf - m) is 0, not NaN.
-      const float m_new = fmaxf(fmaxf(m_used, mx * p.scale_log2), -1e30f);
+      const float m_new = fmaxf(fmaxf(m_used, mx * row_scale), -1e30f);
       if (j == 0) {
         m_used = m_new;
       } else {
@@ -279,7 +319,7 @@ __global__ void __launch_bounds__(640, 1)
       }
       // p = 2^(s*scale - m): packed fp32x2 FMAs, exp2 split between the MUFU pipe and a cubic on the
       // FMA pipe, packed row-sum accumulation.
-      const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
+      const uint64_t scale2 = f2_pack(row_scale, row_scale);
       const uint64_t negm2 = f2_pack(-m_used, -m_used);
       uint64_t ps[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
@@ -372,19 +412,25 @@ __global__ void __launch_bounds__(640, 1)
   if (warp == 17) tmem_dealloc(tmem_base, 512);
 }
 
-template <int HD, int POLY, bool PEER, bool SPARSE, bool CAUSAL>
+template <int HD, int POLY, bool PEER, bool SPARSE, bool CAUSAL, bool QK8 = false>
 static int launch_split_impl(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
                              int B, cudaStream_t st) {
   static bool attr_set[TFB_MAX_DEVICES] = {false};
-  auto* kern = attn_split_kernel<HD, POLY, PEER, SPARSE, CAUSAL>;
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), SplitCfg<HD>::SMEM_BYTES, attr_set)) return rc;
+  auto* kern = attn_split_kernel<HD, POLY, PEER, SPARSE, CAUSAL, QK8>;
+  constexpr int SMEM = SplitCfg<HD, QK8>::SMEM_BYTES;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), SMEM, attr_set)) return rc;
   dim3 grid((p.Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), p.H, B);
-  kern<<<grid, 640, SplitCfg<HD>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  kern<<<grid, 640, SMEM, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 
 int launch_attn_split(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, int B,
                       cudaStream_t st) {
+  if (p.q_scale) {  // int8 scores
+    if (p.head_dim != 128 || p.blk_idx || p.n_peers > 0 || !p.k_scale) return TFB_ERR_BAD_SHAPE;
+    return p.causal ? launch_split_impl<128, 1, false, false, true, true>(tq, tk, tv, p, B, st)
+                    : launch_split_impl<128, 1, false, false, false, true>(tq, tk, tv, p, B, st);
+  }
   if (p.head_dim == 64) {
     if (p.blk_idx || p.n_peers > 0) return TFB_ERR_BAD_SHAPE;
     return p.causal ? launch_split_impl<64, 1, false, false, true>(tq, tk, tv, p, B, st)

@@ -43,6 +43,8 @@ static int attn_fwd_impl(const void* q, long ldq, long bsq, const void* k, long 
   p.max_blocks = max_blocks;
   p.head_dim = D;
   p.causal = causal;
+  p.q_scale = nullptr;
+  p.k_scale = nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (variant >= 20 && variant <= 22) {
     if (D != 128 || causal) return TFB_ERR_BAD_SHAPE;
@@ -110,6 +112,50 @@ extern "C" int tfb_attn_fwd_peer(const void* q, long ldq, long bsq, const void* 
   p.max_blocks = 0;
   p.head_dim = 128;
   p.causal = 0;
+  p.q_scale = nullptr;
+  p.k_scale = nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return (variant >= 20 && variant <= 22) ? launch_attn2(tq, tk, tv, p, B, st) : launch_attn_split(tq, tk, tv, p, B, st);
+}
+
+// Attention with int8 scores (the role of the reference's SageAttention "qk int8, pv fp16" kernels): q8 / k8 are
+// int8 [B, S, H, 128] (strides in bytes = elements), q_scale fp32 [B, H, Sq], k_scale fp32 [B, H]; v and out are
+// bf16. softmax((q8 . k8) * q_scale * k_scale * scale) @ v, the product accumulated in int32 by the tensor core.
+extern "C" int tfb_attn_fwd_qk8(const void* q8, long ldq, long bsq, const void* k8, long ldk, long bsk, const void* v,
+                                long ldv, long bsv, const float* q_scale, const float* k_scale, void* out, long ldo,
+                                long bso, int B, int H, int Sq, int Skv, int causal, float scale, void* stream) {
+  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || !q_scale || !k_scale) return TFB_ERR_BAD_SHAPE;
+  if (causal && Skv < Sq) return TFB_ERR_BAD_SHAPE;
+  if ((ldq | ldk | bsq | bsk) % 16 || (ldv | ldo | bsv | bso) % 8) return TFB_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(q8) | reinterpret_cast<uintptr_t>(k8) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return TFB_ERR_BAD_SHAPE;
+  CUtensorMap tq, tk, tv;
+  int e;
+  if ((e = make_qk8_tmap(&tq, q8, ldq, bsq, B, Sq, H))) return e;
+  if ((e = make_qk8_tmap(&tk, k8, ldk, bsk, B, Skv, H))) return e;
+  if ((e = make_qkv_tmap(&tv, v, ldv, bsv, B, Skv, H, 128))) return e;
+  AttnParams p;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.bso = bso;
+  p.lse = nullptr;
+  p.H = H;
+  p.Sq = Sq;
+  p.Skv = Skv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_word();
+  p.poly = 1;
+  for (int i = 0; i < 8; ++i) p.peer_out[i] = nullptr;
+  p.n_peers = 0;
+  p.rows_per_rank = 1;
+  p.head_off = 0;
+  p.blk_idx = nullptr;
+  p.blk_cnt = nullptr;
+  p.max_blocks = 0;
+  p.head_dim = 128;
+  p.causal = causal;
+  p.q_scale = q_scale;
+  p.k_scale = k_scale;
+  return launch_attn_split(tq, tk, tv, p, B, static_cast<cudaStream_t>(stream));
 }

@@ -11,6 +11,7 @@
 
 #include "tfb_api.h"
 #include "tfb_common.cuh"
+#include "tfb_host.h"
 
 namespace tfb {
 

@@ -49,6 +49,17 @@ int tfb_attn_fwd_sparse(const void* q, long ldq, long bsq, const void* k, long l
                         long bsv, void* out, long ldo, long bso, float* lse, int B, int H, int Sq, int Skv, float scale,
                         const int* blk_idx, const int* blk_cnt, int max_blocks, int variant, void* stream);
 
+// Attention with int8 scores: softmax((q8 . k8) * q_scale[b,h,i] * k_scale[b,h] * scale) @ v. q8 / k8 int8
+// [B, S, H, 128] (strides in elements), v / out bf16, q_scale fp32 [B, H, Sq], k_scale fp32 [B, H].
+int tfb_attn_fwd_qk8(const void* q8, long ldq, long bsq, const void* k8, long ldk, long bsk, const void* v, long ldv,
+                     long bsv, const float* q_scale, const float* k_scale, void* out, long ldo, long bso, int B, int H,
+                     int Sq, int Skv, int causal, float scale, void* stream);
+// Operand preparation for it (attn_quant.cu): per-channel sums and per-head max |k| of K; int8 quantisation of Q
+// (per token and head) and of mean-centred K (per head).
+int tfb_attn_k_stats(const void* k, long ld, long bs, int B, int S, int H, float* sums, float* amax, void* stream);
+int tfb_attn_quant_int8(const void* x, long ld, long bs, void* out, int B, int S, int H, int is_k, const float* mean,
+                        const float* k_scale, float* scale_out, void* stream);
+
 // LayerNorm over the last dim (C), optional affine (bf16 w/b), then optional
 // modulation y = y * (1 + scale) + shift with fp32 scale/shift taken from row
 // (r / rows_per_mod) * ldmod of `shift` / `scale`.

@@ -188,6 +188,7 @@ class WanSelfAttention(nn.Module):
         self.norm_q = RMSNormWeight(dim, eps)
         self.norm_k = RMSNormWeight(dim, eps)
         self._qkv = None
+        self.attention_config = None  # set through the model's `set_attention_config`
         self.sparse_ctx = None  # (RadialMaskMap, decay factor, dense?) set by the model for every forward
 
     def fused_qkv(self):
@@ -214,7 +215,8 @@ class WanSelfAttention(nn.Module):
 
             o = radial_attention(q, k, v, self.sparse_ctx[0], self.sparse_ctx[1])
         else:
-            o = TF.attention(q, k, v)
+            cfg = self.attention_config
+            o = TF.attention(q, k, v, quant="int8" if cfg is not None and cfg.attn_impl.quantized() else None)
         return o.reshape(B, S, C)
 
 

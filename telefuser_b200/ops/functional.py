@@ -353,14 +353,20 @@ def _pad_head_dim(t, D_to):
     return F.pad(t, (0, D_to - t.shape[-1]))
 
 
-def attention(q, k, v, scale=None, return_lse=False, variant=0, causal=False, mask=None):
+def attention(q, k, v, scale=None, return_lse=False, variant=0, causal=False, mask=None, quant=None):
     """Attention, layout BSHD: q [B, Sq, H, D], k / v [B, Skv, H, D] -> [B, Sq, H, D].
+    `quant="int8"` computes the scores on int8 operands (`attention_int8`; no LSE output).
 
     CUDA bf16 / fp16 inputs with D <= 128 run on the tcgen05 kernel (head dims other than 64 / 128 are zero-padded
     to the next of the two, fp16 is computed in bf16); `causal` is handled inside the kernel. A general boolean
     `mask` (True = visible) and head dims above 128 take the fp32 evaluation in query blocks, so that no
     [Sq, Skv] score matrix is ever held for the whole sequence. CPU tensors always take the fp32 evaluation."""
     D = q.shape[-1]
+    if quant is not None:
+        if quant != "int8" or return_lse or mask is not None:
+            raise ValueError("quantised attention: quant='int8', without LSE output or a mask")
+        if D == 128:
+            return attention_int8(q, k, v, scale, causal)
     if not _native(q) or q.dtype not in (torch.bfloat16, torch.float16) or D > 128 or mask is not None or D % 8 \
             or (causal and k.shape[1] < q.shape[1]):  # fmt: skip
         blk = None
@@ -398,6 +404,80 @@ def attention(q, k, v, scale=None, return_lse=False, variant=0, causal=False, ma
     if in_dtype != torch.bfloat16:
         out = out.to(in_dtype)
     return (out, lse) if return_lse else out
+
+
+def quantize_qk_int8_reference(q, k):
+    """q, k [B, S, H, D] -> (q8 int8, q_scale fp32 [B, H, Sq], k8 int8, k_scale fp32 [B, H], k_mean fp32 [B, H, D]).
+
+    Q: one scale per token and head (max |q| / 127). K: the per-channel mean over the tokens is removed (softmax is
+    invariant to it), then one scale per head, taken from the bound max |k| + max |mean| so that it needs no
+    second pass over K."""
+    qf, kf = q.float(), k.float()
+    qs = (qf.abs().amax(-1) / 127.0).clamp_min(1e-12)  # [B, S, H]
+    q8 = torch.round(qf / qs.unsqueeze(-1)).clamp(-127, 127).to(torch.int8)
+    mean = kf.mean(dim=1)  # [B, H, D]
+    ks = ((kf.abs().amax(dim=(1, 3)) + mean.abs().amax(-1)) / 127.0).clamp_min(1e-12)  # [B, H]
+    k8 = torch.round((kf - mean.unsqueeze(1)) / ks[:, None, :, None]).clamp(-127, 127).to(torch.int8)
+    return q8, qs.permute(0, 2, 1).contiguous(), k8, ks, mean
+
+
+def quantize_qk_int8(q, k):
+    """As `quantize_qk_int8_reference`, by the native kernels on CUDA bf16 inputs with head_dim 128."""
+    B, Sq, H, D = q.shape
+    if not _native(q) or q.dtype != torch.bfloat16 or D != 128:
+        return quantize_qk_int8_reference(q, k)
+    lib, st = native.load(), native.stream_ptr()
+    Skv = k.shape[1]
+
+    def prep(t):
+        S = t.shape[1]
+        if t.stride(-1) != 1 or t.stride(2) != D or (B > 1 and t.stride(0) % 8) or t.stride(1) % 8:
+            t = t.contiguous()
+        return t, t.stride(1), (t.stride(0) if B > 1 else S * t.stride(1))
+
+    (q, ldq, bsq), (k, ldk, bsk) = prep(q), prep(k)
+    dev = q.device
+    sums = torch.empty(B, H * D, device=dev, dtype=torch.float32)
+    amax = torch.empty(B, H, device=dev, dtype=torch.float32)
+    native.check(lib.tfb_attn_k_stats(k.data_ptr(), ldk, bsk, B, Skv, H, sums.data_ptr(), amax.data_ptr(), st), "tfb_attn_k_stats")
+    mean = (sums / Skv).view(B, H, D)
+    ks = ((amax + mean.abs().amax(-1)) / 127.0).clamp_min(1e-12).contiguous()
+    q8 = torch.empty(B, Sq, H, D, device=dev, dtype=torch.int8)
+    k8 = torch.empty(B, Skv, H, D, device=dev, dtype=torch.int8)
+    qs = torch.empty(B, H, Sq, device=dev, dtype=torch.float32)
+    native.check(lib.tfb_attn_quant_int8(q.data_ptr(), ldq, bsq, q8.data_ptr(), B, Sq, H, 0, None, None, qs.data_ptr(), st),
+                 "tfb_attn_quant_int8")  # fmt: skip
+    native.check(lib.tfb_attn_quant_int8(k.data_ptr(), ldk, bsk, k8.data_ptr(), B, Skv, H, 1, mean.data_ptr(), ks.data_ptr(),
+                                         None, st), "tfb_attn_quant_int8")  # fmt: skip
+    return q8, qs, k8, ks, mean
+
+
+def attention_int8(q, k, v, scale=None, causal=False):
+    """Attention with int8 scores: Q and K are quantised on the fly (per token / per head, K mean-centred), the score
+    matrix is accumulated in int32 on the tensor core (`tcgen05.mma.kind::i8`), softmax and P.V run as in the bf16
+    kernel. The place of the reference's SageAttention int8-QK modes (telefuser/ops/attention/attention_impl.py:245-300).
+    CPU tensors and shapes the kernel does not cover evaluate the same quantised maths in fp32."""
+    B, Sq, H, D = q.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not _native(q) or q.dtype != torch.bfloat16 or D != 128 or (causal and k.shape[1] < Sq):
+        q8, qs, k8, ks, _ = quantize_qk_int8_reference(q, k)
+        s = torch.einsum("bqhd,bkhd->bhqk", q8.float(), k8.float()) * qs.unsqueeze(-1) * ks[:, :, None, None] * scale
+        if causal:
+            Skv = k.shape[1]
+            rows = torch.arange(Sq, device=q.device).unsqueeze(1) + (Skv - Sq)
+            s = s.masked_fill(torch.arange(Skv, device=q.device).unsqueeze(0) > rows, float("-inf"))
+        return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, dim=-1), v.float()).to(q.dtype)
+    q8, qs, k8, ks, _ = quantize_qk_int8(q, k)
+    Skv = k.shape[1]
+    if v.stride(-1) != 1 or v.stride(2) != D or (B > 1 and v.stride(0) % 8) or v.stride(1) % 8:
+        v = v.contiguous()
+    ldv, bsv = v.stride(1), (v.stride(0) if B > 1 else Skv * v.stride(1))
+    out = torch.empty(B, Sq, H, D, device=q.device, dtype=torch.bfloat16)
+    code = native.load().tfb_attn_fwd_qk8(q8.data_ptr(), H * D, Sq * H * D, k8.data_ptr(), H * D, Skv * H * D, v.data_ptr(), ldv,
+                                          bsv, qs.data_ptr(), ks.data_ptr(), out.data_ptr(), H * D, Sq * H * D, B, H, Sq, Skv,
+                                          int(bool(causal)), scale, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_attn_fwd_qk8")
+    return out
 
 
 def merge_attn_states_reference(o1, lse1, o2, lse2):

@@ -102,6 +102,11 @@ def _declare(lib) -> None:
                          c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "tfb_gemm_mxfp8": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                            c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+        "tfb_attn_fwd_qk8": [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_void_p,
+                             c_void_p, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "tfb_attn_k_stats": [c_void_p, c_long, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "tfb_attn_quant_int8": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                c_void_p, c_void_p],
         "tfb_quant_fp8_rowwise": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "tfb_nf4_dequant": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "tfb_rmsnorm_modulate": [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_float, c_void_p, c_void_p,

@@ -210,3 +210,30 @@ def test_wan_block_native_matches_reference_path():
     finally:
         TF.set_force_reference(False)
     assert rel(got, ref) < 3e-2
+
+
+def test_attention_int8_scores():
+    """Quantisers against their PyTorch statement, then the int8-score kernel against (a) the fp32 evaluation of the
+    same quantised operands (kernel arithmetic) and (b) full-precision attention (what the quantisation costs)."""
+    torch.manual_seed(0)
+    B, Sq, Skv, H = 2, 300, 515, 3
+    q = (torch.randn(B, Sq, H, 128, device="cuda") * 1.5).bfloat16()
+    k = (torch.randn(B, Skv, H, 128, device="cuda") + 0.7).bfloat16()  # a common offset: what the mean removal is for
+    v = torch.randn(B, Skv, H, 128, device="cuda").bfloat16()
+    q8, qs, k8, ks, mean = TF.quantize_qk_int8(q, k)
+    rq8, rqs, rk8, rks, rmean = TF.quantize_qk_int8_reference(q, k)
+    assert torch.allclose(qs, rqs, rtol=1e-5) and torch.allclose(ks, rks, rtol=1e-4) and torch.allclose(mean, rmean, atol=2e-3)
+    assert (q8.int() - rq8.int()).abs().max() <= 1 and (q8 != rq8).float().mean() < 1e-3
+    assert (k8.int() - rk8.int()).abs().max() <= 1 and (k8 != rk8).float().mean() < 2e-2
+    for causal in (False, True):
+        kk, vv = (k, v) if not causal else (k[:, :Sq], v[:, :Sq])
+        got = TF.attention(q, kk, vv, quant="int8", causal=causal)
+        g8, gs, gk8, gks, _ = TF.quantize_qk_int8(q, kk)
+        s = torch.einsum("bqhd,bkhd->bhqk", g8.float(), gk8.float()) * gs.unsqueeze(-1) * gks[:, :, None, None] / 128**0.5
+        if causal:
+            s = s.masked_fill(torch.ones(Sq, Sq, device="cuda", dtype=torch.bool).triu(1), float("-inf"))
+        same_operands = torch.einsum("bhqk,bkhd->bqhd", s.softmax(-1), vv.float())
+        assert rel(got, same_operands) < 1e-2, causal
+        assert rel(got, TF.attention_reference(q, kk, vv, causal=causal)) < 4e-2, causal
+    cpu = TF.attention_int8(q.cpu().float(), k.cpu().float(), v.cpu().float())
+    assert rel(cpu, TF.attention_reference(q.cpu().float(), k.cpu().float(), v.cpu().float())) < 4e-2
