@@ -4,6 +4,13 @@ causal 14B DiT + Wan VAE running on the streaming actor graph (encode -> denoise
     python bench_stream.py --chunks 8 --warmup-chunks 2            # one GPU, all stages on it
     python bench_stream.py --gpus 4 --chunks 8                     # denoise on 4 GPUs (Ulysses), VAE on GPU 0
 
+`--impl reference` would run the reference's own streaming denoising stage on the same shapes; its stage imports
+the reference's UniPC scheduler, which needs the `diffusers` package, and its pipeline needs the UMT5 tokenizer
+files - neither is on this machine, so that arm prints an `unavailable` line with the import error.
+`--session-seconds T` sizes the timed session by duration (chunks = T x fps / frames per chunk) instead of `--chunks`;
+`--lookahead N` is the number of chunks the client may submit ahead of the newest output (1 = interactive use:
+a control takes effect at most one chunk period after the chunk in flight).
+
 Workload (the reference's published setting, examples/lingbot/README.md:181-193): 832x464, chunks of
 4 latent frames (16 video frames), 4 denoising steps + the clean-latent commit per chunk, attention
 window 18 latent frames with 6 sink frames, bf16 DiT, random-init weights, synthetic image / prompt
@@ -48,14 +55,24 @@ def build_pipeline(args, device: str):
         return ModelRuntimeConfig(device_type="cuda", device_id=0, torch_dtype=dtype,
                                   parallel_config=parallel or ParallelConfig())  # fmt: skip
 
+    from telefuser_b200.pipelines.lingbot_world_v2 import resolve_stage_devices
+
+    dit_devices, enc_dev, dec_dev = resolve_stage_devices(args.gpus)
     par = None
-    if args.gpus > 1:
-        par = ParallelConfig(device_ids=list(range(args.gpus)), sp_ulysses_degree=args.gpus)
+    if len(dit_devices) > 1:
+        par = ParallelConfig(device_ids=dit_devices, sp_ulysses_degree=len(dit_devices))
+    args.placement = {"dit": dit_devices, "vae_encode": enc_dev, "vae_decode": dec_dev}
+
+    def rcd(dev_id):
+        c = rc()
+        c.device_id = dev_id
+        return c
+
     cfg = LingBotWorldFastPipelineConfig(
-        dit_config=rc(par), vae_encode_config=rc(), vae_decode_config=rc(), text_encoding_config=rc(),
+        dit_config=rc(par), vae_encode_config=rcd(enc_dev), vae_decode_config=rcd(dec_dev), text_encoding_config=rc(),
         chunk_size=args.chunk_size, local_attn_size=args.window, sink_size=args.sink,
         timestep_indices=tuple(int(i * 1000 / args.steps) for i in range(args.steps)), max_sequence_length=512,
-        enable_denoising_parallel=args.gpus > 1)  # fmt: skip
+        enable_denoising_parallel=par is not None, edge_capacity=max(1, args.lookahead))  # fmt: skip
     pipe = LingBotWorldFastPipeline(device=device, torch_dtype=dtype)
     pipe.init(mm, cfg)
     return pipe
@@ -69,7 +86,8 @@ def run_session(pipe, args, chunks: int, seed: int):
     arrivals = []
     t0 = time.perf_counter()
     video, metrics = pipe.generate_video("", img, n, args.height, args.width, seed=seed, prompt_emb=emb,
-                                         on_chunk=lambda i, f: arrivals.append(time.perf_counter()))  # fmt: skip
+                                         on_chunk=lambda i, f: arrivals.append(time.perf_counter()),
+                                         bind_controls_late=True)  # fmt: skip
     total = time.perf_counter() - t0
     periods = [b - a for a, b in zip(arrivals, arrivals[1:])]
     return dict(video_shape=list(video.shape), finite=bool(torch.isfinite(video.float()).all()), total_s=total,
@@ -95,7 +113,26 @@ def main() -> None:
     ap.add_argument("--sink", type=int, default=6)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--model", default="14b", choices=["14b", "small"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--session-seconds", type=float, default=0.0, help="size the timed session by duration")
+    ap.add_argument("--lookahead", type=int, default=1, help="chunks submitted ahead of the newest output")
     args = ap.parse_args()
+    if args.impl == "reference":
+        import os
+        import sys
+
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref"))
+        try:
+            from telefuser.pipelines.lingbot_world_fast.denoising import LingBotWorldFastDenoisingStage  # noqa: F401
+            from telefuser.pipelines.lingbot_world_fast.pipeline import LingBotWorldFastPipeline  # noqa: F401
+
+            why = "its pipeline needs the UMT5 tokenizer files (google/umt5-xxl), which are not on this machine"
+        except Exception as e:  # noqa: BLE001
+            why = f"{type(e).__name__}: {e}"[:240]
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return
+    if args.session_seconds > 0:
+        args.chunks = max(2, int(round(args.session_seconds * 16 / (args.chunk_size * 4))))
     device = "cuda:0"
     torch.cuda.set_device(0)
     from telefuser_b200.ops import native
@@ -119,12 +156,17 @@ def main() -> None:
         "vae_decode_s_per_chunk_p50": round(statistics.median(busy["decode"]), 4),
         "vae_encode_s_per_chunk_p50": round(statistics.median(busy["encode"]), 4),
         "control_to_output_p50_s": r["metrics"]["control_to_output_p50_s"],
+        "control_bound_to_output_p50_s": r["metrics"].get("control_bound_to_output_p50_s"),
+        "control_bound_to_output_in_chunk_periods": (round(r["metrics"]["control_bound_to_output_p50_s"] / p50, 2)
+                                                     if r["metrics"].get("control_bound_to_output_p50_s") else None),
+        "session_s": round(r["total_s"], 2), "lookahead_chunks": args.lookahead,
+        "stage_placement": getattr(args, "placement", None),
         "dtype": "bf16", "data": "synthetic (random-init weights, random image, prompt embedding and camera walk)",
         "finite_output": r["finite"], "gpu_launches": native.launch_count(),
         "config": {"model": f"lingbot-world-fast causal DiT ({args.model})", "height": args.height, "width": args.width,
                    "chunk_latent_frames": args.chunk_size, "frames_per_chunk": r["frames_per_chunk"],
                    "denoise_steps": args.steps, "window_frames": args.window, "sink_frames": args.sink,
-                   "parallelism": "single" if args.gpus == 1 else f"ulysses{args.gpus} (denoise) + 1 GPU VAE"},
+                   "parallelism": "single" if args.gpus == 1 else f"ulysses{len(args.placement['dit'])} (denoise), VAE encode on GPU {args.placement['vae_encode']}, decode on GPU {args.placement['vae_decode']}"},
         "reference_published": {"2xH100_dit_s_per_chunk": 1.587, "2xH100_chunk_period_s": 2.096,
                                 "4xH100_dit_s_per_chunk": 0.911, "4xH100_chunk_period_s": 1.615},
     }  # fmt: skip

@@ -11,8 +11,10 @@
 //   warps 8..15  softmax group 1 (query tile 1)
 //   warp  16     TMA loader: both Q tiles once, then K0 V0 K1 V1 ... through a 4-slot ring
 //   warp  17     tcgen05.mma issuer and TMEM owner
-//   warps 18,19  only donate registers (setmaxnreg works on whole warpgroups; a scheduler partition holds
-//                16384 registers, i.e. four softmax warps of 112 plus one of these of 40)
+//   warps 18,19  only donate registers (setmaxnreg works on whole warpgroups)
+// Register budget: the CTA is launched with 640 x 96 registers and `setmaxnreg` only moves registers inside that
+// allocation (an increase waits until other warps of the CTA have released enough, for ever if they never do), so
+// the split must balance: 512 x 112 + 128 x 32 = 640 x 96.
 // TMEM (512 columns): S0 | S1 | O0 | O1. P (bf16) is written over the first 64 columns of its S tile
 // and fed to the P.V MMA from TMEM. The two threads of a row exchange their partial row maxima through
 // shared memory and a 64-thread mbarrier (bounded wait) once per K/V tile; that exchange also orders the
@@ -44,6 +46,11 @@ struct SplitCfg {
   static constexpr int O_COL = 256;        // first accumulator column in TMEM
   static constexpr int OC = HD / 2;        // accumulator columns per thread
 };
+
+constexpr int SPLIT_THREADS = 640, SPLIT_LAUNCH_REGS = 96, SPLIT_SOFTMAX_REGS = 112, SPLIT_OTHER_REGS = 32;
+static_assert(512 * SPLIT_SOFTMAX_REGS + 128 * SPLIT_OTHER_REGS <= SPLIT_THREADS * SPLIT_LAUNCH_REGS,
+              "setmaxnreg.inc would wait for registers that no warp of the CTA ever releases");
+static_assert(SPLIT_LAUNCH_REGS == (65536 / SPLIT_THREADS) / 8 * 8, "launch registers follow from the launch bound");
 
 template <int HD, int POLY, bool PEER, bool SPARSE, bool CAUSAL, bool QK8 = false>
 __global__ void __launch_bounds__(640, 1)
@@ -103,7 +110,7 @@ __global__ void __launch_bounds__(640, 1)
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp >= 16) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
     if (warp == 16) {
       // ------------------------------ TMA loader ------------------------------
       if (lane == 0 && n_kv > 0) {

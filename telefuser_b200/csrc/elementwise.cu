@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(256) layernorm_modulate_kernel(
     const __nv_bfloat16* __restrict__ x, long ldx, __nv_bfloat16* __restrict__ out, long ldo, int rows, int C,
     float eps, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
     const float* __restrict__ shift, const float* __restrict__ scale, long ldmod, int rows_per_mod) {
-  __shared__ float red[8];
+  __shared__ float red[16];
   const int row = blockIdx.x;
   if (row >= rows) return;
   const int nvec = C >> 3;
@@ -78,20 +78,31 @@ __global__ void __launch_bounds__(256) layernorm_modulate_kernel(
       for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
     }
   }
-  const float mean = block_sum<256>(s, red) / C;
+  // Mean and variance from one pass over the registers and ONE block reduction (sum and sum of squares side by
+  // side): a row costs two barriers instead of four. fp32 sums of bf16 data; var = E[x^2] - mean^2, floored at 0.
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int vi = threadIdx.x + i * 256;
-    if (vi < nvec) {
+  for (int i = 0; i < NV; ++i)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float d = v[i][e] - mean;
-        ss += d * d;
-      }
+    for (int e = 0; e < 8; ++e) ss = fmaf(v[i][e], v[i][e], ss);
+  s = warp_sum(s);
+  ss = warp_sum(ss);
+  {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+      red[warp] = s;
+      red[8 + warp] = ss;
+    }
+    __syncthreads();
+    s = ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      s += red[i];
+      ss += red[8 + i];
     }
   }
-  const float rstd = rsqrtf(block_sum<256>(ss, red) / C + eps);
+  const float mean = s / C;
+  const float rstd = rsqrtf(fmaxf(ss / C - mean * mean, 0.f) + eps);
   const long mrow = static_cast<long>(row / rows_per_mod) * ldmod;
   uint4* orow = reinterpret_cast<uint4*>(out + row * ldo);
 #pragma unroll

@@ -282,8 +282,11 @@ class LingBotWorldFastPipeline(BasePipeline):
     @torch.no_grad()
     def generate_video(self, prompt, image, num_frames: int = 61, height: int = 480, width: int = 832, seed: int = 0,
                        poses: torch.Tensor | None = None, prompt_emb=None, on_chunk: Callable | None = None,
-                       timeout_s: float = 3600.0):  # fmt: skip
-        """Returns (frames [1, 3, T, H, W], metrics). `poses`: [latent_frames, 4, 4] camera path (default: seeded walk)."""
+                       timeout_s: float = 3600.0, bind_controls_late: bool = False):  # fmt: skip
+        """Returns (frames [1, 3, T, H, W], metrics). `poses`: [latent_frames, 4, 4] camera path (default: seeded walk).
+        `bind_controls_late`: hand each chunk's control to the denoiser as a provider that is read when the chunk is
+        admitted (what the interactive service does); `metrics["control_bound_to_output_p50_s"]` is then the time
+        from that moment to the chunk's frames."""
         rt = self._create_initialized_session(prompt, image, num_frames, height, width, seed, prompt_emb)
         latent_frames = rt.chunk_count * rt.chunk_size
         if poses is None:
@@ -291,6 +294,15 @@ class LingBotWorldFastPipeline(BasePipeline):
         controls = rt.control_builder.build_sequence(poses, rt.control_builder.context.intrinsics)
         session = self.runtime.create_session(rt)
         frames, nxt, t0 = {}, 0, time.monotonic()
+        bound_at, latencies = {}, []
+
+        def provider(i):
+            def bind():
+                bound_at[i] = time.monotonic()
+                return controls[i]
+
+            return bind
+
         try:
             while len(frames) < rt.chunk_count:
                 if time.monotonic() - t0 > timeout_s:
@@ -298,17 +310,22 @@ class LingBotWorldFastPipeline(BasePipeline):
                 if self.runtime.status(session) == StreamingSessionStatus.FAILED:
                     raise RuntimeError("LingBot streaming session failed") from self.runtime.error(session)
                 progressed = False
-                if nxt < rt.chunk_count and self.runtime.try_submit_chunk(session, nxt, controls[nxt]):
+                if nxt < rt.chunk_count and self.runtime.try_submit_chunk(
+                        session, nxt, provider(nxt) if bind_controls_late else controls[nxt]):  # fmt: skip
                     nxt += 1
                     progressed = True
                 for idx, f in self.runtime.poll_frames(session):
                     frames[idx] = f
                     progressed = True
+                    if idx in bound_at:
+                        latencies.append(time.monotonic() - bound_at[idx])
                     if on_chunk is not None:
                         on_chunk(idx, f)
                 if not progressed:
                     time.sleep(0.001)
             metrics = self.runtime.metrics(session)
+            if latencies:
+                metrics["control_bound_to_output_p50_s"] = sorted(latencies)[len(latencies) // 2]
         finally:
             self.release_session(session, cancel=len(frames) < rt.chunk_count)
         video = torch.cat([frames[i] for i in range(rt.chunk_count)], dim=2)

@@ -66,6 +66,8 @@ class LingBotWorldFastSessionState:
     emitted: int = 0
     created_at: float = field(default_factory=time.time)
     finished: bool = False
+    control_bound_at: dict = field(default_factory=dict)  # chunk index -> monotonic time its control was sampled
+    control_latency_s: list = field(default_factory=list)  # control sampled -> frames emitted, per chunk
 
 
 def frame_num_for_duration(max_duration_seconds: float, fps: int, chunk_size: int) -> int:
@@ -268,9 +270,17 @@ class LingBotWorldFastService:
                     break
                 progressed = False
                 if state.submitted < total and runtime.can_submit_chunk(stream):
-                    control, keys = self._next_control(state, state.submitted)
-                    if runtime.try_submit_chunk(stream, state.submitted, control):
-                        pending[state.submitted] = keys
+                    idx = state.submitted
+
+                    def bind_control(idx=idx):
+                        # Latest-wins: called when the denoiser admits the chunk, not when the slot was reserved, so
+                        # the keys held at that moment steer the chunk (one chunk period closer to its output).
+                        control, keys = self._next_control(state, idx)
+                        pending[idx] = keys
+                        state.control_bound_at[idx] = time.monotonic()
+                        return control
+
+                    if runtime.try_submit_chunk(stream, idx, bind_control):
                         state.submitted += 1
                         progressed = True
                 for idx, frames in runtime.poll_frames(stream):
@@ -284,6 +294,10 @@ class LingBotWorldFastService:
             metrics = {}
             try:
                 metrics = runtime.metrics(stream)
+                lat = sorted(state.control_latency_s)
+                if lat:
+                    metrics["control_bound_to_output_p50_s"] = lat[len(lat) // 2]
+                    metrics["control_bound_to_output_max_s"] = lat[-1]
             except Exception:  # noqa: BLE001 - metrics are best effort
                 pass
             self._enqueue(state, {"type": "done", "session_id": state.session_id, "cancelled": cancelled, "chunks": state.emitted,
@@ -308,8 +322,13 @@ class LingBotWorldFastService:
         if state.config.hud:
             arr = overlay_control_hud(arr, keys)
         state.emitted += 1
+        bound = state.control_bound_at.pop(idx, None)
+        latency = None if bound is None else time.monotonic() - bound
+        if latency is not None:
+            state.control_latency_s.append(latency)
         self._enqueue(state, {"type": "frames", "session_id": state.session_id, "chunk_index": idx, "frames": arr, "controls": keys,
-                              "fps": state.config.fps, "elapsed_s": time.time() - state.created_at})  # fmt: skip
+                              "fps": state.config.fps, "elapsed_s": time.time() - state.created_at,
+                              "control_to_output_s": latency})  # fmt: skip
 
     def close_session(self, session_id: str, timeout: float | None = None) -> None:
         state = self._sessions.get(session_id)
