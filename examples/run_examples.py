@@ -189,9 +189,12 @@ def run_case(name: str, device: str, baseline: dict, update: bool) -> dict:
         fail.append(f"peak memory {report['peak_mib']} MiB above {mib_max}")
     if device.startswith("cuda") and report["native_launches"] == 0:
         fail.append("the production run launched no native kernel")
+    kind = device.split(":")[0]
     base = baseline.get(name)
-    if update or base is None:
-        baseline[name] = report["oracle"]
+    if base is not None and base.get("device", "cpu") != kind and not update:
+        report["baseline"] = f"recorded on {base.get('device', 'cpu')}: not compared on {kind}"
+    elif update or base is None:
+        baseline[name] = {**report["oracle"], "device": kind}
         report["baseline"] = "stored"
     else:
         drift = max(abs(report["oracle"][k] - base[k]) for k in ("mean", "std", "abs_mean"))

@@ -74,7 +74,7 @@ def bench_attn(t: Timer, seq: int, heads: int, compare: bool, variant: int = 0, 
                causal: bool = False) -> None:  # fmt: skip
     q, k, v = (torch.randn(1, seq, heads, head_dim, device="cuda").bfloat16() for _ in range(3))
     flops = 4.0 * seq * seq * heads * head_dim * (0.5 if causal else 1.0)
-    variants = [variant] if variant >= 0 else [30, 31, 32, 20, 21, 22]  # -1: every kernel form and exp2 share
+    variants = [variant] if variant >= 0 else [30, 31, 20, 21, 40, 41, 42]  # -1: every kernel form and exp2 share
     for vr in variants:
         report("attn_fwd_tcgen05", t(lambda: TF.attention(q, k, v, variant=vr, causal=causal)), flops, seq=seq,
                heads=heads, head_dim=head_dim, causal=causal, variant=vr)  # fmt: skip
