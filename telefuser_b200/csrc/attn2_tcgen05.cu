@@ -31,13 +31,7 @@ constexpr int A2_SMEM_BYTES = A2_BAR_OFF + 256 + 1024;
 // PEER: the epilogue stores each output row into the buffer of the rank that owns the token.
 // SPARSE: block-sparse attention. Each CTA (256 query rows of one head) visits only the 128-key blocks
 //         listed for it in p.blk_idx (p.blk_cnt of them); everything else is the dense pipeline.
-// STREAM: the softmax of every K/V tile after the first works through the 128 score columns in four chunks
-//         without first reducing the row maximum over all of them: chunk c+1 is loaded from TMEM while chunk c is
-//         exponentiated against the maximum of the EARLIER tiles, P is handed to the tensor core in two halves (the
-//         P.V product of the first 64 keys runs while the second 64 are still in exp2), and the decision to raise the
-//         maximum (and rescale the accumulator) is taken one tile late, when the accumulator is at rest anyway.
-//         Scaling O after old-scale P was added is exact: everything in O is relative to the same maximum.
-template <int POLY, bool PEER = false, bool SPARSE = false, bool STREAM = false>
+template <int POLY, bool PEER = false, bool SPARSE = false>
 __global__ void __launch_bounds__(384, 1)
     attn2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -50,8 +44,7 @@ __global__ void __launch_bounds__(384, 1)
   uint64_t* s_full = bars + 10;    // [2]
   uint64_t* p_ready = bars + 12;   // [2]
   uint64_t* o_final = bars + 14;   // [2]
-  uint64_t* p_half = bars + 16;    // [2] STREAM: first 64 columns of P are in TMEM
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -67,7 +60,6 @@ __global__ void __launch_bounds__(384, 1)
       mbar_init(&q_full[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&p_ready[s], 128);
-      mbar_init(&p_half[s], 128);
       mbar_init(&o_final[s], 1);
     }
     for (int s = 0; s < A2_KV_SLOTS; ++s) {
@@ -132,12 +124,12 @@ __global__ void __launch_bounds__(384, 1)
                     kk ? 1u : 0u);
       }
     };
-    auto issue_pv = [&](int st, int j, int k0, int k1) {  // key blocks [16*k0, 16*k1) of the tile
+    auto issue_pv = [&](int st, int j) {
       const uint32_t v_addr = slot_addr(2 * j + 1);
       const uint32_t o_tmem = tmem_base + 256 + st * 128;
       const uint32_t p_tmem = tmem_base + st * 128;
 #pragma unroll
-      for (int kk = k0; kk < k1; ++kk)
+      for (int kk = 0; kk < 8; ++kk)
         umma_f16_ts(o_tmem, p_tmem + kk * 8, make_desc_mn_sw128(v_addr + kk * 2048, ATT_BOX_BYTES), idesc_pv,
                     (j | kk) ? 1u : 0u);
     };
@@ -160,22 +152,13 @@ __global__ void __launch_bounds__(384, 1)
       if (!mbar_wait_warp(&kv_full[nv & (A2_KV_SLOTS - 1)], (nv / A2_KV_SLOTS) & 1, ctx, 23)) break;
       if (has_next && !mbar_wait_warp(&kv_full[nk & (A2_KV_SLOTS - 1)], (nk / A2_KV_SLOTS) & 1, ctx, 24)) break;
       for (int st = 0; st < 2 && ok; ++st) {
-        if (STREAM) {
-          if (!mbar_wait_warp(&p_half[st], j & 1, ctx, 26)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          if (lane == 0) issue_pv(st, j, 0, 4);
-          __syncwarp();
-        }
         if (!mbar_wait_warp(&p_ready[st], j & 1, ctx, 25)) {
           ok = false;
           break;
         }
         tc_fence_after();
         if (lane == 0) {
-          issue_pv(st, j, STREAM ? 4 : 0, 8);
+          issue_pv(st, j);
           if (has_next) {
             issue_qk(st, j + 1);
             umma_commit(&s_full[st]);
@@ -203,115 +186,6 @@ __global__ void __launch_bounds__(384, 1)
     const uint32_t tmem_o = tmem_base + lane_addr + 256 + st * 128;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    if (STREAM) {
-      // Maximum of 32 scores: two chains of 3-input max.
-      auto chunk_max = [](const uint32_t (&c)[32]) {
-        float a = __uint_as_float(c[0]), b2 = __uint_as_float(c[1]);
-#pragma unroll
-        for (int i = 2; i < 32; i += 4) {
-          a = fmax3(a, __uint_as_float(c[i]), __uint_as_float(c[i + 1]));
-          if (i + 3 < 32) b2 = fmax3(b2, __uint_as_float(c[i + 2]), __uint_as_float(c[i + 3]));
-        }
-        return fmaxf(a, b2);
-      };
-      auto mask_tail = [](uint32_t (&c)[32], int valid) {  // columns >= valid become -inf
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i >= valid) c[i] = 0xff800000u;
-      };
-      float m_pending = -INFINITY;  // maximum (scaled) over all tiles seen, the candidate for m_used
-      for (int j = 0; j < n_kv; ++j) {
-        if (!mbar_wait_warp(&s_full[st], j & 1, ctx, 30)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const int kv_valid = p.Skv - (SPARSE ? __ldg(blk_list + j) : j) * ATT_BN;
-        uint32_t s[2][32];
-        if (j == 0) {
-          // First tile: there is no earlier maximum to exponentiate against, so reduce it over the tile first.
-          float mx = -INFINITY;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tmem_ld_32x32(tmem_s + c * 32, s[0]);
-            tmem_ld_wait_on(s[0]);
-            if (kv_valid < ATT_BN) mask_tail(s[0], kv_valid - c * 32);
-            mx = fmaxf(mx, chunk_max(s[0]));
-          }
-          m_used = fmaxf(mx * p.scale_log2, -1e30f);
-          m_pending = m_used;
-        } else if (__any_sync(0xffffffffu, (m_pending - m_used) > ATT_RESCALE_THRESHOLD)) {
-          // Decision deferred from the previous tile. S(j) is ready, so every P.V issued so far has completed and
-          // O is at rest; O and l hold sums relative to m_used (the previous tile included), one factor fits all.
-          const float alpha = fast_exp2(m_used - m_pending);
-          m_used = m_pending;
-          l *= alpha;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32(tmem_o + c * 32, o);
-            tmem_ld_wait_on(o);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32(tmem_o + c * 32, o);
-          }
-        }
-        const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
-        const uint64_t negm2 = f2_pack(-m_used, -m_used);
-        uint64_t ps[4] = {0ull, 0ull, 0ull, 0ull};
-        float mx_run = -INFINITY;
-        tmem_ld_32x32(tmem_s, s[0]);
-        tmem_ld_wait_on(s[0]);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t(&cur)[32] = s[c & 1];
-          if (c < 3) tmem_ld_32x32(tmem_s + (c + 1) * 32, s[(c + 1) & 1]);  // lands while this chunk is in exp2
-          if (kv_valid < ATT_BN) mask_tail(cur, kv_valid - c * 32);
-          const float mxc = chunk_max(cur);
-          mx_run = fmaxf(mx_run, mxc);
-          // A score more than 2^100 above the running maximum would overflow before the deferred rescale: clamp it.
-          if (__any_sync(0xffffffffu, mxc * p.scale_log2 - m_used > 100.f)) {
-            const float cap = (m_used + 100.f) / p.scale_log2;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) cur[i] = __float_as_uint(fminf(__uint_as_float(cur[i]), cap));
-          }
-          uint32_t t[16];
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(cur[2 * k]), __uint_as_float(cur[2 * k + 1])), scale2,
-                                       negm2);
-            float p0, p1;
-            if ((POLY == 1 && (k & 3) == 3) || (POLY == 2 && (k & 1))) {
-              exp2_poly_pair(x2, p0, p1);
-            } else {
-              float x0, x1;
-              f2_unpack(x2, x0, x1);
-              p0 = fast_exp2(x0);
-              p1 = fast_exp2(x1);
-            }
-            ps[k & 3] = f2_add(ps[k & 3], f2_pack(p0, p1));
-            t[k] = pack_bf16x2(p0, p1);
-          }
-          tmem_st_32x16(tmem_s + c * 16, t);
-          if (c == 1) {  // keys 0..63 of this tile can be multiplied with V now
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&p_half[st]);
-          }
-          if (c < 3) tmem_ld_wait_on(s[(c + 1) & 1]);
-        }
-        {
-          float a0, a1, b0, b1;
-          f2_unpack(f2_add(ps[0], ps[1]), a0, a1);
-          f2_unpack(f2_add(ps[2], ps[3]), b0, b1);
-          l += (a0 + a1) + (b0 + b1);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&p_ready[st]);
-        m_pending = fmaxf(m_used, fmaxf(mx_run * p.scale_log2, -1e30f));
-      }
-    } else
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait_warp(&s_full[st], j & 1, ctx, 30)) {
         ok = false;
@@ -452,14 +326,13 @@ __global__ void __launch_bounds__(384, 1)
   if (warp == 9) tmem_dealloc(tmem_base, 512);
 }
 
-template <int POLY, bool STREAM = false>
+template <int POLY>
 static int launch_attn2_impl(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
                              int B, cudaStream_t st) {
   static bool attr_set[TFB_MAX_DEVICES] = {false};
-  auto* kern = attn2_fwd_kernel<POLY, false, false, STREAM>;
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), A2_SMEM_BYTES, attr_set)) return rc;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&attn2_fwd_kernel<POLY>), A2_SMEM_BYTES, attr_set)) return rc;
   dim3 grid((p.Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), p.H, B);
-  kern<<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
+  attn2_fwd_kernel<POLY><<<grid, 384, A2_SMEM_BYTES, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 
@@ -485,13 +358,6 @@ int launch_attn2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap
                  cudaStream_t st) {
   if (p.blk_idx) return launch_attn2_sparse(tq, tk, tv, p, B, st);
   if (p.n_peers > 0) return launch_attn2_peer(tq, tk, tv, p, B, st);
-  if (p.stream) {
-    switch (p.poly) {
-      case 0: return launch_attn2_impl<0, true>(tq, tk, tv, p, B, st);
-      case 2: return launch_attn2_impl<2, true>(tq, tk, tv, p, B, st);
-      default: return launch_attn2_impl<1, true>(tq, tk, tv, p, B, st);
-    }
-  }
   switch (p.poly) {
     case 0: return launch_attn2_impl<0>(tq, tk, tv, p, B, st);
     case 2: return launch_attn2_impl<2>(tq, tk, tv, p, B, st);

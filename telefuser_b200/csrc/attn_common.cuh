@@ -30,7 +30,6 @@ struct AttnParams {
   // fp32 [B, H] (one per head) restore their magnitudes; both null for bf16 operands.
   const float* q_scale;
   const float* k_scale;
-  int stream;  // one-thread-per-row kernel: chunk-streamed softmax with the deferred rescale (attn2_tcgen05.cu)
 };
 
 constexpr int ATT_BM = 128, ATT_BN = 128, ATT_D = 128;

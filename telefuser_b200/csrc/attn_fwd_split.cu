@@ -435,21 +435,21 @@ int launch_attn_split(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
                       cudaStream_t st) {
   if (p.q_scale) {  // int8 scores
     if (p.head_dim != 128 || p.blk_idx || p.n_peers > 0 || !p.k_scale) return TFB_ERR_BAD_SHAPE;
-    return p.causal ? launch_split_impl<128, 1, false, false, true, true>(tq, tk, tv, p, B, st)
-                    : launch_split_impl<128, 1, false, false, false, true>(tq, tk, tv, p, B, st);
+    return p.causal ? launch_split_impl<128, 0, false, false, true, true>(tq, tk, tv, p, B, st)
+                    : launch_split_impl<128, 0, false, false, false, true>(tq, tk, tv, p, B, st);
   }
   if (p.head_dim == 64) {
     if (p.blk_idx || p.n_peers > 0) return TFB_ERR_BAD_SHAPE;
-    return p.causal ? launch_split_impl<64, 1, false, false, true>(tq, tk, tv, p, B, st)
-                    : launch_split_impl<64, 1, false, false, false>(tq, tk, tv, p, B, st);
+    return p.causal ? launch_split_impl<64, 0, false, false, true>(tq, tk, tv, p, B, st)
+                    : launch_split_impl<64, 0, false, false, false>(tq, tk, tv, p, B, st);
   }
-  if (p.blk_idx) return launch_split_impl<128, 1, false, true, false>(tq, tk, tv, p, B, st);
-  if (p.n_peers > 0) return launch_split_impl<128, 1, true, false, false>(tq, tk, tv, p, B, st);
-  if (p.causal) return launch_split_impl<128, 1, false, false, true>(tq, tk, tv, p, B, st);
+  if (p.blk_idx) return launch_split_impl<128, 0, false, true, false>(tq, tk, tv, p, B, st);
+  if (p.n_peers > 0) return launch_split_impl<128, 0, true, false, false>(tq, tk, tv, p, B, st);
+  if (p.causal) return launch_split_impl<128, 0, false, false, true>(tq, tk, tv, p, B, st);
   switch (p.poly) {
-    case 0: return launch_split_impl<128, 0, false, false, false>(tq, tk, tv, p, B, st);
+    case 1: return launch_split_impl<128, 1, false, false, false>(tq, tk, tv, p, B, st);
     case 2: return launch_split_impl<128, 2, false, false, false>(tq, tk, tv, p, B, st);
-    default: return launch_split_impl<128, 1, false, false, false>(tq, tk, tv, p, B, st);
+    default: return launch_split_impl<128, 0, false, false, false>(tq, tk, tv, p, B, st);
   }
 }
 

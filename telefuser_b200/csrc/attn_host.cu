@@ -1,9 +1,11 @@
 // C entry points of the attention kernels: argument checks, tensor maps, kernel selection.
 //
-// `variant` selects the kernel for benchmarks and regression tests: 0 = default (two threads per query row,
-// a quarter of the exponentials on the FMA pipe), 30 / 31 / 32 = the same with none / a quarter / half of them
-// there, 20 / 21 / 22 = one thread per query row (head_dim 128, no causal mask) with those shares, 40 / 41 / 42 = that
-// kernel with the chunk-streamed softmax (P handed over in halves, rescale decided one tile late).
+// `variant` selects the kernel for benchmarks and regression tests: 30 / 31 / 32 = two threads per query row with
+// none / a quarter / half of the exponentials on the FMA pipe, 20 / 21 / 22 = one thread per query row (head_dim
+// 128, no causal mask) with those shares. 0 = default: all exponentials on the MUFU pipe (the polynomial shares
+// measured slower in both kernels), and for plain dense head_dim-128 attention the kernel by key count: one thread
+// per row below 48k keys (987 vs 933 TFLOP/s at 16k keys x 12 heads), two threads per row from there on (1066 -
+// 1076 vs 1016 - 1039 TFLOP/s at 75,600 keys x 5 heads).
 #include "attn_common.cuh"
 #include "tfb_api.h"
 
@@ -34,9 +36,8 @@ static int attn_fwd_impl(const void* q, long ldq, long bsq, const void* k, long 
   p.Skv = Skv;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word();
-  p.poly = (variant >= 20 && variant <= 22) ? variant - 20 : (variant >= 30 && variant <= 32) ? variant - 30
-           : (variant >= 40 && variant <= 42) ? variant - 40 : 1;
-  p.stream = variant >= 40 && variant <= 42;
+  p.poly = (variant >= 20 && variant <= 22) ? variant - 20 : (variant >= 30 && variant <= 32) ? variant - 30 : 0;
+  if (variant == 0 && D == 128 && !causal && !blk_idx && Skv < 49152) variant = 20;
   for (int i = 0; i < 8; ++i) p.peer_out[i] = nullptr;
   p.n_peers = 0;
   p.rows_per_rank = 1;
@@ -49,7 +50,7 @@ static int attn_fwd_impl(const void* q, long ldq, long bsq, const void* k, long 
   p.q_scale = nullptr;
   p.k_scale = nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if ((variant >= 20 && variant <= 22) || p.stream) {
+  if (variant >= 20 && variant <= 22) {
     if (D != 128 || causal) return TFB_ERR_BAD_SHAPE;
     return launch_attn2(tq, tk, tv, p, B, st);
   }
@@ -117,7 +118,6 @@ extern "C" int tfb_attn_fwd_peer(const void* q, long ldq, long bsq, const void* 
   p.causal = 0;
   p.q_scale = nullptr;
   p.k_scale = nullptr;
-  p.stream = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return (variant >= 20 && variant <= 22) ? launch_attn2(tq, tk, tv, p, B, st) : launch_attn_split(tq, tk, tv, p, B, st);
 }
@@ -161,6 +161,5 @@ extern "C" int tfb_attn_fwd_qk8(const void* q8, long ldq, long bsq, const void* 
   p.causal = causal;
   p.q_scale = q_scale;
   p.k_scale = k_scale;
-  p.stream = 0;
   return launch_attn_split(tq, tk, tv, p, B, static_cast<cudaStream_t>(stream));
 }

@@ -74,7 +74,7 @@ def bench_attn(t: Timer, seq: int, heads: int, compare: bool, variant: int = 0, 
                causal: bool = False) -> None:  # fmt: skip
     q, k, v = (torch.randn(1, seq, heads, head_dim, device="cuda").bfloat16() for _ in range(3))
     flops = 4.0 * seq * seq * heads * head_dim * (0.5 if causal else 1.0)
-    variants = [variant] if variant >= 0 else [30, 31, 20, 21, 40, 41, 42]  # -1: every kernel form and exp2 share
+    variants = [variant] if variant >= 0 else [30, 31, 32, 20, 21, 22]  # -1: every kernel form and exp2 share
     for vr in variants:
         report("attn_fwd_tcgen05", t(lambda: TF.attention(q, k, v, variant=vr, causal=causal)), flops, seq=seq,
                heads=heads, head_dim=head_dim, causal=causal, variant=vr)  # fmt: skip
@@ -120,7 +120,25 @@ def bench_gemm(t: Timer, m: int, n: int, k: int, compare: bool) -> None:
                          bias.data_ptr(), 0, None, 0, None, 0, 1, TF.native.stream_ptr())
 
     report("gemm_fp8_tcgen05 (GEMM only; fraction is of the bf16 peak)", t(gemm_only), flops, m=m, n=n, k=k)
+    if k % 128 == 0:
+        wq, wsf = TF.quantize_weight_mxfp8(w)
+        aq, asf = TF.quant_mxfp8(a, tiled=True)
+        report("quant_mxfp8 (tiled scales)", t(lambda: TF.quant_mxfp8(a, tiled=True)), bytes_=m * k * 3 + m * k // 32, m=m, k=k)
+        report("gemm_mxfp8_tcgen05 block-scaled (+bias, incl. activation quant)", t(lambda: TF.linear_mxfp8(a, wq, wsf, bias)),
+               flops, m=m, n=n, k=k)  # fmt: skip
+
+        def mx_only():
+            lib.tfb_gemm_mxfp8(aq.data_ptr(), k, asf.data_ptr(), wq.data_ptr(), k, wsf.data_ptr(), out.data_ptr(), n, m, n, k,
+                               bias.data_ptr(), 0, None, 0, None, 0, 1, TF.native.stream_ptr())
+
+        report("gemm_mxfp8_tcgen05 (GEMM only; fraction is of the bf16 peak)", t(mx_only), flops, m=m, n=n, k=k)
     if compare:
+        try:  # the library's row-wise FP8 GEMM (cuBLASLt through torch._scaled_mm), same operands and scales
+            fn = lambda: torch._scaled_mm(a8, w8.t(), scale_a=as_.reshape(m, 1), scale_b=ws.reshape(1, n), bias=bias,
+                                          out_dtype=torch.bfloat16)  # noqa: E731
+            report("torch._scaled_mm row-wise FP8 (cuBLASLt, library; fraction is of the bf16 peak)", t(fn), flops, m=m, n=n, k=k)
+        except Exception as e:  # noqa: BLE001 - depends on the library build
+            print(json.dumps({"kernel": "torch._scaled_mm row-wise FP8", "unavailable": f"{type(e).__name__}: {e}"[:200]}), flush=True)
         report("torch F.linear (cuBLAS)", t(lambda: torch.nn.functional.linear(a, w, bias)), flops, m=m, n=n, k=k)
 
 

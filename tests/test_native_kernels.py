@@ -51,7 +51,7 @@ def test_gemm_per_row_gate_and_batched():
                TF.linear_reference(x, w, None, residual=res, gate=gate_tok)) < 6e-3
 
 
-@pytest.mark.parametrize("variant", [0, 21, 40, 41])  # two threads per row (default) / one thread per row / streamed softmax
+@pytest.mark.parametrize("variant", [0, 21, 30, 31])  # default by shape / one thread per row / two threads per row
 @pytest.mark.parametrize("B,Sq,Skv,H", [(1, 128, 128, 1), (1, 256, 384, 2), (2, 300, 500, 3), (1, 1000, 77, 2),
                                          (1, 515, 1029, 2), (1, 4096, 4096, 4)])
 def test_attention(B, Sq, Skv, H, variant):
@@ -119,7 +119,7 @@ def test_attention_long_sequence_and_layer_like_magnitudes():
     q = (q / q.pow(2).mean(-1, keepdim=True).sqrt() * gain).bfloat16()
     k = (k / k.pow(2).mean(-1, keepdim=True).sqrt() * gain * ramp).bfloat16()
     v = torch.randn(1, S, H, 128, device="cuda").bfloat16()
-    for variant in (0, 21, 40):
+    for variant in (0, 20, 30):
         got, lse = TF.attention(q[:, :2048], k, v, return_lse=True, variant=variant)
         ref, lse_ref = TF.attention_reference(q[:, :2048], k, v, return_lse=True)
         assert rel(got, ref) < 1.5e-2, variant
@@ -132,8 +132,8 @@ def test_attention_strided_fused_qkv_and_peaked_scores():
     qkv = torch.randn(1, S, 3 * H * 128, device="cuda").bfloat16()
     q, k, v = (qkv[..., i * H * 128:(i + 1) * H * 128].unflatten(-1, (H, 128)) for i in range(3))
     assert rel(TF.attention(q, k, v), TF.attention_reference(q, k, v)) < 1e-2
-    # large-magnitude scores exercise the lazy rescale of the accumulator (and, streamed, its one-tile delay)
-    for scale_up, variant in ((6, 0), (6, 40), (20, 40), (20, 21)):
+    # large-magnitude scores exercise the lazy rescale of the accumulator 
+    for scale_up, variant in ((6, 0), (6, 30), (20, 30), (20, 21)):
         q2 = (q.float() * scale_up).bfloat16()
         got, lse = TF.attention(q2, k, v, return_lse=True, variant=variant)
         ref, lse_ref = TF.attention_reference(q2, k, v, return_lse=True)
