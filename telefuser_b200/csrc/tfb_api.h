@@ -60,6 +60,18 @@ int tfb_attn_k_stats(const void* k, long ld, long bs, int B, int S, int H, float
 int tfb_attn_quant_int8(const void* x, long ld, long bs, void* out, int B, int S, int H, int is_k, const float* mean,
                         const float* k_scale, float* scale_out, void* stream);
 
+// Causal 3-D convolution, stride 1, channels-last, as an implicit GEMM (conv3d_tcgen05.cu). x [B,T,H,W,Cin],
+// prev [B,prev_T,H,W,Cin] or null (frames in front of x), w [Cout, kt*kh*kw, Cin], out / resid [B,T,H,W,Cout], bf16.
+// pad_t frames of padding in front (the first prev_T of them from `prev`), pad_h / pad_w on both sides.
+int tfb_conv3d_causal(const void* x, const void* prev, int prev_T, const void* w, const void* bias, const void* resid,
+                      void* out, int B, int T, int H, int W, int Cin, int Cout, int kt, int kh, int kw, int pad_t,
+                      int pad_h, int pad_w, void* stream);
+
+// VAE glue on channels-last rows (vae_ops.cu): per-pixel L2 normalisation * sqrt(C) * gamma with optional SiLU, and
+// nearest-neighbour 2x spatial upsampling.
+int tfb_pixel_norm_act(const void* x, void* out, long pixels, int C, const float* gamma, int silu, void* stream);
+int tfb_upsample2x_nearest(const void* x, void* out, long N, int H, int W, int C, void* stream);
+
 // LayerNorm over the last dim (C), optional affine (bf16 w/b), then optional
 // modulation y = y * (1 + scale) + shift with fp32 scale/shift taken from row
 // (r / rows_per_mod) * ldmod of `shift` / `scale`.

@@ -23,6 +23,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from telefuser_b200.core.base_model import BaseModel
+from telefuser_b200.ops import functional as TF
 
 CACHE_T = 2
 
@@ -58,7 +59,30 @@ class CausalConv3d(nn.Conv3d):
         self._pad_hw = (self.padding[2], self.padding[2], self.padding[1], self.padding[1])
         self.padding = (0, 0, 0)
 
-    def forward(self, x, prev=None):
+    def _native_ok(self, x) -> bool:
+        """The tensor-core kernel covers stride-1, undilated, ungrouped convolutions with "same" spatial padding."""
+        kt, kh, kw = self.kernel_size
+        return (x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
+                and self.stride == (1, 1, 1) and self.dilation == (1, 1, 1) and self.groups == 1
+                and self._pad_hw == ((kw - 1) // 2, (kw - 1) // 2, (kh - 1) // 2, (kh - 1) // 2)
+                and self._pad_t == kt - 1 and self.in_channels % 8 == 0
+                and (self.out_channels % 8 == 0 or self.out_channels <= 32) and TF.use_native_kernels(x))  # fmt: skip
+
+    def _taps(self):
+        w = self.weight
+        key = (w.data_ptr(), w._version, w.device)
+        if getattr(self, "_taps_key", None) != key:
+            self._taps_cache, self._taps_key = TF.conv_weight_taps(w), key
+        return self._taps_cache
+
+    def forward(self, x, prev=None, residual=None):
+        if self._native_ok(x):
+            # implicit GEMM on the tensor cores: padding (and `prev`) are read in place, nothing is copied or padded
+            return TF.conv3d_causal(x, self.weight, self.bias, prev, residual, self._pad_t, self._taps())
+        y = self._forward_library(x, prev)
+        return y if residual is None else y + residual
+
+    def _forward_library(self, x, prev=None):
         pad_t = self._pad_t
         if prev is not None and pad_t > 0:
             prev = prev.to(x.device)
@@ -70,16 +94,22 @@ class CausalConv3d(nn.Conv3d):
         return super().forward(x)
 
 
-def causal_step(conv: CausalConv3d, x, state: CausalState | None):
+def _fast(x) -> bool:
+    """CUDA bf16 activations take the native path: channels-last throughout, norm + SiLU in one pass, convolutions as
+    implicit GEMMs on the tensor cores with the residual added in their epilogue."""
+    return x.is_cuda and x.dtype == torch.bfloat16 and TF.use_native_kernels(x)
+
+
+def causal_step(conv: CausalConv3d, x, state: CausalState | None, residual=None):
     """Runs `conv` on a chunk, feeding it the stored tail and storing the new tail."""
     if state is None:
-        return conv(x)
+        return conv(x, None, residual)
     i = state.next_slot()
     old = state.slots[i]
     tail = x[:, :, -CACHE_T:].clone()
     if tail.shape[2] < CACHE_T and old is not None:
         tail = torch.cat([old[:, :, -1:].to(tail.device), tail], dim=2)
-    y = conv(x, old)
+    y = conv(x, old, residual)
     state.slots[i] = tail
     return y
 
@@ -123,6 +153,18 @@ class Resample(nn.Module):
 
     def _spatial(self, x):
         b, c, t, h, w = x.shape
+        if self.mode in ("upsample2d", "upsample3d") and _fast(x) and c % 8 == 0:
+            # frames as a batch of channels-last images: 2x nearest upsample, then the 3x3 convolution as an implicit
+            # GEMM (a 3-D convolution with one tap in time over the frame axis)
+            conv = self.resample[1]
+            img = x.permute(0, 2, 1, 3, 4).reshape(b * t, c, h, w)
+            up = TF.upsample2x_nearest(img)  # [b*t, c, 2h, 2w] channels-last
+            vol = up.permute(1, 0, 2, 3).unsqueeze(0)  # [1, c, b*t, 2h, 2w], channels-last-3d strides, no copy
+            key = (conv.weight.data_ptr(), conv.weight._version)
+            if getattr(self, "_taps_key", None) != key:
+                self._taps_cache, self._taps_key = TF.conv_weight_taps(conv.weight.unsqueeze(2)), key
+            y = TF.conv3d_causal(vol, conv.weight.unsqueeze(2), conv.bias, pad_t=0, weight_taps=self._taps_cache)
+            return y.reshape(1, -1, b, t, 2 * h, 2 * w).squeeze(0).permute(1, 0, 2, 3, 4) if b > 1 else y
         y = self.resample(x.permute(0, 2, 1, 3, 4).reshape(b * t, c, h, w))
         return y.reshape(b, t, *y.shape[1:]).permute(0, 2, 1, 3, 4)
 
@@ -140,8 +182,13 @@ class Resample(nn.Module):
                     tail = torch.cat([head, tail], dim=2)
                 y = self.time_conv(x) if isinstance(old, str) else self.time_conv(x, old)
                 state.slots[i] = tail
-                y = y.reshape(b, 2, c, t, h, w)
-                x = torch.stack((y[:, 0], y[:, 1]), dim=3).reshape(b, c, t * 2, h, w)
+                if _fast(y) and y.permute(0, 2, 3, 4, 1).is_contiguous():
+                    # channels-last: frame 2t + k takes channels [k*c, (k+1)*c) of frame t; one copy, layout kept
+                    yl = y.permute(0, 2, 3, 4, 1).reshape(b, t, h, w, 2, c).permute(0, 1, 4, 2, 3, 5)
+                    x = yl.reshape(b, 2 * t, h, w, c).permute(0, 4, 1, 2, 3)
+                else:
+                    y = y.reshape(b, 2, c, t, h, w)
+                    x = torch.stack((y[:, 0], y[:, 1]), dim=3).reshape(b, c, t * 2, h, w)
         x = self._spatial(x)
         if self.mode == "downsample3d" and state is not None:
             i = state.next_slot()
@@ -166,6 +213,10 @@ class ResidualBlock(nn.Module):
 
     def forward(self, x, state: CausalState | None = None):
         h = self.shortcut(x)
+        n1, _, c1, n2, _, _, c2 = self.residual
+        if _fast(x) and not torch.is_tensor(n1.bias) and not torch.is_tensor(n2.bias):
+            y = causal_step(c1, TF.pixel_norm_act(x, n1.gamma), state)
+            return causal_step(c2, TF.pixel_norm_act(y, n2.gamma), state, residual=h)  # + h in the conv's epilogue
         for layer in self.residual:
             x = causal_step(layer, x, state) if isinstance(layer, CausalConv3d) else layer(x)
         return x + h
@@ -192,6 +243,10 @@ class AttentionBlock(nn.Module):
 
 
 def _run(layers, x, state):
+    layers = list(layers)
+    if (len(layers) == 3 and isinstance(layers[0], RMS_norm) and isinstance(layers[1], nn.SiLU) and _fast(x)
+            and not torch.is_tensor(layers[0].bias)):  # the norm -> SiLU -> conv head
+        return causal_step(layers[2], TF.pixel_norm_act(x, layers[0].gamma), state)
     for layer in layers:
         if isinstance(layer, (ResidualBlock, Resample, AttentionBlock)):
             x = layer(x, state)

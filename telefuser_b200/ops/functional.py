@@ -137,6 +137,11 @@ def quant_fp8_rowwise(x):
     return q.view(x.shape), s.view(*x.shape[:-1], 1)
 
 
+def use_native_kernels(t) -> bool:
+    """True when ops on `t` run on the native kernels (a CUDA tensor and the fp32 oracle is not forced)."""
+    return _native(t)
+
+
 def fp8_weight_scale(weight):
     """Per-output-channel scale tagged on an e4m3 weight (`tfb_scale`), on the weight's own device.
 
@@ -602,6 +607,101 @@ def cfg_euler_step(x, cond, uncond, cfg_scale, dsigma, return_v=False):
         float(cfg_scale), float(dsigma), xo.data_ptr(), native.ptr(v), x.numel(), native.stream_ptr())  # fmt: skip
     native.check(code, "tfb_cfg_euler_step")
     return (xo, v) if return_v else xo
+
+
+# ---------------------------------------------------------------------------
+# Causal 3-D convolution (VAE)
+# ---------------------------------------------------------------------------
+def conv3d_causal_reference(x, weight, bias=None, prev=None, residual=None, pad_t=None):
+    """x [B, Cin, T, H, W], weight [Cout, Cin, kt, kh, kw], stride 1: zero padding (kh-1)/2, (kw-1)/2 in space and
+    `pad_t` (default kt - 1) frames in front in time, of which the last `prev.shape[2]` are the frames of `prev`."""
+    kt, kh, kw = weight.shape[2:]
+    pad_t = kt - 1 if pad_t is None else pad_t
+    xf = x.float()
+    if prev is not None and pad_t > 0:
+        prev = prev[:, :, -pad_t:]
+        xf = torch.cat([prev.float().to(x.device), xf], dim=2)
+        pad_t -= prev.shape[2]
+    xf = F.pad(xf, ((kw - 1) // 2, (kw - 1) // 2, (kh - 1) // 2, (kh - 1) // 2, pad_t, 0))
+    y = F.conv3d(xf, weight.float(), None if bias is None else bias.float())
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def conv_weight_taps(weight: torch.Tensor) -> torch.Tensor:
+    """[Cout, Cin, kt, kh, kw] -> [Cout, kt*kh*kw, Cin] bf16 contiguous, the operand layout of the native kernel."""
+    co, ci = weight.shape[:2]
+    return weight.detach().reshape(co, ci, -1).permute(0, 2, 1).to(torch.bfloat16).contiguous()
+
+
+def conv3d_causal(x, weight, bias=None, prev=None, residual=None, pad_t=None, weight_taps=None):
+    """Causal stride-1 3-D convolution on the tensor cores. Tensors are logically [B, C, T, H, W]; CUDA bf16 inputs are
+    used in channels-last-3d memory (converted when they are not) and the result comes back in that format, so a chain
+    of convolutions, norms and activations never changes layout. Spatial and causal padding are produced by the
+    loads' out-of-range fill (no padded copy); `prev` (the last frames of the previous chunk) is read in place.
+    Other inputs take the fp32 evaluation. `weight_taps`: cached `conv_weight_taps(weight)`."""
+    co, ci, kt, kh, kw = weight.shape
+    pad_t = kt - 1 if pad_t is None else pad_t
+    ok = (_native(x) and x.dtype == torch.bfloat16 and ci % 8 == 0 and ci >= 8 and (co % 8 == 0 or co <= 32)
+          and kh % 2 == 1 and kw % 2 == 1)  # fmt: skip
+    if not ok:
+        return conv3d_causal_reference(x, weight, bias, prev, residual, pad_t)
+    B, _, T, H, W = x.shape
+    cl = torch.channels_last_3d
+    x = x.contiguous(memory_format=cl)
+    prev_T = 0
+    if prev is not None and pad_t > 0:
+        prev = prev[:, :, -pad_t:].to(device=x.device, dtype=x.dtype).contiguous(memory_format=cl)
+        if prev.shape[2] > 1 and not prev.permute(0, 2, 3, 4, 1).is_contiguous():
+            prev = prev.permute(0, 2, 3, 4, 1).contiguous().permute(0, 4, 1, 2, 3)
+        prev_T = prev.shape[2]
+    if residual is not None:
+        residual = residual.to(x.dtype).contiguous(memory_format=cl)
+    wt = weight_taps if weight_taps is not None else conv_weight_taps(weight)
+    if bias is not None and bias.dtype != torch.bfloat16:
+        bias = bias.to(torch.bfloat16)
+    out = torch.empty((B, co, T, H, W), device=x.device, dtype=torch.bfloat16, memory_format=cl)
+    native.same_device(x, wt, bias, prev, residual)
+    code = native.load().tfb_conv3d_causal(x.data_ptr(), native.ptr(prev) if prev_T else None, prev_T, wt.data_ptr(),
+                                           native.ptr(bias), native.ptr(residual), out.data_ptr(), B, T, H, W, ci, co, kt, kh,
+                                           kw, pad_t, (kh - 1) // 2, (kw - 1) // 2, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_conv3d_causal")
+    return out
+
+
+def pixel_norm_act(x, gamma, silu: bool = True):
+    """x [B, C, ...] (channel dim 1): per-position L2 normalisation over the channels times sqrt(C) * gamma, then SiLU
+    when asked: the norm + activation pair in front of every convolution of the video VAE, one pass instead of five.
+    CUDA bf16 tensors are used in channels-last memory (2-D or 3-D) and stay in it."""
+    C = x.shape[1]
+    g = gamma.reshape(-1)
+    if not _native(x) or x.dtype != torch.bfloat16 or x.dim() not in (4, 5) or C % 8:
+        y = F.normalize(x.float(), dim=1) * (C**0.5) * g.float().view(1, C, *([1] * (x.dim() - 2)))
+        return (F.silu(y) if silu else y).to(x.dtype)
+    fmt = torch.channels_last_3d if x.dim() == 5 else torch.channels_last
+    x = x.contiguous(memory_format=fmt)
+    out = torch.empty_like(x, memory_format=fmt)
+    gf = g.to(device=x.device, dtype=torch.float32).contiguous()
+    code = native.load().tfb_pixel_norm_act(x.data_ptr(), out.data_ptr(), x.numel() // C, C, gf.data_ptr(), int(silu),
+                                            native.stream_ptr())  # fmt: skip
+    if code == 2:  # a channel count the row kernel has no instance for
+        y = F.normalize(x.float(), dim=1) * (C**0.5) * g.float().view(1, C, *([1] * (x.dim() - 2)))
+        return (F.silu(y) if silu else y).to(x.dtype)
+    native.check(code, "tfb_pixel_norm_act")
+    return out
+
+
+def upsample2x_nearest(x):
+    """[N, C, H, W] -> [N, C, 2H, 2W], out(h, w) = in(h // 2, w // 2) (what `nearest-exact` gives at scale 2)."""
+    N, C, H, W = x.shape
+    if not _native(x) or x.dtype != torch.bfloat16 or C % 8:
+        return x.repeat_interleave(2, dim=-2).repeat_interleave(2, dim=-1)
+    x = x.contiguous(memory_format=torch.channels_last)
+    out = torch.empty((N, C, 2 * H, 2 * W), device=x.device, dtype=x.dtype, memory_format=torch.channels_last)
+    native.check(native.load().tfb_upsample2x_nearest(x.data_ptr(), out.data_ptr(), N, H, W, C, native.stream_ptr()),
+                 "tfb_upsample2x_nearest")  # fmt: skip
+    return out
 
 
 # ---------------------------------------------------------------------------

@@ -4,6 +4,7 @@
     python -m telefuser_b200.ops.kernel_bench gemm  --m 8192 --n 5120 --k 5120
     python -m telefuser_b200.ops.kernel_bench elementwise --rows 75600 --dim 5120
     python -m telefuser_b200.ops.kernel_bench moe   --tokens 16384
+    python -m telefuser_b200.ops.kernel_bench vae   --frames 17 --height 480 --width 832
     python -m telefuser_b200.ops.kernel_bench all
 
 Timing: CUDA events on the launching stream, `--warmup` untimed launches, then `--iters` timed ones;
@@ -207,9 +208,48 @@ def bench_moe(t: Timer, tokens: int, compare: bool) -> None:
             print(json.dumps({"kernel": "torch._grouped_mm", "unavailable": str(e)[:120]}))
 
 
+def bench_vae(t: Timer, frames: int, height: int, width: int, compare: bool) -> None:
+    """Wan VAE decode of `frames` video frames at height x width (random-init weights, bf16): the native path
+    (implicit-GEMM convolutions, fused norm + SiLU, channels-last) against the same module on the library path
+    (cuDNN convolutions, torch elementwise ops), plus the single convolution that dominates it."""
+    from telefuser_b200.models.wan_vae import WanVideoVAE
+    from telefuser_b200.testing.synthetic import random_init_
+
+    vae = random_init_(WanVideoVAE().to("cuda").to(torch.bfloat16), 0, std=0.03).eval()
+    z = torch.randn(1, 16, (frames - 1) // 4 + 1, height // 8, width // 8, device="cuda").bfloat16()
+    out_bytes = 3 * frames * height * width * 2
+    with torch.no_grad():
+        ms = t(lambda: vae.model.decode(z, vae.scale))
+        report("wan_vae_decode native", ms, bytes_=out_bytes, frames=frames, height=height, width=width,
+               frames_per_s=round(frames / ms * 1e3, 1))  # fmt: skip
+        if compare:
+            TF.set_force_reference(True)
+            try:
+                ms = t(lambda: vae.model.decode(z, vae.scale))
+            finally:
+                TF.set_force_reference(False)
+            report("wan_vae_decode library path (cuDNN + torch ops)", ms, bytes_=out_bytes, frames=frames, height=height,
+                   width=width, frames_per_s=round(frames / ms * 1e3, 1))  # fmt: skip
+    T = min(frames, 8)
+    x = torch.randn(1, 96, T, height, width, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last_3d)
+    w = (torch.randn(96, 96, 3, 3, 3, device="cuda") / 50).bfloat16()
+    b = torch.zeros(96, device="cuda").bfloat16()
+    wt = TF.conv_weight_taps(w)
+    flops = 2.0 * T * height * width * 96 * 96 * 27
+    report("conv3d_tcgen05 96->96 3x3x3 (full resolution)", t(lambda: TF.conv3d_causal(x, w, b, weight_taps=wt)), flops,
+           frames=T, height=height, width=width)  # fmt: skip
+    if compare:
+        xp = torch.nn.functional.pad(x, (1, 1, 1, 1, 2, 0)).contiguous(memory_format=torch.channels_last_3d)
+        report("torch conv3d (cuDNN, library; input already padded)", t(lambda: torch.nn.functional.conv3d(xp, w, b)), flops,
+               frames=T, height=height, width=width)  # fmt: skip
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn", "gemm", "elementwise", "moe", "all"])
+    ap.add_argument("what", choices=["attn", "gemm", "elementwise", "moe", "vae", "all"])
+    ap.add_argument("--frames", type=int, default=17)
+    ap.add_argument("--height", type=int, default=480)
+    ap.add_argument("--width", type=int, default=832)
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--m", type=int, default=8192)
@@ -238,6 +278,8 @@ def main() -> None:
         bench_elementwise(t, a.rows, a.dim)
     if a.what in ("moe", "all"):
         bench_moe(t, a.tokens, cmp_)
+    if a.what == "vae":
+        bench_vae(t, a.frames, a.height, a.width, cmp_)
 
 
 if __name__ == "__main__":

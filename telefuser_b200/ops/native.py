@@ -107,6 +107,10 @@ def _declare(lib) -> None:
         "tfb_attn_k_stats": [c_void_p, c_long, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "tfb_attn_quant_int8": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                 c_void_p, c_void_p],
+        "tfb_conv3d_causal": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tfb_pixel_norm_act": [c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_void_p],
+        "tfb_upsample2x_nearest": [c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
         "tfb_quant_fp8_rowwise": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "tfb_nf4_dequant": [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "tfb_rmsnorm_modulate": [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_float, c_void_p, c_void_p,
