@@ -11,6 +11,12 @@
 // b sit at (r % 32) * 16 + (r / 32) * 4 + b. The quantiser (elementwise.cu, tiled mode) writes that order
 // directly, so neither operand's scales are ever re-laid-out.
 //
+// The tile is 128 x 192: one K=32 MMA then reads 4 KB of A and 6 KB of B per 96 tensor-core clocks, which stays under
+// the shared-memory read rate (a 128 x 128 tile needs the full rate and measured half the throughput), and two
+// accumulators (384 columns) leave TMEM room for double-buffered scale columns. A 192-row B tile starts on a 64-row
+// boundary of the 128-row scale tiles: the producer always brings the two scale tiles that cover it and the MMA's
+// scale address skips two columns (64 rows) for odd tiles.
+//
 // Roles (192 threads): warp 0 producer, warp 1 MMA issuer + TMEM owner, warps 2..5 epilogue.
 // Replaces the reference's block-scaled FP8 GEMM (tf-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:41-198)
 // with the micro-scaling format that sm_100a multiplies natively.
@@ -33,20 +39,23 @@ struct MxGemmParams {
   int ldg, rows_per_gate;
   int epi;
   int m_tiles, n_tiles;
+  int sfb_tiles;  // 128-row scale tiles of B: ceil(N / 128)
   int* status;
 };
 
 struct MxCfg {
-  static constexpr int BM = 128, BN = 128, BK = 128;  // BK in elements = bytes
-  static constexpr int STAGES = 6;
+  static constexpr int BM = 128, BN = 192, BK = 128;  // BK in elements = bytes
+  static constexpr int STAGES = 5;
   static constexpr int A_BYTES = BM * BK;
   static constexpr int B_BYTES = BN * BK;
-  static constexpr int SF_BYTES = 512;  // one scale tile: 128 rows x 4 k-blocks
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;  // 33 KB, keeps 1024-byte alignment
-  static constexpr int ACC_COLS = 2 * BN;   // double-buffered accumulator
-  static constexpr int SFA_COL = ACC_COLS;  // 4 columns each
-  static constexpr int SFB_COL = ACC_COLS + 4;
+  static constexpr int SF_BYTES = 512;        // one scale tile: 128 rows x 4 k-blocks
+  static constexpr int SF_REGION = 2048;      // A tile, two B tiles, padding that keeps stages 1024-byte aligned
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_REGION;  // 42 KB
+  static constexpr int ACC_COLS = 2 * BN;     // double-buffered accumulator
+  static constexpr int SFA_COL = ACC_COLS;    // 2 x 4 columns (alternating by k-block)
+  static constexpr int SFB_COL = ACC_COLS + 8;  // 2 x 8 columns
   static constexpr int TMEM_COLS = 512;
+  static_assert(SFB_COL + 16 <= TMEM_COLS && STAGE_BYTES % 1024 == 0, "TMEM / shared-memory budget");
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
@@ -128,7 +137,11 @@ __global__ void __launch_bounds__(192, 1)
         int m_blk, n_blk;
         map_tile(t, m_blk, n_blk);
         const uint8_t* sfa = p.sfa + static_cast<size_t>(m_blk) * k_blocks * Cfg::SF_BYTES;
-        const uint8_t* sfb = p.sfb + static_cast<size_t>(n_blk) * k_blocks * Cfg::SF_BYTES;
+        // rows [192 n, 192 n + 192) live in scale tiles floor(3 n / 2) and the next one
+        const int sfb_tile = (3 * n_blk) >> 1;
+        const bool two_b = sfb_tile + 1 < p.sfb_tiles;
+        const uint8_t* sfb = p.sfb + static_cast<size_t>(sfb_tile) * k_blocks * Cfg::SF_BYTES;
+        const uint8_t* sfb2 = sfb + static_cast<size_t>(k_blocks) * Cfg::SF_BYTES;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -139,12 +152,15 @@ __global__ void __launch_bounds__(192, 1)
           uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
           uint8_t* sf_dst = b_dst + Cfg::B_BYTES;
-          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES + (two_b ? 3 : 2) * Cfg::SF_BYTES);
           tma_load_2d(a_dst, &tmA, &full[s], kb * Cfg::BK, m_blk * Cfg::BM);
           tma_load_2d(b_dst, &tmB, &full[s], kb * Cfg::BK, n_blk * Cfg::BN);
           mx_bulk_load(sf_dst, sfa + static_cast<size_t>(kb) * Cfg::SF_BYTES, Cfg::SF_BYTES, &full[s]);
           mx_bulk_load(sf_dst + Cfg::SF_BYTES, sfb + static_cast<size_t>(kb) * Cfg::SF_BYTES, Cfg::SF_BYTES,
                        &full[s]);
+          if (two_b)  // past the last scale tile only columns beyond N would use it; those are never stored
+            mx_bulk_load(sf_dst + 2 * Cfg::SF_BYTES, sfb2 + static_cast<size_t>(kb) * Cfg::SF_BYTES, Cfg::SF_BYTES,
+                         &full[s]);
         }
       }
     }
@@ -153,9 +169,10 @@ __global__ void __launch_bounds__(192, 1)
     // ---------------- MMA issuer ----------------
     uint32_t it = 0, tile_iter = 0;
     bool ok = true;
-    const uint32_t sfa_tmem = tmem_base + Cfg::SFA_COL;
-    const uint32_t sfb_tmem = tmem_base + Cfg::SFB_COL;
     for (int t = cta; t < num_tiles && ok; t += n_cta) {
+      int m_blk, n_blk;
+      map_tile(t, m_blk, n_blk);
+      const uint32_t sfb_shift = (n_blk & 1) * 2;  // odd tiles start 64 rows into their first scale tile
       const uint32_t acc = tile_iter & 1;
       const uint32_t accph = (tile_iter >> 1) & 1;
       ++tile_iter;
@@ -177,15 +194,18 @@ __global__ void __launch_bounds__(192, 1)
           const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
           const uint32_t b_addr = a_addr + Cfg::A_BYTES;
           const uint32_t sf_addr = b_addr + Cfg::B_BYTES;
-          // tcgen05.cp and tcgen05.mma of one thread run in issue order: the previous k-block's MMAs have read
-          // the scale columns before these copies overwrite them.
+          // tcgen05.cp and tcgen05.mma of one thread run in issue order; the scale columns alternate between two
+          // sets so that a copy never has to wait for the previous k-block's MMAs to drain.
+          const uint32_t sfa_tmem = tmem_base + Cfg::SFA_COL + (kb & 1) * 4;
+          const uint32_t sfb_tmem = tmem_base + Cfg::SFB_COL + (kb & 1) * 8;
           tmem_cp_sf(sfa_tmem, sf_addr);
           tmem_cp_sf(sfb_tmem, sf_addr + Cfg::SF_BYTES);
+          tmem_cp_sf(sfb_tmem + 4, sf_addr + 2 * Cfg::SF_BYTES);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint32_t idesc = make_idesc_mx(128, Cfg::BN, 0, 0, kk, kk);
             umma_mxf8_ss(d_tmem, make_desc_k_sw128(a_addr + kk * 32), make_desc_k_sw128(b_addr + kk * 32), idesc,
-                         sfa_tmem, sfb_tmem, (kb | kk) != 0 ? 1u : 0u);
+                         sfa_tmem, sfb_tmem + sfb_shift, (kb | kk) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[s]);
           if (kb == k_blocks - 1) umma_commit(&tfull[acc]);
@@ -328,7 +348,7 @@ extern "C" int tfb_gemm_mxfp8(const void* A, int lda, const void* sfa, const voi
   {
     uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     uint64_t str[1] = {static_cast<uint64_t>(ldb)};
-    uint32_t box[2] = {128u, 128u};
+    uint32_t box[2] = {128u, static_cast<uint32_t>(MxCfg::BN)};
     if (int e = make_tmap(&tmB, B, TM_U8, 2, dims, str, box, TM_SW_128)) return e;
   }
   MxGemmParams p;
@@ -347,7 +367,8 @@ extern "C" int tfb_gemm_mxfp8(const void* A, int lda, const void* sfa, const voi
   p.rows_per_gate = rows_per_gate < 1 ? 1 : rows_per_gate;
   p.epi = epi;
   p.m_tiles = (M + 127) / 128;
-  p.n_tiles = (N + 127) / 128;
+  p.n_tiles = (N + MxCfg::BN - 1) / MxCfg::BN;
+  p.sfb_tiles = (N + 127) / 128;
   p.status = status_word();
   static bool attr_set[TFB_MAX_DEVICES] = {false};
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_mxfp8_kernel), MxCfg::SMEM_BYTES, attr_set))

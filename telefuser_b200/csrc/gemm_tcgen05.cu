@@ -34,6 +34,8 @@ struct GemmParams {
   // FP8 (e4m3) operands: out = act((A @ B^T) * a_scale[row] * b_scale[col] + bias); null for bf16.
   const float* a_scale;
   const float* b_scale;
+  // With the 8-bit template: operands are signed int8 (tcgen05 kind::i8, int32 accumulators) instead of e4m3.
+  int int8;
   // Distributed modes (tensor parallel group of n_seg ranks, M = n_seg * seg_rows, one segment per rank;
   // n_seg == 0 otherwise). Tiles never straddle segments: segment s owns M tiles [s*seg_tiles, +seg_tiles).
   // Tile order is rotated by seg_rot tiles so that every rank starts with its own segment.
@@ -308,6 +310,8 @@ __global__ void __launch_bounds__(192, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     constexpr uint32_t idesc = FP8 ? make_idesc(128, BN, 0, 0, 0, 0) : make_idesc(128, BN, 1, 1, 0, 0);
+    constexpr uint32_t idesc_i8 = make_idesc_i8(128, BN);
+    const bool int8 = FP8 && p.int8;
     uint32_t it = 0;
     uint32_t tile_iter = 0;
     bool ok = true;
@@ -337,7 +341,9 @@ __global__ void __launch_bounds__(192, 1)
           for (int kk = 0; kk < Cfg::BK / 16; ++kk) {
             const uint64_t ad = make_desc_k_sw128(a_addr + kk * 32);
             const uint64_t bd = make_desc_k_sw128(b_addr + kk * 32);
-            if (FP8)
+            if (FP8 && int8)
+              umma_i8_ss(d_tmem, ad, bd, idesc_i8, (kb | kk) != 0 ? 1u : 0u);
+            else if (FP8)
               umma_f8_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
             else
               umma_f16_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
@@ -385,6 +391,10 @@ __global__ void __launch_bounds__(192, 1)
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
           const bool full_chunk = col0 + 32 <= p.N;
+          if (FP8 && p.int8) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = static_cast<float>(static_cast<int>(r[i]));
+          }
           if (FP8) {
             const float as = __ldg(p.a_scale + row);
 #pragma unroll
@@ -523,6 +533,7 @@ extern "C" int tfb_gemm_bf16(const void* A, int lda, const void* B, int ldb, voi
   p.status = status_word();
   p.tile_expert = nullptr;
   p.a_scale = p.b_scale = nullptr;
+  p.int8 = 0;
   p.n_seg = 0;
   p.n_copiers = 0;
   CUtensorMap tmA;
@@ -579,6 +590,7 @@ extern "C" int tfb_gemm_bf16_grouped(const void* A, int lda, const void* B, int 
   p.status = status_word();
   p.tile_expert = tile_expert;
   p.a_scale = p.b_scale = nullptr;
+  p.int8 = 0;
   p.n_seg = 0;
   p.n_copiers = 0;
   CUtensorMap tmA;
@@ -598,9 +610,9 @@ extern "C" int tfb_gemm_bf16_grouped(const void* A, int lda, const void* B, int 
 
 // W8A8 GEMM: A e4m3 [M, K] with one fp32 scale per row (per-token), B e4m3 [N, K] with one fp32 scale
 // per row (per-output-channel); out bf16 = epilogue((A @ B^T) * a_scale[m] * b_scale[n]).
-extern "C" int tfb_gemm_fp8(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K,
-                            const float* a_scale, const float* b_scale, const void* bias, int epi, const void* resid,
-                            int ldr, const float* gate, int ldg, int rows_per_gate, void* stream) {
+static int gemm_8bit(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K,
+                     const float* a_scale, const float* b_scale, const void* bias, int epi, const void* resid, int ldr,
+                     const float* gate, int ldg, int rows_per_gate, int int8, void* stream) {
   using namespace tfb;
   if (M <= 0 || N <= 0 || K <= 0 || !a_scale || !b_scale) return TFB_ERR_BAD_SHAPE;
   if ((K % 16) || (lda % 16) || (ldb % 16) || (ldo % 8) || (N % 8)) return TFB_ERR_BAD_SHAPE;
@@ -626,6 +638,7 @@ extern "C" int tfb_gemm_fp8(const void* A, int lda, const void* B, int ldb, void
   p.tile_expert = nullptr;
   p.a_scale = a_scale;
   p.b_scale = b_scale;
+  p.int8 = int8;
   p.n_seg = 0;
   p.n_copiers = 0;
   CUtensorMap tmA;
@@ -643,6 +656,23 @@ extern "C" int tfb_gemm_fp8(const void* A, int lda, const void* B, int ldb, void
   return launch_gemm<64, true>(tmA, B, ldb, p, st);
 }
 
+// W8A8 with e4m3 operands: out = epilogue((A @ B^T) * a_scale[row] * b_scale[col]).
+extern "C" int tfb_gemm_fp8(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K,
+                            const float* a_scale, const float* b_scale, const void* bias, int epi, const void* resid,
+                            int ldr, const float* gate, int ldg, int rows_per_gate, void* stream) {
+  return gemm_8bit(A, lda, B, ldb, out, ldo, M, N, K, a_scale, b_scale, bias, epi, resid, ldr, gate, ldg, rows_per_gate, 0,
+                   stream);
+}
+
+// W8A8 with signed 8-bit integer operands (tcgen05 kind::i8, exact int32 accumulation), same scales and epilogue.
+// Takes the place of the reference's int8 scaled GEMM (tf-kernel/csrc/gemm/int8_gemm_kernel.cu).
+extern "C" int tfb_gemm_int8(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K,
+                             const float* a_scale, const float* b_scale, const void* bias, int epi, const void* resid,
+                             int ldr, const float* gate, int ldg, int rows_per_gate, void* stream) {
+  return gemm_8bit(A, lda, B, ldb, out, ldo, M, N, K, a_scale, b_scale, bias, epi, resid, ldr, gate, ldg, rows_per_gate, 1,
+                   stream);
+}
+
 namespace tfb {
 static void dist_defaults(GemmParams& p, int n_seg, int rank, int seg_rows, int N, int K) {
   p.M = n_seg * seg_rows;
@@ -658,6 +688,7 @@ static void dist_defaults(GemmParams& p, int n_seg, int rank, int seg_rows, int 
   p.status = status_word();
   p.tile_expert = nullptr;
   p.a_scale = p.b_scale = nullptr;
+  p.int8 = 0;
   p.n_seg = n_seg;
   p.seg_rows = seg_rows;
   p.seg_tiles = (seg_rows + 127) / 128;

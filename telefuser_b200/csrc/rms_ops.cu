@@ -152,8 +152,31 @@ __global__ void headnorm_rope_kernel(__nv_bfloat16* __restrict__ x, long ldx, lo
   }
 }
 
-// Per-token FP8 quantisation for the W8A8 GEMM: q = e4m3(x / s), s = max(row amax / 448, 1e-12).
-// One CTA per row; the row is read twice (the second read hits L1/L2).
+// Per-token 8-bit quantisation for the W8A8 GEMMs. FP8: q = e4m3(x / s), s = max(row amax / 448, 1e-12);
+// INT8: q = round(x / s) in [-127, 127], s = max(row amax / 127, 1e-12). One CTA per row. With NV > 0 the row
+// (up to 2048 * NV elements) stays in registers between the amax pass and the conversion, so it is read from
+// memory once; NV == 0 is the any-width form that reads the row twice (the second read hits L1 / L2).
+template <bool INT8>
+__device__ __forceinline__ uint2 quant8_pack(const float (&f)[8], float inv) {
+  if (INT8) {
+    uint32_t b[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      int v;
+      asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(v) : "f"(fminf(fmaxf(f[e] * inv, -127.f), 127.f)));
+      b[e] = static_cast<uint32_t>(v) & 0xffu;
+    }
+    return make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24));
+  }
+  uint16_t h[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h[e]) : "f"(f[2 * e + 1] * inv), "f"(f[2 * e] * inv));
+  return make_uint2(static_cast<uint32_t>(h[0]) | (static_cast<uint32_t>(h[1]) << 16),
+                    static_cast<uint32_t>(h[2]) | (static_cast<uint32_t>(h[3]) << 16));
+}
+
+template <int NV, bool INT8>
 __global__ void __launch_bounds__(256) quant_fp8_row_kernel(const __nv_bfloat16* __restrict__ x, long ldx,
                                                             uint8_t* __restrict__ q, long ldq,
                                                             float* __restrict__ scale, int C) {
@@ -161,12 +184,29 @@ __global__ void __launch_bounds__(256) quant_fp8_row_kernel(const __nv_bfloat16*
   const long row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
   const int nvec = C >> 3;
+  constexpr int NR = NV > 0 ? NV : 1;
+  uint4 held[NR];
   float amax = 0.f;
-  for (int vi = threadIdx.x; vi < nvec; vi += 256) {
-    float f[8];
-    r_unpack8(xr[vi], f);
+  if (NV > 0) {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+    for (int i = 0; i < NR; ++i) {
+      const int vi = threadIdx.x + i * 256;
+      held[i] = vi < nvec ? xr[vi] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      float f[8];
+      r_unpack8(held[i], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+    }
+  } else {
+    for (int vi = threadIdx.x; vi < nvec; vi += 256) {
+      float f[8];
+      r_unpack8(xr[vi], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+    }
   }
   amax = warp_max(amax);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -175,32 +215,131 @@ __global__ void __launch_bounds__(256) quant_fp8_row_kernel(const __nv_bfloat16*
   amax = red[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
-  const float s = fmaxf(amax * (1.f / 448.f), 1e-12f);
+  const float s = fmaxf(amax * (INT8 ? 1.f / 127.f : 1.f / 448.f), 1e-12f);
   const float inv = __fdiv_rn(1.f, s);
   if (threadIdx.x == 0) scale[row] = s;
   uint2* qr = reinterpret_cast<uint2*>(q + row * ldq);
-  for (int vi = threadIdx.x; vi < nvec; vi += 256) {
-    float f[8];
-    r_unpack8(xr[vi], f);
-    uint16_t h[4];
+  if (NV > 0) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h[e]) : "f"(f[2 * e + 1] * inv), "f"(f[2 * e] * inv));
-    qr[vi] = make_uint2(static_cast<uint32_t>(h[0]) | (static_cast<uint32_t>(h[1]) << 16),
-                        static_cast<uint32_t>(h[2]) | (static_cast<uint32_t>(h[3]) << 16));
+    for (int i = 0; i < NR; ++i) {
+      const int vi = threadIdx.x + i * 256;
+      if (vi < nvec) {
+        float f[8];
+        r_unpack8(held[i], f);
+        qr[vi] = quant8_pack<INT8>(f, inv);
+      }
+    }
+  } else {
+    for (int vi = threadIdx.x; vi < nvec; vi += 256) {
+      float f[8];
+      r_unpack8(xr[vi], f);
+      qr[vi] = quant8_pack<INT8>(f, inv);
+    }
   }
+}
+
+// Per-tensor FP8 quantisation: one scale for the whole tensor. Pass 1 reduces |x| to a single maximum (the bit
+// pattern of a non-negative float orders like an unsigned integer, so atomicMax on the bits is exact); pass 2
+// converts with s = max(amax / 448, 1e-12) read from device memory, so a static (calibrated) scale skips pass 1.
+__global__ void __launch_bounds__(256) absmax_kernel(const __nv_bfloat16* __restrict__ x, long n8, long n,
+                                                     unsigned* __restrict__ amax_bits) {
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  float amax = 0.f;
+  for (long i = blockIdx.x * 256L + threadIdx.x; i < n8; i += gridDim.x * 256L) {
+    float f[8];
+    r_unpack8(xv[i], f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+  }
+  if (blockIdx.x == 0)
+    for (long i = n8 * 8 + threadIdx.x; i < n; i += 256) amax = fmaxf(amax, fabsf(__bfloat162float(x[i])));
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0 && amax > 0.f) atomicMax(amax_bits, __float_as_uint(amax));
+}
+__global__ void __launch_bounds__(256) quant_fp8_tensor_kernel(const __nv_bfloat16* __restrict__ x, long n8, long n,
+                                                               uint8_t* __restrict__ q, float* __restrict__ scale,
+                                                               const unsigned* __restrict__ amax_bits) {
+  float s;
+  if (amax_bits) {
+    s = fmaxf(__uint_as_float(*amax_bits) * (1.f / 448.f), 1e-12f);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale = s;
+  } else {
+    s = *scale;
+  }
+  const float inv = __fdiv_rn(1.f, s);
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  uint2* qv = reinterpret_cast<uint2*>(q);
+  for (long i = blockIdx.x * 256L + threadIdx.x; i < n8; i += gridDim.x * 256L) {
+    float f[8];
+    r_unpack8(xv[i], f);
+    qv[i] = quant8_pack<false>(f, inv);
+  }
+  if (blockIdx.x == 0)
+    for (long i = n8 * 8 + threadIdx.x; i < n; i += 256) {
+      uint16_t h;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h) : "f"(0.f), "f"(__bfloat162float(x[i]) * inv));
+      q[i] = static_cast<uint8_t>(h & 0xff);
+    }
 }
 
 }  // namespace tfb
 
 using namespace tfb;
 
-extern "C" int tfb_quant_fp8_rowwise(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int C,
-                                     void* stream) {
+template <bool INT8>
+static int launch_quant_row8(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int C, void* stream) {
   if (rows <= 0) return TFB_OK;
   if (C % 8 || ldx % 8 || ldq % 8) return TFB_ERR_BAD_SHAPE;
-  quant_fp8_row_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), ldq, scale, C);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  uint8_t* qp = static_cast<uint8_t*>(q);
+  const int nv = (C / 8 + 255) / 256;
+#define TFB_Q8(NV_) quant_fp8_row_kernel<NV_, INT8><<<rows, 256, 0, st>>>(xp, ldx, qp, ldq, scale, C)
+  switch (nv) {
+    case 1: TFB_Q8(1); break;
+    case 2: TFB_Q8(2); break;
+    case 3: TFB_Q8(3); break;
+    case 4: TFB_Q8(4); break;
+    case 5: case 6: TFB_Q8(6); break;
+    case 7: case 8: TFB_Q8(8); break;
+    default: TFB_Q8(0); break;
+  }
+#undef TFB_Q8
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+extern "C" int tfb_quant_fp8_rowwise(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int C,
+                                     void* stream) {
+  return launch_quant_row8<false>(x, ldx, q, ldq, scale, rows, C, stream);
+}
+
+// Per-token int8 quantisation (symmetric, [-127, 127]); the reference's per-token int8 path
+// (tf-kernel/csrc/gemm/per_token_group_quant_8bit.cu with a whole-row group).
+extern "C" int tfb_quant_int8_rowwise(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int C,
+                                      void* stream) {
+  return launch_quant_row8<true>(x, ldx, q, ldq, scale, rows, C, stream);
+}
+
+// Per-tensor FP8 quantisation of n contiguous bf16 values. `scale` (device, one float) receives the scale; with
+// is_static != 0 it is read instead (a calibrated scale) and no reduction runs. `scratch` is one device word used
+// for the reduction (cleared here, stream-ordered). Role of tf-kernel/csrc/gemm/per_tensor_quant_fp8.cu.
+extern "C" int tfb_quant_fp8_per_tensor(const void* x, void* q, float* scale, unsigned* scratch, long n, int is_static,
+                                        void* stream) {
+  if (n <= 0) return TFB_OK;
+  if (!scale || (!is_static && !scratch)) return TFB_ERR_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7)) return TFB_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const long n8 = n / 8;
+  long blocks = (n8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  if (!is_static) {
+    if (cudaMemsetAsync(scratch, 0, sizeof(unsigned), st) != cudaSuccess) return TFB_ERR_LAUNCH;
+    absmax_kernel<<<blocks, 256, 0, st>>>(xp, n8, n, scratch);
+  }
+  quant_fp8_tensor_kernel<<<blocks, 256, 0, st>>>(xp, n8, n, static_cast<uint8_t*>(q), scale,
+                                                  is_static ? nullptr : scratch);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 

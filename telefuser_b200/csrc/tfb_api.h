@@ -160,6 +160,16 @@ int tfb_gemm_fp8(const void* A, int lda, const void* B, int ldb, void* out, int 
                  const float* gate, int ldg, int rows_per_gate, void* stream);
 // x bf16 [rows, C] -> q e4m3 [rows, C] + scale fp32 [rows] (= max(amax/448, 1e-12)).
 int tfb_quant_fp8_rowwise(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int C, void* stream);
+// The same GEMM on signed 8-bit integers (exact int32 accumulation): A int8 [M,K], B int8 [N,K].
+int tfb_gemm_int8(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K,
+                  const float* a_scale, const float* b_scale, const void* bias, int epi, const void* resid, int ldr,
+                  const float* gate, int ldg, int rows_per_gate, void* stream);
+// x bf16 [rows, C] -> q int8 [rows, C] in [-127, 127] + scale fp32 [rows] (= max(amax/127, 1e-12)).
+int tfb_quant_int8_rowwise(const void* x, long ldx, void* q, long ldq, float* scale, int rows, int C, void* stream);
+// n contiguous bf16 values -> e4m3 with ONE scale (device float). is_static: read *scale (calibrated) instead of
+// reducing the tensor's amax; otherwise *scale = max(amax/448, 1e-12) is written. scratch: one device word.
+int tfb_quant_fp8_per_tensor(const void* x, void* q, float* scale, unsigned* scratch, long n, int is_static,
+                             void* stream);
 
 // ---- RMSNorm block glue of sandwich-norm DiTs (rms_ops.cu); norm weights and tables are fp32 ----
 // out = (w * x * rstd) * (1 + scale) + shift; w / shift / scale may be null; table row = row / rows_per_mod.

@@ -508,7 +508,8 @@ class WanModel(BaseModel):
 
     def enable_quant(self, quant=None) -> int:
         """W8A8 for the block projections (attention q/k/v/o and both FFN layers): block-scaled MXFP8 when the
-        configuration says `QuantType.MXFP8` (or "mxfp8"), per-token x per-channel FP8 otherwise; embeddings, the
+        configuration says `QuantType.MXFP8` (or "mxfp8"), integer W8A8 for `QuantType.INT8` ("int8"), per-token x
+        per-channel FP8 otherwise; embeddings, the
         head and all norms / modulation tables stay in bf16 / fp32. Returns the number of layers converted."""
         from telefuser_b200.core.config import QuantType
         from telefuser_b200.ops.quant import quantize_model_fp8_
@@ -517,7 +518,8 @@ class WanModel(BaseModel):
                                                               "patch_embedding", "text_embedding", "img_emb"))  # fmt: skip
         kind = getattr(quant, "quant_type", quant)
         mx = kind is QuantType.MXFP8 or (isinstance(kind, str) and kind.lower() == "mxfp8")
-        return quantize_model_fp8_(self, ("blocks.*",), skip, block_scaled=mx)
+        i8 = kind is QuantType.INT8 or (isinstance(kind, str) and kind.lower() == "int8")
+        return quantize_model_fp8_(self, ("blocks.*",), skip, block_scaled=mx, int8=i8)
 
     # ---- parallel plans --------------------------------------------------------
     def get_fsdp_module_names(self) -> list[str]:

@@ -65,6 +65,12 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
             out.copy_(r)
             return out
         return r
+    if weight.dtype == torch.int8:
+        r = linear_int8(x, weight, fp8_weight_scale(weight), bias, act, residual, gate)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
     if weight.dtype == torch.uint8 and hasattr(weight, "tfb_nf4_absmax"):
         from telefuser_b200.ops.nf4 import expand_nf4_weight
 
@@ -155,15 +161,58 @@ def fp8_weight_scale(weight):
     return s
 
 
-def linear_fp8(x, weight, weight_scale, bias=None, act=None, residual=None, gate=None):
-    """W8A8: weight e4m3 [N, K] with per-output-channel scale [N] or [N, 1]; activations are quantised
-    per token on the fly; fp32 accumulate; epilogue as `linear`."""
+def quant_int8_rowwise(x):
+    """x [..., C] -> (int8 [..., C] in [-127, 127], fp32 scale [..., 1]) with scale = row amax / 127 (floor 1e-12)."""
+    C = x.shape[-1]
+    if not _native(x) or x.dtype != torch.bfloat16 or C % 8:
+        s = (x.float().abs().amax(-1, keepdim=True) / 127.0).clamp_min(1e-12)
+        return torch.round(x.float() / s).clamp(-127, 127).to(torch.int8), s
+    x2 = x.reshape(-1, C)
+    if x2.stride(-1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    q = torch.empty(x2.shape, device=x.device, dtype=torch.int8)
+    s = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
+    code = native.load().tfb_quant_int8_rowwise(x2.data_ptr(), x2.stride(0), q.data_ptr(), C, s.data_ptr(), x2.shape[0],
+                                                C, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_quant_int8_rowwise")
+    return q.view(x.shape), s.view(*x.shape[:-1], 1)
+
+
+def quantize_weight_int8(weight):
+    """[N, K] weight -> (int8 [N, K], fp32 per-output-channel scale [N]); symmetric, range [-127, 127]."""
+    w = weight.float()
+    s = (w.abs().amax(-1, keepdim=True) / 127.0).clamp_min(1e-12)
+    return torch.round(w / s).clamp(-127, 127).to(torch.int8), s.reshape(-1)
+
+
+def quant_fp8_per_tensor(x, scale=None):
+    """Whole-tensor FP8 quantisation: (e4m3 tensor of x's shape, fp32 scale [1]). With `scale` given (a calibrated,
+    static scale) it is used as is; otherwise scale = amax / 448 (floor 1e-12). Role of the reference's
+    tf_per_tensor_quant_fp8 (tf-kernel/tf_kernel/gemm.py:123)."""
+    if not _native(x) or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        s = (x.float().abs().amax() / 448.0).clamp_min(1e-12).reshape(1) if scale is None else scale.float().reshape(1)
+        return (x.float() / s).clamp(-448, 448).to(torch.float8_e4m3fn), s
+    q = torch.empty(x.shape, device=x.device, dtype=torch.float8_e4m3fn)
+    static = scale is not None
+    s = scale.to(device=x.device, dtype=torch.float32).reshape(1).clone() if static else torch.empty(1, device=x.device)
+    scratch = torch.empty(1, device=x.device, dtype=torch.int32)
+    code = native.load().tfb_quant_fp8_per_tensor(x.data_ptr(), q.data_ptr(), s.data_ptr(), scratch.data_ptr(), x.numel(),
+                                                  1 if static else 0, native.stream_ptr())  # fmt: skip
+    native.check(code, "tfb_quant_fp8_per_tensor")
+    return q, s
+
+
+def _linear_w8a8(x, weight, weight_scale, bias, act, residual, gate, int8):
+    """Shared body of the two W8A8 linears (e4m3 or int8 operands): quantise the activations per token, multiply on
+    the 8-bit tensor-core path, apply both scale vectors and the epilogue in fp32."""
+    name = "int8" if int8 else "fp8"
     if weight_scale is None:
-        raise ValueError("an fp8 weight needs its per-channel scale (attribute `tfb_scale` or argument)")
+        raise ValueError(f"an {name} weight needs its per-channel scale (attribute `tfb_scale` or argument)")
     ws = weight_scale.to(device=x.device, dtype=torch.float32).reshape(-1)
+    quant = quant_int8_rowwise if int8 else quant_fp8_rowwise
     K, N = x.shape[-1], weight.shape[0]
     if not _native(x) or x.dtype != torch.bfloat16 or K % 16 or N % 8:
-        q, s = quant_fp8_rowwise(x)
+        q, s = quant(x)
         y = (q.float() @ weight.float().t()) * s.float() * ws
         if bias is not None:
             y = y + bias.float()
@@ -176,7 +225,7 @@ def linear_fp8(x, weight, weight_scale, bias=None, act=None, residual=None, gate
         if residual is not None:
             y = y + residual.float()
         return y.to(x.dtype)
-    q, s = quant_fp8_rowwise(x.reshape(-1, K))
+    q, s = quant(x.reshape(-1, K))
     M = q.shape[0]
     ws = ws.contiguous()
     out = torch.empty(*x.shape[:-1], N, device=x.device, dtype=torch.bfloat16)
@@ -191,12 +240,25 @@ def linear_fp8(x, weight, weight_scale, bias=None, act=None, residual=None, gate
         raise ValueError(f"unknown activation {act}")
     w = weight if weight.stride(-1) == 1 else weight.contiguous()
     native.same_device(x, w, ws, bias, res2, g2)
-    code = native.load().tfb_gemm_fp8(q.data_ptr(), K, w.data_ptr(), w.stride(0), out.data_ptr(), N, M, N, K,
-                                      s.data_ptr(), ws.data_ptr(), native.ptr(bias), 1 if act == "gelu_tanh" else 0,
-                                      native.ptr(res2), N if res2 is not None else 0, gate_ptr, ldg, rpg,
-                                      native.stream_ptr())  # fmt: skip
-    native.check(code, "tfb_gemm_fp8")
+    fn = native.load().tfb_gemm_int8 if int8 else native.load().tfb_gemm_fp8
+    code = fn(q.data_ptr(), K, w.data_ptr(), w.stride(0), out.data_ptr(), N, M, N, K, s.data_ptr(), ws.data_ptr(),
+              native.ptr(bias), 1 if act == "gelu_tanh" else 0, native.ptr(res2), N if res2 is not None else 0, gate_ptr,
+              ldg, rpg, native.stream_ptr())  # fmt: skip
+    native.check(code, f"tfb_gemm_{name}")
     return out
+
+
+def linear_fp8(x, weight, weight_scale, bias=None, act=None, residual=None, gate=None):
+    """W8A8: weight e4m3 [N, K] with per-output-channel scale [N] or [N, 1]; activations are quantised
+    per token on the fly; fp32 accumulate; epilogue as `linear`."""
+    return _linear_w8a8(x, weight, weight_scale, bias, act, residual, gate, False)
+
+
+def linear_int8(x, weight, weight_scale, bias=None, act=None, residual=None, gate=None):
+    """W8A8 on integers: weight int8 [N, K] with per-output-channel scale, activations quantised per token to
+    [-127, 127]; exact int32 accumulation on the tensor cores; epilogue as `linear`. Role of the reference's
+    int8_scaled_mm (tf-kernel/tf_kernel/gemm.py:8)."""
+    return _linear_w8a8(x, weight, weight_scale, bias, act, residual, gate, True)
 
 
 # ---------------------------------------------------------------------------

@@ -101,6 +101,30 @@ def quantize_linear_fp8_(lin: nn.Linear) -> nn.Linear:
     return lin
 
 
+class QuantizedLinearInt8(_ScaleTagged, nn.Linear):
+    """An `nn.Linear` quantised in place to W8A8 on integers: int8 weight with a per-output-channel scale
+    (`weight_scale`, tag `weight.tfb_scale`), activations quantised per token, exact int32 accumulation."""
+
+    def forward(self, x):
+        return TF.linear_int8(x, self.weight, self.weight_scale, self.bias)
+
+
+def quantize_linear_int8_(lin: nn.Linear) -> nn.Linear:
+    """In place, symmetric int8 (range [-127, 127]); same bookkeeping as `quantize_linear_fp8_`."""
+    if lin.weight.dtype in (torch.int8, torch.float8_e4m3fn):
+        return lin
+    q, s = TF.quantize_weight_int8(lin.weight.data)
+    lin.weight = nn.Parameter(q, requires_grad=False)
+    if "weight_scale" in lin._buffers:
+        lin.weight_scale = s.reshape(-1, 1)
+    else:
+        lin.register_buffer("weight_scale", s.reshape(-1, 1))
+    if type(lin) is nn.Linear:
+        lin.__class__ = QuantizedLinearInt8
+    lin.weight.tfb_scale = lin.weight_scale
+    return lin
+
+
 class QuantizedLinearMX(_ScaleTagged, nn.Linear):
     """An `nn.Linear` quantised in place to block-scaled MXFP8: e4m3 weight plus one UE8M0 scale per 32 input
     channels, kept in the tile order the tensor core reads (buffer `weight_scale_mx`, tag `weight.tfb_mx_sf`)."""
@@ -127,11 +151,12 @@ def quantize_linear_mxfp8_(lin: nn.Linear) -> nn.Linear:
 
 def quantize_model_fp8_(model: nn.Module, quantize_modules=("*attn*", "*ffn*"), skip_modules=("head", "time_embedding",
                         "time_projection", "patch_embedding", "text_embedding", "img_emb"), min_features: int = 64,
-                        block_scaled: bool = False) -> int:  # fmt: skip
+                        block_scaled: bool = False, int8: bool = False) -> int:  # fmt: skip
     """Quantises every `nn.Linear` whose qualified name matches one of `quantize_modules` (fnmatch) and
     none of `skip_modules` (substring); returns the number of layers converted. `block_scaled=True` selects
     MXFP8 (a scale per 32 input channels) for layers whose input width is a multiple of 128; the others, and
-    everything when it is False, get per-channel FP8."""
+    everything when it is False, get per-channel FP8. `int8=True` selects symmetric int8 weights and activations
+    (exact integer accumulation) instead of e4m3."""
     n = 0
     for name, m in model.named_modules():
         if not isinstance(m, nn.Linear) or min(m.in_features, m.out_features) < min_features:
@@ -140,7 +165,9 @@ def quantize_model_fp8_(model: nn.Module, quantize_modules=("*attn*", "*ffn*"), 
             continue
         if any(s in name for s in skip_modules) or not any(fnmatch.fnmatchcase(name, p) for p in quantize_modules):
             continue
-        if block_scaled and m.in_features % 128 == 0:
+        if int8:
+            quantize_linear_int8_(m)
+        elif block_scaled and m.in_features % 128 == 0:
             quantize_linear_mxfp8_(m)
         else:
             quantize_linear_fp8_(m)

@@ -168,11 +168,12 @@ def test_mxfp8_linear_reference_path_and_model_conversion():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 200, 512), (1024, 1536, 5120), (77, 72, 128)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 200, 512), (1024, 1536, 5120), (77, 72, 128), (512, 960, 256)])
 def test_mxfp8_gemm_matches_fp32_product_of_the_dequantised_operands(M, N, K):
     torch.manual_seed(0)
     x = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 4).bfloat16()
-    w = (torch.randn(N, K, device="cuda") / K**0.5).bfloat16()
+    # every weight row gets its own power-of-two magnitude: a scale factor read from the wrong row shows as a 2x error
+    w = (torch.randn(N, K, device="cuda") / K**0.5 * torch.exp2(torch.randint(-3, 4, (N, 1), device="cuda"))).bfloat16()
     bias = torch.randn(N, device="cuda").bfloat16()
     res = torch.randn(M, N, device="cuda").bfloat16()
     gate = torch.randn(1, N, device="cuda")
@@ -221,3 +222,91 @@ def test_quantised_sidecar_round_trip(tmp_path, kind):
 
         save_file({"x": torch.zeros(1)}, str(tmp_path / "other.safetensors"))
         load_quantized_sidecar(fresh, str(tmp_path / "other.safetensors"))
+
+
+def test_int8_linear_and_per_tensor_quantisation_reference_paths():
+    torch.manual_seed(0)
+    x, w = torch.randn(9, 64), torch.randn(48, 64) / 8
+    q, s = TF.quantize_weight_int8(w)
+    assert q.dtype == torch.int8 and s.shape == (48,) and int(q.abs().max()) == 127
+    xq, xs = TF.quant_int8_rowwise(x)
+    assert xq.dtype == torch.int8 and (xq.float() * xs - x).abs().max() <= x.abs().max() / 127 * 0.51
+    full = x @ w.t()
+    got = TF.linear_int8(x, q, s)
+    assert ((got - full).norm() / full.norm()).item() < 0.02
+    q.tfb_scale = s
+    assert torch.equal(TF.linear(x, q), got)  # the functional linear dispatches on the int8 weight
+    from telefuser_b200.ops.quant import QuantizedLinearInt8, quantize_linear_int8_
+
+    lin = nn.Linear(64, 48)
+    ref = lin(x)
+    quantize_linear_int8_(lin)
+    assert isinstance(lin, QuantizedLinearInt8) and lin.weight.dtype == torch.int8
+    assert ((lin(x) - ref).norm() / ref.norm()).item() < 0.02
+    model = make_tiny_model()
+    latents, ctx, _ = make_tiny_inputs()
+    t = torch.tensor([500.0])
+    ref = model(latents, t, ctx)
+    assert model.enable_quant("int8") == 20 and model.blocks[0].ffn[0].weight.dtype == torch.int8
+    out = model(latents, t, ctx)
+    assert ((out - ref).norm() / ref.norm()).item() < 0.05
+    # per-tensor: dynamic scale = amax / 448, static scale used as given
+    pq, ps = TF.quant_fp8_per_tensor(x)
+    assert ps.shape == (1,) and torch.allclose(ps, x.abs().amax().reshape(1) / 448)
+    assert (pq.float() * ps - x).abs().max() <= x.abs().max() * 0.07
+    pq2, ps2 = TF.quant_fp8_per_tensor(x, scale=torch.tensor([0.05]))
+    assert float(ps2) == pytest.approx(0.05) and torch.equal(pq2, (x / 0.05).clamp(-448, 448).to(torch.float8_e4m3fn))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(300, 256, 512), (1024, 1536, 5120), (77, 72, 144)])
+def test_int8_gemm_is_exact_on_the_integer_product(M, N, K):
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 4).bfloat16()
+    w = torch.randn(N, K, device="cuda") / K**0.5
+    bias = torch.randn(N, device="cuda").bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    gate = torch.randn(1, N, device="cuda")
+    wq, ws = TF.quantize_weight_int8(w)
+    xq, xs = TF.quant_int8_rowwise(x)
+    xq_r = torch.round(x.float() / xs).clamp(-127, 127).to(torch.int8)
+    assert torch.allclose(xs, (x.float().abs().amax(-1, keepdim=True) / 127).clamp_min(1e-12), rtol=1e-6)
+    assert (xq.int() - xq_r.int()).abs().max().item() <= 1 and (xq != xq_r).float().mean().item() < 1e-3
+    prod = (xq.double() @ wq.double().t()).float()  # exact: |sum| < 2^24 * 127 fits a double easily
+    base = prod * xs * ws
+    for kw in (dict(), dict(bias=bias), dict(bias=bias, act="gelu_tanh"), dict(bias=bias, residual=res, gate=gate)):
+        got = TF.linear_int8(x, wq, ws, **kw).float()
+        want = base.clone()
+        if "bias" in kw:
+            want = want + bias.float()
+        if kw.get("act"):
+            want = torch.nn.functional.gelu(want, approximate="tanh")
+        if "gate" in kw:
+            want = want * gate
+        if "residual" in kw:
+            want = want + res.float()
+        err = ((got - want).abs() / (1 + want.abs())).max().item()
+        assert err <= 1e-2, (kw.keys(), err)  # bf16 rounding of the output only
+    full = x.float() @ w.t()
+    assert ((TF.linear_int8(x, wq, ws).float() - full).norm() / full.norm()).item() < 0.02
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("C", [64, 5120, 13824, 20480])
+def test_row_and_tensor_quantisers_match_their_references_at_every_width(C):
+    torch.manual_seed(0)
+    x = (torch.randn(37, C, device="cuda") * torch.rand(37, 1, device="cuda") * 3).bfloat16()
+    q, s = TF.quant_fp8_rowwise(x)
+    s_ref = (x.float().abs().amax(-1, keepdim=True) / 448).clamp_min(1e-12)
+    assert torch.allclose(s, s_ref, rtol=1e-6)
+    assert torch.equal(q.float(), (x.float() * (1 / s_ref)).to(torch.float8_e4m3fn).float()) or \
+        ((q.float() - (x.float() / s_ref).to(torch.float8_e4m3fn).float()).abs() > 0).float().mean().item() < 1e-3
+    q8, s8 = TF.quant_int8_rowwise(x)
+    assert (q8.float() * s8 - x.float()).abs().max().item() <= (s8.max().item() * 0.51 + 1e-6)
+    pq, ps = TF.quant_fp8_per_tensor(x)
+    assert torch.allclose(ps, x.float().abs().amax().reshape(1) / 448, rtol=1e-6)
+    want = (x.float() / ps).to(torch.float8_e4m3fn).float()
+    assert ((pq.float() - want).abs() > 0).float().mean().item() < 1e-3
+    pq2, ps2 = TF.quant_fp8_per_tensor(x, scale=torch.tensor([0.02], device="cuda"))
+    assert float(ps2) == pytest.approx(0.02)
+    assert ((pq2.float() - (x.float() / 0.02).clamp(-448, 448).to(torch.float8_e4m3fn).float()).abs() > 0).float().mean().item() < 1e-3
