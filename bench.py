@@ -310,7 +310,12 @@ def build_reference(args, layout, world, local):
                         tp_degree=layout["tp_degree"])  # fmt: skip
     sp = layout["sp_ulysses_degree"]
     tokens = ((args.frames - 1) // 4 + 1) * (args.height // 16) * (args.width // 16)
-    impl, table = pick_reference_attention(args, AttentionConfig, AttnImplType, ref_attention, m["num_heads"] // sp, tokens)
+    try:
+        impl, table = pick_reference_attention(args, AttentionConfig, AttnImplType, ref_attention, m["num_heads"] // sp,
+                                               tokens)  # fmt: skip
+    except Exception as e:  # noqa: BLE001 - the selection is an optimisation of the arm, never a reason to lose it
+        impl, table = AttnImplType.TORCH_SDPA, {"selection_failed": f"{type(e).__name__}: {e}"[:200]}
+    torch.cuda.empty_cache()
     cfg = ModelRuntimeConfig(torch_dtype=torch.bfloat16, parallel_config=pc, device_type="cuda", device_id=local,
                              attention_config=AttentionConfig.dense_attention(impl))  # fmt: skip
     stage = SingleDitDenoisingStage("dit_denoise", mm, cfg, FlowMatchScheduler("Wan"))

@@ -52,93 +52,118 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // ---------------------------------------------------------------------------
-// LayerNorm (+affine) (+modulate). One CTA of 256 threads per row; NV uint4 per thread.
+// LayerNorm (+affine) (+modulate). One CTA of 256 threads walks LN_ROWS consecutive rows; NV uint4 per thread and
+// row. The per-column factors (affine weight / bias, 1 + scale, shift) are folded into one multiplier and one
+// addend per column, held in registers and rebuilt only when the modulation row changes: a row then costs its own
+// 2 x C x 2 bytes of traffic instead of dragging 8 x C bytes of fp32 table through L1 with it. The next row is
+// loaded (still packed) before the current one is reduced, so each thread keeps two rows of loads in flight.
 // ---------------------------------------------------------------------------
+constexpr int LN_ROWS = 16;
 template <int NV>
-__global__ void __launch_bounds__(256) layernorm_modulate_kernel(
+__global__ void __launch_bounds__(256, NV >= 4 ? 1 : 2) layernorm_modulate_kernel(
     const __nv_bfloat16* __restrict__ x, long ldx, __nv_bfloat16* __restrict__ out, long ldo, int rows, int C,
     float eps, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
     const float* __restrict__ shift, const float* __restrict__ scale, long ldmod, int rows_per_mod) {
-  __shared__ float red[16];
-  const int row = blockIdx.x;
-  if (row >= rows) return;
+  __shared__ float red[2][16];
+  const int row0 = blockIdx.x * LN_ROWS;
+  const int row_end = min(rows, row0 + LN_ROWS);
   const int nvec = C >> 3;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
-  float v[NV][8];
-  float s = 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float mul[NV][8], add[NV][8];
+  long cached_mod = -1;
+  uint4 nxt[NV];
+  {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row0 * ldx);
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int vi = threadIdx.x + i * 256;
-    if (vi < nvec) {
-      unpack8(xr[vi], v[i]);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) s += v[i][e];
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * 256;
+      nxt[i] = vi < nvec ? xr[vi] : make_uint4(0, 0, 0, 0);
     }
   }
-  // Mean and variance from one pass over the registers and ONE block reduction (sum and sum of squares side by
-  // side): a row costs two barriers instead of four. fp32 sums of bf16 data; var = E[x^2] - mean^2, floored at 0.
-  float ss = 0.f;
+  for (int row = row0; row < row_end; ++row) {
+    float v[NV][8];
+    float s = 0.f, ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
+    for (int i = 0; i < NV; ++i) {
+      unpack8(nxt[i], v[i]);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) ss = fmaf(v[i][e], v[i][e], ss);
-  s = warp_sum(s);
-  ss = warp_sum(ss);
-  {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+      for (int e = 0; e < 8; ++e) {
+        s += v[i][e];
+        ss = fmaf(v[i][e], v[i][e], ss);
+      }
+    }
+    if (row + 1 < row_end) {
+      const uint4* xr = reinterpret_cast<const uint4*>(x + (row + 1) * ldx);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int vi = threadIdx.x + i * 256;
+        nxt[i] = vi < nvec ? xr[vi] : make_uint4(0, 0, 0, 0);
+      }
+    }
+    const long mod = row / rows_per_mod;
+    if (mod != cached_mod) {
+      cached_mod = mod;
+      const long mrow = mod * ldmod;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int vi = threadIdx.x + i * 256;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          mul[i][e] = 1.f;
+          add[i][e] = 0.f;
+        }
+        if (vi < nvec) {
+          if (w) unpack8(__ldg(reinterpret_cast<const uint4*>(w) + vi), mul[i]);
+          if (b) unpack8(__ldg(reinterpret_cast<const uint4*>(b) + vi), add[i]);
+          if (scale) {
+            const float4* sp = reinterpret_cast<const float4*>(scale + mrow) + vi * 2;
+            const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {  // (y w + b)(1 + sc) = y (w (1 + sc)) + b (1 + sc)
+              mul[i][e] *= (1.f + sc[e]);
+              add[i][e] *= (1.f + sc[e]);
+            }
+          }
+          if (shift) {
+            const float4* sp = reinterpret_cast<const float4*>(shift + mrow) + vi * 2;
+            const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            const float sh[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) add[i][e] += sh[e];
+          }
+        }
+      }
+    }
+    // Mean and variance from one pass over the registers and ONE block reduction (sum and sum of squares side by
+    // side; the scratch alternates between rows, so a row costs a single barrier). fp32 sums of bf16 data;
+    // var = E[x^2] - mean^2, floored at 0.
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    float* rd = red[(row - row0) & 1];
     if (lane == 0) {
-      red[warp] = s;
-      red[8 + warp] = ss;
+      rd[warp] = s;
+      rd[8 + warp] = ss;
     }
     __syncthreads();
     s = ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      s += red[i];
-      ss += red[8 + i];
+      s += rd[i];
+      ss += rd[8 + i];
     }
-  }
-  const float mean = s / C;
-  const float rstd = rsqrtf(fmaxf(ss / C - mean * mean, 0.f) + eps);
-  const long mrow = static_cast<long>(row / rows_per_mod) * ldmod;
-  uint4* orow = reinterpret_cast<uint4*>(out + row * ldo);
+    const float mean = s / C;
+    const float rstd = rsqrtf(fmaxf(ss / C - mean * mean, 0.f) + eps);
+    uint4* orow = reinterpret_cast<uint4*>(out + row * ldo);
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int vi = threadIdx.x + i * 256;
-    if (vi < nvec) {
-      float y[8];
+    for (int i = 0; i < NV; ++i) {
+      const int vi = threadIdx.x + i * 256;
+      if (vi < nvec) {
+        float y[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = (v[i][e] - mean) * rstd;
-      if (w) {
-        float wf[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(w) + vi), wf);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] *= wf[e];
+        for (int e = 0; e < 8; ++e) y[e] = fmaf((v[i][e] - mean) * rstd, mul[i][e], add[i][e]);
+        orow[vi] = pack8(y);
       }
-      if (b) {
-        float bf[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(b) + vi), bf);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] += bf[e];
-      }
-      if (scale) {
-        const float4* sp = reinterpret_cast<const float4*>(scale + mrow) + vi * 2;
-        const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
-        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] *= (1.f + sc[e]);
-      }
-      if (shift) {
-        const float4* sp = reinterpret_cast<const float4*>(shift + mrow) + vi * 2;
-        const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
-        const float sh[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] += sh[e];
-      }
-      orow[vi] = pack8(y);
     }
   }
 }
@@ -229,6 +254,55 @@ __global__ void __launch_bounds__(256) gated_residual_kernel(const uint4* __rest
       for (int e = 0; e < 8; ++e) xf[e] += yf[e];
     }
     out[i] = pack8(xf);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Row softmax in place: x[r, :] = softmax(scale * x[r, :]) over C columns (bf16 storage, fp32 maths). One CTA per
+// row: an online max / sum pass, then the exponentials (the second read of the row comes from L1 / L2). Used by the
+// unfused attention of heads wider than 128 (single-head VAE attention: scores GEMM -> this -> P.V GEMM).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) softmax_rows_kernel(__nv_bfloat16* __restrict__ x, long ldx, int C, float scale) {
+  __shared__ float red_m[8], red_s[8];
+  uint4* xr = reinterpret_cast<uint4*>(x + blockIdx.x * ldx);
+  const int nvec = C >> 3;
+  const float k = scale * 1.4426950408889634f;  // exponentials in base 2
+  float m = -INFINITY, sum = 0.f;
+  for (int vi = threadIdx.x; vi < nvec; vi += 256) {
+    float f[8];
+    unpack8(xr[vi], f);
+    float cm = f[0];
+#pragma unroll
+    for (int e = 1; e < 8; ++e) cm = fmaxf(cm, f[e]);
+    cm *= k;  // k > 0 is required by the launcher, so the scaled maximum is the maximum of the scaled values
+    if (cm > m) {
+      sum *= fast_exp2(m - cm);
+      m = cm;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum += fast_exp2(fmaf(f[e], k, -m));
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float wm = warp_max(m);
+  sum = warp_sum(m == -INFINITY ? 0.f : sum * fast_exp2(m - wm));
+  if (lane == 0) {
+    red_m[warp] = wm;
+    red_s[warp] = sum;
+  }
+  __syncthreads();
+  float bm = red_m[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) bm = fmaxf(bm, red_m[i]);
+  float bs = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) bs += red_m[i] == -INFINITY ? 0.f : red_s[i] * fast_exp2(red_m[i] - bm);
+  const float inv = 1.f / bs;
+  for (int vi = threadIdx.x; vi < nvec; vi += 256) {
+    float f[8];
+    unpack8(xr[vi], f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = fast_exp2(fmaf(f[e], k, -bm)) * inv;
+    xr[vi] = pack8(f);
   }
 }
 
@@ -368,7 +442,7 @@ extern "C" int tfb_layernorm_modulate(const void* x, long ldx, void* out, long l
   const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(b);
   if (rows_per_mod <= 0) rows_per_mod = 1;
 #define TFB_LN_LAUNCH(NV_)                                                                                        \
-  layernorm_modulate_kernel<NV_><<<rows, 256, 0, st>>>(xp, ldx, op, ldo, rows, C, eps, wp, bp, shift, scale, ldmod, \
+  layernorm_modulate_kernel<NV_><<<(rows + LN_ROWS - 1) / LN_ROWS, 256, 0, st>>>(xp, ldx, op, ldo, rows, C, eps, wp, bp, shift, scale, ldmod, \
                                                        rows_per_mod)
   switch (nv) {
     case 1: TFB_LN_LAUNCH(1); break;
@@ -411,6 +485,13 @@ extern "C" int tfb_gated_residual(const void* x, const void* y, void* out, int r
   gated_residual_kernel<<<grid_for(nvec), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), static_cast<const uint4*>(y), static_cast<uint4*>(out), nvec, C / 8, gate, ldg,
       rows_per_gate > 0 ? rows_per_gate : 1);
+  return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
+}
+
+extern "C" int tfb_softmax_rows(void* x, long ldx, int rows, int C, float scale, void* stream) {
+  if (rows <= 0) return TFB_OK;
+  if (C < 8 || C % 8 || ldx % 8 || !(scale > 0.f) || (reinterpret_cast<uintptr_t>(x) & 15)) return TFB_ERR_BAD_SHAPE;
+  softmax_rows_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(x), ldx, C, scale);
   return cudaGetLastError() == cudaSuccess ? TFB_OK : TFB_ERR_LAUNCH;
 }
 

@@ -91,6 +91,8 @@ int tfb_rmsnorm_rope(void* x, long ldx, long mat_stride, int nmat, int rows, int
 int tfb_gated_residual(const void* x, const void* y, void* out, int rows, int C, const float* gate, long ldg,
                        int rows_per_gate, void* stream);
 
+// x[r, :] = softmax(scale * x[r, :]) in place over C columns (bf16, fp32 maths); C % 8 == 0, scale > 0.
+int tfb_softmax_rows(void* x, long ldx, int rows, int C, float scale, void* stream);
 // act(x[:, :d]) * x[:, d:]   with act = 0 silu, 1 gelu-tanh, 2 gelu-erf.   x: [rows, 2d] bf16
 int tfb_act_mul(const void* x, void* out, int rows, int d, int act, void* stream);
 

@@ -23,6 +23,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from telefuser_b200.core.base_model import BaseModel
+from telefuser_b200.ops import functional as TF
 
 
 class RMSNorm(nn.Module):
@@ -67,10 +68,10 @@ class AttnBlock(nn.Module):
     def forward(self, x):
         h = self.norm(x)
         b, c, f, hh, ww = h.shape
-        q, k, v = (m(h).flatten(2).transpose(1, 2).unsqueeze(1) for m in (self.q, self.k, self.v))
+        q, k, v = (m(h).flatten(2).transpose(1, 2).unsqueeze(2) for m in (self.q, self.k, self.v))
         mask = None if f == 1 else frame_causal_mask(f, hh * ww, h.device)
-        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
-        return x + self.proj_out(o.squeeze(1).transpose(1, 2).reshape(b, c, f, hh, ww))
+        o = TF.attention(q, k, v, mask=mask)
+        return x + self.proj_out(o.squeeze(2).transpose(1, 2).reshape(b, c, f, hh, ww))
 
 
 class ResnetBlock(nn.Module):

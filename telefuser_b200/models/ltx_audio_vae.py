@@ -21,6 +21,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from telefuser_b200.ops import functional as TF
+
 LRELU_SLOPE = 0.1
 
 
@@ -100,8 +102,8 @@ class AttnBlock(nn.Module):
     def forward(self, x):
         h = self.norm(x)
         b, c, hh, ww = h.shape
-        q, k, v = (m(h).reshape(b, c, hh * ww).transpose(1, 2).unsqueeze(1) for m in (self.q, self.k, self.v))
-        o = F.scaled_dot_product_attention(q, k, v, scale=float(c) ** -0.5).squeeze(1)
+        q, k, v = (m(h).reshape(b, c, hh * ww).transpose(1, 2).unsqueeze(2) for m in (self.q, self.k, self.v))
+        o = TF.attention(q, k, v, scale=float(c) ** -0.5).squeeze(2)
         return x + self.proj_out(o.transpose(1, 2).reshape(b, c, hh, ww))
 
 

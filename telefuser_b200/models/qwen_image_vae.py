@@ -15,6 +15,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from telefuser_b200.core.base_model import BaseModel
+from telefuser_b200.ops import functional as TF
 
 LATENT_MEAN = [-0.7571, -0.7089, -0.9113, 0.1075, -0.1745, 0.9653, -0.1517, 1.5508, 0.4134, -0.0715, 0.5517, -0.3632, -0.1922, -0.9497,
                0.2503, -0.2921]  # fmt: skip
@@ -78,9 +79,9 @@ class QwenImageAttentionBlock(nn.Module):
 
     def forward(self, x):
         b, c, h, w = x.shape
-        q, k, v = self.to_qkv(self.norm(x)).reshape(b, 1, 3 * c, h * w).transpose(2, 3).chunk(3, dim=-1)
-        o = F.scaled_dot_product_attention(q, k, v)
-        return x + self.proj(o.squeeze(1).transpose(1, 2).reshape(b, c, h, w))
+        q, k, v = self.to_qkv(self.norm(x)).reshape(b, 1, 3 * c, h * w).permute(0, 3, 1, 2).chunk(3, dim=-1)
+        o = TF.attention(q, k, v)  # [b, h w, 1, c]: one head of width c
+        return x + self.proj(o.squeeze(2).transpose(1, 2).reshape(b, c, h, w))
 
 
 class QwenImageResample(nn.Module):

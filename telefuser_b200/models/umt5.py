@@ -69,17 +69,17 @@ class T5Attention(nn.Module):
     def forward(self, x, mask=None, pos_bias=None):
         B, L, _ = x.shape
         H, D = self.num_heads, self.head_dim
-        q = TF.linear(x, self.q.weight).view(B, L, H, D).transpose(1, 2)
-        k = TF.linear(x, self.k.weight).view(B, L, H, D).transpose(1, 2)
-        v = TF.linear(x, self.v.weight).view(B, L, H, D).transpose(1, 2)
+        q = TF.linear(x, self.q.weight).view(B, L, H, D)
+        k = TF.linear(x, self.k.weight).view(B, L, H, D)
+        v = TF.linear(x, self.v.weight).view(B, L, H, D)
         if pos_bias is not None and pos_bias.shape[1] != H:  # heads split over TP ranks
             pos_bias = pos_bias[:, getattr(self, "head_start", 0) :][:, :H]
         bias = pos_bias.to(q.dtype) if pos_bias is not None else torch.zeros(1, H, L, L, device=x.device, dtype=q.dtype)
         if mask is not None:
             m = mask.view(B, 1, 1, -1) if mask.dim() == 2 else mask.unsqueeze(1)
             bias = bias.expand(B, -1, -1, -1).masked_fill(m == 0, torch.finfo(q.dtype).min)
-        o = F.scaled_dot_product_attention(q, k, v, attn_mask=bias, scale=1.0)  # T5: no 1/sqrt(d)
-        return TF.linear(o.transpose(1, 2).reshape(B, L, H * D), self.o.weight)
+        o = TF.attention(q, k, v, scale=1.0, bias=bias)  # T5: no 1/sqrt(d); relative-position bias on the scores
+        return TF.linear(o.reshape(B, L, H * D), self.o.weight)
 
 
 class T5FeedForward(nn.Module):

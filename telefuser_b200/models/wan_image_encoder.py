@@ -31,8 +31,8 @@ class _Attention(nn.Module):
     def forward(self, x):
         B, S, C = x.shape
         q, k, v = TF.linear(x, self.to_qkv.weight, self.to_qkv.bias).view(B, S, 3, self.num_heads, self.head_dim).unbind(2)
-        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
-        return TF.linear(o.transpose(1, 2).reshape(B, S, C), self.proj.weight, self.proj.bias)
+        o = TF.attention(q, k, v)
+        return TF.linear(o.reshape(B, S, C), self.proj.weight, self.proj.bias)
 
 
 class _Block(nn.Module):

@@ -236,9 +236,9 @@ class AttentionBlock(nn.Module):
     def forward(self, x, state=None):
         b, c, t, h, w = x.shape
         y = self.norm(x.permute(0, 2, 1, 3, 4).reshape(b * t, c, h, w))
-        q, k, v = self.to_qkv(y).reshape(b * t, 1, c * 3, h * w).permute(0, 1, 3, 2).contiguous().chunk(3, dim=-1)
-        y = F.scaled_dot_product_attention(q, k, v)
-        y = self.proj(y.squeeze(1).permute(0, 2, 1).reshape(b * t, c, h, w))
+        q, k, v = self.to_qkv(y).reshape(b * t, 1, c * 3, h * w).permute(0, 3, 1, 2).contiguous().chunk(3, dim=-1)
+        y = TF.attention(q, k, v)  # [b t, h w, 1, c]: one head of width c
+        y = self.proj(y.squeeze(2).permute(0, 2, 1).reshape(b * t, c, h, w))
         return y.reshape(b, t, c, h, w).permute(0, 2, 1, 3, 4) + x
 
 

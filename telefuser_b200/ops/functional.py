@@ -386,11 +386,13 @@ def rmsnorm_rope_(x, weight, num_heads, cos=None, sin=None, eps=1e-6, x2=None, w
 # ---------------------------------------------------------------------------
 # Attention
 # ---------------------------------------------------------------------------
-def attention_reference(q, k, v, scale=None, return_lse=False, causal=False, mask=None, q_block: int | None = None):
+def attention_reference(q, k, v, scale=None, return_lse=False, causal=False, mask=None, q_block: int | None = None,
+                        bias=None):
     """q: [B, Sq, H, D], k/v: [B, Skv, H, D] -> [B, Sq, H, D] (fp32 softmax).
 
     `causal`: key j is visible to query i when j <= i + (Skv - Sq). `mask`: boolean, broadcastable to
-    [B, H, Sq, Skv], True = visible. `q_block` bounds the score matrix held at once to [B, H, q_block, Skv]."""
+    [B, H, Sq, Skv], True = visible. `bias`: added to the scaled scores, broadcastable to [B, H, Sq, Skv].
+    `q_block` bounds the score matrix held at once to [B, H, q_block, Skv]."""
     D = q.shape[-1]
     Sq, Skv = q.shape[1], k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
@@ -404,6 +406,8 @@ def attention_reference(q, k, v, scale=None, return_lse=False, causal=False, mas
         if causal:
             rows = torch.arange(s0, s1, device=q.device).unsqueeze(1) + (Skv - Sq)
             s = s.masked_fill(torch.arange(Skv, device=q.device).unsqueeze(0) > rows, float("-inf"))
+        if bias is not None:
+            s = s + (bias if bias.dim() < 2 or bias.shape[-2] == 1 else bias[..., s0:s1, :]).float()
         if mask is not None:
             m = mask if mask.dim() < 2 or mask.shape[-2] == 1 else mask[..., s0:s1, :]
             s = s.masked_fill(~m, float("-inf"))
@@ -420,26 +424,57 @@ def _pad_head_dim(t, D_to):
     return F.pad(t, (0, D_to - t.shape[-1]))
 
 
-def attention(q, k, v, scale=None, return_lse=False, variant=0, causal=False, mask=None, quant=None):
+def softmax_rows_(x, scale: float = 1.0):
+    """In place: x[r, :] = softmax(scale * x[r, :]) for a 2-D bf16 CUDA tensor (fp32 maths); other inputs go through
+    torch.softmax in fp32."""
+    C = x.shape[-1]
+    if not _native(x) or x.dtype != torch.bfloat16 or x.dim() != 2 or C % 8 or x.stride(1) != 1 or x.stride(0) % 8 \
+            or scale <= 0:  # fmt: skip
+        x.copy_(torch.softmax(x.float() * scale, dim=-1))
+        return x
+    code = native.load().tfb_softmax_rows(x.data_ptr(), x.stride(0), x.shape[0], C, float(scale), native.stream_ptr())
+    native.check(code, "tfb_softmax_rows")
+    return x
+
+
+def _attention_wide_heads(q, k, v, scale):
+    """Heads wider than 128 (the single-head attention of the VAEs: D = 384 / 512) on the native kernels, unfused:
+    per (batch, head) a scores GEMM [Sq, Skv], the row softmax in place, and the P.V GEMM. The score matrix of ONE
+    head is held at a time (bf16)."""
+    B, Sq, H, D = q.shape
+    out = torch.empty(B, Sq, H, D, device=q.device, dtype=q.dtype)
+    for b in range(B):
+        for h in range(H):
+            p = linear(q[b, :, h].contiguous(), k[b, :, h].contiguous())  # [Sq, Skv]
+            softmax_rows_(p, scale)
+            out[b, :, h] = linear(p, v[b, :, h].t().contiguous())  # weight [D, Skv]
+    return out
+
+
+def attention(q, k, v, scale=None, return_lse=False, variant=0, causal=False, mask=None, quant=None, bias=None):
     """Attention, layout BSHD: q [B, Sq, H, D], k / v [B, Skv, H, D] -> [B, Sq, H, D].
     `quant="int8"` computes the scores on int8 operands (`attention_int8`; no LSE output).
 
     CUDA bf16 / fp16 inputs with D <= 128 run on the tcgen05 kernel (head dims other than 64 / 128 are zero-padded
-    to the next of the two, fp16 is computed in bf16); `causal` is handled inside the kernel. A general boolean
-    `mask` (True = visible) and head dims above 128 take the fp32 evaluation in query blocks, so that no
-    [Sq, Skv] score matrix is ever held for the whole sequence. CPU tensors always take the fp32 evaluation."""
+    to the next of the two, fp16 is computed in bf16); `causal` is handled inside the kernel. Heads wider than 128
+    without mask / bias run as two tensor-core GEMMs around a row-softmax kernel. A general boolean `mask`
+    (True = visible) or an additive `bias` take the fp32 evaluation in query blocks, so that no [Sq, Skv] score
+    matrix is ever held for the whole sequence. CPU tensors always take the fp32 evaluation."""
     D = q.shape[-1]
+    if (_native(q) and q.dtype == torch.bfloat16 and D > 128 and D % 8 == 0 and mask is None and bias is None
+            and not causal and not return_lse and quant is None and k.shape[1] % 8 == 0 and k.shape[1] >= 8):
+        return _attention_wide_heads(q, k, v, scale if scale is not None else 1.0 / math.sqrt(D))
     if quant is not None:
-        if quant != "int8" or return_lse or mask is not None:
+        if quant != "int8" or return_lse or mask is not None or bias is not None:
             raise ValueError("quantised attention: quant='int8', without LSE output or a mask")
         if D == 128:
             return attention_int8(q, k, v, scale, causal)
     if not _native(q) or q.dtype not in (torch.bfloat16, torch.float16) or D > 128 or mask is not None or D % 8 \
-            or (causal and k.shape[1] < q.shape[1]):  # fmt: skip
+            or bias is not None or (causal and k.shape[1] < q.shape[1]):  # fmt: skip
         blk = None
         if q.is_cuda and q.shape[1] * k.shape[1] > (1 << 24):
             blk = max(128, (1 << 24) // k.shape[1])
-        return attention_reference(q, k, v, scale, return_lse, causal, mask, blk)
+        return attention_reference(q, k, v, scale, return_lse, causal, mask, blk, bias)
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     in_dtype = q.dtype
     if in_dtype != torch.bfloat16:

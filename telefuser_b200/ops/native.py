@@ -112,6 +112,7 @@ def _declare(lib) -> None:
         "tfb_pixel_norm_act": [c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_void_p],
         "tfb_upsample2x_nearest": [c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
         "tfb_quant_fp8_rowwise": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
+        "tfb_softmax_rows": [c_void_p, c_long, c_int, c_int, c_float, c_void_p],
         "tfb_quant_int8_rowwise": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "tfb_quant_fp8_per_tensor": [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "tfb_gemm_int8": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,

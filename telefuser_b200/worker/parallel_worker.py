@@ -67,10 +67,12 @@ def _rank_device(device_type: str, device_ids, rank: int):
 
 
 def _worker_loop(rank: int, stage, world_size: int, port: int, device_type: str, device_ids, timeout_s: int,
-                 intra_op_threads: int, queues_in, queue_out, empty_cache_each_call: bool) -> None:  # fmt: skip
+                 intra_op_threads: int, queues_in, queue_out, empty_cache_each_call: bool,
+                 results_on_device: bool = False) -> None:  # fmt: skip
     import torch.distributed as dist
 
     initialised = False
+    held = None  # the last device-resident result stays referenced here until the next call replaces it
     device = _rank_device(device_type, device_ids, rank)
     try:
         if world_size > 1:
@@ -110,7 +112,17 @@ def _worker_loop(rank: int, stage, world_size: int, port: int, device_type: str,
             if empty_cache_each_call and device.type == "cuda":
                 torch.cuda.empty_cache()
             # every rank acknowledges every call, so a failure on any rank is seen by the parent
-            queue_out.put(("ok", rank, to_device(result, "cpu") if rank == 0 else None))
+            if rank != 0:
+                queue_out.put(("ok", rank, None))
+            elif results_on_device and device.type == "cuda":
+                # The result crosses to the parent as a CUDA IPC handle (no host copy): the consumer has no stream
+                # order with this process, so the producing work is finished first, and the memory stays referenced
+                # here until the next call.
+                held = to_device(result, device)
+                torch.cuda.synchronize(device)
+                queue_out.put(("ok", rank, held))
+            else:
+                queue_out.put(("ok", rank, to_device(result, "cpu")))
     except BaseException as e:  # noqa: BLE001 - reported to the parent, then the rank exits
         try:
             queue_out.put(("error", rank, RemoteError(rank, e)))
@@ -160,7 +172,7 @@ class ParallelWorker:
                 target=_worker_loop,
                 args=(rank, self.stage, self.world_size, self.port, self.device_type, self.device_ids, self.timeout,
                       self.parallel_config.worker_intra_op_threads, self.queues_in, self.queue_out,
-                      self.empty_cache_each_call),  # fmt: skip
+                      self.empty_cache_each_call, bool(getattr(self.parallel_config, "results_on_device", False))),  # fmt: skip
                 daemon=True,
             )
             p.start()

@@ -241,3 +241,41 @@ def test_attention_int8_scores():
         assert rel(got, TF.attention_reference(q, kk, vv, causal=causal)) < 4e-2, causal
     cpu = TF.attention_int8(q.cpu().float(), k.cpu().float(), v.cpu().float())
     assert rel(cpu, TF.attention_reference(q.cpu().float(), k.cpu().float(), v.cpu().float())) < 4e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,C,scale", [(37, 64, 1.0), (130, 3000, 0.05), (5, 14400, 0.051)])
+def test_softmax_rows_in_place_matches_fp32(rows, C, scale):
+    torch.manual_seed(0)
+    x = (torch.randn(rows, C, device="cuda") * 6).bfloat16()
+    want = torch.softmax(x.float() * scale, dim=-1)
+    got = TF.softmax_rows_(x.clone(), scale).float()
+    assert (got - want).abs().max().item() <= 4e-3 * want.max().item() + 1e-6
+    assert (got.sum(-1) - 1).abs().max().item() < 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("S,D", [(1560, 384), (200, 512), (333, 384)])
+def test_wide_single_head_attention_runs_as_gemm_softmax_gemm(S, D):
+    """The VAE mid-block attention (one head, D = 384 / 512): tensor-core GEMMs around the row softmax when the key
+    count is a multiple of 8, the blocked fp32 evaluation otherwise; both against the fp32 oracle."""
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(2, S, 1, D, device="cuda").bfloat16() for _ in range(3))
+    before = native.launch_count()
+    got = TF.attention(q, k, v).float()
+    if S % 8 == 0:
+        assert native.launch_count() > before
+    want = TF.attention_reference(q.float(), k.float(), v.float())
+    assert ((got - want).norm() / want.norm()).item() < 2e-2
+
+
+@pytest.mark.gpu
+def test_attention_with_additive_bias_matches_torch():
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(2, 77, 4, 64, device="cuda").bfloat16() for _ in range(3))
+    bias = torch.randn(1, 4, 77, 77, device="cuda")
+    got = TF.attention(q, k, v, scale=1.0, bias=bias).float()
+    want = torch.nn.functional.scaled_dot_product_attention(
+        q.float().transpose(1, 2), k.float().transpose(1, 2), v.float().transpose(1, 2), attn_mask=bias, scale=1.0).transpose(1, 2)
+    assert (got - want).abs().max().item() < 3e-2
+

@@ -65,3 +65,27 @@ def test_timeout_and_dead_rank_are_detected():
         assert w2.failed
     finally:
         w2.close()
+
+
+@pytest.mark.gpu
+def test_results_stay_on_the_device_when_asked():
+    """One rank on cuda:0 with `results_on_device`: the parent receives CUDA tensors (an IPC handle, no host copy) and
+    the values survive the next call of the worker."""
+    from telefuser_b200.core.config import ModelRuntimeConfig, ParallelConfig
+
+    cfg = ModelRuntimeConfig(device_type="cuda", device_id=0, torch_dtype=torch.float32,
+                             parallel_config=ParallelConfig(timeout=120, results_on_device=True))  # fmt: skip
+    stage = AllReduceStage(cfg)
+    stage.device_type = "cuda"
+    w = ParallelWorker(stage)
+    try:
+        a = w.process(torch.arange(8.0))
+        assert a.is_cuda and torch.equal(a.cpu(), torch.arange(8.0))
+        b = w.process(torch.ones(8, device="cuda"))  # a CUDA argument crosses the same way
+        assert b.is_cuda and torch.equal(b.cpu(), torch.ones(8))
+        kept = a.clone()
+        del a
+        c = w.process(torch.full((8,), 5.0))
+        assert torch.equal(kept.cpu(), torch.arange(8.0)) and torch.equal(c.cpu(), torch.full((8,), 5.0))
+    finally:
+        w.close()

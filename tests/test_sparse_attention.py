@@ -113,3 +113,15 @@ def test_radial_attention_on_gpu():
     ref = SA.block_sparse_attention_reference(q.float(), k.float(), v.float(), mm.query_block_mask(s, 0.5, "cuda"))
     assert (out - ref).abs().max() <= 3e-2
     assert (SA.radial_attention(q, k, v, mm, dense=True).float() - TF.attention(q, k, v).float()).abs().max() == 0
+
+
+def test_reference_attention_bias_and_blocking_on_cpu():
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(2, 19, 3, 16) for _ in range(3))
+    bias = torch.randn(1, 3, 19, 19)
+    want = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=bias, scale=1.0).transpose(1, 2)
+    assert torch.allclose(TF.attention(q, k, v, scale=1.0, bias=bias), want, atol=1e-5)
+    assert torch.allclose(TF.attention_reference(q, k, v, 1.0, bias=bias, q_block=5), want, atol=1e-5)
+    x = torch.randn(4, 24)
+    assert torch.allclose(TF.softmax_rows_(x.clone(), 0.3), torch.softmax(x * 0.3, -1), atol=1e-6)
