@@ -457,12 +457,13 @@ def attention(q, k, v, scale=None, return_lse=False, variant=0, causal=False, ma
 
     CUDA bf16 / fp16 inputs with D <= 128 run on the tcgen05 kernel (head dims other than 64 / 128 are zero-padded
     to the next of the two, fp16 is computed in bf16); `causal` is handled inside the kernel. Heads wider than 128
-    without mask / bias run as two tensor-core GEMMs around a row-softmax kernel. A general boolean `mask`
+    without mask / bias and with at least 1024 keys run as two tensor-core GEMMs around a row-softmax kernel (the
+    scores pass through bf16 there; shorter sequences, where speed does not matter, keep fp32 scores). A general boolean `mask`
     (True = visible) or an additive `bias` take the fp32 evaluation in query blocks, so that no [Sq, Skv] score
     matrix is ever held for the whole sequence. CPU tensors always take the fp32 evaluation."""
     D = q.shape[-1]
     if (_native(q) and q.dtype == torch.bfloat16 and D > 128 and D % 8 == 0 and mask is None and bias is None
-            and not causal and not return_lse and quant is None and k.shape[1] % 8 == 0 and k.shape[1] >= 8):
+            and not causal and not return_lse and quant is None and k.shape[1] % 8 == 0 and k.shape[1] >= 1024):
         return _attention_wide_heads(q, k, v, scale if scale is not None else 1.0 / math.sqrt(D))
     if quant is not None:
         if quant != "int8" or return_lse or mask is not None or bias is not None:
