@@ -52,3 +52,41 @@ def test_comm_test_single_process_and_gloo(tmp_path):
     col = rep["collectives"][0]
     assert rep["world"] == 2 and col["world"] == 2 and {"all_reduce", "all_gather", "send_recv_ring"} <= set(col)
     assert col["all_reduce"]["bus_gbs"] > 0 and abs(col["all_reduce"]["bus_gbs"] / col["all_reduce"]["alg_gbs"] - 1.0) < 1e-6  # 2(P-1)/P = 1 at P = 2
+
+
+def test_lingbot_video_validation_tool_inspect_capture_compare_bench(tmp_path):
+    """Checkpoint inspection, a single-process capture against a 2-rank (Ulysses + expert-parallel) capture of the
+    same seeded run, and the benchmark line, all on CPU ranks."""
+    import json
+    import subprocess
+    import sys
+
+    import torch
+    from safetensors.torch import save_file
+
+    from telefuser_b200.models.lingbot_video import LingBotVideoConfig, LingBotVideoTransformer3DModel
+    from telefuser_b200.tools import lingbot_video_validation as V
+
+    model = LingBotVideoTransformer3DModel(LingBotVideoConfig.preset("tiny-moe"))
+    save_file({k: v.contiguous() for k, v in model.state_dict().items()}, str(tmp_path / "m.safetensors"))
+    rep = V.inspect_shapes(V.read_checkpoint_shapes(str(tmp_path / "m.safetensors")))
+    assert rep["kind"] == "moe" and rep["depth"] == 2 and rep["num_experts"] == 8 and rep["resolved_preset"] == "moe-30b-a3b"
+    assert rep["parameters"] == sum(p.numel() for p in model.state_dict().values()) and rep["shape_mismatches"]  # tiny vs 30B
+    single, sp = str(tmp_path / "single.pt"), str(tmp_path / "sp.pt")
+    assert V.main(["capture", "--preset", "tiny-moe", "--out", single]) == 0
+    env = {**__import__("os").environ, "PYTHONPATH": str(__import__("pathlib").Path(__file__).resolve().parents[1])}
+    run = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29541", "-m", "telefuser_b200.tools.lingbot_video_validation"]  # fmt: skip
+    r = subprocess.run(run + ["capture", "--preset", "tiny-moe", "--layout", "u2", "--expert-parallel", "--out", sp],
+                       capture_output=True, text=True, timeout=300, env=env)  # fmt: skip
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert V.main(["compare", single, sp, "--tol", "1e-4"]) == 0
+    a = torch.load(single, weights_only=False)
+    a["tensors"]["latent_step01"] += 0.1
+    torch.save(a, single)
+    assert V.main(["compare", single, sp, "--tol", "1e-4"]) == 1
+    r = subprocess.run(run + ["bench", "--preset", "tiny-moe", "--layout", "cfg2", "--steps", "1"], capture_output=True, text=True,
+                       timeout=300, env=env)  # fmt: skip
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads([x for x in r.stdout.splitlines() if x.startswith("{")][-1])
+    assert line["n_gpus"] == 2 and line["finite_output"] and line["config"]["parallelism"] == "cfg2 x ulysses1"
