@@ -261,6 +261,15 @@ class ApiServer:
         app.include_router(self._files_router())
         if self.stream_service is not None:
             app.include_router(self._stream_router())
+
+            @app.get("/ui", include_in_schema=False)
+            async def stream_ui():
+                """The browser front end of the streaming service (one static page; it talks to /v1/stream/ws).
+                Role of the reference's webui/stream_app.py, without a UI framework on the server."""
+                from fastapi.responses import HTMLResponse
+
+                page = Path(__file__).resolve().parent / "webui" / "stream.html"
+                return HTMLResponse(page.read_text(encoding="utf-8"))
         from .openai_api import build_openai_routers
 
         for r in build_openai_routers(self):

@@ -363,6 +363,8 @@ def test_stream_websocket_bidirectional(tmp_path):
             assert json.loads(ws.receive_text())["type"] == "done"
         assert client.get("/v1/stream/sessions/abc/status").json()["status"] == "unknown"
         assert client.post("/v1/stream/webrtc/offer", json={"sdp": "x", "task": "t2v"}).status_code == 501
+        ui = client.get("/ui")  # the browser front end: one static page that talks to the WebSocket transport
+        assert ui.status_code == 200 and "text/html" in ui.headers["content-type"] and "/v1/stream/ws" in ui.text
 
 
 # ---------------------------------------------------------------------------
