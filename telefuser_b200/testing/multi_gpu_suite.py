@@ -179,7 +179,8 @@ def check_expert_parallel(rank: int, world: int, device: str) -> dict:
 
     if 8 % world:
         return {"skipped": "8 experts are not divisible by the world size"}
-    over = dict(hidden_size=256, num_attention_heads=2, axes_dims=(32, 48, 48), moe_intermediate_size=128)
+    heads = max(2, world)  # the Ulysses + EP case splits the heads over all ranks
+    over = dict(hidden_size=128 * heads, num_attention_heads=heads, axes_dims=(32, 48, 48), moe_intermediate_size=128)
     kw = dict(frames=2, size=16, text_len=8)  # 520 tokens: divisible by 8
     out = {}
     single = make_model("tiny-moe", torch.bfloat16, device, **over)
@@ -245,22 +246,35 @@ def main(argv=None) -> int:
     report: dict = {"world": world, "backend": a.backend}
     failures: list[str] = []
     try:
+        def section(name: str, fn) -> None:
+            """One part of the sweep: an exception is recorded as that part's failure (the other parts still run), and
+            rank 0 rewrites the report file after every part so that a later crash does not lose what was measured."""
+            try:
+                report[name] = fn()
+            except Exception as e:  # noqa: BLE001
+                report[name] = {"error": f"{type(e).__name__}: {e}"[:400]}
+                failures.append(f"{name}: {report[name]['error']}")
+            if rank == 0 and a.out:
+                with open(a.out, "w") as f:
+                    json.dump({"world": world, "backend": a.backend, "partial": True, "rank0": report,
+                               "failures_so_far": failures}, f, indent=1)  # fmt: skip
+
         if "layouts" not in skip:
-            report["layouts"] = check_layouts(rank, world, device, dtype, gpu)
+            section("layouts", lambda: check_layouts(rank, world, device, dtype, gpu))
             tol = TOLERANCES["layout"] if gpu else 1e-4
             for k, v in report["layouts"].items():
-                if "error" in v or v["rel_err"] > tol:
+                if isinstance(v, dict) and ("error" in v or v.get("rel_err", 0.0) > tol):
                     failures.append(f"layout {k}: {v}")
         if gpu and "peer" not in skip:
-            report["peer"] = check_peer_kernels(rank, world, torch.device(device))
+            section("peer", lambda: check_peer_kernels(rank, world, torch.device(device)))
         if gpu and "ep" not in skip:
-            report["ep"] = check_expert_parallel(rank, world, device)
+            section("ep", lambda: check_expert_parallel(rank, world, device))
         if "vae" not in skip:
-            report["vae"] = check_vae(rank, world, device, dtype)
-        for section in ("peer", "ep", "vae"):
-            for k, v in report.get(section, {}).items():
+            section("vae", lambda: check_vae(rank, world, device, dtype))
+        for part in ("peer", "ep", "vae"):
+            for k, v in report.get(part, {}).items():
                 if isinstance(v, (int, float)) and k in TOLERANCES and v > (TOLERANCES[k] if gpu else 1e-4):
-                    failures.append(f"{section}.{k} = {v}")
+                    failures.append(f"{part}.{k} = {v}")
         if gpu:
             from telefuser_b200.ops import native
 

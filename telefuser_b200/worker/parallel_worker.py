@@ -95,6 +95,10 @@ def _worker_loop(rank: int, stage, world_size: int, port: int, device_type: str,
 
         profiler.mark_as_worker_process()
         stage.device = device
+        if getattr(stage, "onload_models_flag", False) and device.type == "cuda" and hasattr(stage, "onload_models"):
+            # The parent marked the models as resident, but they arrive where the parent held them (every rank
+            # unpickles the same device index): bring them to this rank's own GPU before anything runs.
+            stage.onload_models()
         if hasattr(stage, "configure_device_waits"):
             stage.configure_device_waits()
         if world_size > 1:

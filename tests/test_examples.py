@@ -92,3 +92,60 @@ def test_regression_runner_bf16_kernels_against_the_fp32_oracle():
     for rep in reports:
         assert rep["passed"], rep
         assert rep["native_launches"] > 0 and rep["psnr_db"] >= 25.0
+
+
+def test_frame_replay_service_streams_paced_chunks():
+    """The model-free server-push example: loaded by the stream service under strict validation, it pushes the test
+    card as paced chunks whose frame counts add up to the clip."""
+    import asyncio
+
+    from telefuser_b200.service.stream_service import StreamPipelineService
+
+    svc = StreamPipelineService(ServerConfig(security_level="strict"))
+    assert svc.start_service(str(EXAMPLES / "stream_server" / "stream_frame_replay.py"))
+    assert svc.stream_mode == "server_push"
+
+    async def collect():
+        t0 = time.perf_counter()
+        chunks = [c async for c in svc.stream_task({"fps": 400})]
+        return chunks, time.perf_counter() - t0
+
+    try:
+        chunks, seconds = asyncio.run(collect())
+    finally:
+        svc.service.stop()
+    assert [c["chunk_index"] for c in chunks] == list(range(6)) and sum(c["frames"].shape[0] for c in chunks) == 96
+    assert chunks[0]["frames"].dtype == torch.uint8 and chunks[0]["frames"].shape[1:] == (240, 416, 3)
+    assert 0.15 < seconds < 5.0  # 96 frames at 400 fps: paced, not dumped at once
+
+
+@pytest.mark.parametrize("path", REQUEST_FILES + [STREAM_FILE], ids=lambda p: Path(p).stem)
+def test_example_imports_and_exposes_the_service_entry_points(path):
+    """Importing a pipeline file must not load weights; the names the servers look up exist and every keyword that
+    `run_with_file` / `get_pipeline` use resolves (their local imports are executed here too)."""
+    import importlib.util
+    import inspect
+
+    spec = importlib.util.spec_from_file_location("example_" + Path(path).stem, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    if hasattr(mod, "get_service"):
+        assert callable(mod.get_service)
+        return
+    assert callable(mod.get_pipeline) and callable(mod.run_with_file)
+    assert isinstance(mod.PIPELINE_MANIFEST["tasks"], list) and mod.PPL_CONFIG["name"]
+    params = inspect.signature(mod.run_with_file).parameters
+    assert "pipeline" in params and "output_path" in params
+    for task, needed in mod.PIPELINE_MANIFEST["required_inputs"].items():
+        assert task in mod.PIPELINE_MANIFEST["tasks"] and all(n in params for n in needed), (task, needed)
+    # the imports inside get_pipeline / run_with_file must resolve (names that do not exist would only fail with weights)
+    import ast
+    import importlib
+    import textwrap
+
+    for fn in (mod.get_pipeline, mod.run_with_file):
+        for node in ast.walk(ast.parse(textwrap.dedent(inspect.getsource(fn)))):
+            if isinstance(node, ast.ImportFrom) and node.module and node.module.startswith("telefuser_b200"):
+                target = importlib.import_module(node.module)
+                for alias in node.names:
+                    assert hasattr(target, alias.name), f"{node.module} has no {alias.name}"
