@@ -69,6 +69,16 @@ class BasePipeline:
     def _get_stages(self) -> list:
         return []
 
+    def close(self) -> None:
+        """Ends the worker processes of every stage that runs as SPMD ranks (idempotent). Pipelines that hold other
+        resources override it and call this."""
+        seen = set()
+        for st in list(self._get_stages()) + [v for v in vars(self).values() if hasattr(v, "processes")]:
+            if id(st) in seen or not hasattr(st, "processes") or not callable(getattr(st, "close", None)):
+                continue
+            seen.add(id(st))
+            st.close()
+
     def enable_metrics(self, registry: Any | None = None) -> None:
         self.metrics_enabled = True
         for st in self._get_stages():
