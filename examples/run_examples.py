@@ -95,28 +95,7 @@ CASES = {
 # ---------------------------------------------------------------------------------------------------
 # metrics
 # ---------------------------------------------------------------------------------------------------
-def psnr(a, b, peak: float = 2.0) -> float:
-    import torch
-
-    mse = torch.mean((a.double() - b.double()) ** 2).item()
-    return float("inf") if mse == 0 else 10.0 * float(torch.log10(torch.tensor(peak * peak / mse)))
-
-
-def ssim(a, b, peak: float = 2.0, window: int = 7) -> float:
-    """Mean structural similarity over frames and channels (uniform window; inputs [C, T, H, W])."""
-    import torch
-    import torch.nn.functional as F
-
-    x = a.double().permute(1, 0, 2, 3).reshape(-1, 1, *a.shape[-2:])
-    y = b.double().permute(1, 0, 2, 3).reshape(-1, 1, *b.shape[-2:])
-    k = torch.ones(1, 1, window, window, dtype=torch.float64) / (window * window)
-    mu_x, mu_y = F.conv2d(x, k), F.conv2d(y, k)
-    sxx = F.conv2d(x * x, k) - mu_x**2
-    syy = F.conv2d(y * y, k) - mu_y**2
-    sxy = F.conv2d(x * y, k) - mu_x * mu_y
-    c1, c2 = (0.01 * peak) ** 2, (0.03 * peak) ** 2
-    s = ((2 * mu_x * mu_y + c1) * (2 * sxy + c2)) / ((mu_x**2 + mu_y**2 + c1) * (sxx + syy + c2))
-    return float(s.mean())
+from telefuser_b200.utils.quality import psnr, ssim  # noqa: E402
 
 
 def summary(video) -> dict:

@@ -118,3 +118,22 @@ def test_stream_session_bench_against_a_live_stream_service(tmp_path):
     ev = [json.loads(line) for line in (tmp_path / "art" / "events_0.jsonl").read_text().splitlines()]
     assert [e["event"] for e in ev].count("control") == 6 and [e["event"] for e in ev].count("chunk") == 6
     assert (tmp_path / "art" / "server_metrics.jsonl").read_text().count('"status": 200') >= 2
+
+
+def test_feature_cache_bench_reports_skipped_steps_and_similarity(capsys):
+    import torch
+
+    from telefuser_b200.utils.quality import psnr, ssim
+
+    x = torch.rand(3, 2, 16, 16) * 2 - 1
+    assert psnr(x, x) == float("inf") and ssim(x, x) == pytest.approx(1.0)
+    y = (x + 0.05 * torch.randn_like(x)).clamp(-1, 1)
+    assert 20 < psnr(y, x) < 45 and 0.5 < ssim(y, x) < 1.0 and ssim(y[:, 0], x[:, 0]) > 0.5  # single images too
+    fb = load("feature_cache_bench")
+    assert fb.main(["--random-init", "--preset", "tiny", "--device", "cpu", "--steps", "12", "--frames", "5", "--height", "32",
+                    "--width", "32", "--orders", "0,1"]) == 0  # fmt: skip
+    lines = [json.loads(line) for line in capsys.readouterr().out.splitlines() if line.startswith("{")]
+    summary = lines[-1]["summary"]
+    assert [r["config"] for r in summary] == ["no cache", "adaptive Taylor cache, order 0", "adaptive Taylor cache, order 1"]
+    assert summary[0]["computed_steps"] == 12 and all(r["computed_steps"] < 12 and r["finite"] for r in summary[1:])
+    assert all(r["psnr_db"] > 25 and r["ssim"] > 0.85 for r in summary[1:])
