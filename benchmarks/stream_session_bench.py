@@ -7,7 +7,9 @@ One session = connect, send the session config, replay a timed control trace (ke
 chunk messages and their JPEG frames, close after `session_duration_s`. `warmup_sessions` run first and are not
 counted. Per session the harness records: connect and session-open latency, time to the first chunk and first frame,
 frames and chunks received, stream fps over the session, chunk inter-arrival p50 / p99, and for every control event
-the time until the next chunk message that arrives after it (`control_to_next_chunk_ms`). With `server_metrics` the
+the time until the next media chunk that arrives after it (`control_to_next_chunk_ms`); every control is sent with a
+`revision`, and a service that acknowledges revisions and reports the revision each chunk was steered by (the
+LingBot-World service does) also yields `control_ack_ms` and `control_applied_ms`. With `server_metrics` the
 service's Prometheus text (`/v1/service/metrics`) is sampled beside the run. Output: `sessions.jsonl`, one
 `events_<n>.jsonl` trace per session, `server_metrics.jsonl`, and `summary.json` in `artifacts_dir`; the summary is also
 printed as one JSON line.
@@ -92,8 +94,12 @@ async def run_session(cfg: dict, index: int, trace: list[dict], events_path: Pat
     if cfg.get("image_path"):
         session_cfg["image_path"] = cfg["image_path"]
     chunk_times: list[float] = []
-    control_sent: list[float] = []
+    control_sent: list[float] = []  # send times of controls not yet followed by a media chunk
     control_lat: list[float] = []
+    sent_by_revision: dict[int, float] = {}
+    ack_lat: list[float] = []
+    applied_lat: list[float] = []  # control sent -> first media chunk that reports its revision (or a later one) as applied
+    unapplied: dict[int, float] = {}
     pending_frames = 0
     try:
         timeout = aiohttp.ClientTimeout(total=None, sock_connect=tr["connect_timeout_s"])
@@ -115,9 +121,13 @@ async def run_session(cfg: dict, index: int, trace: list[dict], events_path: Pat
                             await asyncio.sleep(delay)
                         if time.perf_counter() - t_open >= cfg["session_duration_s"]:
                             return
-                        await ws.send_str(json.dumps(ev["message"]))
-                        control_sent.append(time.perf_counter())
-                        mark("control", message=ev["message"])
+                        message = dict(ev["message"])
+                        revision = message.setdefault("revision", len(sent_by_revision) + 1)
+                        await ws.send_str(json.dumps(message))
+                        now = time.perf_counter()
+                        control_sent.append(now)
+                        sent_by_revision[revision] = unapplied[revision] = now
+                        mark("control", message=message)
 
                 ctl = asyncio.create_task(controls())
                 try:
@@ -134,7 +144,16 @@ async def run_session(cfg: dict, index: int, trace: list[dict], events_path: Pat
                                 rec["first_frame_ms"] = round(mark("first_frame") * 1e3, 3)
                         elif msg.type == aiohttp.WSMsgType.TEXT:
                             body = json.loads(msg.data)
-                            if body.get("type") == "chunk":
+                            data = body.get("data") if isinstance(body.get("data"), dict) else {}
+                            if body.get("type") == "chunk" and int(body.get("num_frames", 0)) == 0 and not body.get("error"):
+                                # a service message without media (status, control acknowledgement)
+                                now = time.perf_counter()
+                                if data.get("type") == "control_ack" and data.get("revision") in sent_by_revision:
+                                    ack_lat.append((now - sent_by_revision[data["revision"]]) * 1e3)
+                                mark("message", message_type=data.get("type"), revision=data.get("revision"))
+                                if data.get("type") in ("done", "error") or data.get("done"):
+                                    break
+                            elif body.get("type") == "chunk":
                                 now = time.perf_counter()
                                 chunk_times.append(now)
                                 rec["chunks"] += 1
@@ -143,7 +162,13 @@ async def run_session(cfg: dict, index: int, trace: list[dict], events_path: Pat
                                     rec["first_chunk_ms"] = round((now - t_start) * 1e3, 3)
                                 while control_sent and control_sent[0] <= now:  # controls answered by this chunk
                                     control_lat.append((now - control_sent.pop(0)) * 1e3)
-                                mark("chunk", chunk=body.get("index"), num_frames=body.get("num_frames"))
+                                applied = data.get("control_revision")
+                                if isinstance(applied, int):
+                                    for rev in [r for r in unapplied if r <= applied]:
+                                        applied_lat.append((now - unapplied.pop(rev)) * 1e3)
+                                mark("chunk", chunk=body.get("index"), num_frames=body.get("num_frames"), control_revision=applied)
+                                if data.get("done"):
+                                    break
                             elif body.get("type") in ("done", "error"):
                                 mark(body["type"], detail=body.get("error"))
                                 if body.get("type") == "error":
@@ -167,7 +192,9 @@ async def run_session(cfg: dict, index: int, trace: list[dict], events_path: Pat
                stream_fps=round((rec["frames"] - rec["frames"] / max(rec["chunks"], 1)) / span, 3) if span > 0 else None,
                chunk_gap_ms_p50=percentile(gaps, 50), chunk_gap_ms_p99=percentile(gaps, 99),
                control_to_next_chunk_ms_p50=percentile(control_lat, 50),
-               control_to_next_chunk_ms_p99=percentile(control_lat, 99), controls_sent=len(control_lat) + len(control_sent))  # fmt: skip
+               control_to_next_chunk_ms_p99=percentile(control_lat, 99), controls_sent=len(control_lat) + len(control_sent),
+               control_ack_ms_p50=percentile(ack_lat, 50), control_ack_ms_p99=percentile(ack_lat, 99),
+               control_applied_ms_p50=percentile(applied_lat, 50), control_applied_ms_p99=percentile(applied_lat, 99))  # fmt: skip
     if events_path is not None:
         events_path.write_text("".join(json.dumps(e) + "\n" for e in events))
     return rec
@@ -224,7 +251,8 @@ async def run(cfg: dict) -> dict:
                "frames_received": sum(s["frames"] for s in sessions), "chunks_received": sum(s["chunks"] for s in sessions),
                **{k: agg(k) for k in ("connect_ms", "session_open_ms", "first_chunk_ms", "first_frame_ms", "stream_fps",
                                       "chunk_gap_ms_p50", "chunk_gap_ms_p99", "control_to_next_chunk_ms_p50",
-                                      "control_to_next_chunk_ms_p99", "session_runtime_s")},
+                                      "control_to_next_chunk_ms_p99", "control_ack_ms_p50", "control_applied_ms_p50",
+                                      "session_runtime_s")},
                "config": {k: cfg[k] for k in ("server_url", "fps", "session_count", "warmup_sessions", "session_duration_s",
                                               "stagger_s", "control_trace_path", "request_extra")}}  # fmt: skip
     (art / "summary.json").write_text(json.dumps(summary, indent=1))

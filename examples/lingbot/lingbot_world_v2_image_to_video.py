@@ -51,6 +51,11 @@ def _modules(device: str, dtype) -> ModuleManager:
         dit.dtype = dtype
         mm.add_module(random_init_(dit).eval(), "lingbot_world_fast_dit")
         mm.add_module(random_init_(vae, std=0.02).eval(), "wan_video_vae")
+        text_dim = kw.get("text_dim", 4096)  # a short random UMT5 stack of the right width stands in for the prompt encoder
+        with torch.device(device):
+            te = WanTextEncoder(vocab=4096, dim=text_dim, dim_attn=text_dim, dim_ffn=2 * text_dim,
+                                num_heads=max(1, text_dim // 64), num_layers=2).to(dtype)  # fmt: skip
+        mm.add_module(random_init_(te, seed=1).eval(), "random_text_encoder")
         return mm
     shards = sorted(str(p) for p in Path(PPL_CONFIG["dit_dir"]).glob("model-*-of-*.safetensors"))
     mm.load_model(shards, model_class=LingBotWorldFastDiT, name="lingbot_world_fast_dit")
@@ -77,7 +82,16 @@ def get_pipeline(parallelism: int = PPL_CONFIG["parallelism"]) -> LingBotWorldV2
         local_attn_size=PPL_CONFIG["local_attn_size"], sink_size=PPL_CONFIG["sink_size"],
         timestep_indices=PPL_CONFIG["timestep_indices"], fps=PPL_CONFIG["target_fps"], enable_denoising_parallel=par is not None)  # fmt: skip
     pipe = LingBotWorldV2Pipeline(device=device, torch_dtype=dtype)
-    pipe.init(_modules(device, dtype), config)
+    mm = _modules(device, dtype)
+    text_stage = None
+    if mm.fetch_module("random_text_encoder") is not None:
+        from telefuser_b200.pipelines.wan.stages import TextEncodingStage
+        from telefuser_b200.testing.synthetic import HashTokenizer
+
+        text_stage = TextEncodingStage("text_encoding", mm, config.text_encoding_config, config.max_sequence_length,
+                                       text_encoder=mm.fetch_module("random_text_encoder"), tokenizer=HashTokenizer(4096, 512))  # fmt: skip
+        text_stage.onload_models_flag = True
+    pipe.init(mm, config, text_stage=text_stage)
     return pipe
 
 

@@ -46,6 +46,7 @@ class LingBotWorldFastSessionConfig:
     turn_step_deg: float = 1.5
     hud: bool = False
     output_queue_size: int = 8
+    benchmark_metrics: bool = False  # a "status" message with the runtime snapshot follows every chunk
 
 
 @dataclass
@@ -68,6 +69,17 @@ class LingBotWorldFastSessionState:
     finished: bool = False
     control_bound_at: dict = field(default_factory=dict)  # chunk index -> monotonic time its control was sampled
     control_latency_s: list = field(default_factory=list)  # control sampled -> frames emitted, per chunk
+    # measurements a client or a load generator reads through status messages / `session_metrics`
+    created_mono: float = field(default_factory=time.monotonic)
+    worker_started_mono: float | None = None
+    first_chunk_mono: float | None = None
+    queue_high_watermark: int = 0
+    controls_received: int = 0
+    controls_superseded: int = 0  # key snapshots replaced by a newer one before any chunk sampled them
+    explicit_overwritten: int = 0  # pose chunks dropped because a newer one arrived first (latest wins)
+    control_revision_received: int = 0
+    control_revision_applied: int = 0
+    unsampled_snapshot: bool = False
 
 
 def frame_num_for_duration(max_duration_seconds: float, fps: int, chunk_size: int) -> int:
@@ -174,23 +186,79 @@ class LingBotWorldFastService:
 
     # ---- client -> service ---------------------------------------------------------------------
     def push_chunk(self, session_id: str, chunk: dict) -> None:
+        """One client message. Key events edit the held-key set; a key snapshot or a direction replaces it; a pose /
+        control-tensor chunk steers the next chunk directly. Only the newest pending control of each kind is kept
+        (an interactive session wants the latest intent, not a backlog). A message that carries `revision` is
+        acknowledged with a `control_ack`, and the revision of the control that a chunk finally used is reported with
+        that chunk, so a client can measure both the acknowledgement and the control-to-picture latency."""
         state = self._state(session_id)
         kind = chunk.get("type", "control")
+        ack = None
         with state.lock:
             if kind == "stop":
                 state.stop_event.set()
-            elif kind == "key_down" and str(chunk.get("key", "")).lower() in _VALID_KEYS:
-                state.held_keys.add(str(chunk["key"]).lower())
-            elif kind == "key_up":
-                state.held_keys.discard(str(chunk.get("key", "")).lower())
-            elif "poses" in chunk or "control_tensor" in chunk:
-                state.explicit_chunks.append(chunk)  # used for the next chunk instead of the key snapshot
             else:
-                keys = keys_from_chunk(chunk)
-                if keys is None and chunk.get("direction") in DIRECTION_KEYS:
-                    keys = {DIRECTION_KEYS[chunk["direction"]]}
-                if keys is not None:
-                    state.held_keys = keys
+                state.controls_received += 1
+                if isinstance(chunk.get("revision"), int):
+                    state.control_revision_received = max(state.control_revision_received, chunk["revision"])
+                    ack = chunk["revision"]
+                if kind == "key_down" and str(chunk.get("key", "")).lower() in _VALID_KEYS:
+                    state.held_keys.add(str(chunk["key"]).lower())
+                elif kind == "key_up":
+                    state.held_keys.discard(str(chunk.get("key", "")).lower())
+                elif "poses" in chunk or "control_tensor" in chunk:
+                    if state.explicit_chunks and not chunk.get("queue", False):
+                        state.explicit_overwritten += len(state.explicit_chunks)
+                        state.explicit_chunks.clear()
+                    state.explicit_chunks.append(chunk)  # used for the next chunk instead of the key snapshot
+                else:
+                    keys = keys_from_chunk(chunk)
+                    if keys is None and chunk.get("direction") in DIRECTION_KEYS:
+                        keys = {DIRECTION_KEYS[chunk["direction"]]}
+                    if keys is not None:
+                        if state.unsampled_snapshot:
+                            state.controls_superseded += 1
+                        state.held_keys, state.unsampled_snapshot = keys, True
+        if ack is not None:
+            self._enqueue(state, {"type": "control_ack", "session_id": session_id, "revision": ack,
+                                  "elapsed_s": time.monotonic() - state.created_mono})  # fmt: skip
+
+    # ---- measurements ---------------------------------------------------------------------------
+    def session_metrics(self, session_id: str) -> dict:
+        """Runtime snapshot of one session (also sent as `status` messages when `benchmark_metrics` is on)."""
+        return self._snapshot(self._state(session_id))
+
+    @staticmethod
+    def _snapshot(state: LingBotWorldFastSessionState) -> dict:
+        now = time.monotonic()
+        with state.lock:
+            lat = sorted(state.control_latency_s)
+            out = {"session_age_s": round(now - state.created_mono, 6), "chunks_submitted": state.submitted,
+                   "chunks_emitted": state.emitted, "dropped_chunks": state.dropped_chunks,
+                   "output_queue_depth": state.outputs.qsize(), "output_queue_high_watermark": state.queue_high_watermark,
+                   "controls_received": state.controls_received, "controls_superseded": state.controls_superseded,
+                   "explicit_controls_overwritten": state.explicit_overwritten, "explicit_controls_pending": len(state.explicit_chunks),
+                   "control_revision_received": state.control_revision_received,
+                   "control_revision_applied": state.control_revision_applied}  # fmt: skip
+            if state.worker_started_mono is not None:
+                out["worker_start_s"] = round(state.worker_started_mono - state.created_mono, 6)
+            if state.first_chunk_mono is not None:
+                out["first_chunk_s"] = round(state.first_chunk_mono - state.created_mono, 6)
+            if lat:
+                out["control_to_output_p50_s"] = round(lat[len(lat) // 2], 6)
+                out["control_to_output_max_s"] = round(lat[-1], 6)
+        return out
+
+    @staticmethod
+    def _progress(state: LingBotWorldFastSessionState) -> dict:
+        """How far the session is: frames and seconds of video generated out of the requested total."""
+        g, fps = state.generation, state.config.fps
+        total_frames = (g.chunk_count * g.chunk_size - 1) * 4 + 1
+        done_latent = state.emitted * g.chunk_size
+        done_frames = 0 if state.emitted == 0 else min(total_frames, (done_latent - 1) * 4 + 1)
+        return {"total_chunks": g.chunk_count, "completed_chunks": state.emitted, "target_frames": total_frames,
+                "generated_frames": done_frames, "fps": fps, "target_duration_s": round((total_frames - 1) / fps, 3),
+                "generated_duration_s": round(max(done_frames - 1, 0) / fps, 3)}  # fmt: skip
 
     # ---- service -> client ---------------------------------------------------------------------
     @staticmethod
@@ -208,6 +276,9 @@ class LingBotWorldFastService:
                                 state.dropped_chunks += 1
                                 break
         q.put(payload)
+        depth = q.qsize()
+        if depth > state.queue_high_watermark:
+            state.queue_high_watermark = depth
 
     async def pull_chunks(self, session_id: str) -> AsyncGenerator[dict, None]:
         state = self._state(session_id)
@@ -246,6 +317,8 @@ class LingBotWorldFastService:
         with state.lock:
             explicit = state.explicit_chunks.pop(0) if state.explicit_chunks else None
             keys = sorted(state.held_keys)
+            state.unsampled_snapshot = False
+            state.control_revision_applied = state.control_revision_received
         if explicit is not None:
             if "poses" in explicit:
                 state.pose = torch.as_tensor(np.asarray(explicit["poses"]), dtype=torch.float32)[-1].cpu()
@@ -263,6 +336,7 @@ class LingBotWorldFastService:
         pending: dict[int, list | None] = {}
         cancelled = False
         try:
+            state.worker_started_mono = time.monotonic()
             self._enqueue(state, {"type": "status", "stage": "running", "session_id": state.session_id})
             while state.emitted < total:
                 if state.stop_event.is_set():
@@ -298,6 +372,7 @@ class LingBotWorldFastService:
                 if lat:
                     metrics["control_bound_to_output_p50_s"] = lat[len(lat) // 2]
                     metrics["control_bound_to_output_max_s"] = lat[-1]
+                metrics["session"] = self._snapshot(state)
             except Exception:  # noqa: BLE001 - metrics are best effort
                 pass
             self._enqueue(state, {"type": "done", "session_id": state.session_id, "cancelled": cancelled, "chunks": state.emitted,
@@ -322,13 +397,19 @@ class LingBotWorldFastService:
         if state.config.hud:
             arr = overlay_control_hud(arr, keys)
         state.emitted += 1
+        if state.first_chunk_mono is None:
+            state.first_chunk_mono = time.monotonic()
         bound = state.control_bound_at.pop(idx, None)
         latency = None if bound is None else time.monotonic() - bound
         if latency is not None:
             state.control_latency_s.append(latency)
         self._enqueue(state, {"type": "frames", "session_id": state.session_id, "chunk_index": idx, "frames": arr, "controls": keys,
                               "fps": state.config.fps, "elapsed_s": time.time() - state.created_at,
-                              "control_to_output_s": latency})  # fmt: skip
+                              "control_to_output_s": latency, "control_revision": state.control_revision_applied,
+                              "progress": self._progress(state)})  # fmt: skip
+        if state.config.benchmark_metrics:
+            self._enqueue(state, {"type": "status", "stage": "chunk", "session_id": state.session_id, "chunk_index": idx,
+                                  "metrics": self._snapshot(state)})  # fmt: skip
 
     def close_session(self, session_id: str, timeout: float | None = None) -> None:
         state = self._sessions.get(session_id)

@@ -25,6 +25,7 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, AsyncGenerator, Protocol, runtime_checkable
 
+import numpy as np
 import torch
 
 from telefuser_b200.utils.logging import logger
@@ -181,6 +182,7 @@ class ChunkRouter:
 
     def route(self, chunk: dict, session_id: str, index: int) -> tuple[list, dict]:
         frames: list = []
+        media_keys: set = set()
         for k in self.FRAME_KEYS:
             v = chunk.get(k)
             if v is None:
@@ -190,12 +192,19 @@ class ChunkRouter:
                 if v.dim() == 3:
                     v = v[None]
                 frames.extend(v.unbind(0))
+                media_keys.add(k)
+            elif isinstance(v, np.ndarray) and v.ndim in (3, 4):
+                frames.extend(list(v) if v.ndim == 4 else [v])
+                media_keys.add(k)
             elif isinstance(v, (list, tuple)):
                 frames.extend(v)
-            else:
+                media_keys.add(k)
+            elif isinstance(v, (bytes, bytearray)) or hasattr(v, "save"):  # an encoded image or a PIL image
                 frames.append(v)
+                media_keys.add(k)
+            # anything else under these names (a frame count, a flag) is ordinary data and stays in the message
         msg = {"type": "chunk", "session_id": session_id, "index": index, "num_frames": len(frames),
-               "data": serialisable_chunk({k: v for k, v in chunk.items() if k not in self.FRAME_KEYS}),
+               "data": serialisable_chunk({k: v for k, v in chunk.items() if k not in media_keys}),
                "timestamp": time.time()}  # fmt: skip
         if chunk.get("error"):
             msg["error"] = str(chunk["error"])

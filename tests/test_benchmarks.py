@@ -137,3 +137,34 @@ def test_feature_cache_bench_reports_skipped_steps_and_similarity(capsys):
     assert [r["config"] for r in summary] == ["no cache", "adaptive Taylor cache, order 0", "adaptive Taylor cache, order 1"]
     assert summary[0]["computed_steps"] == 12 and all(r["computed_steps"] < 12 and r["finite"] for r in summary[1:])
     assert all(r["psnr_db"] > 25 and r["ssim"] > 0.85 for r in summary[1:])
+
+
+def test_stream_session_bench_against_the_world_model_example(tmp_path, monkeypatch):
+    """Full stack on CPU: the LingBot-World example file (tiny random-init model) behind the stream API, driven by the
+    load generator over a real socket; acknowledgements and applied revisions give the two control latencies."""
+    import asyncio
+
+    monkeypatch.setenv("TFB_RANDOM_INIT", "1")
+    monkeypatch.setenv("TFB_TINY", "1")
+    sb = load("stream_session_bench")
+    config = ServerConfig(cache_dir=str(tmp_path / "cache"), security_level="strict")
+    svc = StreamPipelineService(config)
+    assert svc.start_service(str(ROOT / "examples" / "lingbot" / "lingbot_world_v2_image_to_video.py"), gpu_num=1)
+    trace = tmp_path / "trace.json"
+    trace.write_text(json.dumps({"events": [{"t": 0.05, "message": {"keys": ["w"]}}, {"t": 0.4, "message": {"keys": ["a"]}}]}))
+    try:
+        with LiveServer(ApiServer(config, None, svc).app) as srv:
+            cfg = sb.load_config(None, {"server_url": srv.url, "session_count": 1, "session_duration_s": 60.0,
+                                        "warmup_sessions": 0, "artifacts_dir": str(tmp_path / "art")})  # fmt: skip
+            cfg["control_trace_path"] = str(trace)
+            from PIL import Image
+
+            Image.new("RGB", (64, 64), (90, 120, 150)).save(tmp_path / "first.png")
+            cfg["image_path"] = str(tmp_path / "first.png")
+            cfg["request_extra"] = {"height": 64, "width": 64, "max_duration_seconds": 2.0, "benchmark_metrics": True}
+            summary = asyncio.run(sb.run(cfg))
+    finally:
+        svc.service.stop()
+    assert summary["success_rate"] == 1.0 and summary["chunks_received"] >= 2 and summary["frames_received"] >= 9
+    assert summary["control_ack_ms_p50"] is not None and summary["control_applied_ms_p50"] is not None
+    assert summary["control_ack_ms_p50"]["p50"] <= summary["control_applied_ms_p50"]["p50"]

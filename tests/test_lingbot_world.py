@@ -107,8 +107,33 @@ def test_interactive_service_session():
     frames = [m for m in msgs if m["type"] == "frames"]
     assert [m["chunk_index"] for m in frames] == [0, 1, 2, 3] and frames[0]["frames"].shape == (5, 32, 32, 3) and frames[1]["frames"].shape == (8, 32, 32, 3)
     assert frames[0]["frames"].dtype == np.uint8 and msgs[-1]["chunks"] == 4 and not msgs[-1]["cancelled"]
+    # progress travels with every chunk; the final message carries the session's measurement snapshot
+    assert frames[-1]["progress"]["completed_chunks"] == 4 and frames[-1]["progress"]["total_chunks"] == 4
+    assert frames[-1]["progress"]["generated_frames"] == frames[-1]["progress"]["target_frames"] == 29
+    assert frames[0]["progress"]["generated_frames"] == 5 and frames[-1]["progress"]["generated_duration_s"] == 1.75
+    snap = msgs[-1]["metrics"]["session"]
+    assert snap["chunks_emitted"] == 4 and snap["controls_received"] == 2 and snap["first_chunk_s"] >= snap["worker_start_s"] >= 0
+    assert snap["output_queue_high_watermark"] >= 1 and "control_to_output_p50_s" in snap
     svc.close_session(sid)
     assert not svc.has_session(sid)
+    # control revisions: acknowledged at once, newest snapshot wins, the applied revision is reported with the chunk,
+    # and with `benchmark_metrics` a status message with the snapshot follows every chunk
+    sid3 = svc.create_session({"image": img, "prompt_emb": emb, "seed": 1, "benchmark_metrics": True})
+    for rev, keys in ((1, ["w"]), (2, ["a"]), (3, ["d"])):
+        svc.push_chunk(sid3, {"keys": keys, "revision": rev})
+    svc.push_chunk(sid3, {"poses": random_walk_trajectory(2, seed=1), "relative": True})
+    svc.push_chunk(sid3, {"poses": random_walk_trajectory(2, seed=2), "relative": True, "revision": 4})  # replaces the first
+    msgs3 = svc.drain(sid3, timeout=120.0)
+    acks = [m["revision"] for m in msgs3 if m["type"] == "control_ack"]
+    assert acks == [1, 2, 3, 4]
+    fr3 = [m for m in msgs3 if m["type"] == "frames"]
+    assert len(fr3) == 4 and fr3[-1]["control_revision"] == 4
+    stat3 = [m for m in msgs3 if m["type"] == "status" and m.get("stage") == "chunk"]
+    assert len(stat3) == 4 and stat3[-1]["metrics"]["chunks_emitted"] == 4
+    m3 = svc.session_metrics(sid3)
+    assert m3["explicit_controls_overwritten"] == 1 and m3["control_revision_received"] == 4 and m3["controls_received"] == 5
+    assert m3["controls_superseded"] >= 1  # of three snapshots pushed back to back at most two could each steer a chunk
+    svc.close_session(sid3)
     # explicit pose chunks and an early stop
     poses = random_walk_trajectory(2, seed=3)
     sid2 = svc.create_session({"image": img, "prompt_emb": emb, "seed": 1, "max_duration_seconds": 3.0, "hud": False,
