@@ -5,6 +5,7 @@ import os
 import subprocess
 import sys
 
+import pytest
 import torch
 from safetensors.torch import save_file
 
@@ -90,3 +91,32 @@ def test_lingbot_video_validation_tool_inspect_capture_compare_bench(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     line = json.loads([x for x in r.stdout.splitlines() if x.startswith("{")][-1])
     assert line["n_gpus"] == 2 and line["finite_output"] and line["config"]["parallelism"] == "cfg2 x ulysses1"
+
+
+def test_resource_monitor_records_and_tells_a_leak_from_a_plateau(tmp_path):
+    import os
+
+    from telefuser_b200.tools import resource_monitor as M
+
+    class FakeGPU:
+        def __init__(self):
+            self.n = 0
+
+        def sample(self):
+            self.n += 1
+            # gpu0 leaks 1 MB per sample, gpu1 fills a cache for 10 samples and then stays flat
+            return [{"index": 0, "util": 50.0, "mem_used_mb": 1000.0 + self.n, "mem_total_mb": 180000.0},
+                    {"index": 1, "util": 10.0, "mem_used_mb": 2000.0 + min(self.n, 10) * 5, "mem_total_mb": 180000.0}]
+
+    now = [0.0]
+    path = str(tmp_path / "run.csv")
+    rows = M.record(path, 10.0, 600.0, None, os.getpid(), collector=FakeGPU(), clock=lambda: now[0],
+                    sleep=lambda s: now.__setitem__(0, now[0] + s))  # fmt: skip
+    assert rows == 61
+    rep = M.report(path, warmup_s=120.0, leak_per_hour=50.0)
+    assert rep["samples"] == 61 and rep["leaking_series"] == ["gpu0_mem_mb"]
+    assert rep["series"]["gpu0_mem_mb"]["slope_per_hour"] == pytest.approx(360.0, rel=1e-3)
+    assert rep["series"]["gpu1_mem_mb"]["leak"] is False and rep["series"]["rss_mb"]["min"] > 0
+    assert rep["series"]["processes"]["min"] >= 1
+    assert M.main(["report", path, "--warmup-s", "120"]) == 1  # non-zero exit when something leaks
+    assert M.fit_slope([0, 1, 2], [1, 3, 5]) == pytest.approx(2.0) and M.analyse([]) == {}
