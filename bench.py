@@ -393,8 +393,16 @@ def main():
         raise SystemExit("bench.py needs a CUDA device")
     rank, world, local = dist_setup(args.gpus)
     layout = layout_for(world, args.layout)
+    t_start = time.perf_counter()
+
+    def progress(what: str) -> None:
+        """Milestones on stderr (rank 0), so that a run cut short by a time limit still says how far it got."""
+        if rank == 0:
+            print(f"[bench {args.impl}] {what} at {time.perf_counter() - t_start:.1f} s", file=sys.stderr, flush=True)
+
     try:
         run, native, extra = (build_reference if args.impl == "reference" else build_ours)(args, layout, world, local)
+        progress(f"arm built ({extra})" if extra else "arm built")
     except Exception as e:  # noqa: BLE001 - report why the arm cannot run
         if args.impl == "reference":
             if rank == 0:
@@ -411,6 +419,7 @@ def main():
     if args.warmup > 0:
         run(lat, args.warmup, posi, nega)
     barrier_sync(world)
+    progress(f"{args.warmup} warm-up steps done")
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -425,6 +434,7 @@ def main():
     launches = native.launch_count() if native is not None else None
     clocks = sampler.stop() if rank == 0 else None
     finite = bool(torch.isfinite(out.float()).all().item())
+    progress(f"{args.steps} timed steps done: {ms_step:.1f} ms/step, finite={finite}")
 
     # ---- end to end through the stage API: pinned host -> device -> step -> host, every step ----
     e2e = None
@@ -445,9 +455,11 @@ def main():
                "h2d_bytes_per_step": lat_h.numel() * 4 + posi_h.numel() * 2 + nega_h.numel() * 2,
                "d2h_bytes_per_step": res_h.numel() * 4}  # fmt: skip
 
+    progress("end-to-end steps done" if e2e is not None else "end-to-end steps skipped")
     stages = None
     if rank == 0 and not args.no_pipeline_stages:
         stages = time_pipeline_stages(args)
+        progress(f"pipeline stages timed: {stages}")
     barrier_sync(world)
 
     if rank == 0:
