@@ -248,6 +248,44 @@ def _linear_w8a8(x, weight, weight_scale, bias, act, residual, gate, int8):
     return out
 
 
+def bmm_fp8(a, b, a_scale, b_scale, out_dtype=torch.bfloat16, out=None):
+    """Batched FP8 product with one scale per operand: out[i] = (a[i] @ b[i]) * a_scale * b_scale.
+
+    a: e4m3 [B, M, K]; b: e4m3 [B, K, N] whose K axis is the contiguous one (a transposed view of a [B, N, K] tensor,
+    the column-major operand a batched FP8 library GEMM takes); a_scale / b_scale: one fp32 value each. On CUDA
+    every batch entry runs on the W8A8 tensor-core GEMM with the two scalars broadcast as its per-row / per-column scale
+    vectors; elsewhere the product is evaluated in fp32. Role of the reference's `bmm_fp8`
+    (tf-kernel/tf_kernel/gemm.py:60, tf-kernel/csrc/gemm/bmm_fp8.cu)."""
+    if a.dim() != 3 or b.dim() != 3 or a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
+        raise ValueError(f"bmm_fp8: shapes {tuple(a.shape)} x {tuple(b.shape)} do not multiply")
+    B, M, K = a.shape
+    N = b.shape[2]
+    sa = a_scale.to(device=a.device, dtype=torch.float32).reshape(-1)[:1]
+    sb = b_scale.to(device=a.device, dtype=torch.float32).reshape(-1)[:1]
+    if out is None:
+        out = torch.empty(B, M, N, device=a.device, dtype=out_dtype)
+    bt = b.transpose(1, 2)  # [B, N, K]
+    native_ok = (_native(a) and a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn and K % 16 == 0
+                 and N % 8 == 0 and a.stride(2) == 1 and bt.stride(2) == 1 and a.stride(1) % 16 == 0 and bt.stride(1) % 16 == 0)  # fmt: skip
+    if not native_ok:
+        out.copy_((torch.bmm(a.float(), b.float()) * (sa * sb)).to(out.dtype))
+        return out
+    row_scale, col_scale = sa.expand(M).contiguous(), sb.expand(N).contiguous()
+    lib = native.load()
+    tmp = out if out.dtype == torch.bfloat16 and out.is_contiguous() else torch.empty(B, M, N, device=a.device, dtype=torch.bfloat16)
+    for i in range(B):
+        ai, bi = a[i], bt[i]
+        if ai.data_ptr() % 16 or bi.data_ptr() % 16:
+            ai, bi = ai.contiguous(), bi.contiguous()
+        code = lib.tfb_gemm_fp8(ai.data_ptr(), ai.stride(0), bi.data_ptr(), bi.stride(0), tmp[i].data_ptr(), N, M, N, K,
+                                row_scale.data_ptr(), col_scale.data_ptr(), None, 0, None, 0, None, 0, 1,
+                                native.stream_ptr())  # fmt: skip
+        native.check(code, "tfb_gemm_fp8")
+    if tmp is not out:
+        out.copy_(tmp)
+    return out
+
+
 def linear_fp8(x, weight, weight_scale, bias=None, act=None, residual=None, gate=None):
     """W8A8: weight e4m3 [N, K] with per-output-channel scale [N] or [N, 1]; activations are quantised
     per token on the fly; fp32 accumulate; epilogue as `linear`."""

@@ -310,3 +310,34 @@ def test_row_and_tensor_quantisers_match_their_references_at_every_width(C):
     pq2, ps2 = TF.quant_fp8_per_tensor(x, scale=torch.tensor([0.02], device="cuda"))
     assert float(ps2) == pytest.approx(0.02)
     assert ((pq2.float() - (x.float() / 0.02).clamp(-448, 448).to(torch.float8_e4m3fn).float()).abs() > 0).float().mean().item() < 1e-3
+
+
+def test_bmm_fp8_reference_path():
+    torch.manual_seed(0)
+    a = (torch.randn(3, 5, 32) * 4).to(torch.float8_e4m3fn)
+    b = (torch.randn(3, 7, 32) * 4).to(torch.float8_e4m3fn).transpose(1, 2)  # [B, K, N] with K contiguous
+    sa, sb = torch.tensor([0.25]), torch.tensor(0.5)
+    got = TF.bmm_fp8(a, b, sa, sb, torch.float32)
+    assert got.shape == (3, 5, 7) and torch.allclose(got, torch.bmm(a.float(), b.float()) * 0.125)
+    out = torch.empty(3, 5, 7, dtype=torch.bfloat16)
+    assert TF.bmm_fp8(a, b, sa, sb, out=out) is out and torch.allclose(out.float(), got, rtol=1e-2, atol=1e-2)
+    with pytest.raises(ValueError):
+        TF.bmm_fp8(a, b[:, :16], sa, sb)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,M,N,K", [(2, 300, 256, 512), (3, 77, 72, 144)])
+def test_bmm_fp8_runs_every_batch_entry_on_the_fp8_gemm(B, M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn(B, M, K, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(B, N, K, device="cuda").to(torch.float8_e4m3fn).transpose(1, 2)
+    sa, sb = torch.tensor([0.02], device="cuda"), torch.tensor([3.0], device="cuda")
+    from telefuser_b200.ops import native
+
+    before = native.launch_count()
+    got = TF.bmm_fp8(a, b, sa, sb).float()
+    assert native.launch_count() - before == B
+    want = torch.bmm(a.float(), b.float()) * 0.06
+    assert ((got - want).abs() / (1 + want.abs())).max().item() <= 1e-2  # bf16 rounding of the output only
+    f32 = TF.bmm_fp8(a, b, sa, sb, torch.float32)
+    assert f32.dtype == torch.float32 and torch.allclose(f32, got, atol=1e-6)

@@ -117,3 +117,41 @@ def test_single_rank_sharding_keeps_outputs_and_fused_views():
     assert W.data_ptr() == attn.q.weight.data_ptr() and W.shape[0] == 3 * attn.q.weight.shape[0]  # zero-copy view
     assert torch.equal(_tiny_forward(model), ref)
     assert torch.equal(_tiny_forward(model), ref)
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_async_offload_ring_on_the_device_rotates_slots_and_keeps_outputs():
+    """Four blocks behind two device slots: every forward streams each block from pinned host memory on the copy stream
+    while the previous block computes; the result must equal the all-resident run bit for bit, forward after forward,
+    and sequential offload must agree as well."""
+    from telefuser_b200.models.wan_dit import WanModel
+
+    def build():
+        torch.manual_seed(0)
+        m = WanModel(dim=512, ffn_dim=1024, num_heads=4, num_layers=4, text_dim=256).to(torch.bfloat16).cuda().eval()
+        m.dtype = torch.bfloat16
+        return m
+
+    latents, ctx, _ = make_tiny_inputs()
+    args = (latents.cuda(), torch.tensor([500.0], device="cuda"), ctx.cuda().bfloat16())
+    with torch.no_grad():
+        ref = build()(*args)
+        model = build()
+        mgr = AsyncOffloadManager(model.blocks, enabled=True, offload_ratio=1.0, prefetch_size=1, device="cuda", min_numel=1)
+        model.async_offload_manager, model.async_offload_flag = mgr, True
+        assert mgr.first_offloaded == 0 and len(mgr.slots) == 2 and mgr.offloaded_bytes() > 0
+        outs = [model(*args) for _ in range(3)]
+        torch.cuda.synchronize()
+        assert all(torch.equal(o, ref) for o in outs)
+        assert mgr.copies >= 3 * 4 - 2  # two slots for four blocks: (almost) every block is copied again on every forward
+        half = build()
+        mgr2 = AsyncOffloadManager(half.blocks, offload_ratio=0.5, prefetch_size=1, device="cuda", min_numel=1)
+        half.async_offload_manager, half.async_offload_flag = mgr2, True
+        assert mgr2.first_offloaded == 2
+        assert torch.equal(half(*args), ref) and torch.equal(half(*args), ref)
+        seq = build()
+        units = enable_sequential_cpu_offload(seq, "cuda")
+        assert len(units) == 4 and torch.equal(seq(*args), ref) and all(u.state == 0 for u in units)
