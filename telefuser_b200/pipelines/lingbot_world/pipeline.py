@@ -227,6 +227,15 @@ class LingBotWorldFastPipeline(BasePipeline):
         self.vae_decode_stage = LingBotWorldFastVAEDecodeStage("vae_decode", module_manager, config.vae_decode_config)
         self.denoise_stage = LingBotWorldFastDenoisingStage("denoise", module_manager, config.dit_config)
         self.dit_meta = dict(patch=self.denoise_stage.dit.patch_size, control_type=self.denoise_stage.dit.control_type)
+        enc, dec = self.vae_encode_stage, self.vae_decode_stage
+        if enc.device.type == "cuda" and dec.vae is enc.vae and dec.device != enc.device:
+            # The two VAE actors may sit on different GPUs (decode next to the last denoiser rank): the module they
+            # fetched is one object, so the decoder gets its own copy on its own device (a few hundred MB).
+            import copy
+
+            dec.vae = copy.deepcopy(enc.vae).to(dec.device)
+        if enc.device.type == "cuda" and next(enc.vae.parameters()).device != enc.device:
+            enc.vae.to(enc.device)
         for st in (self.vae_encode_stage, self.vae_decode_stage, self.denoise_stage):
             st.onload_models_flag = True
         if config.enable_denoising_parallel:
