@@ -1,7 +1,8 @@
 """Multi-GPU plumbing on real devices: Ulysses and CFG-parallel denoising equal the single-GPU run
 (peer-memory kernels by default, the NCCL path with TFB_FUSED_COLLECTIVES=0), the peer-memory
 paths equal the collective-library paths op by op, and a peer wait that nobody answers runs out
-with a status instead of hanging."""
+with a status instead of hanging. The file sorts after the single-GPU files on purpose: with `pytest -x` a failure that
+needs several GPUs to show must not hide the single-GPU results."""
 import ctypes
 
 import pytest
