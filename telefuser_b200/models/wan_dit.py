@@ -171,6 +171,13 @@ def _with_fused_scale(W: torch.Tensor, linears: list[nn.Linear]) -> torch.Tensor
             rows = [TF.mx_untile_scales(s, lin.weight.shape[0]) for s, lin in zip(mx, linears)]
             W.tfb_mx_sf = TF.mx_tile_scales(torch.cat(rows, dim=0))
         return W
+    f4 = [getattr(lin.weight, "tfb_nvfp4_sf", None) for lin in linears]
+    if all(s is not None for s in f4):
+        # NVFP4 parts keep their own tensor scale: the fused view carries one global scale per output row
+        W.tfb_nvfp4_sf = torch.cat([s.to(W.device) for s in f4], dim=0).contiguous()
+        W.tfb_nvfp4_global = torch.cat([lin.weight.tfb_nvfp4_global.to(W.device).reshape(1).expand(lin.weight.shape[0])
+                                        for lin in linears]).contiguous()  # fmt: skip
+        return W
     scales = [TF.fp8_weight_scale(lin.weight) for lin in linears]
     if all(s is not None for s in scales):
         W.tfb_scale = torch.cat([s.reshape(-1) for s in scales]).contiguous()
@@ -519,6 +526,10 @@ class WanModel(BaseModel):
         kind = getattr(quant, "quant_type", quant)
         mx = kind is QuantType.MXFP8 or (isinstance(kind, str) and kind.lower() == "mxfp8")
         i8 = kind is QuantType.INT8 or (isinstance(kind, str) and kind.lower() == "int8")
+        if kind is QuantType.NVFP4 or (isinstance(kind, str) and kind.lower() == "nvfp4"):
+            from telefuser_b200.ops.nvfp4 import quantize_model_nvfp4_
+
+            return quantize_model_nvfp4_(self, ("blocks.*",), skip)  # weight-only storage format; the GEMM stays bf16
         return quantize_model_fp8_(self, ("blocks.*",), skip, block_scaled=mx, int8=i8)
 
     # ---- parallel plans --------------------------------------------------------

@@ -75,6 +75,10 @@ def linear(x, weight, bias=None, act=None, residual=None, gate=None, out=None):
         from telefuser_b200.ops.nf4 import expand_nf4_weight
 
         weight = expand_nf4_weight(weight, x.dtype)  # packed 4-bit codes -> [N, K] in a shared scratch buffer
+    elif weight.dtype == torch.uint8 and hasattr(weight, "tfb_nvfp4_sf"):
+        from telefuser_b200.ops.nvfp4 import expand_nvfp4_weight
+
+        weight = expand_nvfp4_weight(weight, x.dtype)  # e2m1 codes + e4m3 block scales -> [N, K]
     K = x.shape[-1]
     N = weight.shape[0]
     # The tensor-core kernel moves 16-byte rows: widths that are not multiples of 8 elements (toy configurations)
