@@ -186,17 +186,25 @@ SIDECAR_FORMAT = "telefuser_b200.quantized_linears.v1"
 
 
 def quantized_state(model: nn.Module) -> dict:
-    """Tensors of the quantised linears only, keyed like a state dict: `<name>.weight` (e4m3 bytes as uint8),
-    `<name>.weight_scale` (fp32 per output channel) or `<name>.weight_scale_mx` (tiled UE8M0 bytes)."""
+    """Tensors of the quantised linears only, keyed like a state dict: `<name>.weight` (e4m3 bytes as uint8, int8 values
+    as they are, or packed NVFP4 codes) with `<name>.weight_scale` (fp32 per output channel; e4m3 per 16 inputs for
+    NVFP4), `<name>.weight_scale_mx` (tiled UE8M0 bytes) or `<name>.weight_global_scale` (NVFP4)."""
     out: dict = {}
     for name, m in model.named_modules():
         w = getattr(m, "weight", None)
-        if not isinstance(m, (nn.Linear, LinearFP8)) or w is None or w.dtype != torch.float8_e4m3fn:
+        if not isinstance(m, (nn.Linear, LinearFP8)) or w is None:
             continue
-        out[f"{name}.weight"] = w.data.view(torch.uint8).cpu()
-        for buf in ("weight_scale", "weight_scale_mx"):
+        nvfp4 = w.dtype == torch.uint8 and hasattr(w, "tfb_nvfp4_sf")
+        if w.dtype == torch.float8_e4m3fn:
+            out[f"{name}.weight"] = w.data.view(torch.uint8).cpu()
+        elif w.dtype == torch.int8 or nvfp4:
+            out[f"{name}.weight"] = w.data.cpu()
+        else:
+            continue
+        for buf in ("weight_scale", "weight_scale_mx", "weight_global_scale"):
             if buf in m._buffers:
-                out[f"{name}.{buf}"] = m._buffers[buf].cpu()
+                t = m._buffers[buf].cpu()
+                out[f"{name}.{buf}"] = t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
     return out
 
 
@@ -207,7 +215,12 @@ def save_quantized_sidecar(model: nn.Module, path: str) -> int:
 
     state = quantized_state(model)
     layers = sum(1 for k in state if k.endswith(".weight"))
-    kinds = {"mxfp8" if any(k.endswith("weight_scale_mx") for k in state) else "fp8"} if state else set()
+    kinds = set()
+    for k, v in state.items():
+        if k.endswith(".weight"):
+            base = k[: -len(".weight")]
+            kinds.add("nvfp4" if f"{base}.weight_global_scale" in state else "int8" if v.dtype == torch.int8
+                      else "mxfp8" if f"{base}.weight_scale_mx" in state else "fp8")  # fmt: skip
     save_file({k: v.contiguous() for k, v in state.items()}, path,
               metadata={"format": SIDECAR_FORMAT, "layers": str(layers), "kind": ",".join(sorted(kinds))})  # fmt: skip
     return layers
@@ -234,9 +247,27 @@ def load_quantized_sidecar(model: nn.Module, path: str, strict: bool = True) -> 
             continue
         dev = m.weight.device
         w8 = state[key]
+        gs = state.get(f"{name}.weight_global_scale")
+        if gs is not None:  # NVFP4: packed codes [N, K / 2], e4m3 block scales (stored as bytes), one tensor scale
+            from telefuser_b200.ops.nvfp4 import QuantizedLinearNVFP4
+
+            if tuple(w8.shape) != (m.out_features, m.in_features // 2):
+                raise ValueError(f"{name}: side-car NVFP4 weight {tuple(w8.shape)} vs layer {(m.out_features, m.in_features)}")
+            m.weight = nn.Parameter(w8.to(dev), requires_grad=False)
+            for buf, val in (("weight_scale", state[f"{name}.weight_scale"].view(torch.float8_e4m3fn)), ("weight_global_scale", gs)):
+                if buf in m._buffers:
+                    m._buffers[buf] = val.to(dev)
+                else:
+                    m.register_buffer(buf, val.to(dev))
+            if type(m) is nn.Linear:
+                m.__class__ = QuantizedLinearNVFP4
+            m.weight.tfb_nvfp4_sf, m.weight.tfb_nvfp4_global = m.weight_scale, m.weight_global_scale
+            n += 1
+            continue
         if tuple(w8.shape) != tuple(m.weight.shape):
             raise ValueError(f"{name}: side-car weight {tuple(w8.shape)} vs layer {tuple(m.weight.shape)}")
-        m.weight = nn.Parameter(w8.view(torch.float8_e4m3fn).to(dev), requires_grad=False)
+        int8 = w8.dtype == torch.int8
+        m.weight = nn.Parameter((w8 if int8 else w8.view(torch.float8_e4m3fn)).to(dev), requires_grad=False)
         mx = state.get(f"{name}.weight_scale_mx")
         per_channel = state.get(f"{name}.weight_scale")
         for buf, val in (("weight_scale_mx", mx), ("weight_scale", per_channel)):
@@ -249,7 +280,7 @@ def load_quantized_sidecar(model: nn.Module, path: str, strict: bool = True) -> 
         if mx is None and per_channel is None:
             raise ValueError(f"{name}: the side-car holds no scale for this layer")
         if type(m) is nn.Linear:
-            m.__class__ = QuantizedLinearMX if mx is not None else QuantizedLinear
+            m.__class__ = QuantizedLinearInt8 if int8 else QuantizedLinearMX if mx is not None else QuantizedLinear
         if hasattr(m.weight, "tfb_scale") and per_channel is None:
             del m.weight.tfb_scale
         m._sync()

@@ -3,12 +3,13 @@
     python -m telefuser_b200.tools.convert -s <ckpt file or dir> -o <out dir> [-o_n name]
         [--direction forward|backward --model_type wan_dit] [--rule 'regex=>replacement' ...]
         [--lora_path a.safetensors --lora_strength 1.0]
-        [--quantized --linear_dtype fp8|mxfp8 --quantize_modules attn ffn] [--save_by_block]
+        [--quantized --linear_dtype fp8|int8|mxfp8|nvfp4 --quantize_modules attn ffn] [--save_by_block]
 
 * key mapping: built-in rule sets (diffusers -> native Wan DiT names, and back) plus ad-hoc regex rules
 * LoRA merge before any quantisation (same loader as run-time)
 * fp8: e4m3 weight + per-output-channel fp32 `weight_scale [out, 1]` (scale = row amax / 448) — the layout
-  the W8A8 linear consumes; mxfp8: e4m3 payload + UE8M0 scale per 32 input elements in `weight_sf`
+  the W8A8 linear consumes (int8: the same with int8 values in [-127, 127]); mxfp8: e4m3 payload + UE8M0 scale per 32
+  input elements in `weight_sf`; nvfp4: packed e2m1 codes + e4m3 `weight_scale` per 16 + fp32 `weight_global_scale`
 * output: one safetensors file, or one file per transformer block plus an index json
 Role parity: tools/convert/converter.py:32-937 (key mapping, quantize_model, load_loras, save by block).
 """
@@ -119,7 +120,7 @@ def quantize_model(sd: dict, linear_dtype: str = "fp8", quantize_modules=("attn"
     for k, v in sd.items():
         is_target = (k.endswith(".weight") and v.dim() == 2 and min(v.shape) >= min_dim
                      and any(m in k for m in quantize_modules) and not any(s in k for s in skip))  # fmt: skip
-        if not is_target or (linear_dtype == "mxfp8" and v.shape[1] % 32):
+        if not is_target or (linear_dtype == "mxfp8" and v.shape[1] % 32) or (linear_dtype == "nvfp4" and v.shape[1] % 16):
             out[k] = v
             continue
         base = k[: -len(".weight")]
@@ -129,6 +130,16 @@ def quantize_model(sd: dict, linear_dtype: str = "fp8", quantize_modules=("attn"
         elif linear_dtype == "mxfp8":
             q, sf = quantize_mxfp8(v)
             out[k], out[base + ".weight_sf"] = q, sf
+        elif linear_dtype == "int8":
+            from telefuser_b200.ops.functional import quantize_weight_int8
+
+            q, s = quantize_weight_int8(v)
+            out[k], out[base + ".weight_scale"] = q, s.reshape(-1, 1)
+        elif linear_dtype == "nvfp4":
+            from telefuser_b200.ops.nvfp4 import quantize_nvfp4
+
+            packed, sf, gs = quantize_nvfp4(v)
+            out[k], out[base + ".weight_scale"], out[base + ".weight_global_scale"] = packed, sf, gs
         else:
             raise ValueError(f"unknown linear dtype {linear_dtype!r}")
         n += 1
@@ -221,7 +232,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--lora_path", nargs="*")
     p.add_argument("--lora_strength", type=float, default=1.0)
     p.add_argument("--quantized", action="store_true")
-    p.add_argument("--linear_dtype", default="fp8", choices=["fp8", "mxfp8"])
+    p.add_argument("--linear_dtype", default="fp8", choices=["fp8", "int8", "mxfp8", "nvfp4"])
     p.add_argument("--quantize_modules", nargs="*", default=["attn", "ffn"])
     p.add_argument("--dtype", default=None, choices=[None, "bfloat16", "float16", "float32"])
     p.add_argument("-b", "--save_by_block", action="store_true")

@@ -199,7 +199,7 @@ def test_mxfp8_gemm_matches_fp32_product_of_the_dequantised_operands(M, N, K):
     assert ((TF.linear_mxfp8(x, wq, wsf).float() - full).norm() / full.norm()).item() < 0.05
 
 
-@pytest.mark.parametrize("kind", ["fp8", "mxfp8"])
+@pytest.mark.parametrize("kind", ["fp8", "mxfp8", "int8", "nvfp4"])
 def test_quantised_sidecar_round_trip(tmp_path, kind):
     from telefuser_b200.ops.quant import load_quantized_sidecar, save_quantized_sidecar
 
@@ -214,8 +214,13 @@ def test_quantised_sidecar_round_trip(tmp_path, kind):
     assert fresh.blocks[0].ffn[0].weight.dtype != torch.float8_e4m3fn
     assert load_quantized_sidecar(fresh, path) == 20
     lin = fresh.blocks[0].ffn[0]
-    assert lin.weight.dtype == torch.float8_e4m3fn
-    assert (lin.weight.tfb_mx_sf is lin.weight_scale_mx) if kind == "mxfp8" else (lin.weight.tfb_scale is lin.weight_scale)
+    assert lin.weight.dtype == {"int8": torch.int8, "nvfp4": torch.uint8}.get(kind, torch.float8_e4m3fn)
+    if kind == "mxfp8":
+        assert lin.weight.tfb_mx_sf is lin.weight_scale_mx
+    elif kind == "nvfp4":
+        assert lin.weight.tfb_nvfp4_sf is lin.weight_scale and lin.weight_scale.dtype == torch.float8_e4m3fn
+    else:
+        assert lin.weight.tfb_scale is lin.weight_scale
     assert torch.equal(fresh(latents, t, ctx), want)  # no second quantisation: bit-identical weights and scales
     with pytest.raises(ValueError, match="not a quantised side-car"):
         from safetensors.torch import save_file

@@ -44,6 +44,19 @@ def test_convert_key_mapping_round_trip_and_quantise(tmp_path):
     convert.main(["-s", str(src), "-o", str(tmp_path / "m"), "--quantized", "--linear_dtype", "mxfp8"])
     m = load_state_dict(str(tmp_path / "m" / "converted.safetensors"))
     assert m["blocks.0.ffn.0.weight_sf"].shape == (512, 128 // 32) and m["blocks.0.ffn.0.weight_sf"].dtype == torch.uint8
+    # int8 per output channel; NVFP4 codes with block and tensor scales (both read back and de-quantised)
+    convert.main(["-s", str(src), "-o", str(tmp_path / "i"), "--quantized", "--linear_dtype", "int8"])
+    i8 = load_state_dict(str(tmp_path / "i" / "converted.safetensors"))
+    assert i8["blocks.0.self_attn.q.weight"].dtype == torch.int8
+    assert (i8["blocks.0.self_attn.q.weight"].float() * i8["blocks.0.self_attn.q.weight_scale"] - w).abs().max() <= w.abs().max() / 127
+    convert.main(["-s", str(src), "-o", str(tmp_path / "f4"), "--quantized", "--linear_dtype", "nvfp4"])
+    f4 = load_state_dict(str(tmp_path / "f4" / "converted.safetensors"))
+    from telefuser_b200.ops.nvfp4 import dequantize_nvfp4
+
+    key = "blocks.0.self_attn.q"
+    assert f4[key + ".weight"].dtype == torch.uint8 and f4[key + ".weight"].shape == (w.shape[0], w.shape[1] // 2)
+    back4 = dequantize_nvfp4(f4[key + ".weight"], f4[key + ".weight_scale"], f4[key + ".weight_global_scale"])
+    assert ((back4 - w.float()).norm() / w.float().norm()).item() < 0.13
 
 
 def test_lora_extract_then_merge_recovers_the_tuned_weights(tmp_path):
