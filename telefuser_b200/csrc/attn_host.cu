@@ -6,6 +6,8 @@
 // measured slower in both kernels), and for plain dense head_dim-128 attention the kernel by key count: one thread
 // per row below 48k keys (987 vs 933 TFLOP/s at 16k keys x 12 heads), two threads per row from there on (1066 -
 // 1076 vs 1016 - 1039 TFLOP/s at 75,600 keys x 5 heads).
+// Role in the reference: the attention dispatch of telefuser/ops/attention/attention_impl.py:213-300 (SDPA, cuDNN,
+// FlashAttention and SageAttention back ends behind one call).
 #include "attn_common.cuh"
 #include "tfb_api.h"
 

@@ -1,6 +1,7 @@
 // Peer-mapped ("symmetric") buffers for the ranks of one node: each rank allocates a buffer, publishes
 // its CUDA IPC handle, and maps every other rank's buffer. The mappings are plain device pointers
 // usable by any kernel (peer loads / stores over NVLink).
+// The reference has no counterpart: its ranks exchange data only through NCCL (telefuser/distributed/).
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>

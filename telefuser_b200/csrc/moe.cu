@@ -4,6 +4,8 @@
 //   permute : token rows -> expert-sorted rows (slot claimed with one atomic per (token, k))
 //   combine : weighted sum of each token's k expert outputs in fp32
 // The grouped GEMM in gemm_tcgen05.cu consumes `tile_expert` from `plan`.
+// Role in the reference: the router and the grouped expert forward of telefuser/ops/moe.py (torch top-k + per-expert
+// loops / grouped library GEMMs) and the expert-specialised GEMM glue under tf-kernel/csrc/expert_specialization/.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>

@@ -5,6 +5,8 @@
 //   peer_barrier        : all ranks signal each other and wait (epoch counters, never reset)
 //   ulysses_scatter     : sequence-sharded q/k/v -> head-sharded slabs of every peer in ONE pass
 //   peer_push_rows      : this rank's row block -> the same rows of every peer's full buffer (all-gather)
+// Role in the reference: the NCCL all-to-all / all-gather calls of telefuser/distributed/ulysses_comm.py:53-124 and
+// telefuser/distributed/parallel_shard.py (sequence shard / unshard); there the collective library moves the data.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>

@@ -2,6 +2,10 @@
 // quantisation, log-sum-exp merge of partial attention results, Taylor feature-cache update / apply,
 // Pluecker ray maps folded to the latent grid, decoded frames -> uint8 HWC.
 // All are single-pass, 16-byte vectorised where the layout allows, grid-stride over 148 x 16 CTAs.
+// Role in the reference: the torch-op KV-cache roll of the LingBot-World DiT (telefuser/models/lingbot_world_fast_dit.py),
+// the fp8 KV cache of LiveAct (telefuser/cache/kv_cache.py), the Taylor cache arithmetic of
+// telefuser/feature_cache/ada_taylor_cache/ada_taylor_cache.py, the Pluecker control maths of telefuser/pipelines/lingbot_world_fast/ and the
+// Triton LSE-merge kernel its ring attention imports (`fused_merge_attn_states`, telefuser/distributed/ring.py:25).
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
