@@ -65,3 +65,32 @@ def test_record_replay_and_script(tmp_path, monkeypatch):
         assert "toy_denoise" in str(e)
     else:
         raise AssertionError("a missing stage must be reported")
+
+
+def test_memory_checkpoints_report_growth_peaks_and_pool_overhead():
+    from telefuser_b200.utils import memory_snapshot as M
+
+    readings = iter([(100 << 20, 128 << 20, 100 << 20, 128 << 20),      # baseline: weights
+                     (150 << 20, 192 << 20, 400 << 20, 448 << 20),      # after the text encoder
+                     (130 << 20, 512 << 20, 900 << 20, 1024 << 20),     # after denoising: highest peak
+                     (140 << 20, 512 << 20, 300 << 20, 1024 << 20),     # a second denoising call reads lower
+                     (120 << 20, 512 << 20, 600 << 20, 1024 << 20)])    # after the decode
+    cp = M.MemoryCheckpoints(reader=lambda device: next(readings))
+    base = cp.set_baseline()
+    assert base.allocated_mb == 100 and base.pool_overhead_mb == 28 and round(base.pool_overhead_pct, 3) == 21.875
+    cp.record("text")
+    cp.record("denoise")
+    cp.record("denoise")  # keeps the worse of the two readings per counter
+    cp.record("decode")
+    a = cp.analysis()
+    rows = {r["checkpoint"]: r for r in a["checkpoints"]}
+    assert list(rows) == ["text", "denoise", "decode"]
+    assert rows["text"]["allocated_over_baseline_mb"] == 50 and rows["denoise"]["allocated_over_previous_mb"] == -10
+    assert rows["denoise"]["allocated_mb"] == 140 and rows["denoise"]["peak_allocated_mb"] == 900
+    assert a["highest_peak_checkpoint"] == "denoise" and a["highest_peak_reserved_mb"] == 1024
+    assert "highest peak: 900.0 MiB at 'denoise'" in cp.summary()
+    assert (cp.points["denoise"] - base).allocated_mb == 40
+    M.reset_memory_registry()
+    M.set_memory_baseline()
+    snap = M.record_memory_snapshot("anything")  # without a GPU every counter is zero; with one they are non-negative
+    assert snap.allocated_mb >= 0 and "anything" in M.get_memory_snapshots() and M.get_memory_analysis()["checkpoints"]
