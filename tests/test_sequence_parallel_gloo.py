@@ -177,3 +177,45 @@ def test_multi_gpu_suite_host_logic_on_two_cpu_ranks(tmp_path):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     rep = json.loads(out.read_text())
     assert rep["passed"] and {"cfg2/collectives", "u2/collectives", "r2/collectives", "tp2/collectives"} <= set(rep["rank0"]["layouts"])
+
+
+def test_mesh_groups_partition_the_world_for_every_layout():
+    """Without a process group (rank and world size given): every dimension's groups partition the ranks, members of a
+    group differ in that coordinate only, the SP group is ring x Ulysses, and EP groups are contiguous slices of the
+    CFG x SP ranks."""
+    import itertools
+
+    from telefuser_b200.core.config import ParallelConfig
+    from telefuser_b200.parallel.mesh import DIM_NAMES, create_mesh, set_mesh
+
+    layouts = [dict(cfg_degree=2, sp_ulysses_degree=4), dict(sp_ring_degree=2, sp_ulysses_degree=4), dict(dp_degree=2, cfg_degree=2, sp_ulysses_degree=2),
+               dict(pp_degree=2, sp_ulysses_degree=2, cfg_degree=2), dict(tp_degree=8), dict(dp_degree=2, pp_degree=2, tp_degree=2),
+               dict(cfg_degree=2, sp_ring_degree=2, sp_ulysses_degree=2, ep_degree=4), dict(sp_ulysses_degree=8, ep_degree=8)]  # fmt: skip
+    try:
+        for kw in layouts:
+            cfg = ParallelConfig(device_ids=list(range(8)), **kw)
+            meshes = [create_mesh(cfg, rank=r, world_size=8) for r in range(8)]
+            for i, name in enumerate(DIM_NAMES):
+                groups = {tuple(m.ranks(name)) for m in meshes}
+                assert sorted(itertools.chain.from_iterable(groups)) == list(range(8)), (kw, name)  # a partition
+                for m in meshes:
+                    assert m.rank in m.ranks(name) and len(m.ranks(name)) == m.size(name) == m.dims[i]
+                    assert m.ranks(name).index(m.rank) == m.coord(name)
+                    for other in m.ranks(name):  # same group: all other coordinates agree
+                        o = meshes[other]
+                        assert all(o.coord(n) == m.coord(n) for n in DIM_NAMES if n != name), (kw, name)
+            for m in meshes:
+                assert len(m.ranks("sp")) == m.size("ring") * m.size("ulysses") == m.size("sp")
+                assert set(m.ranks("ring")) | set(m.ranks("ulysses")) <= set(m.ranks("sp"))
+                if kw.get("ep_degree", 1) > 1:
+                    ep = m.ranks("ep")
+                    assert len(ep) == kw["ep_degree"] == m.size("ep") and m.rank in ep and ep == list(range(ep[0], ep[0] + len(ep)))
+                    assert m.coord("ep") == ep.index(m.rank)
+        import pytest
+
+        with pytest.raises(RuntimeError, match="do not match world size"):
+            create_mesh(ParallelConfig(device_ids=list(range(8)), sp_ulysses_degree=4), rank=0, world_size=8)
+        with pytest.raises(ValueError, match="cannot be combined"):
+            create_mesh(ParallelConfig(device_ids=list(range(8)), sp_ulysses_degree=4, tp_degree=2), rank=0, world_size=8)
+    finally:
+        set_mesh(None)
