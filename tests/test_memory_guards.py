@@ -71,3 +71,39 @@ def test_kernels_at_edge_shapes_leave_the_guards_alone():
         lat = torch.randn(1, 16, 3, 10, 14, device=dev)
         TF.cfg_euler_step(lat, lat.bfloat16(), lat.bfloat16(), 5.0, -0.1)
     assert g.check() > 20
+
+
+def test_peer_region_table_recarves_in_place_on_cpu_memory():
+    """The region table of the peer workspace, exercised on a plain CPU buffer (no IPC): a name that comes back smaller
+    keeps its offset, a name that outgrows its reservation resets the whole table, canary strips sit right behind every
+    region and are checked, and a request beyond the buffer is refused."""
+    import torch
+
+    from telefuser_b200.parallel import symm
+
+    ws = object.__new__(symm.PeerWorkspace)
+    ws.nbytes = 1 << 20
+    ws.local = torch.zeros(ws.nbytes, dtype=torch.uint8)
+    ws.flag_off = ws.nbytes - symm.FLAG_BYTES
+    ws._regions, ws._cursor, ws.canaries, ws._canaries = {}, 0, True, {}
+    ws.ptrs, ws.rank, ws.world = [1000, 5000], 0, 2
+    a = ws.region("q", (4, 64, 2, 128))  # 131072 bytes
+    b = ws.region("o", (4, 64, 2, 128))
+    assert a.shape == (4, 64, 2, 128) and a.dtype == torch.bfloat16
+    off_a, off_b = ws._regions["q"][0], ws._regions["o"][0]
+    assert off_a == 0 and off_b == 131072 + symm.CANARY_BYTES and off_b % 256 == 0
+    assert ws.peer_ptr(1, "o") == 5000 + off_b
+    ws.check_canaries()
+    small = ws.region("q", (2, 64, 2, 128))  # fits the reservation: same place, other shape
+    assert ws._regions["q"][0] == 0 and small.shape == (2, 64, 2, 128) and ws._regions["o"][0] == off_b
+    a.view(torch.uint8).reshape(-1)[-1] = 7  # the last byte of the region itself: allowed
+    ws.check_canaries()
+    ws.local[ws._canaries["q"][0] + 3] = 0  # one byte behind the end of "q"
+    with pytest.raises(AssertionError, match="'q'.*first at \\+3"):
+        ws.check_canaries()
+    big = ws.region("q", (8, 64, 2, 128))  # outgrows its reservation: everything is carved anew from offset 0
+    assert big.shape == (8, 64, 2, 128) and list(ws._regions) == ["q"] and ws._regions["q"][0] == 0
+    ws.check_canaries()  # the strips were rewritten with the new table
+    assert ws.region("o", (4, 64, 2, 128)).data_ptr() == ws.local.data_ptr() + ws._regions["o"][0]
+    with pytest.raises(MemoryError):
+        ws.region("huge", (1 << 20,))
