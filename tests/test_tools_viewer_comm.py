@@ -77,7 +77,7 @@ def test_lingbot_video_validation_tool_inspect_capture_compare_bench(tmp_path):
     assert V.main(["capture", "--preset", "tiny-moe", "--out", single]) == 0
     env = {**__import__("os").environ, "PYTHONPATH": str(__import__("pathlib").Path(__file__).resolve().parents[1])}
     run = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29541", "-m", "telefuser_b200.tools.lingbot_video_validation"]  # fmt: skip
+           "--master-port", str(find_free_port()), "-m", "telefuser_b200.tools.lingbot_video_validation"]  # fmt: skip
     r = subprocess.run(run + ["capture", "--preset", "tiny-moe", "--layout", "u2", "--expert-parallel", "--out", sp],
                        capture_output=True, text=True, timeout=300, env=env)  # fmt: skip
     assert r.returncode == 0, r.stderr[-2000:]
