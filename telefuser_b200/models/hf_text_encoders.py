@@ -8,7 +8,6 @@ Role parity: telefuser/models/qwen_image_text_encoder.py:11-196, telefuser/model
 
 from __future__ import annotations
 
-import torch
 from torch import nn
 
 from telefuser_b200.core.base_model import BaseModel

@@ -28,7 +28,6 @@ from telefuser_b200.core.base_model import BaseModel
 from telefuser_b200.ops import functional as TF
 from telefuser_b200.parallel import mesh as pmesh
 from telefuser_b200.parallel import shard as pshard
-from telefuser_b200.parallel import ulysses
 
 
 @dataclass

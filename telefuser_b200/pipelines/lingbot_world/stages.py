@@ -14,7 +14,7 @@ cache (5 forwards per chunk for a 4-step schedule).
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any
 
 import torch
