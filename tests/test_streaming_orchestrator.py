@@ -336,3 +336,77 @@ def test_local_actor_mailbox_and_failure():
     actor.close()
     with pytest.raises(StreamingActorFailedError):
         actor.submit(inv)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_sessions_with_jitter_cancellations_and_shared_devices_leave_nothing_behind(seed):
+    """Several sessions at once through actors with random delays, stages sharing a resource group, some sessions
+    cancelled mid-flight and re-created: every surviving session gets every chunk exactly once and in order with the
+    right value, and the scheduler ends with no slot, no reference, no leak and no unexplained result."""
+    import random
+
+    rng = random.Random(seed)
+    groups = (StreamingResourceGroupSpec("gpu0", 1),)
+    spec = three_stage_spec(capacity=rng.choice([1, 2, 3]), out_capacity=rng.choice([1, 2]), groups=groups,
+                            group_of={"encode": "gpu0", "decode": "gpu0"})  # fmt: skip
+    delays = {st: rng.uniform(0.0, 0.004) for st in ("encode", "denoise", "decode")}
+    running = {"gpu0": 0, "max": 0}
+    lock = threading.Lock()
+
+    def handler(stage, out):
+        def run(inv):
+            shared = stage in ("encode", "decode")
+            if shared:
+                with lock:
+                    running["gpu0"] += 1
+                    running["max"] = max(running["max"], running["gpu0"])
+            time.sleep(delays[stage] * rng.random())
+            if shared:
+                with lock:
+                    running["gpu0"] -= 1
+            val = "+".join(str(inv.inputs[k]) for k in sorted(inv.inputs))
+            return {out: f"{stage}({val})"}
+
+        return run
+
+    actors = {"encode": LocalStageActor("encode", handler("encode", "cond"), 2),
+              "denoise": LocalStageActor("denoise", handler("denoise", "latent"), 2),
+              "decode": LocalStageActor("decode", handler("decode", "frames"), 2)}  # fmt: skip
+    orch = StreamingPipelineOrchestrator(spec, actors)
+    n_chunks = 12
+    sessions = [f"s{i}" for i in range(4)]
+    cancel_at = {"s1": rng.randrange(2, 8), "s3": rng.randrange(2, 8)}  # pushed chunks after which the session is cancelled once
+    got = {s: [] for s in sessions}
+    nxt = {s: 0 for s in sessions}
+    cancelled_once = set()
+    for s in sessions:
+        orch.create_session(s, final_sequence_id=n_chunks - 1)
+    deadline = time.monotonic() + 60
+    while any(len(got[s]) < n_chunks for s in sessions):
+        assert time.monotonic() < deadline, {s: len(v) for s, v in got.items()}
+        for s in rng.sample(sessions, len(sessions)):
+            if s in cancel_at and s not in cancelled_once and nxt[s] >= cancel_at[s]:
+                orch.cancel_session(s, timeout=10.0)
+                assert orch.status(s) == StreamingSessionStatus.CANCELLED and orch.artifact_stats(s).slot_count == 0
+                cancelled_once.add(s)
+                assert orch.create_session(s, final_sequence_id=n_chunks - 1) == 2  # a new epoch of the same id
+                got[s], nxt[s] = [], 0
+                continue
+            if nxt[s] < n_chunks and orch.try_push_inputs(s, nxt[s], {"request": f"{s}r{nxt[s]}", "control": f"c{nxt[s]}"}):
+                nxt[s] += 1
+            if rng.random() < 0.7:
+                got[s].extend(orch.poll_outputs(s))
+        time.sleep(0.0005)
+    for s in sessions:
+        assert [g[0] for g in got[s]] == list(range(n_chunks)), s
+        assert all(g == (i, "frames", f"decode(denoise(encode(c{i}+{s}r{i})))") for i, g in enumerate(got[s])), s
+        assert orch.wait_until_idle(s)
+        orch.close_session(s)
+        assert orch.status(s) == StreamingSessionStatus.CLOSED
+        st = orch.artifact_stats(s)
+        assert st.slot_count == 0 and st.reference_count == 0
+    d = orch.diagnostics()
+    assert d.slot_leaks == 0 and d.cleanup_failures == 0 and d.duplicate_results == 0 and d.orphaned_results == 0
+    assert running["max"] == 1  # the two stages that share a device never ran at the same time
+    assert orch.resource_group_usage("gpu0") == 0
+    orch.close()
