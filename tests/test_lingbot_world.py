@@ -182,3 +182,37 @@ def test_denoising_session_snapshot_resumes_with_identical_chunks():
     with pytest.raises(ValueError, match="another resolution"):
         other.restore_cache(7, bad)
     pipe.close()
+
+
+def test_rolling_cache_against_a_list_model_over_random_chunk_streams():
+    """Chunks of random length, each written one to three times (the denoising steps and the clean commit of one chunk
+    land on the same slot), against a plain list model: the sink tokens stay, the oldest of the rest leave first, a
+    re-run overwrites in place, and the window view is the newest `max_attention_size` entries."""
+    import random
+
+    for seed in range(8):
+        rng = random.Random(seed)
+        n = rng.choice([2, 3, 4])
+        sink = rng.choice([0, n, 2 * n])
+        cap = sink + n * rng.choice([2, 3, 4])
+        cache = RollingKVCache(1, cap, 1, 2, "cpu", torch.float32, sink_tokens=sink)
+        model: list[tuple[int, int]] = []  # (absolute position, version written)
+        for chunk in range(rng.randrange(6, 14)):
+            start = chunk * n
+            for version in range(rng.randrange(1, 4)):
+                k = torch.tensor([[[[float(start + i), float(version)]] for i in range(n)]])  # [1, n, 1, 2]
+                end = cache.append(k, -k, start)
+                if version == 0:  # a new chunk: make room among the non-sink entries, then append
+                    overflow = len(model) + n - cap
+                    if overflow > 0:
+                        del model[sink : sink + overflow]
+                    model.extend((start + i, 0) for i in range(n))
+                else:  # a re-run of the newest chunk overwrites it
+                    model[-n:] = [(start + i, version) for i in range(n)]
+                assert end == len(model) == cache.local_end and cache.global_end == start + n
+                want = torch.tensor([[p, ver] for p, ver in model], dtype=torch.float32)
+                assert torch.equal(cache.k[0, :end, 0], want) and torch.equal(cache.v[0, :end, 0], -want), (seed, chunk, version)
+                win = rng.randrange(1, cap + 1)
+                wk, wv = cache.window(win)
+                assert torch.equal(wk[0, :, 0], want[-win:]) and torch.equal(wv, -wk)
+        assert [p for p, _ in model[:sink]] == list(range(sink))  # the first tokens ever written are still pinned
