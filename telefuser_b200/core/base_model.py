@@ -76,8 +76,20 @@ class BaseModel(nn.Module):
             if m is not self and hasattr(m, "attention_config"):
                 m.attention_config = config
 
-    def enable_quant(self, quant: QuantConfig | torch.dtype | str) -> None:
-        raise NotImplementedError(f"{type(self).__name__} has no quantised path")
+    def enable_quant(self, quant: QuantConfig | torch.dtype | str | None = None) -> int:
+        """Quantises the linears of the model's block lists (`get_fsdp_module_names()`) in the requested format (FP8 by
+        default; "int8", "mxfp8", "nvfp4", "nf4" or the matching `QuantType`); embeddings, heads, norms and modulation
+        tables outside the blocks stay as they are. Models override this to name what must be skipped inside a block.
+        Returns the number of layers converted."""
+        from telefuser_b200.ops.quant import quantize_model_
+
+        try:
+            lists = list(self.get_fsdp_module_names())
+        except NotImplementedError:
+            lists = []
+        if not lists:
+            raise NotImplementedError(f"{type(self).__name__} names no block list to quantise")
+        return quantize_model_(self, quant, tuple(f"{name}.*" for name in lists), ("modulation", "adaLN", "router", "gate."))
 
     def enable_async_offload(self, device: torch.device, offload_config: OffloadConfig) -> None:
         from telefuser_b200.offload.async_offload import AsyncOffloadManager

@@ -221,7 +221,7 @@ class Flux2ParallelSelfAttention(nn.Module):
         o = _joint_attention(q, k, v, self.usp).reshape(B, S, C)
         m = TF.silu_and_mul(fused[..., 3 * C :])
         W = self.to_out.weight
-        if W.dtype == torch.float8_e4m3fn:  # quantised weights carry one scale per output row: no K-slicing
+        if TF.is_quantized_weight(W):  # quantised weights carry scales per output row or per K block: no K-slicing
             return TF.linear(torch.cat([o, m], dim=-1), W, residual=residual, gate=gate)
         h = TF.linear(o, W[:, :C], residual=residual, gate=gate)
         return TF.linear(m, W[:, C:], residual=h, gate=gate)
@@ -275,9 +275,9 @@ class Flux2DiT(BaseModel):
         return ["transformer_blocks", "single_transformer_blocks"]
 
     def enable_quant(self, quant=None) -> int:
-        from telefuser_b200.ops.quant import quantize_model_fp8_
+        from telefuser_b200.ops.quant import quantize_model_
 
-        return quantize_model_fp8_(self, ("transformer_blocks.*", "single_transformer_blocks.*"), ())
+        return quantize_model_(self, quant, ("transformer_blocks.*", "single_transformer_blocks.*"))
 
     def _offload(self):
         return getattr(self, "async_offload_manager", None) if self.async_offload_flag else None

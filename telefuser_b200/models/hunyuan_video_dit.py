@@ -290,6 +290,8 @@ class MMSingleStreamBlock(nn.Module):
         o = _joint_attention(q, k, v, self.usp).reshape(B, S, C)
         m = F.gelu(fused[..., 3 * C :], approximate="tanh")
         W = self.linear2.fc.weight
+        if TF.is_quantized_weight(W):  # scales per output row or per K block: one GEMM over the joined input
+            return TF.linear(torch.cat([o, m], dim=-1), W, self.linear2.fc.bias, residual=x, gate=gate)
         h = TF.linear(o, W[:, :C], self.linear2.fc.bias, residual=x, gate=gate)  # the output projection in two K-slices
         return TF.linear(m, W[:, C:], residual=h, gate=gate)
 
@@ -340,6 +342,13 @@ class HunyuanVideoDiT(BaseModel):
 
     def get_fsdp_module_names(self) -> list[str]:
         return ["double_blocks", "single_blocks"]
+
+    def enable_quant(self, quant=None) -> int:
+        """Attention and MLP projections of both block lists in the requested stored format; the modulation linears
+        (`img_mod`, `txt_mod`, `modulation`) are evaluated in fp32 from the time embedding and stay as they are."""
+        from telefuser_b200.ops.quant import quantize_model_
+
+        return quantize_model_(self, quant, ("double_blocks.*", "single_blocks.*"), ("_mod.", "modulation"))
 
     def get_rotary_pos_embed(self, rope_sizes, device="cpu"):
         return rope_tables(self.rope_dim_list, rope_sizes, self.rope_theta, device)

@@ -592,20 +592,12 @@ class LTXVideoTransformer(BaseModel):
 
     def enable_quant(self, quant=None) -> int:
         """`quant`: a QuantConfig, a QuantType or a name. NF4 packs the block linears to 4.5 bits per weight (the 22B
-        model then fits one GPU several times over); anything else selects W8A8 FP8."""
-        kind = getattr(quant, "quant_type", quant)
-        name = str(getattr(kind, "name", kind)).lower()
-        include = getattr(quant, "quantize_modules", None)
-        exclude = tuple(getattr(quant, "skip_modules", None) or ()) + ("to_gate_logits",)
-        if name.endswith("nf4"):
-            from telefuser_b200.ops.nf4 import quantize_model_nf4_
+        model then fits one GPU several times over); "fp8" (the default), "int8", "mxfp8" and "nvfp4" select the other
+        stored formats. The per-head gate projections stay in bf16."""
+        from telefuser_b200.ops.quant import quantize_model_
 
-            self.quant_type = kind
-            return quantize_model_nf4_(self.velocity_model.transformer_blocks, include, exclude)
-        from telefuser_b200.ops.quant import quantize_model_fp8_
-
-        self.quant_type = kind
-        return quantize_model_fp8_(self, ("velocity_model.transformer_blocks.*",), exclude)
+        self.quant_type = getattr(quant, "quant_type", quant)
+        return quantize_model_(self, quant, ("velocity_model.transformer_blocks.*",), ("to_gate_logits",))
 
     def forward(self, video: Modality | None, audio: Modality | None = None, perturbations=None, x0: bool = False):
         if x0:

@@ -224,9 +224,9 @@ class QwenImageDiT(BaseModel):
         return ["transformer_blocks"]
 
     def enable_quant(self, quant=None) -> int:
-        from telefuser_b200.ops.quant import quantize_model_fp8_
+        from telefuser_b200.ops.quant import quantize_model_
 
-        return quantize_model_fp8_(self, ("transformer_blocks.*",), ("img_mod", "txt_mod"))
+        return quantize_model_(self, quant, ("transformer_blocks.*",), ("img_mod", "txt_mod"))
 
     @staticmethod
     def _patchify(x):

@@ -158,7 +158,8 @@ def _fuse_linear_weights(linears: list[nn.Linear]):
 
 
 def _with_fused_scale(W: torch.Tensor, linears: list[nn.Linear]) -> torch.Tensor:
-    """fp8 weights carry one scale per output channel (`tfb_scale`); the fused view gets their concatenation."""
+    """Quantised parts carry their scales as tags on the weight (`tfb_scale` per output channel for e4m3 / int8, tiled
+    block scales for MXFP8 / NVFP4, block maxima for NF4); the fused view gets the matching concatenation."""
     mx = [getattr(lin.weight, "tfb_mx_sf", None) for lin in linears]
     if all(s is not None for s in mx):
         # block-scaled weights: the scale tiles cover 128 output rows each, so they concatenate tile-wise when
@@ -176,6 +177,15 @@ def _with_fused_scale(W: torch.Tensor, linears: list[nn.Linear]) -> torch.Tensor
         W.tfb_nvfp4_sf = torch.cat([s.to(W.device) for s in f4], dim=0).contiguous()
         W.tfb_nvfp4_global = torch.cat([lin.weight.tfb_nvfp4_global.to(W.device).reshape(1).expand(lin.weight.shape[0])
                                         for lin in linears]).contiguous()  # fmt: skip
+        return W
+    nf4 = [getattr(lin.weight, "tfb_nf4_absmax", None) for lin in linears]
+    if all(s is not None for s in nf4):
+        # NF4 blocks run over the flattened weight: parts that are whole numbers of blocks concatenate as they are
+        block = getattr(linears[0].weight, "tfb_nf4_block", 64)
+        if any((lin.weight.numel() * 2) % block for lin in linears):
+            raise ValueError(f"NF4 weights of {[tuple(lin.weight.shape) for lin in linears]} packed bytes do not end on "
+                             f"a {block}-value block: they cannot share one fused matrix")
+        W.tfb_nf4_absmax, W.tfb_nf4_block = torch.cat([s.to(W.device) for s in nf4]).contiguous(), block
         return W
     scales = [TF.fp8_weight_scale(lin.weight) for lin in linears]
     if all(s is not None for s in scales):
@@ -513,23 +523,14 @@ class WanModel(BaseModel):
         return self.unpatchify(x, grid)
 
     def enable_quant(self, quant=None) -> int:
-        """W8A8 for the block projections (attention q/k/v/o and both FFN layers): block-scaled MXFP8 when the
-        configuration says `QuantType.MXFP8` (or "mxfp8"), integer W8A8 for `QuantType.INT8` ("int8"), per-token x
-        per-channel FP8 otherwise; embeddings, the
-        head and all norms / modulation tables stay in bf16 / fp32. Returns the number of layers converted."""
-        from telefuser_b200.core.config import QuantType
-        from telefuser_b200.ops.quant import quantize_model_fp8_
+        """Quantised block projections (attention q/k/v/o and both FFN layers): per-token x per-channel FP8 by default,
+        block-scaled MXFP8 for `QuantType.MXFP8` ("mxfp8"), integer W8A8 for `QuantType.INT8` ("int8"), NVFP4 or NF4
+        weight storage for "nvfp4" / "nf4"; embeddings, the head and all norms / modulation tables stay in bf16 /
+        fp32. A `QuantConfig` adds its `skip_modules` to that list. Returns the number of layers converted."""
+        from telefuser_b200.ops.quant import quantize_model_
 
-        skip = tuple(getattr(quant, "skip_modules", None) or ("head", "time_embedding", "time_projection",
-                                                              "patch_embedding", "text_embedding", "img_emb"))  # fmt: skip
-        kind = getattr(quant, "quant_type", quant)
-        mx = kind is QuantType.MXFP8 or (isinstance(kind, str) and kind.lower() == "mxfp8")
-        i8 = kind is QuantType.INT8 or (isinstance(kind, str) and kind.lower() == "int8")
-        if kind is QuantType.NVFP4 or (isinstance(kind, str) and kind.lower() == "nvfp4"):
-            from telefuser_b200.ops.nvfp4 import quantize_model_nvfp4_
-
-            return quantize_model_nvfp4_(self, ("blocks.*",), skip)  # weight-only storage format; the GEMM stays bf16
-        return quantize_model_fp8_(self, ("blocks.*",), skip, block_scaled=mx, int8=i8)
+        return quantize_model_(self, quant, ("blocks.*",), ("head", "time_embedding", "time_projection", "patch_embedding",
+                                                            "text_embedding", "img_emb"))  # fmt: skip
 
     # ---- parallel plans --------------------------------------------------------
     def get_fsdp_module_names(self) -> list[str]:

@@ -204,9 +204,9 @@ class ZImageTransformer2DModel(BaseModel):
         return ["layers"]
 
     def enable_quant(self, quant=None) -> int:
-        from telefuser_b200.ops.quant import quantize_model_fp8_
+        from telefuser_b200.ops.quant import quantize_model_
 
-        return quantize_model_fp8_(self, ("layers.*",), ("adaLN_modulation",))
+        return quantize_model_(self, quant, ("layers.*",), ("adaLN_modulation",))
 
     def enable_async_offload(self, device, offload_config) -> None:
         from telefuser_b200.offload.async_offload import AsyncOffloadManager

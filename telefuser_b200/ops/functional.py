@@ -152,6 +152,12 @@ def use_native_kernels(t) -> bool:
     return _native(t)
 
 
+def is_quantized_weight(weight) -> bool:
+    """True for every stored format whose rows cannot be sliced along K like a dense matrix: e4m3 and int8 (one scale
+    per output row), MXFP8 / NVFP4 (scale per K block, tiled layout) and packed NF4."""
+    return weight.dtype in (torch.float8_e4m3fn, torch.int8, torch.uint8)
+
+
 def fp8_weight_scale(weight):
     """Per-output-channel scale tagged on an e4m3 weight (`tfb_scale`), on the weight's own device.
 

@@ -182,8 +182,7 @@ def quantize_model_nvfp4_(model: nn.Module, include_names=None, exclude_names=No
             continue
         quantize_linear_nvfp4_(m)
         n += 1
-    for m in model.modules():  # cached fused views must be rebuilt from the new weights
-        for attr in ("_qkv", "_kv", "_gu", "_fused"):
-            if hasattr(m, attr):
-                setattr(m, attr, None)
+    from telefuser_b200.ops.quant import invalidate_fused_caches
+
+    invalidate_fused_caches(model)
     return n

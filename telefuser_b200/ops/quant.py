@@ -172,11 +172,58 @@ def quantize_model_fp8_(model: nn.Module, quantize_modules=("*attn*", "*ffn*"), 
         else:
             quantize_linear_fp8_(m)
         n += 1
-    for m in model.modules():  # cached fused views must be rebuilt from the new weights
-        for attr in ("_qkv", "_kv", "_gu", "_fused"):
-            if hasattr(m, attr):
-                setattr(m, attr, None)
+    invalidate_fused_caches(model)
     return n
+
+
+FUSED_CACHE_SLOTS = ("_qkv", "_kv", "_gu", "_fused", "_img", "_txt")
+
+
+def invalidate_fused_caches(model: nn.Module) -> None:
+    """Drops the concatenated-weight views that attention / MLP modules cache (QKV, KV, gate+up, joint streams), so
+    the next forward rebuilds them from the converted weights. A slot name that a module uses for a METHOD (the
+    builder of such a view) is left alone."""
+    for m in model.modules():
+        for attr in FUSED_CACHE_SLOTS:
+            if attr in m.__dict__ and not callable(m.__dict__[attr]):
+                m.__dict__[attr] = None
+
+
+def resolve_quant_kind(quant) -> str:
+    """What a `QuantConfig`, a `QuantType`, a string, a dtype or None asks for: "fp8" (the default), "int8", "mxfp8",
+    "nvfp4" or "nf4"."""
+    kind = getattr(quant, "quant_type", quant)
+    if kind is None:
+        return "fp8"
+    if isinstance(kind, torch.dtype):
+        return {torch.int8: "int8", torch.float8_e4m3fn: "fp8"}.get(kind, "fp8")
+    name = (kind.name if hasattr(kind, "name") else str(kind)).lower()
+    for key, out in (("nvfp4", "nvfp4"), ("nf4", "nf4"), ("mxfp8", "mxfp8"), ("int8", "int8")):
+        if key in name:
+            return out
+    return "fp8"
+
+
+def quantize_model_(model: nn.Module, quant, quantize_modules, skip_modules=()) -> int:
+    """Quantises the linears of `model` that match `quantize_modules` (fnmatch on qualified names) and none of
+    `skip_modules` (substrings) in the format `quant` names; returns the number of layers converted. One entry point
+    for every model's `enable_quant`, so each format works for each model family."""
+    kind = resolve_quant_kind(quant)
+    # a QuantConfig may narrow the selection (its own patterns) and widen the exclusions; what the model itself says
+    # must stay unquantised inside a block (routers, modulation tables) is always kept
+    quantize_modules = tuple(getattr(quant, "quantize_modules", None) or quantize_modules)
+    skip = tuple(dict.fromkeys(tuple(getattr(quant, "skip_modules", None) or ()) + tuple(skip_modules)))
+    if kind == "nvfp4":
+        from telefuser_b200.ops.nvfp4 import quantize_model_nvfp4_
+
+        return quantize_model_nvfp4_(model, tuple(quantize_modules), skip)
+    if kind == "nf4":
+        from telefuser_b200.ops.nf4 import quantize_model_nf4_
+
+        n = quantize_model_nf4_(model, tuple(quantize_modules), skip)
+        invalidate_fused_caches(model)
+        return n
+    return quantize_model_fp8_(model, tuple(quantize_modules), skip, block_scaled=kind == "mxfp8", int8=kind == "int8")
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -285,8 +332,5 @@ def load_quantized_sidecar(model: nn.Module, path: str, strict: bool = True) -> 
             del m.weight.tfb_scale
         m._sync()
         n += 1
-    for m in model.modules():  # fused views cached from the bf16 weights are stale now
-        for attr in ("_qkv", "_kv", "_gu", "_fused"):
-            if hasattr(m, attr):
-                setattr(m, attr, None)
+    invalidate_fused_caches(model)
     return n
