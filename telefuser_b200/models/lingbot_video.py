@@ -124,8 +124,34 @@ class LingBotVideoGroupedExperts(nn.Module):
         self.w1 = nn.Parameter(torch.empty(num_experts, inter, hidden))
         self.w2 = nn.Parameter(torch.empty(num_experts, hidden, inter))
         self.w3 = nn.Parameter(torch.empty(num_experts, inter, hidden))
+        # per-output-channel scales of e4m3 expert weights; None until `quantize_fp8_`
+        self.register_buffer("w1_scale", None, persistent=True)
+        self.register_buffer("w2_scale", None, persistent=True)
+        self.register_buffer("w3_scale", None, persistent=True)
         self._w13 = None
+        self._w13_scale = None
         self.ep = None  # expert-parallel state set by `enable_expert_parallel`
+
+    def quantize_fp8_(self) -> None:
+        """In place: the three stacked expert weights become e4m3 with one scale per output channel of each expert
+        (W8A8 at run time: tokens are quantised per row in front of each GEMM). Role parity:
+        telefuser/models/lingbot_video_moe.py:76-87."""
+        if self.w1.dtype == torch.float8_e4m3fn:
+            return
+        if self.ep is not None:
+            raise RuntimeError("quantise the experts before `enable_expert_parallel`; the sharded exchange path is bf16")
+        for name in ("w1", "w2", "w3"):
+            q, scale = MOE.quantize_expert_weight_fp8(getattr(self, name).detach())
+            setattr(self, name, nn.Parameter(q, requires_grad=False))
+            setattr(self, name + "_scale", scale)
+        self._w13 = self._w13_scale = None
+
+    def fused_w13_scale(self):
+        """[E, 2I] fp32: gate-row scales then up-row scales, matching `fused_w13`."""
+        s = self._w13_scale
+        if s is None or s.device != self.w1.device:
+            s = self._w13_scale = torch.cat([self.w1_scale, self.w3_scale], dim=1).to(self.w1.device).contiguous()
+        return s
 
     def fused_w13(self):
         """[E, 2I, C]: gate rows then up rows of every expert; w1 / w3 become views of it."""
@@ -141,6 +167,11 @@ class LingBotVideoGroupedExperts(nn.Module):
         return self._w13
 
     def forward(self, tokens, indices, weights, counts=None):
+        if self.w2.dtype == torch.float8_e4m3fn:
+            if self.ep is not None:
+                raise RuntimeError("expert parallelism exchanges bf16 expert inputs; e4m3 experts run unsharded")
+            return MOE.experts_forward_fp8(tokens, indices, weights, self.fused_w13(), self.fused_w13_scale(), self.w2.data,
+                                           self.w2_scale, counts=counts)  # fmt: skip
         if self.ep is not None:
             from telefuser_b200.parallel.expert import experts_forward_ep
 
@@ -333,6 +364,26 @@ class LingBotVideoTransformer3DModel(BaseModel):
 
     def get_fsdp_module_names(self) -> list[str]:
         return ["blocks"]
+
+    def quantize_experts_fp8_(self) -> int:
+        """Routed expert weights of every sparse block to e4m3 (the shared experts and attention projections are
+        `nn.Linear` layers and follow `enable_quant`); returns the number of expert banks converted."""
+        n = 0
+        for b in self.blocks:
+            if isinstance(b.ffn, LingBotVideoSparseMoeBlock):
+                b.ffn.experts.quantize_fp8_()
+                n += 1
+        return n
+
+    def enable_quant(self, quant=None) -> int:
+        """The block linears in the requested format (routers and gates stay as they are); for FP8 the stacked routed
+        experts are quantised too, since they hold most of a MoE checkpoint's bytes."""
+        from telefuser_b200.ops.quant import resolve_quant_kind
+
+        n = super().enable_quant(quant)
+        if resolve_quant_kind(quant) == "fp8":
+            n += self.quantize_experts_fp8_()
+        return n
 
     def promote_stability_layers_to_fp32(self) -> None:
         """Norm weights, modulation tables, time MLPs and routers stay fp32 (the kernels read them as fp32)."""

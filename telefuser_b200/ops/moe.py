@@ -6,7 +6,8 @@ expert segments + per-tile expert table) -> permute kernel -> grouped tcgen05 GE
 SiLU-mul -> grouped GEMM (down) -> weighted combine in fp32. Buffers are sized for the worst case
 `T*K + E*127` rows, so nothing depends on the routing outcome on the host.
 CPU path: plain PyTorch with the same semantics (the numerics oracle).
-Role parity: telefuser/ops/moe.py:9-133 (`route_topk`, `grouped_expert_forward`).
+Role parity: telefuser/ops/moe.py:9-133 (`route_topk`, `grouped_expert_forward`); the W8A8 expert path
+(`quantize_expert_weight_fp8`, `experts_forward_fp8`) is at the end of this file.
 """
 
 from __future__ import annotations
@@ -147,5 +148,85 @@ def experts_forward(x, indices, weights, w13, w2, counts=None, residual=None, wo
     return out
 
 
+def quantize_expert_weight_fp8(weight: torch.Tensor):
+    """Stacked expert weights [E, out, in] -> (e4m3 [E, out, in], fp32 scale [E, out]) with one scale per output
+    channel of each expert (amax / 448). Role parity: telefuser/ops/moe.py:136-146."""
+    if weight.ndim != 3:
+        raise ValueError(f"expert weights are stacked as [experts, out_features, in_features], got {tuple(weight.shape)}")
+    w = weight.float()
+    scale = (w.abs().amax(dim=2) / 448.0).clamp_min(1e-12)
+    return (w / scale.unsqueeze(2)).clamp(-448, 448).to(torch.float8_e4m3fn), scale
+
+
+def experts_forward_fp8_reference(x, indices, weights, w13, w13_scale, w2, w2_scale):
+    """The W8A8 expert FFN spelled out per expert: rows quantised per token before each GEMM, e4m3 weights with
+    per-channel scales, fp32 accumulation and fp32 route reduction."""
+    from .functional import linear_fp8
+
+    T, C = x.shape
+    out = torch.zeros(T, C, dtype=torch.float32, device=x.device)
+    for e in range(w13.shape[0]):
+        tok, slot = (indices == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = act_mul(linear_fp8(x[tok], w13[e], w13_scale[e]), "silu")
+        y = linear_fp8(h, w2[e], w2_scale[e])
+        out.index_add_(0, tok, y.float() * weights[tok, slot].float().unsqueeze(-1))
+    return out.to(x.dtype)
+
+
+def experts_forward_fp8(x, indices, weights, w13, w13_scale, w2, w2_scale, counts=None, residual=None,
+                        workspace: MoEWorkspace | None = None):  # fmt: skip
+    """Routed expert FFN on e4m3 weights (`quantize_expert_weight_fp8`): w13 [E, 2I, C] gate rows then up rows with
+    scale [E, 2I]; w2 [E, C, I] with scale [E, C]. Activations are quantised per token in front of each GEMM.
+
+    CUDA path: the plan / permute / combine kernels of the bf16 path around one W8A8 tensor-core GEMM pair per
+    non-empty expert segment; the segment bounds are read back once per call (the per-expert launches need them on
+    the host), so unlike the bf16 path this one is not capturable in a CUDA graph.
+    Role parity: telefuser/ops/moe.py:148-206 (`fp8_expert_forward`)."""
+    from .functional import linear_fp8
+
+    if w13.dtype != torch.float8_e4m3fn or w2.dtype != torch.float8_e4m3fn:
+        raise ValueError("expert weights must be quantised (quantize_expert_weight_fp8) before the FP8 forward")
+    T, C = x.shape
+    E, two_i, _ = w13.shape
+    inter = two_i // 2
+    K = indices.shape[1]
+    ok = _native(x) and x.dtype == torch.bfloat16 and C % 64 == 0 and inter % 64 == 0
+    if not ok:
+        out = experts_forward_fp8_reference(x, indices.long(), weights, w13, w13_scale, w2, w2_scale)
+        return out if residual is None else (out.float() + residual.float()).to(x.dtype)
+    lib = native.load()
+    st = native.stream_ptr()
+    ws = workspace
+    if ws is None:
+        key = (T, K, E, C, inter, x.device.index)
+        ws = _WORKSPACES.get(key)
+        if ws is None:
+            ws = _WORKSPACES[key] = MoEWorkspace(T, K, E, C, inter, x.device)
+    ids = indices.to(torch.int32).contiguous()
+    wts = weights.float().contiguous()
+    if counts is None:
+        counts = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
+    xc = x.contiguous()
+    native.check(lib.tfb_moe_plan(counts.data_ptr(), E, ALIGN, ws.offsets.data_ptr(), ws.tile_expert.data_ptr(),
+                                  ws.rows // ALIGN, st), "tfb_moe_plan")  # fmt: skip
+    native.check(lib.tfb_moe_permute(xc.data_ptr(), C, ids.data_ptr(), ws.offsets.data_ptr(), ws.cursor.data_ptr(), E,
+                                     T, K, ws.x_perm.data_ptr(), ws.row_map.data_ptr(), st), "tfb_moe_permute")  # fmt: skip
+    bounds = ws.offsets.tolist()  # 128-row-aligned segment starts, one per expert, plus the end
+    w13_scale, w2_scale = w13_scale.to(x.device, torch.float32), w2_scale.to(x.device, torch.float32)
+    for e in range(E):
+        lo, hi = bounds[e], bounds[e + 1]
+        if hi <= lo:
+            continue
+        h = act_mul(linear_fp8(ws.x_perm[lo:hi], w13[e], w13_scale[e]), "silu")
+        ws.y[lo:hi].copy_(linear_fp8(h, w2[e], w2_scale[e]))
+    out = torch.empty_like(xc)
+    res = None if residual is None else residual.contiguous()
+    native.check(lib.tfb_moe_combine(ws.y.data_ptr(), C, ws.row_map.data_ptr(), wts.data_ptr(), T, K, native.ptr(res),
+                                     out.data_ptr(), st), "tfb_moe_combine")  # fmt: skip
+    return out
+
+
 __all__ = ["route_topk", "route_topk_reference", "experts_forward", "experts_forward_reference", "MoEWorkspace",
-           "act_mul"]  # fmt: skip
+           "act_mul", "quantize_expert_weight_fp8", "experts_forward_fp8", "experts_forward_fp8_reference"]  # fmt: skip

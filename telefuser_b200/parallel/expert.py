@@ -38,6 +38,8 @@ class ExpertParallelState:
     @classmethod
     def shard_(cls, experts, group) -> "ExpertParallelState":
         """Keeps this rank's slice of `experts.w1 / w2 / w3` (in place) and returns the EP state."""
+        if experts.w1.dtype == torch.float8_e4m3fn:
+            raise ValueError("expert parallelism shards bf16 experts; e4m3 experts (quantize_fp8_) run unsharded")
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         E = experts.w1.shape[0]
         if E % world:

@@ -61,6 +61,49 @@ def test_routed_experts_equal_dense_evaluation():
     assert (got - dense).abs().max() <= 1e-4
 
 
+def test_fp8_experts_follow_the_bf16_experts_and_the_model_switch():
+    torch.manual_seed(0)
+    T, C, I, E, K = 40, 64, 64, 8, 2
+    x = torch.randn(T, C)
+    w13, w2 = torch.randn(E, 2 * I, C) * 0.1, torch.randn(E, C, I) * 0.1
+    ids, w = MOE.route_topk(torch.randn(T, E), 1, 1, K)
+    q13, s13 = MOE.quantize_expert_weight_fp8(w13)
+    q2, s2 = MOE.quantize_expert_weight_fp8(w2)
+    assert q13.dtype == torch.float8_e4m3fn and s13.shape == (E, 2 * I) and s2.shape == (E, C)
+    assert torch.allclose(q13.float() * s13.unsqueeze(2), w13, atol=(w13.abs().amax(2, keepdim=True) / 16).max().item())
+    assert torch.equal((q13.float().abs().amax(2) - 448).abs() < 1e-3, torch.ones(E, 2 * I, dtype=torch.bool))  # full range used
+    ref = MOE.experts_forward(x, ids, w, w13, w2)
+    got = MOE.experts_forward_fp8(x, ids, w, q13, s13, q2, s2)
+    assert torch.equal(got, MOE.experts_forward_fp8_reference(x, ids.long(), w, q13, s13, q2, s2))
+    assert (got - ref).norm() / ref.norm() < 0.09  # two GEMMs with e4m3 operands on both sides
+    res = torch.randn(T, C)
+    assert torch.allclose(MOE.experts_forward_fp8(x, ids, w, q13, s13, q2, s2, residual=res), got + res, atol=1e-5)
+    with pytest.raises(ValueError, match="quantised"):
+        MOE.experts_forward_fp8(x, ids, w, w13, s13, q2, s2)
+    with pytest.raises(ValueError, match="stacked"):
+        MOE.quantize_expert_weight_fp8(w13[0])
+
+    m = make_model("tiny-moe", hidden_size=128, num_attention_heads=2, moe_intermediate_size=64, intermediate_size=256)
+    lat, ts, txt = make_inputs(text_dim=m.config.text_dim, size=8)
+    with torch.no_grad():
+        base = m(lat, ts, txt)
+        banks = sum(1 for b in m.blocks if hasattr(b.ffn, "experts"))
+        linears_only = make_model("tiny-moe", hidden_size=128, num_attention_heads=2, moe_intermediate_size=64, intermediate_size=256).enable_quant("int8")
+        n = m.enable_quant("fp8")
+        assert banks > 0 and n == linears_only + banks  # the stacked experts are counted on top of the block linears
+        ex = next(b.ffn.experts for b in m.blocks if hasattr(b.ffn, "experts"))
+        assert ex.w1.dtype == ex.w2.dtype == ex.w3.dtype == torch.float8_e4m3fn and ex.w1_scale.shape == ex.w1.shape[:2]
+        assert ex.fused_w13_scale().shape == (ex.w1.shape[0], 2 * ex.w1.shape[1])
+        assert {"w1_scale", "w2_scale", "w3_scale"} <= {k.rsplit(".", 1)[1] for k in m.state_dict() if ".experts." in k}
+        out = m(lat, ts, txt)
+        assert torch.isfinite(out).all() and (out - base).norm() / base.norm() < 0.15
+        assert m.quantize_experts_fp8_() == banks and torch.equal(m(lat, ts, txt), out)  # a second call changes nothing
+    from telefuser_b200.parallel.expert import ExpertParallelState
+
+    with pytest.raises(ValueError, match="unsharded"):
+        ExpertParallelState.shard_(ex, None)
+
+
 def test_ulysses2_and_expert_parallel2_match_single_process():
     for preset in ("tiny", "tiny-moe"):
         m = make_model(preset)
