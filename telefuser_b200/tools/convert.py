@@ -3,15 +3,21 @@
     python -m telefuser_b200.tools.convert -s <ckpt file or dir> -o <out dir> [-o_n name]
         [--direction forward|backward --model_type wan_dit] [--rule 'regex=>replacement' ...]
         [--lora_path a.safetensors --lora_strength 1.0]
-        [--quantized --linear_dtype fp8|int8|mxfp8|nvfp4 --quantize_modules attn ffn] [--save_by_block]
+        [--quantized --linear_dtype fp8|int8|mxfp8|nvfp4|mxfp4|mxfp6 --quantize_modules attn ffn] [--save_by_block]
+        [--dequantize [--dtype bfloat16]]
 
 * key mapping: built-in rule sets (diffusers -> native Wan DiT names, and back) plus ad-hoc regex rules
 * LoRA merge before any quantisation (same loader as run-time)
 * fp8: e4m3 weight + per-output-channel fp32 `weight_scale [out, 1]` (scale = row amax / 448) — the layout
   the W8A8 linear consumes (int8: the same with int8 values in [-127, 127]); mxfp8: e4m3 payload + UE8M0 scale per 32
-  input elements in `weight_sf`; nvfp4: packed e2m1 codes + e4m3 `weight_scale` per 16 + fp32 `weight_global_scale`
+  input elements in `weight_sf`; nvfp4: packed e2m1 codes + e4m3 `weight_scale` per 16 + fp32 `weight_global_scale`;
+  mxfp4 / mxfp6 (`mxfp6_e3m2`, `mxfp6_e2m3`): bit-packed codes + UE8M0 `weight_sf` per 32 + `weight_mx_format`
+  (exponent and mantissa widths) — storage formats (`ops/mxfp.py`), expanded again by `--dequantize`
+* `--dequantize` turns any checkpoint written by `--quantized` back into dense weights (it runs before `--quantized`,
+  so one call can also re-quantise into another format)
 * output: one safetensors file, or one file per transformer block plus an index json
-Role parity: tools/convert/converter.py:32-937 (key mapping, quantize_model, load_loras, save by block).
+Role parity: tools/convert/converter.py:32-937 (key mapping, quantize_model, load_loras, save by block),
+tools/convert/quant.py:28-145 (the weight formats).
 """
 
 from __future__ import annotations
@@ -120,7 +126,7 @@ def quantize_model(sd: dict, linear_dtype: str = "fp8", quantize_modules=("attn"
     for k, v in sd.items():
         is_target = (k.endswith(".weight") and v.dim() == 2 and min(v.shape) >= min_dim
                      and any(m in k for m in quantize_modules) and not any(s in k for s in skip))  # fmt: skip
-        if not is_target or (linear_dtype == "mxfp8" and v.shape[1] % 32) or (linear_dtype == "nvfp4" and v.shape[1] % 16):
+        if not is_target or (linear_dtype.startswith("mxfp") and v.shape[1] % 32) or (linear_dtype == "nvfp4" and v.shape[1] % 16):
             out[k] = v
             continue
         base = k[: -len(".weight")]
@@ -140,9 +146,50 @@ def quantize_model(sd: dict, linear_dtype: str = "fp8", quantize_modules=("attn"
 
             packed, sf, gs = quantize_nvfp4(v)
             out[k], out[base + ".weight_scale"], out[base + ".weight_global_scale"] = packed, sf, gs
+        elif linear_dtype in MX_SUBBYTE:
+            from telefuser_b200.ops.mxfp import mx_format, quantize_mx
+
+            f = mx_format(linear_dtype)
+            packed, sf = quantize_mx(v, f)
+            out[k], out[base + ".weight_sf"] = packed, sf
+            out[base + ".weight_mx_format"] = torch.tensor([f.exp_bits, f.man_bits], dtype=torch.uint8)
         else:
             raise ValueError(f"unknown linear dtype {linear_dtype!r}")
         n += 1
+    return out, n
+
+
+MX_SUBBYTE = ("mxfp4", "mxfp6", "mxfp6_e2m3", "mxfp6_e3m2")
+_SIDE_TENSORS = (".weight_scale", ".weight_sf", ".weight_global_scale", ".weight_mx_format")
+
+
+def dequantize_model(sd: dict, dtype=torch.bfloat16) -> tuple[dict, int]:
+    """Inverse of `quantize_model` for every format it writes: quantised `<name>.weight` entries become dense
+    `dtype` matrices and their side tensors are dropped, so a 4- / 6- / 8-bit checkpoint loads anywhere."""
+    out, n = {}, 0
+    for k, v in sd.items():
+        if k.endswith(_SIDE_TENSORS):
+            continue
+        base = k[: -len(".weight")] if k.endswith(".weight") else None
+        scale, sf = (sd.get(f"{base}.weight_scale"), sd.get(f"{base}.weight_sf")) if base else (None, None)
+        if base is None or (scale is None and sf is None):
+            out[k] = v
+            continue
+        n += 1
+        if f"{base}.weight_mx_format" in sd:
+            from telefuser_b200.ops.mxfp import MXFormat, dequantize_mx
+
+            e, m = (int(t) for t in sd[f"{base}.weight_mx_format"])
+            out[k] = dequantize_mx(v, sf, MXFormat("checkpoint", e, m, 1 if e == 2 else 3), dtype)
+        elif f"{base}.weight_global_scale" in sd:
+            from telefuser_b200.ops.nvfp4 import dequantize_nvfp4
+
+            out[k] = dequantize_nvfp4(v, scale, sd[f"{base}.weight_global_scale"], dtype)
+        elif sf is not None:  # MXFP8: e4m3 payload, UE8M0 byte per 32 input elements
+            w = v.float().reshape(v.shape[0], -1, 32) * torch.exp2(sf.float() - 127.0).unsqueeze(-1)
+            out[k] = w.reshape(v.shape).to(dtype)
+        else:  # e4m3 or int8 with one scale per output channel
+            out[k] = (v.float() * scale.float().reshape(-1, 1)).to(dtype)
     return out, n
 
 
@@ -202,12 +249,14 @@ def convert_weights(args) -> dict:
         for k, p in params.items():
             sd[k] = p.data.to(sd[k].dtype)
     nq = 0
+    if getattr(args, "dequantize", False):
+        sd, nq = dequantize_model(sd, getattr(torch, args.dtype or "bfloat16"))
     if args.quantized:
         sd, nq = quantize_model(sd, args.linear_dtype, tuple(args.quantize_modules))
     if args.dtype:
         dt = getattr(torch, args.dtype)
         sd = {k: (v.to(dt) if v.is_floating_point() and v.dtype in (torch.float32, torch.float16, torch.bfloat16)
-                  and not k.endswith(("weight_scale", "weight_sf")) else v) for k, v in sd.items()}  # fmt: skip
+                  and not k.endswith(_SIDE_TENSORS) else v) for k, v in sd.items()}  # fmt: skip
     os.makedirs(args.output, exist_ok=True)
     if args.save_by_block:
         save_by_block(sd, args.output, args.output_name)
@@ -232,7 +281,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--lora_path", nargs="*")
     p.add_argument("--lora_strength", type=float, default=1.0)
     p.add_argument("--quantized", action="store_true")
-    p.add_argument("--linear_dtype", default="fp8", choices=["fp8", "int8", "mxfp8", "nvfp4"])
+    p.add_argument("--linear_dtype", default="fp8", choices=["fp8", "int8", "mxfp8", "nvfp4", *MX_SUBBYTE])
+    p.add_argument("--dequantize", action="store_true", help="expand a quantised checkpoint back to dense weights first")
     p.add_argument("--quantize_modules", nargs="*", default=["attn", "ffn"])
     p.add_argument("--dtype", default=None, choices=[None, "bfloat16", "float16", "float32"])
     p.add_argument("-b", "--save_by_block", action="store_true")
