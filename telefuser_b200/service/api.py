@@ -388,11 +388,20 @@ class ApiServer:
             return JSONResponse({"ready": ok}, status_code=200 if ok else 503)
 
         @r.get("/metrics")
-        async def metrics():
+        async def metrics(format: str = "prometheus"):
+            """Prometheus text by default; `?format=opentelemetry` (OTLP/JSON) or `?format=statsd` (lines)."""
             if self.metrics is None:
                 raise HTTPException(404, "metrics are disabled")
             self._update_queue_metrics()
-            return PlainTextResponse(self.metrics.registry.to_prometheus(), media_type="text/plain; version=0.0.4")
+            if format == "prometheus":
+                return PlainTextResponse(self.metrics.registry.to_prometheus(), media_type="text/plain; version=0.0.4")
+            from telefuser_b200.metrics.exporters import get_exporter
+
+            try:
+                exporter = get_exporter(format)
+            except ValueError as e:
+                raise HTTPException(400, str(e)) from None
+            return PlainTextResponse(exporter.export(self.metrics.registry), media_type=exporter.content_type)
 
         @r.get("/metrics/json")
         async def metrics_json() -> dict:

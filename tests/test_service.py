@@ -285,6 +285,10 @@ def test_http_task_flow(tmp_path, ppl_file):
         assert q["active_count"] == 0 and q["queue_size"] == 100
         prom = client.get("/v1/service/metrics").text
         assert "telefuser" in prom and "tasks" in prom
+        otlp = client.get("/v1/service/metrics", params={"format": "opentelemetry"})
+        assert otlp.headers["content-type"].startswith("application/json") and otlp.json()["resourceMetrics"][0]["scopeMetrics"][0]["metrics"]
+        assert "|g" in client.get("/v1/service/metrics", params={"format": "statsd"}).text
+        assert client.get("/v1/service/metrics", params={"format": "graphite"}).status_code == 400
         assert client.get("/v1/service/status").json()["pipeline_ready"] is True
 
 
