@@ -258,3 +258,124 @@ class LingBotWorldFastControlBuilder:
                 item["action"] = self._align_action(a, c.latent_frames)[s : s + c.chunk_size]
             out.append(self.build(item))
         return out
+
+
+# ---- offline control inputs: files, resampling, windows, deferred materialisation ----
+
+def _quaternions(rot: np.ndarray) -> np.ndarray:
+    """Rotation matrices [N, 3, 3] -> unit quaternions [N, 4] as (w, x, y, z), each on the hemisphere of its
+    predecessor so that interpolation takes the short way round."""
+    m = rot.astype(np.float64)
+    q = np.empty((m.shape[0], 4))
+    tr = np.trace(m, axis1=1, axis2=2)
+    for i in range(m.shape[0]):
+        r = m[i]
+        if tr[i] > 0:
+            s = 2.0 * math.sqrt(tr[i] + 1.0)
+            q[i] = (0.25 * s, (r[2, 1] - r[1, 2]) / s, (r[0, 2] - r[2, 0]) / s, (r[1, 0] - r[0, 1]) / s)
+        else:
+            a = int(np.argmax(np.diag(r)))
+            b, c = (a + 1) % 3, (a + 2) % 3
+            s = 2.0 * math.sqrt(max(1.0 + r[a, a] - r[b, b] - r[c, c], 1e-30))
+            v = np.empty(4)
+            v[0], v[1 + a], v[1 + b], v[1 + c] = (r[c, b] - r[b, c]) / s, 0.25 * s, (r[b, a] + r[a, b]) / s, (r[c, a] + r[a, c]) / s
+            q[i] = v
+        q[i] /= np.linalg.norm(q[i])
+        if i and np.dot(q[i], q[i - 1]) < 0:
+            q[i] = -q[i]
+    return q
+
+
+def _rotation_matrices(q: np.ndarray) -> np.ndarray:
+    w, x, y, z = q[:, 0], q[:, 1], q[:, 2], q[:, 3]
+    return np.stack([np.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (x * z + y * w)], -1),
+                     np.stack([2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w)], -1),
+                     np.stack([2 * (x * z - y * w), 2 * (y * z + x * w), 1 - 2 * (x * x + y * y)], -1)], 1)  # fmt: skip
+
+
+def interpolate_camera_poses(src_indices, src_rot_mat, src_trans_vec, tgt_indices) -> torch.Tensor:
+    """Camera path given at `src_indices` (ascending frame numbers) resampled at `tgt_indices`: translations linearly
+    (extrapolated beyond the ends), rotations by spherical linear interpolation between the two neighbouring key
+    frames (held at the ends). Returns [len(tgt), 4, 4] fp32 camera-to-world matrices.
+    Role parity: telefuser/pipelines/lingbot_world_fast/control.py:57-89."""
+    src = np.asarray(src_indices, dtype=np.float64)
+    tgt = np.asarray(tgt_indices, dtype=np.float64)
+    trans = np.asarray(src_trans_vec, dtype=np.float64)
+    if src.ndim != 1 or src.size < 2 or np.any(np.diff(src) <= 0):
+        raise ValueError("key-frame indices must be at least two strictly ascending numbers")
+    hi = np.clip(np.searchsorted(src, tgt, side="right"), 1, src.size - 1)
+    lo = hi - 1
+    t = (tgt - src[lo]) / (src[hi] - src[lo])
+    out_t = trans[lo] + (trans[hi] - trans[lo]) * t[:, None]
+    q = _quaternions(np.asarray(src_rot_mat))
+    tc = np.clip(t, 0.0, 1.0)
+    dot = np.clip(np.sum(q[lo] * q[hi], axis=1), -1.0, 1.0)
+    theta = np.arccos(dot)
+    small = theta < 1e-6
+    sin = np.where(small, 1.0, np.sin(theta))
+    wa = np.where(small, 1.0 - tc, np.sin((1.0 - tc) * theta) / sin)
+    wb = np.where(small, tc, np.sin(tc * theta) / sin)
+    qi = wa[:, None] * q[lo] + wb[:, None] * q[hi]
+    qi /= np.linalg.norm(qi, axis=1, keepdims=True)
+    poses = np.zeros((tgt.size, 4, 4), dtype=np.float32)
+    poses[:, :3, :3] = _rotation_matrices(qi)
+    poses[:, :3, 3] = out_t
+    poses[:, 3, 3] = 1.0
+    return torch.from_numpy(poses)
+
+
+def truncate_control_sequence(poses, intrinsics, action, frame_num: int):
+    """The first `frame_num` video-rate poses (and actions) of a recorded trajectory, with the FIRST intrinsics row as
+    the session's fixed calibration. Recordings shorter than the session are refused."""
+    if frame_num < 1 or (frame_num - 1) % 4:
+        raise ValueError(f"frame_num must have the form 4n+1, got {frame_num}")
+    if len(poses) < frame_num:
+        raise ValueError(f"the pose recording has {len(poses)} frames, the session needs {frame_num}")
+    ks = np.asarray(intrinsics)
+    if ks.ndim not in (1, 2) or ks.shape[-1] != 4 or ks.shape[0] < 1:
+        raise ValueError(f"intrinsics are (fx, fy, cx, cy) or one such row per frame, got shape {ks.shape}")
+    if action is not None and len(action) < frame_num:
+        raise ValueError(f"the action recording has {len(action)} frames, the session needs {frame_num}")
+    return poses[:frame_num], (ks[0] if ks.ndim == 2 else ks), (None if action is None else action[:frame_num])
+
+
+class LingBotWorldFastOfflineControlSource:
+    """A recorded trajectory kept outside the generation session: `control_at(i)` hands out a provider for chunk
+    i, and the whole trajectory is converted to control tensors once, when the first provider is called (i.e. when
+    the first chunk is admitted to the denoiser, not when the session is set up)."""
+
+    def __init__(self, builder: LingBotWorldFastControlBuilder, poses, intrinsics, action=None) -> None:
+        self._builder, self._inputs = builder, (poses, intrinsics, action)
+        self._controls: list[torch.Tensor] | None = None
+        self.materialize_count = 0
+
+    def control_at(self, chunk_index: int):
+        if chunk_index < 0:
+            raise ValueError(f"chunk indices start at 0, got {chunk_index}")
+
+        def provider() -> torch.Tensor:
+            return self._materialized()[chunk_index]
+
+        provider.source = self
+        return provider
+
+    def _materialized(self) -> list[torch.Tensor]:
+        if self._controls is None:
+            self._controls = self._builder.build_sequence(*self._inputs)
+            self.materialize_count += 1
+        return self._controls
+
+
+def load_camera_control_inputs(action_path, intrinsics_path):
+    """(`poses.npy` [frames, 4, 4] under `action_path`, the intrinsics file given explicitly)."""
+    from pathlib import Path
+
+    return np.load(Path(action_path) / "poses.npy"), np.load(Path(intrinsics_path))
+
+
+def load_action_control_inputs(action_path, intrinsics_path):
+    """As `load_camera_control_inputs`, plus `action.npy` [frames, 4] from the same folder."""
+    from pathlib import Path
+
+    poses, ks = load_camera_control_inputs(action_path, intrinsics_path)
+    return poses, ks, np.load(Path(action_path) / "action.npy")

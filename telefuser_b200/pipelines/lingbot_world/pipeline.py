@@ -30,8 +30,10 @@ from telefuser_b200.orchestrator.worker_actor import ParallelWorkerStageActor
 from telefuser_b200.utils.logging import logger
 from telefuser_b200.worker.parallel_worker import ParallelWorker
 
-from .control import (LingBotWorldFastControlBuilder, LingBotWorldFastControlContext, pinhole_intrinsics,
-                      random_walk_trajectory)  # fmt: skip
+from .control import (LingBotWorldFastControlBuilder, LingBotWorldFastControlContext, LingBotWorldFastOfflineControlSource,
+                      load_action_control_inputs, load_camera_control_inputs, pinhole_intrinsics, random_walk_trajectory,
+                      truncate_control_sequence)  # fmt: skip
+from .session import LingBotWorldFastSessionConfig, resolve_lingbot_frame_count
 from .stages import LingBotWorldFastDenoisingStage, LingBotWorldFastVAEDecodeStage, LingBotWorldFastVAEEncodeStage
 
 
@@ -51,6 +53,11 @@ class LingBotWorldFastPipelineConfig:
     control_type: str = "cam"
     enable_denoising_parallel: bool = False
     edge_capacity: int = 2
+    # the output resolution of a session keeps the reference image's aspect ratio at (about) this many pixels;
+    # orig_height / orig_width: the image size that recorded intrinsics files refer to unless the caller says otherwise
+    max_area: int = 480 * 832
+    orig_height: int = 480
+    orig_width: int = 832
 
 
 @dataclass
@@ -266,6 +273,9 @@ class LingBotWorldFastPipeline(BasePipeline):
             prompt_emb = self.text_encoding_stage.process([prompt])[0]
         if isinstance(image, torch.Tensor):
             cond = image
+            if tuple(cond.shape[-2:]) != (height, width):  # a tensor image of another size: resample as a PIL image would be
+                cond = torch.nn.functional.interpolate(cond.reshape(1, *cond.shape[-3:]).float(), size=(height, width),
+                                                       mode="bilinear", antialias=True, align_corners=False)[0].to(image.dtype)  # fmt: skip
         else:
             cond = self.preprocess_image(image, height, width)[0]
         handle = next(self._handles)
@@ -287,20 +297,120 @@ class LingBotWorldFastPipeline(BasePipeline):
     def release_session(self, session: LingBotWorldFastStreamingSession, cancel: bool = False) -> None:
         self.runtime.close_session(session, cancel)
 
+    # ---- session records, output geometry, recorded trajectories ----------------------------------
+    @staticmethod
+    def best_output_size(width: int, height: int, expected_area: int, dw: int = 16, dh: int = 16) -> tuple[int, int]:
+        """(width, height) of about `expected_area` pixels with the aspect ratio of a width x height image, each side
+        rounded DOWN to its own multiple (16 by default: stride-8 VAE x patch 2)."""
+        import math
+
+        aspect = height / width
+        return int(math.sqrt(expected_area / aspect) // dw * dw), int(math.sqrt(expected_area * aspect) // dh * dh)
+
+    @staticmethod
+    def _image_size(image) -> tuple[int, int]:
+        if isinstance(image, torch.Tensor):
+            return int(image.shape[-1]), int(image.shape[-2])
+        return int(image.width), int(image.height)
+
+    def control_context(self, session_config: LingBotWorldFastSessionConfig) -> LingBotWorldFastControlContext:
+        """Geometry of a session's control tensors, worked out from the record alone (no caches are allocated, no
+        model runs): output size from the reference image and `max_area`, latent frame count from the frame policy,
+        intrinsics either given (first row, with their calibration size) or a pinhole of focal length = image width.
+        Role parity: telefuser/pipelines/lingbot_world_fast/pipeline.py:192-242."""
+        cfg = self.config
+        session_config.validate(self.dit_meta["control_type"])
+        img_w, img_h = self._image_size(session_config.image)
+        width, height = self.best_output_size(img_w, img_h, cfg.max_area)
+        height, width = self.check_resize_height_width(height, width)
+        _, latent_frames = resolve_lingbot_frame_count(session_config.frame_num, session_config.chunk_size,
+                                                       session_config.frame_policy)  # fmt: skip
+        if session_config.intrinsics is None:
+            cal_w, cal_h = img_w, img_h
+            ks = torch.tensor([float(img_w), float(img_w), img_w * 0.5, img_h * 0.5], dtype=torch.float32, device=self.device)
+        else:
+            cal_w = session_config.intrinsics_width or cfg.orig_width
+            cal_h = session_config.intrinsics_height or cfg.orig_height
+            ks = torch.as_tensor(session_config.intrinsics, dtype=torch.float32, device=self.device)
+            if ks.ndim == 2 and ks.shape[0] >= 1 and ks.shape[1] == 4:
+                ks = ks[0]
+            if ks.shape != (4,):
+                raise ValueError(f"session intrinsics are (fx, fy, cx, cy) or one such row per frame, got {tuple(ks.shape)}")
+        return LingBotWorldFastControlContext(
+            control_type=self.dit_meta["control_type"], device=self.device, control_dtype=self.torch_dtype,
+            orig_height=cal_h, orig_width=cal_w, height=height, width=width, latent_h=height // 8, latent_w=width // 8,
+            latent_frames=latent_frames, chunk_size=session_config.chunk_size, intrinsics=ks)  # fmt: skip
+
+    def prepare_offline_controls(self, session_config: LingBotWorldFastSessionConfig, action_path, intrinsics_path,
+                                 intrinsics_width: int | None = None, intrinsics_height: int | None = None) -> list:  # fmt: skip
+        """One deferred control per chunk from a recorded trajectory (`poses.npy`, for the action mode also
+        `action.npy`, under `action_path`; the intrinsics file is named explicitly). The recording is cut to the
+        session's length, its first intrinsics row is the calibration (measured on `intrinsics_width` x
+        `intrinsics_height` pixels; default: the configured original size), and the conversion to control tensors runs
+        once, when the first chunk asks for its control."""
+        if (intrinsics_width is None) != (intrinsics_height is None):
+            raise ValueError("intrinsics_width and intrinsics_height name one calibration image: give both or neither")
+        for name, v in (("intrinsics_width", intrinsics_width), ("intrinsics_height", intrinsics_height)):
+            if v is not None and (isinstance(v, bool) or not isinstance(v, int) or v < 1):
+                raise ValueError(f"{name} must be a positive integer, got {v!r}")
+        from dataclasses import replace
+
+        ctx = replace(self.control_context(session_config), orig_width=intrinsics_width or self.config.orig_width,
+                      orig_height=intrinsics_height or self.config.orig_height)  # fmt: skip
+        if ctx.control_type == "act":
+            poses, ks, action = load_action_control_inputs(action_path, intrinsics_path)
+        else:
+            (poses, ks), action = load_camera_control_inputs(action_path, intrinsics_path), None
+        poses, ks, action = truncate_control_sequence(poses, ks, action, session_config.frame_num)
+        source = LingBotWorldFastOfflineControlSource(LingBotWorldFastControlBuilder(ctx), poses, ks, action)
+        return [source.control_at(i) for i in range(ctx.latent_frames // ctx.chunk_size)]
+
+    def validate_control(self, rt: LingBotWorldFastGenerationSession, control: torch.Tensor) -> None:
+        """A control tensor must be [1, c * (H / h) * (W / w), chunk, h, w] with c = 6 (camera) or 7 (action)."""
+        per_pixel = 7 if self.dit_meta["control_type"] == "act" else 6
+        fold = max(1, rt.height // rt.latent_h) * max(1, rt.width // rt.latent_w)
+        want = (1, per_pixel * fold, rt.chunk_size, rt.latent_h, rt.latent_w)
+        if tuple(control.shape) != want:
+            raise ValueError(f"control tensor has shape {tuple(control.shape)}, this session takes {want}")
+
+    def create_session(self, session_config: LingBotWorldFastSessionConfig, prompt_emb: torch.Tensor | None = None):
+        """Generation session for a session record: the frame policy is applied, the output size follows the reference
+        image, and the session's calibration is taken from the record. Returns (generation session, control context)."""
+        ctx = self.control_context(session_config)
+        if session_config.chunk_size != self.config.chunk_size:
+            raise ValueError(f"the session asks for chunks of {session_config.chunk_size} latent frames, the pipeline was "
+                             f"initialised with {self.config.chunk_size}")  # fmt: skip
+        rt = self._create_initialized_session(session_config.prompt, session_config.image, session_config.frame_num,
+                                              ctx.height, ctx.width, session_config.seed, prompt_emb)  # fmt: skip
+        rt.control_builder = LingBotWorldFastControlBuilder(ctx)
+        return rt, ctx
+
     # ---- offline generation through the streaming graph ---------------------------------------
     @torch.no_grad()
     def generate_video(self, prompt, image, num_frames: int = 61, height: int = 480, width: int = 832, seed: int = 0,
                        poses: torch.Tensor | None = None, prompt_emb=None, on_chunk: Callable | None = None,
-                       timeout_s: float = 3600.0, bind_controls_late: bool = False):  # fmt: skip
+                       timeout_s: float = 3600.0, bind_controls_late: bool = False, controls: list | None = None,
+                       frame_policy: str = "strict", session_config: LingBotWorldFastSessionConfig | None = None):  # fmt: skip
         """Returns (frames [1, 3, T, H, W], metrics). `poses`: [latent_frames, 4, 4] camera path (default: seeded walk).
+        `controls`: one ready control tensor or provider per chunk instead of `poses` (what `prepare_offline_controls`
+        returns). `frame_policy="truncate"` rounds `num_frames` down to a whole number of chunks. `session_config`: a
+        session record in place of the individual arguments (its image fixes the output size).
         `bind_controls_late`: hand each chunk's control to the denoiser as a provider that is read when the chunk is
         admitted (what the interactive service does); `metrics["control_bound_to_output_p50_s"]` is then the time
         from that moment to the chunk's frames."""
-        rt = self._create_initialized_session(prompt, image, num_frames, height, width, seed, prompt_emb)
+        if session_config is not None:
+            rt, _ = self.create_session(session_config, prompt_emb)
+            seed = session_config.seed
+        else:
+            num_frames, _ = resolve_lingbot_frame_count(num_frames, self.config.chunk_size, frame_policy)
+            rt = self._create_initialized_session(prompt, image, num_frames, height, width, seed, prompt_emb)
         latent_frames = rt.chunk_count * rt.chunk_size
-        if poses is None:
-            poses = random_walk_trajectory(latent_frames, seed=seed)
-        controls = rt.control_builder.build_sequence(poses, rt.control_builder.context.intrinsics)
+        if controls is None:
+            if poses is None:
+                poses = random_walk_trajectory(latent_frames, seed=seed)
+            controls = rt.control_builder.build_sequence(poses, rt.control_builder.context.intrinsics)
+        elif len(controls) < rt.chunk_count:
+            raise ValueError(f"{len(controls)} controls were given for {rt.chunk_count} chunks")
         session = self.runtime.create_session(rt)
         frames, nxt, t0 = {}, 0, time.monotonic()
         bound_at, latencies = {}, []
@@ -308,7 +418,7 @@ class LingBotWorldFastPipeline(BasePipeline):
         def provider(i):
             def bind():
                 bound_at[i] = time.monotonic()
-                return controls[i]
+                return controls[i]() if callable(controls[i]) else controls[i]
 
             return bind
 

@@ -168,8 +168,20 @@ class LingBotWorldFastService:
                 raise ValueError(f"{name} must be positive")
         chunk_size = self.pipeline.config.chunk_size
         frames = frame_num_for_duration(cfg.max_duration_seconds, cfg.fps, chunk_size)
-        generation = self.pipeline._create_initialized_session(cfg.prompt, load_image(config), frames, cfg.height, cfg.width, cfg.seed,
+        image = load_image(config)
+        if config.get("fit_image"):  # output size from the reference image's aspect ratio at the pipeline's pixel budget
+            w, h = self.pipeline.best_output_size(*self.pipeline._image_size(image), self.pipeline.config.max_area)
+            cfg.height, cfg.width = self.pipeline.check_resize_height_width(h, w)
+        generation = self.pipeline._create_initialized_session(cfg.prompt, image, frames, cfg.height, cfg.width, cfg.seed,
                                                                prompt_emb=config.get("prompt_emb"))  # fmt: skip
+        if config.get("intrinsics") is not None:  # the client's calibration (fx, fy, cx, cy) and the image size it refers to
+            import dataclasses
+
+            ks = torch.as_tensor(config["intrinsics"], dtype=torch.float32).reshape(-1, 4)[0]
+            ctx = generation.control_builder.context
+            generation.control_builder.context = dataclasses.replace(
+                ctx, intrinsics=ks.to(ctx.intrinsics.device), orig_width=int(config.get("intrinsics_width") or ctx.orig_width),
+                orig_height=int(config.get("intrinsics_height") or ctx.orig_height))  # fmt: skip
         stream = self.pipeline.runtime.create_session(generation)
         sid = config.get("session_id") or uuid.uuid4().hex
         state = LingBotWorldFastSessionState(sid, cfg, generation, stream, queue.Queue())

@@ -134,6 +134,17 @@ def test_interactive_service_session():
     assert m3["explicit_controls_overwritten"] == 1 and m3["control_revision_received"] == 4 and m3["controls_received"] == 5
     assert m3["controls_superseded"] >= 1  # of three snapshots pushed back to back at most two could each steer a chunk
     svc.close_session(sid3)
+    # output size from the reference image, calibration from the client
+    pipe.config.max_area = 32 * 48
+    wide = torch.rand(3, 64, 96) * 2 - 1
+    sid4 = svc.create_session({"image": wide, "prompt_emb": emb, "fit_image": True, "max_duration_seconds": 0.5,
+                               "intrinsics": [[80.0, 80.0, 48.0, 32.0]], "intrinsics_width": 96, "intrinsics_height": 64})  # fmt: skip
+    ctx4 = svc._state(sid4).generation.control_builder.context
+    assert ctx4.intrinsics.tolist() == [80.0, 80.0, 48.0, 32.0] and (ctx4.orig_width, ctx4.orig_height) == (96, 64)
+    msgs4 = svc.drain(sid4, timeout=120.0)
+    assert msgs4[0]["height"] == 32 and msgs4[0]["width"] == 48
+    assert next(m for m in msgs4 if m["type"] == "frames")["frames"].shape[1:] == (32, 48, 3)
+    svc.close_session(sid4)
     # explicit pose chunks and an early stop
     poses = random_walk_trajectory(2, seed=3)
     sid2 = svc.create_session({"image": img, "prompt_emb": emb, "seed": 1, "max_duration_seconds": 3.0, "hud": False,
@@ -216,3 +227,117 @@ def test_rolling_cache_against_a_list_model_over_random_chunk_streams():
                 wk, wv = cache.window(win)
                 assert torch.equal(wk[0, :, 0], want[-win:]) and torch.equal(wv, -wk)
         assert [p for p, _ in model[:sink]] == list(range(sink))  # the first tokens ever written are still pinned
+
+
+def test_frame_count_rule_and_session_record():
+    from telefuser_b200.pipelines.lingbot_world.session import LingBotWorldFastSessionConfig, resolve_lingbot_frame_count
+
+    assert resolve_lingbot_frame_count(81, 3) == (81, 21)  # 21 latent frames = 7 whole chunks
+    assert resolve_lingbot_frame_count(81, 4, "truncate") == (77, 20)  # 21 -> 20 latent frames
+    assert resolve_lingbot_frame_count(77, 4, "strict") == (77, 20)
+    for args, msg in (((81, 4, "strict"), "whole number of chunks"), ((5, 3, "truncate"), "shorter than the first chunk"),
+                      ((80, 3, "truncate"), "4n\\+1"), ((81, 0, "truncate"), "positive integer"), ((81, True, "strict"), "positive integer"),
+                      ((81.0, 3, "strict"), "must be an integer"), ((81, 3, "round"), "frame_policy")):  # fmt: skip
+        with pytest.raises(ValueError, match=msg):
+            resolve_lingbot_frame_count(*args)
+    img = torch.zeros(3, 32, 32)
+    cfg = LingBotWorldFastSessionConfig("p", img, chunk_size=4, frame_num=81).validate("cam")
+    assert cfg.frame_num == 77
+    with pytest.raises(ValueError, match="control mode 'act'"):
+        LingBotWorldFastSessionConfig("p", img, control_mode="act").validate("cam")
+    with pytest.raises(ValueError, match="both or neither"):
+        LingBotWorldFastSessionConfig("p", img, intrinsics=[1, 1, 1, 1], intrinsics_width=10).validate()
+    with pytest.raises(ValueError, match="nothing to apply to"):
+        LingBotWorldFastSessionConfig("p", img, intrinsics_width=10, intrinsics_height=10).validate()
+    with pytest.raises(ValueError, match="positive integer"):
+        LingBotWorldFastSessionConfig("p", img, intrinsics=[1, 1, 1, 1], intrinsics_width=0, intrinsics_height=10).validate()
+
+
+def test_pose_resampling_and_recorded_windows():
+    import numpy as np
+
+    from telefuser_b200.pipelines.lingbot_world import control as C
+
+    def rot_y(a):
+        return np.array([[np.cos(a), 0, np.sin(a)], [0, 1, 0], [-np.sin(a), 0, np.cos(a)]])
+
+    src = np.array([0.0, 4.0, 8.0])
+    rots = np.stack([rot_y(0.0), rot_y(1.0), rot_y(3.0)])  # 0 -> 1 rad -> 3 rad about y
+    trans = np.array([[0.0, 0, 0], [4.0, 0, 0], [4.0, 8, 0]])
+    out = C.interpolate_camera_poses(src, rots, trans, np.arange(-1, 11))
+    assert out.shape == (12, 4, 4) and out.dtype == torch.float32 and (out[:, 3] == torch.tensor([0.0, 0, 0, 1])).all()
+    for frame, angle in ((2, 0.5), (4, 1.0), (6, 2.0), (8, 3.0)):  # constant angular speed inside each segment
+        assert torch.allclose(out[frame + 1, :3, :3], torch.from_numpy(rot_y(angle)).float(), atol=1e-6)
+    assert torch.allclose(out[0, :3, :3], torch.eye(3), atol=1e-6)  # rotation is held outside the key frames ...
+    assert torch.allclose(out[:, :3, 3][0], torch.tensor([-1.0, 0, 0]), atol=1e-6)  # ... translation is extrapolated
+    assert torch.allclose(out[:, :3, 3][11], torch.tensor([4.0, 12, 0]), atol=1e-6)
+    det = torch.linalg.det(out[:, :3, :3].double())
+    assert torch.allclose(det, torch.ones_like(det), atol=1e-6)
+    with pytest.raises(ValueError, match="strictly ascending"):
+        C.interpolate_camera_poses([0, 0, 1], rots, trans, [0])
+
+    poses, ks, act = np.zeros((40, 4, 4)), np.arange(12.0).reshape(3, 4), np.ones((40, 4))
+    p, k, a = C.truncate_control_sequence(poses, ks, act, 29)
+    assert p.shape[0] == 29 and a.shape[0] == 29 and k.tolist() == [0.0, 1.0, 2.0, 3.0]  # the first row is the calibration
+    assert C.truncate_control_sequence(poses, ks[1], None, 29)[1].tolist() == [4.0, 5.0, 6.0, 7.0]
+    for args, msg in (((poses, ks, act, 41), "pose recording has 40"), ((poses, ks, act[:10], 29), "action recording has 10"),
+                      ((poses, np.zeros((0, 4)), None, 29), "intrinsics are"), ((poses, np.zeros(3), None, 29), "intrinsics are"),
+                      ((poses, ks, None, 30), "4n\\+1")):  # fmt: skip
+        with pytest.raises(ValueError, match=msg):
+            C.truncate_control_sequence(*args)
+
+
+def test_recorded_trajectory_drives_a_session_from_files(tmp_path):
+    import numpy as np
+
+    from telefuser_b200.pipelines.lingbot_world.control import random_walk_trajectory
+    from telefuser_b200.pipelines.lingbot_world.session import LingBotWorldFastSessionConfig
+
+    pipe = tiny_pipeline()
+    assert pipe.best_output_size(832, 480, 480 * 832) == (832, 464)  # floating-point floor: the published 480p runs are 832 x 464
+    assert pipe.best_output_size(1000, 1000, 480 * 832) == (624, 624)
+    pipe.config.max_area = 32 * 32
+    img = torch.rand(3, 64, 64) * 2 - 1
+    record = LingBotWorldFastSessionConfig("", img, chunk_size=2, frame_num=33, seed=1)  # 9 latent frames -> 8 -> 29 frames
+    ctx = pipe.control_context(record)
+    assert record.frame_num == 29 and (ctx.height, ctx.width, ctx.latent_frames, ctx.chunk_size) == (32, 32, 8, 2)
+    assert ctx.intrinsics.tolist() == [64.0, 64.0, 32.0, 32.0] and (ctx.orig_width, ctx.orig_height) == (64, 64)
+    given = LingBotWorldFastSessionConfig("", img, chunk_size=2, frame_num=29, intrinsics=[[50.0, 50, 20, 20], [1, 1, 1, 1]])
+    assert pipe.control_context(given).intrinsics.tolist() == [50.0, 50.0, 20.0, 20.0]
+    assert (pipe.control_context(given).orig_width, pipe.control_context(given).orig_height) == (832, 480)  # configured calibration size
+    with pytest.raises(ValueError, match="control mode"):
+        pipe.control_context(LingBotWorldFastSessionConfig("", img, control_mode="act", chunk_size=2, frame_num=29))
+
+    video_rate = random_walk_trajectory(40, seed=3).numpy()
+    np.save(tmp_path / "poses.npy", video_rate)
+    np.save(tmp_path / "intrinsics.npy", np.array([[40.0, 40.0, 32.0, 32.0]] * 40))
+    with pytest.raises(ValueError, match="both or neither"):
+        pipe.prepare_offline_controls(record, tmp_path, tmp_path / "intrinsics.npy", intrinsics_width=64)
+    controls = pipe.prepare_offline_controls(record, tmp_path, tmp_path / "intrinsics.npy", intrinsics_width=64, intrinsics_height=64)
+    assert len(controls) == 4 and all(callable(c) for c in controls)
+    source = controls[0].source
+    assert all(c.source is source for c in controls)
+    assert source.materialize_count == 0  # nothing is converted until a chunk asks
+    first = controls[0]()
+    assert first.shape == (1, 6 * 64, 2, 4, 4) and source.materialize_count == 1 and controls[3]().shape == first.shape
+    assert source.materialize_count == 1
+    emb = torch.randn(1, 8, 32)
+    video, metrics = pipe.generate_video("", img, prompt_emb=emb, controls=controls, session_config=record)
+    assert video.shape == (1, 3, 29, 32, 32) and torch.isfinite(video).all() and metrics["chunks"] == 4
+    # the same trajectory given as latent-rate poses with the same calibration produces the same video
+    rt, ctx2 = pipe.create_session(LingBotWorldFastSessionConfig("", img, chunk_size=2, frame_num=29, seed=1, intrinsics=[40.0, 40, 32, 32],
+                                                                 intrinsics_width=64, intrinsics_height=64), emb)  # fmt: skip
+    pipe.validate_control(rt, first)
+    with pytest.raises(ValueError, match="this session takes"):
+        pipe.validate_control(rt, first[:, :6])
+    direct = rt.control_builder.build_sequence(video_rate[:29], ctx2.intrinsics)
+    assert all(torch.allclose(d, c(), atol=1e-6) for d, c in zip(direct, controls))
+    pipe.denoise_stage.release_cache(rt.cache_handle)
+    with pytest.raises(ValueError, match="controls were given"):
+        pipe.generate_video("", img, prompt_emb=emb, controls=controls[:2], session_config=record)
+    v2, _ = pipe.generate_video("", img, num_frames=33, height=32, width=32, seed=1, prompt_emb=emb, controls=[c() for c in controls],
+                                frame_policy="truncate")  # fmt: skip
+    assert torch.equal(v2, video)
+    with pytest.raises(ValueError, match="whole number of chunks"):
+        pipe.generate_video("", img, num_frames=33, height=32, width=32, prompt_emb=emb)
+    pipe.close()
