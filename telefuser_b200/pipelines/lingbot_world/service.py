@@ -29,9 +29,19 @@ from telefuser_b200.utils.logging import logger
 
 from .control import KEY_MOVES, KEY_TURNS, integrate_keys
 
-DIRECTION_KEYS = {"forward": "w", "backward": "s", "left": "a", "right": "d", "up": "e", "down": "q", "turn_left": "j", "turn_right": "l",
+DIRECTION_KEYS = {"forward": "w", "backward": "s", "left": "a", "right": "d", "rise": "e", "descend": "q", "turn_left": "j", "turn_right": "l",
                   "look_up": "i", "look_down": "k"}  # fmt: skip
 _VALID_KEYS = set(KEY_MOVES) | set(KEY_TURNS)
+# what a browser or a game pad may call a control: DOM `KeyboardEvent.code` / `.key` names, arrows (movement), words
+KEY_ALIASES = {**{k: k for k in _VALID_KEYS}, **{f"key{k}": k for k in _VALID_KEYS}, **DIRECTION_KEYS,
+               "arrowup": "w", "arrowdown": "s", "arrowleft": "a", "arrowright": "d", "up": "w", "down": "s", "left": "a", "right": "d",
+               "pageup": "e", "pagedown": "q", "space": "e"}  # fmt: skip
+MAX_GENERATION_SECONDS = 20.0  # longest session a client may ask for (the rolling KV cache bounds memory, this bounds occupancy)
+
+
+def canonical_key(name) -> str | None:
+    """The movement / turn key a client-side name stands for (`ArrowUp`, `KeyW`, `forward`, `w` -> "w"), else None."""
+    return KEY_ALIASES.get(str(name).strip().lower().replace("_", "")) or KEY_ALIASES.get(str(name).strip().lower())
 
 
 @dataclass
@@ -108,12 +118,12 @@ def load_image(config: dict):
 def keys_from_chunk(chunk: dict) -> set | None:
     """Held-key snapshot carried by a control message, or None when the message is not a snapshot."""
     if "keys" in chunk:
-        keys = {str(k).lower() for k in chunk["keys"]}
+        names = chunk["keys"]
     elif "directions" in chunk:
-        keys = {DIRECTION_KEYS[d] for d in chunk["directions"] if d in DIRECTION_KEYS}
+        names = chunk["directions"]
     else:
         return None
-    return keys & _VALID_KEYS
+    return {k for k in map(canonical_key, names) if k is not None}
 
 
 def overlay_control_hud(frames: np.ndarray, keys) -> np.ndarray:
@@ -132,8 +142,10 @@ def overlay_control_hud(frames: np.ndarray, keys) -> np.ndarray:
 
 
 class LingBotWorldFastService:
-    def __init__(self, pipeline, default_config: LingBotWorldFastSessionConfig | None = None, warmup: bool = False) -> None:
+    def __init__(self, pipeline, default_config: LingBotWorldFastSessionConfig | None = None, warmup: bool = False,
+                 max_generation_seconds: float = MAX_GENERATION_SECONDS) -> None:  # fmt: skip
         self.pipeline, self.default_config, self._warmup = pipeline, default_config or LingBotWorldFastSessionConfig(), warmup
+        self.max_generation_seconds = float(max_generation_seconds)
         self._sessions: dict[str, LingBotWorldFastSessionState] = {}
         self._lock = threading.Lock()
         self._started = False
@@ -168,6 +180,9 @@ class LingBotWorldFastService:
                 raise ValueError(f"{name} must be positive")
         chunk_size = self.pipeline.config.chunk_size
         frames = frame_num_for_duration(cfg.max_duration_seconds, cfg.fps, chunk_size)
+        if (frames - 1) / cfg.fps > self.max_generation_seconds:  # judged on what would be generated, after rounding to chunks
+            raise ValueError(f"a session may generate at most {self.max_generation_seconds:g} s of video; "
+                             f"{cfg.max_duration_seconds:g} s at {cfg.fps} fps was asked for")  # fmt: skip
         image = load_image(config)
         if config.get("fit_image"):  # output size from the reference image's aspect ratio at the pipeline's pixel budget
             w, h = self.pipeline.best_output_size(*self.pipeline._image_size(image), self.pipeline.config.max_area)
@@ -192,9 +207,29 @@ class LingBotWorldFastService:
             self._sessions[sid] = state
         self._enqueue(state, {"type": "status", "stage": "created", "session_id": sid, "frames": frames, "chunks": generation.chunk_count,
                               "chunk_size": chunk_size, "height": cfg.height, "width": cfg.width, "fps": cfg.fps})  # fmt: skip
+        if config.get("preview", False):
+            self._emit_preview(state, image)
         state.worker = threading.Thread(target=self._worker_loop, args=(state,), name=f"lingbot-session-{sid[:8]}", daemon=True)
         state.worker.start()
         return sid
+
+    def _emit_preview(self, state: LingBotWorldFastSessionState, image) -> None:
+        """The reference image at the session's output size (with the idle HUD when enabled), so a client has a picture
+        on screen while the first chunk is still being generated."""
+        h, w = state.config.height, state.config.width
+        if isinstance(image, torch.Tensor):
+            t = image.detach().float().cpu().reshape(1, *image.shape[-3:])
+            if tuple(t.shape[-2:]) != (h, w):
+                t = torch.nn.functional.interpolate(t, size=(h, w), mode="bilinear", antialias=True, align_corners=False)
+            arr = ((t[0].clamp(-1, 1) + 1) * 127.5).round().to(torch.uint8).permute(1, 2, 0).numpy()[None]
+        else:
+            from PIL import Image
+
+            pil = image if isinstance(image, Image.Image) else Image.fromarray(np.asarray(image))
+            arr = np.asarray(pil.convert("RGB").resize((w, h), Image.BICUBIC))[None]
+        if state.config.hud:
+            arr = overlay_control_hud(arr, None)
+        self._enqueue(state, {"type": "preview", "session_id": state.session_id, "chunk_index": -1, "frames": arr, "fps": state.config.fps})
 
     # ---- client -> service ---------------------------------------------------------------------
     def push_chunk(self, session_id: str, chunk: dict) -> None:
@@ -202,10 +237,16 @@ class LingBotWorldFastService:
         control-tensor chunk steers the next chunk directly. Only the newest pending control of each kind is kept
         (an interactive session wants the latest intent, not a backlog). A message that carries `revision` is
         acknowledged with a `control_ack`, and the revision of the control that a chunk finally used is reported with
-        that chunk, so a client can measure both the acknowledgement and the control-to-picture latency."""
+        that chunk, so a client can measure both the acknowledgement and the control-to-picture latency.
+
+        Keys may be named as a browser names them (`ArrowUp`, `KeyW`), by letter or by word (`forward`, `turn_left`).
+        Event form: `{"key" | "control" | "direction": name, "event": "press" | "release"}` edits the held set like
+        `key_down` / `key_up`; `{"type": "reset"}` (or `"event": "reset"`) drops held keys and pending controls,
+        `reset_pose` also returns the camera to the origin. Event and reset messages are answered with a `status`
+        message of stage `control_state` listing the keys now held."""
         state = self._state(session_id)
         kind = chunk.get("type", "control")
-        ack = None
+        ack, report_state = None, False
         with state.lock:
             if kind == "stop":
                 state.stop_event.set()
@@ -214,10 +255,25 @@ class LingBotWorldFastService:
                 if isinstance(chunk.get("revision"), int):
                     state.control_revision_received = max(state.control_revision_received, chunk["revision"])
                     ack = chunk["revision"]
-                if kind == "key_down" and str(chunk.get("key", "")).lower() in _VALID_KEYS:
-                    state.held_keys.add(str(chunk["key"]).lower())
-                elif kind == "key_up":
-                    state.held_keys.discard(str(chunk.get("key", "")).lower())
+                named = canonical_key(chunk.get("key") or chunk.get("control") or chunk.get("direction") or "")
+                event = str(chunk["event"]).lower() if "event" in chunk else None
+                if kind in ("reset", "reset_pose") or event in ("reset", "reset_pose"):
+                    # drop every pending intent; `reset_pose` also puts the camera back at the origin
+                    state.held_keys = set()
+                    state.explicit_chunks.clear()
+                    state.unsampled_snapshot = False
+                    if "reset_pose" in (kind, event):
+                        state.pose = torch.eye(4)
+                    report_state = True
+                elif kind == "key_down" or event == "press":
+                    if named is not None:
+                        state.held_keys.add(named)
+                    report_state = event is not None
+                elif kind == "key_up" or event in ("release", "keyup", "end"):
+                    state.held_keys.discard(named)
+                    report_state = event is not None
+                elif event is not None:
+                    logger.warning(f"LingBot session {session_id}: control event {event!r} is not one of press / release / reset / reset_pose")
                 elif "poses" in chunk or "control_tensor" in chunk:
                     if state.explicit_chunks and not chunk.get("queue", False):
                         state.explicit_overwritten += len(state.explicit_chunks)
@@ -225,8 +281,8 @@ class LingBotWorldFastService:
                     state.explicit_chunks.append(chunk)  # used for the next chunk instead of the key snapshot
                 else:
                     keys = keys_from_chunk(chunk)
-                    if keys is None and chunk.get("direction") in DIRECTION_KEYS:
-                        keys = {DIRECTION_KEYS[chunk["direction"]]}
+                    if keys is None and canonical_key(chunk.get("direction", "")) is not None:
+                        keys = {canonical_key(chunk["direction"])}
                     if keys is not None:
                         if state.unsampled_snapshot:
                             state.controls_superseded += 1
@@ -234,6 +290,9 @@ class LingBotWorldFastService:
         if ack is not None:
             self._enqueue(state, {"type": "control_ack", "session_id": session_id, "revision": ack,
                                   "elapsed_s": time.monotonic() - state.created_mono})  # fmt: skip
+        if report_state:
+            self._enqueue(state, {"type": "status", "stage": "control_state", "session_id": session_id,
+                                  "controls": sorted(state.held_keys), "revision": state.control_revision_received})  # fmt: skip
 
     # ---- measurements ---------------------------------------------------------------------------
     def session_metrics(self, session_id: str) -> dict:

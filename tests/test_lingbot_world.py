@@ -145,6 +145,35 @@ def test_interactive_service_session():
     assert msgs4[0]["height"] == 32 and msgs4[0]["width"] == 48
     assert next(m for m in msgs4 if m["type"] == "frames")["frames"].shape[1:] == (32, 48, 3)
     svc.close_session(sid4)
+    # browser key names, press / release events, resets, the preview picture, the duration cap
+    from telefuser_b200.pipelines.lingbot_world.service import canonical_key
+
+    assert [canonical_key(n) for n in ("ArrowUp", "KeyA", "forward", "turn_left", "L", "PageUp", "F13")] == ["w", "a", "w", "j", "l", "e", None]
+    sid5 = svc.create_session({"image": img, "prompt_emb": emb, "seed": 1, "max_duration_seconds": 20.0, "preview": True, "hud": True})
+    st5 = svc._state(sid5)
+    svc.push_chunk(sid5, {"key": "ArrowUp", "event": "press"})
+    svc.push_chunk(sid5, {"control": "KeyL", "event": "press"})
+    svc.push_chunk(sid5, {"direction": "forward", "event": "release"})
+    assert st5.held_keys == {"l"}
+    svc.push_chunk(sid5, {"keys": ["ArrowLeft", "KeyI", "F13"]})
+    assert st5.held_keys == {"a", "i"}
+    svc.push_chunk(sid5, {"poses": random_walk_trajectory(2, seed=5), "relative": True})
+    svc.push_chunk(sid5, {"key": "w", "event": "hold"})  # unknown event: ignored
+    assert st5.held_keys == {"a", "i"} and len(st5.explicit_chunks) <= 1
+    st5.pose = torch.eye(4) * 2
+    svc.push_chunk(sid5, {"type": "reset"})
+    assert st5.held_keys == set() and not st5.explicit_chunks and st5.pose[0, 0] == 2  # the pose survives a control reset
+    svc.push_chunk(sid5, {"key": "d", "event": "reset_pose"})
+    assert torch.equal(st5.pose, torch.eye(4)) or st5.submitted > 0  # (a chunk bound in between may have moved it again)
+    svc.push_chunk(sid5, {"type": "stop"})
+    msgs5 = svc.drain(sid5, timeout=60.0)
+    prev = [m for m in msgs5 if m["type"] == "preview"]
+    assert len(prev) == 1 and prev[0]["frames"].shape == (1, 32, 32, 3) and prev[0]["frames"].dtype == np.uint8 and prev[0]["chunk_index"] == -1
+    states = [m["controls"] for m in msgs5 if m["type"] == "status" and m.get("stage") == "control_state"]
+    assert states[:3] == [["w"], ["l", "w"], ["l"]] and states[-2:] == [[], []]
+    svc.close_session(sid5)
+    with pytest.raises(ValueError, match="at most 20 s"):
+        svc.create_session({"image": img, "prompt_emb": emb, "max_duration_seconds": 30.0})
     # explicit pose chunks and an early stop
     poses = random_walk_trajectory(2, seed=3)
     sid2 = svc.create_session({"image": img, "prompt_emb": emb, "seed": 1, "max_duration_seconds": 3.0, "hud": False,
