@@ -58,6 +58,9 @@ class LingBotWorldFastPipelineConfig:
     max_area: int = 480 * 832
     orig_height: int = 480
     orig_width: int = 832
+    # > 0: keep the chunk latents of generated worlds (on the host, least recently used first out) so that a session
+    # of the same image / prompt / seed replays matching chunks with one forward pass each instead of denoising them
+    world_cache_bytes: int = 0
 
 
 @dataclass
@@ -75,6 +78,8 @@ class LingBotWorldFastGenerationSession:
     max_attention_size: int
     control_builder: LingBotWorldFastControlBuilder
     created_at: float = field(default_factory=time.monotonic)
+    world: object | None = None  # WorldKVBinding when the session reads / feeds the world cache
+    control_digests: dict = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -102,7 +107,7 @@ class LingBotWorldFastStreamingRuntime:
             "encode": self._actor("encode", pipeline.vae_encode_stage, "encode_condition_chunk", self._encode_inputs,
                                   lambda r, inv: {"condition": r}, self._release("vae_encode_stage")),  # fmt: skip
             "denoise": self._actor("denoise", pipeline.denoise_stage, "denoise_and_update_cache", self._denoise_inputs,
-                                   lambda r, inv: {"latent": r}, self._release("denoise_stage")),  # fmt: skip
+                                   self._denoise_outputs, self._release("denoise_stage")),  # fmt: skip
             "decode": self._actor("decode", pipeline.vae_decode_stage, "decode_chunk", self._decode_inputs,
                                   lambda r, inv: {"frames": r}, self._release("vae_decode_stage")),  # fmt: skip
         }
@@ -150,7 +155,24 @@ class LingBotWorldFastStreamingRuntime:
         if callable(control):
             control = control()
         start = inv.key.sequence_id * rt.chunk_size * rt.frame_tokens
-        return (rt.cache_handle, inv.inputs["condition"], rt.prompt_emb, control, start, rt.max_attention_size), {}
+        kwargs = {}
+        if rt.world is not None:
+            from telefuser_b200.cache.world_kv import tensor_digest
+
+            digest = rt.control_digests[inv.key.sequence_id] = tensor_digest(control)
+            cached = rt.world.lookup(inv.key.sequence_id, digest)
+            if cached is not None:
+                kwargs["cached_latent"] = cached
+        return (rt.cache_handle, inv.inputs["condition"], rt.prompt_emb, control, start, rt.max_attention_size), kwargs
+
+    def _denoise_outputs(self, latent, inv):
+        rt = self._entry(inv.key.session_id)
+        if rt.world is not None:
+            try:
+                rt.world.finalize(inv.key.sequence_id, rt.control_digests.pop(inv.key.sequence_id), latent)
+            except Exception as exc:  # noqa: BLE001 - the cache is best effort; the session goes on
+                logger.warning(f"world cache: chunk {inv.key.sequence_id} was not recorded: {exc}")
+        return {"latent": latent}
 
     def _decode_inputs(self, inv):
         rt = self._entry(inv.key.session_id)
@@ -201,7 +223,12 @@ class LingBotWorldFastStreamingRuntime:
         return {"first_output_latency_s": m.first_output_latency_seconds,
                 "chunk_period_p50_s": m.chunk_period.p50_seconds, "chunk_period_p95_s": m.chunk_period.p95_seconds,
                 "control_to_output_p50_s": m.control_to_output_latency.p50_seconds, "chunks": len(m.output_emitted_at),
-                "stage_busy_s": busy, "stage_idle_s": idle}  # fmt: skip
+                "stage_busy_s": busy, "stage_idle_s": idle, **self._world_metrics(session)}  # fmt: skip
+
+    def _world_metrics(self, session) -> dict:
+        entry = self._sessions.get(session.session_id)
+        world = entry[0].world if entry is not None else None
+        return {} if world is None else {"world_cache_hits": world.hits, "world_cache_misses": world.misses}
 
     def close_session(self, session, cancel: bool = False) -> None:
         try:
@@ -253,11 +280,18 @@ class LingBotWorldFastPipeline(BasePipeline):
 
             self.text_encoding_stage = TextEncodingStage("text_encoding", module_manager, config.text_encoding_config,
                                                          config.max_sequence_length)  # fmt: skip
+        self.world_store = None
+        if config.world_cache_bytes > 0:
+            from telefuser_b200.cache.world_kv import WorldKVStore
+
+            self.world_store = WorldKVStore(config.world_cache_bytes)
         self.runtime = LingBotWorldFastStreamingRuntime(self)
 
     # ---- sessions -------------------------------------------------------------------------
     def _create_initialized_session(self, prompt, image, num_frames: int, height: int, width: int, seed: int = 0,
-                                    prompt_emb: torch.Tensor | None = None) -> LingBotWorldFastGenerationSession:  # fmt: skip
+                                    prompt_emb: torch.Tensor | None = None, world_cache: bool | str = True) -> LingBotWorldFastGenerationSession:  # fmt: skip
+        """`world_cache`: True reads and feeds the pipeline's world store (when it has one), "read" / "write" only one
+        side, False neither."""
         cfg = self.config
         if (num_frames - 1) % 4:
             raise ValueError(f"num_frames must be 4n+1, got {num_frames}")
@@ -288,11 +322,18 @@ class LingBotWorldFastPipeline(BasePipeline):
             control_type=self.dit_meta["control_type"], device=self.device, control_dtype=self.torch_dtype,
             orig_height=height, orig_width=width, height=height, width=width, latent_h=latent_h, latent_w=latent_w,
             latent_frames=latent_frames, chunk_size=cfg.chunk_size, intrinsics=pinhole_intrinsics(height, width))  # fmt: skip
+        world = None
+        if self.world_store is not None and world_cache:
+            from telefuser_b200.cache.world_kv import WorldKVBinding, world_key
+
+            key = world_key(cond, prompt_emb, seed, height=height, width=width, chunk=cfg.chunk_size, window=cfg.local_attn_size,
+                            sink=cfg.sink_size, steps=tuple(cfg.timestep_indices), shift=cfg.sample_shift, dtype=str(self.torch_dtype))  # fmt: skip
+            world = WorldKVBinding(self.world_store, key, read=world_cache in (True, "read"), write=world_cache in (True, "write"))
         return LingBotWorldFastGenerationSession(
             cache_handle=handle, prompt_emb=prompt_emb, chunk_count=latent_frames // cfg.chunk_size,
             chunk_size=cfg.chunk_size, height=height, width=width, latent_h=latent_h, latent_w=latent_w,
             frame_tokens=frame_tokens, kv_size=kv_size, max_attention_size=kv_size,
-            control_builder=LingBotWorldFastControlBuilder(ctx))  # fmt: skip
+            control_builder=LingBotWorldFastControlBuilder(ctx), world=world)  # fmt: skip
 
     def release_session(self, session: LingBotWorldFastStreamingSession, cancel: bool = False) -> None:
         self.runtime.close_session(session, cancel)
@@ -390,11 +431,15 @@ class LingBotWorldFastPipeline(BasePipeline):
     def generate_video(self, prompt, image, num_frames: int = 61, height: int = 480, width: int = 832, seed: int = 0,
                        poses: torch.Tensor | None = None, prompt_emb=None, on_chunk: Callable | None = None,
                        timeout_s: float = 3600.0, bind_controls_late: bool = False, controls: list | None = None,
-                       frame_policy: str = "strict", session_config: LingBotWorldFastSessionConfig | None = None):  # fmt: skip
+                       frame_policy: str = "strict", session_config: LingBotWorldFastSessionConfig | None = None,
+                       world_cache: bool | str = True):  # fmt: skip
         """Returns (frames [1, 3, T, H, W], metrics). `poses`: [latent_frames, 4, 4] camera path (default: seeded walk).
         `controls`: one ready control tensor or provider per chunk instead of `poses` (what `prepare_offline_controls`
         returns). `frame_policy="truncate"` rounds `num_frames` down to a whole number of chunks. `session_config`: a
-        session record in place of the individual arguments (its image fixes the output size).
+        session record in place of the individual arguments (its image fixes the output size). `world_cache`: whether the
+        session reads / feeds the pipeline's world store (`LingBotWorldFastPipelineConfig.world_cache_bytes`): chunks whose
+        controls match an earlier session of the same image, prompt and seed are replayed with one forward pass each;
+        `metrics["world_cache_hits"]` counts them.
         `bind_controls_late`: hand each chunk's control to the denoiser as a provider that is read when the chunk is
         admitted (what the interactive service does); `metrics["control_bound_to_output_p50_s"]` is then the time
         from that moment to the chunk's frames."""
@@ -403,7 +448,7 @@ class LingBotWorldFastPipeline(BasePipeline):
             seed = session_config.seed
         else:
             num_frames, _ = resolve_lingbot_frame_count(num_frames, self.config.chunk_size, frame_policy)
-            rt = self._create_initialized_session(prompt, image, num_frames, height, width, seed, prompt_emb)
+            rt = self._create_initialized_session(prompt, image, num_frames, height, width, seed, prompt_emb, world_cache)
         latent_frames = rt.chunk_count * rt.chunk_size
         if controls is None:
             if poses is None:

@@ -188,7 +188,8 @@ class LingBotWorldFastService:
             w, h = self.pipeline.best_output_size(*self.pipeline._image_size(image), self.pipeline.config.max_area)
             cfg.height, cfg.width = self.pipeline.check_resize_height_width(h, w)
         generation = self.pipeline._create_initialized_session(cfg.prompt, image, frames, cfg.height, cfg.width, cfg.seed,
-                                                               prompt_emb=config.get("prompt_emb"))  # fmt: skip
+                                                               prompt_emb=config.get("prompt_emb"),
+                                                               world_cache=config.get("world_cache", True))  # fmt: skip
         if config.get("intrinsics") is not None:  # the client's calibration (fx, fy, cx, cy) and the image size it refers to
             import dataclasses
 

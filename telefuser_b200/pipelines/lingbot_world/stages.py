@@ -165,12 +165,22 @@ class LingBotWorldFastDenoisingStage(BaseStage):
     @with_model_offload(["dit"])
     @torch.no_grad()
     def denoise_and_update_cache(self, cache_handle: int, condition_chunk, prompt_emb, control_chunk, current_start: int,
-                                 max_attention_size: int):  # fmt: skip
+                                 max_attention_size: int, cached_latent=None):  # fmt: skip
+        """One chunk: denoise from fresh noise, then the commit pass. With `cached_latent` (the clean latent this very
+        chunk had in an earlier session of the same world) the denoising steps are skipped: both random generators
+        are advanced by what those steps would have drawn and only the commit pass runs, so the rolling cache and the
+        generators end up exactly where a full run leaves them."""
         st = self._state(cache_handle)
         cond = condition_chunk.to(self.device, self.torch_dtype)
         ctrl = None if control_chunk is None else control_chunk.to(self.device, self.torch_dtype)
         emb = prompt_emb.to(self.device, self.torch_dtype)
-        clean = self.denoise_chunk(self._next_noise(st), cond, emb, st, ctrl, current_start, max_attention_size)
+        if cached_latent is None:
+            clean = self.denoise_chunk(self._next_noise(st), cond, emb, st, ctrl, current_start, max_attention_size)
+        else:
+            self._next_noise(st)
+            for _ in range(len(st.timesteps) - 1):  # the re-noising draws between denoising steps
+                torch.randn(st.noise_shape, generator=st.generator, device=self.device, dtype=self.torch_dtype)
+            clean = cached_latent.to(self.device, self.torch_dtype)
         # commit pass: K/V of the clean latent become the history that later chunks attend to
         self.dit(clean.to(self.torch_dtype), torch.zeros(1, device=self.device), emb, y=cond, control_tensor=ctrl,
                  cache=st.model_cache, current_start=current_start, max_attention_size=max_attention_size)  # fmt: skip

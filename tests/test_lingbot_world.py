@@ -370,3 +370,64 @@ def test_recorded_trajectory_drives_a_session_from_files(tmp_path):
     with pytest.raises(ValueError, match="whole number of chunks"):
         pipe.generate_video("", img, num_frames=33, height=32, width=32, prompt_emb=emb)
     pipe.close()
+
+
+def test_world_cache_replays_matching_chunks_and_diverges_exactly():
+    from telefuser_b200.cache.world_kv import WorldKVBinding, WorldKVStore, tensor_digest, world_key
+
+    # the store on its own: one control sequence per world, truncation on divergence, LRU by bytes
+    store = WorldKVStore(max_bytes=3 * 4 * 16)
+    lat = [torch.full((4, 4), float(i)) for i in range(4)]
+    a = WorldKVBinding(store, "world-a")
+    assert a.lookup(0, "c0") is None and a.misses == 1  # empty store; from now on this session only records
+    for i in range(3):
+        a.finalize(i, f"c{i}", lat[i])
+    b = WorldKVBinding(store, "world-a")
+    assert torch.equal(b.lookup(0, "c0"), lat[0]) and torch.equal(b.lookup(1, "c1"), lat[1]) and b.lookup(2, "other") is None
+    assert b.lookup(2, "c2") is None and (b.hits, b.misses) == (2, 2)  # after a divergence nothing matches any more
+    b.finalize(2, "other", lat[3])
+    assert store.get("world-a").control_digests == ["c0", "c1", "other"] and torch.equal(store.get("world-a").latents[2], lat[3])
+    store.record_chunk("world-a", 5, "gap", lat[0])  # not contiguous: ignored
+    assert len(store.get("world-a")) == 3
+    store.record_chunk("world-b", 0, "x", lat[0])  # over budget: the older world goes
+    assert store.get("world-a") is None and store.stats()["worlds"] == 1 and store.stats()["evictions"] == 1
+    assert tensor_digest(torch.zeros(3)) != tensor_digest(torch.zeros(3, 1)) and tensor_digest(torch.zeros(2)) != tensor_digest(torch.zeros(2).half())
+    assert world_key(lat[0], lat[1], 1, h=2) == world_key(lat[0].clone(), lat[1], 1, h=2) != world_key(lat[0], lat[1], 2, h=2)
+
+    # through the pipeline
+    def run(pipe, controls, **kw):
+        calls = {"n": 0}
+        hook = pipe.denoise_stage.dit.register_forward_pre_hook(lambda *_: calls.__setitem__("n", calls["n"] + 1))
+        video, metrics = pipe.generate_video("", img, num_frames=29, height=32, width=32, seed=1, prompt_emb=emb, controls=controls, **kw)
+        hook.remove()
+        return video, metrics, calls["n"]
+
+    emb, img = torch.randn(1, 8, 32), torch.rand(3, 32, 32) * 2 - 1
+    plain = tiny_pipeline()
+    rt = plain._create_initialized_session("", img, 29, 32, 32, 1, emb)
+    walk, other = (rt.control_builder.build_sequence(random_walk_trajectory(8, seed=s), rt.control_builder.context.intrinsics) for s in (1, 2))
+    for stage in (plain.denoise_stage, plain.vae_encode_stage, plain.vae_decode_stage):
+        stage.release_cache(rt.cache_handle)
+    mixed = walk[:2] + other[2:]  # the same first two chunks, then another way
+    cold_walk, m0, n0 = run(plain, walk)
+    cold_mixed, _, _ = run(plain, mixed)
+    assert n0 == 4 * 3 and "world_cache_hits" not in m0  # two denoising steps + the commit pass per chunk
+    plain.close()
+
+    pipe = tiny_pipeline()
+    pipe.world_store = WorldKVStore(1 << 20)
+    first, m1, n1 = run(pipe, walk)
+    assert torch.equal(first, cold_walk) and (m1["world_cache_hits"], m1["world_cache_misses"], n1) == (0, 4, 12)
+    again, m2, n2 = run(pipe, walk)
+    assert torch.equal(again, cold_walk) and (m2["world_cache_hits"], n2) == (4, 4)  # one forward (the commit) per chunk
+    forked, m3, n3 = run(pipe, mixed)
+    assert (m3["world_cache_hits"], m3["world_cache_misses"], n3) == (2, 2, 2 * 1 + 2 * 3)
+    assert torch.equal(forked, cold_mixed)  # the replayed prefix left cache and generators exactly as a cold run does
+    _, m4, _ = run(pipe, mixed)
+    assert m4["world_cache_hits"] == 4  # the record now follows the newer path ...
+    _, m5, _ = run(pipe, walk)
+    assert m5["world_cache_hits"] == 2  # ... so the older one matches only up to the fork
+    other_seed, m7 = pipe.generate_video("", img, num_frames=29, height=32, width=32, seed=2, prompt_emb=emb, controls=walk)
+    assert m7["world_cache_hits"] == 0 and not torch.equal(other_seed, cold_walk)
+    assert pipe.world_store.stats()["worlds"] == 2
+    pipe.close()
