@@ -26,8 +26,7 @@ from telefuser_b200.parallel import mesh as pmesh
 from telefuser_b200.parallel import shard as pshard
 from telefuser_b200.schedulers.flow_match import FlowMatchScheduler
 
-DEFAULT_NEGATIVE_PROMPT = ("low quality, blurry, distorted, static frame, over-saturated, jpeg artefacts, watermark, text, "
-                           "extra limbs, deformed, flicker")  # fmt: skip
+from .data import DEFAULT_NEGATIVE_PROMPT, default_negative_caption  # noqa: F401 (re-exported)
 
 
 @dataclass
@@ -103,21 +102,26 @@ def transformer_timestep(timestep: torch.Tensor, dtype: torch.dtype) -> torch.Te
 
 def compute_refiner_sigmas(sigma_max: float, sigma_min: float, num_inference_steps: int, shift: float,
                            t_thresh: float | None, tail_steps: int = 0):  # fmt: skip
+    """Descending sigmas of the low-noise refiner pass: the shifted `num_inference_steps`-step schedule restricted to
+    sigma <= `t_thresh` (with `t_thresh` itself put in front when the schedule does not hit it), followed by `tail_steps`
+    extra, evenly spaced sigmas between the last one and `sigma_min`. None when no threshold is given (full schedule)."""
     if t_thresh is None:
         return None
-    if not 0 < t_thresh <= 1 or num_inference_steps < 1 or tail_steps < 0:
-        raise ValueError("invalid refiner sigma configuration")
-    base = np.linspace(sigma_max, sigma_min, num_inference_steps + 1)[:-1]
-    shifted = shift * base / (1.0 + (shift - 1.0) * base)
-    sig = shifted[shifted <= t_thresh + 1e-6]
-    if not len(sig) or abs(float(sig[0]) - t_thresh) > 1e-6:
-        sig = np.concatenate([[t_thresh], sig])
+    if not (0 < t_thresh <= 1 and num_inference_steps >= 1 and tail_steps >= 0):
+        raise ValueError(f"refiner schedule: t_thresh in (0, 1], steps >= 1, tail_steps >= 0; got {t_thresh}, "
+                         f"{num_inference_steps}, {tail_steps}")  # fmt: skip
+    grid = np.linspace(sigma_max, sigma_min, num_inference_steps + 1)[:-1]
+    grid = shift * grid / (1.0 + (shift - 1.0) * grid)
+    kept = grid[grid <= t_thresh + 1e-6]
+    if kept.size == 0 or abs(float(kept[0]) - t_thresh) > 1e-6:
+        kept = np.concatenate([[t_thresh], kept])
     if tail_steps:
-        tail = np.linspace(float(sig[-1]), min(sigma_min, float(sig[-1])), tail_steps + 2)[1:-1]
-        sig = np.concatenate([sig, tail])
-    if np.any(~np.isfinite(sig)) or np.any(sig < 0) or np.any(sig > 1) or np.any(np.diff(sig) >= 0):
-        raise ValueError("refiner sigma schedule must be finite, descending and within [0, 1]")
-    return sig.astype(np.float32)
+        last = float(kept[-1])
+        kept = np.concatenate([kept, np.linspace(last, min(sigma_min, last), tail_steps + 2)[1:-1]])
+    ok = np.all(np.isfinite(kept)) and kept.min() >= 0 and kept.max() <= 1 and np.all(np.diff(kept) < 0)
+    if not ok:
+        raise ValueError(f"refiner schedule is not a finite, strictly descending sequence in [0, 1]: {kept.tolist()}")
+    return kept.astype(np.float32)
 
 
 def prepare_refiner_latent(x_up, noise, t_thresh):
@@ -297,13 +301,15 @@ class LingBotVideoPipeline(BasePipeline):
                  negative_prompt_embeds=None, prompt_mask=None, negative_prompt_mask=None, decode: bool = True):  # fmt: skip
         cfg = self.config
         frames, lh, lw = latent_shape(request.num_frames, request.height, request.width)
+        if request.image is not None and request.num_frames == 1:
+            raise ValueError("image conditioning continues a video from its first frame; a one-frame request has nothing to generate")
         pos, pos_mask = (prompt_embeds, prompt_mask) if prompt_embeds is not None else self._encode_text(request.caption)
         neg = neg_mask = None
         if cfg.guidance_scale > 1.0:
             if negative_prompt_embeds is not None:
                 neg, neg_mask = negative_prompt_embeds, negative_prompt_mask
             else:
-                neg, neg_mask = self._encode_text(negative_caption or DEFAULT_NEGATIVE_PROMPT)
+                neg, neg_mask = self._encode_text(negative_caption or default_negative_caption(request.num_frames))
         condition = mask = None
         if request.image is not None:
             if self.vae_stage is None:

@@ -149,3 +149,74 @@ def test_example_imports_and_exposes_the_service_entry_points(path):
                 target = importlib.import_module(node.module)
                 for alias in node.names:
                     assert hasattr(target, alias.name), f"{node.module} has no {alias.name}"
+
+
+def test_lingbot_video_example_request_handling(tmp_path, monkeypatch):
+    """The LingBot-Video pipeline files on a tiny random-init model: a rewriter prompt file sets caption and length, a
+    one-frame request is saved as a PNG, an image request conditions frame 0, `refine` goes through the refiner stage."""
+    import importlib.util
+    import json
+
+    import numpy as np
+    from PIL import Image
+
+    from telefuser_b200.core.config import ModelRuntimeConfig
+    from telefuser_b200.core.module_manager import ModuleManager
+    from telefuser_b200.models.wan_vae import WanVideoVAE
+    from telefuser_b200.pipelines.lingbot_video import LingBotVideoPipeline, LingBotVideoPipelineConfig
+    from telefuser_b200.pipelines.lingbot_video.refiner import LingBotVideoRefinerStage
+    from telefuser_b200.testing.lingbot_video_checks import make_model
+    from telefuser_b200.testing.synthetic import random_init_
+
+    def load(name):
+        spec = importlib.util.spec_from_file_location(f"_example_{name}", EXAMPLES / "lingbot_video" / f"{name}.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    moe, dense = load("lingbot_video_moe_text_to_video"), load("lingbot_video_dense_text_to_video")
+    assert moe.PPL_CONFIG["supports_refiner"] and not dense.PPL_CONFIG["supports_refiner"]
+    m = make_model("tiny")
+    captions = []
+
+    def text_stage(caption):
+        captions.append(caption)
+        return torch.randn(1, 5, m.config.text_dim, generator=torch.Generator().manual_seed(len(caption)))
+
+    mm = ModuleManager(torch_dtype=torch.float32, device="cpu")
+    mm.add_module(m, "lingbot_video_transformer")
+    mm.add_module(random_init_(WanVideoVAE(dim=8).float(), std=0.05).eval(), "wan_video_vae")
+    rc = lambda: ModelRuntimeConfig(device_type="cpu", torch_dtype=torch.float32)  # noqa: E731
+    pipe = LingBotVideoPipeline(device="cpu", torch_dtype=torch.float32)
+    pipe.init(mm, LingBotVideoPipelineConfig(text_encoding_config=rc(), dit_config=rc(), vae_config=rc(), num_inference_steps=1), text_stage=text_stage)
+    monkeypatch.setitem(moe.PPL_CONFIG, "refiner_height", 32)
+    monkeypatch.setitem(moe.PPL_CONFIG, "refiner_width", 48)
+    monkeypatch.setitem(moe.PPL_CONFIG, "refiner_steps", 2)
+
+    prompt_file = tmp_path / "rewritten.json"
+    prompt_file.write_text(json.dumps({"caption": {"subject": "a fox"}, "duration": 0.3, "fps": 24}))
+    out = moe.run_with_file(pipe, str(prompt_file), str(tmp_path / "a.mp4"), height=16, width=32)
+    assert out["num_frames"] == 9 and os.path.getsize(out["output_path"]) > 0 and captions[0] == '{"subject":"a fox"}'
+
+    still = dense.run_with_file(pipe, "a fox", str(tmp_path / "b.mp4"), num_frames=1, height=16, width=32)
+    assert still["output_path"].endswith("b.png") and Image.open(still["output_path"]).size == (32, 16)
+    assert json.loads(captions[-1])["universal_negative"] and "temporal_and_motion_stability" not in captions[-1]  # still-image negative
+
+    Image.fromarray(np.random.default_rng(0).integers(0, 255, (40, 50, 3), dtype=np.uint8)).save(tmp_path / "first.png")
+    built = []
+
+    def fake_refiner(pipeline):
+        built.append(1)
+        return LingBotVideoRefinerStage(pipeline.denoising_stage, pipeline.vae_stage, device="cpu", torch_dtype=torch.float32)
+
+    monkeypatch.setattr(moe, "build_refiner", fake_refiner)
+    ref = moe.run_with_file(pipe, "a fox", str(tmp_path / "c.mp4"), num_frames=5, height=16, width=32, image_path=str(tmp_path / "first.png"),
+                            negative_prompt="bad", refine=True)  # fmt: skip
+    assert ref["refined"] and built == [1] and captions[-1] == "bad"
+    import cv2
+
+    cap = cv2.VideoCapture(ref["output_path"])
+    assert (int(cap.get(cv2.CAP_PROP_FRAME_WIDTH)), int(cap.get(cv2.CAP_PROP_FRAME_HEIGHT))) == (48, 32)  # the refiner's size
+    cap.release()
+    with pytest.raises(FileNotFoundError, match="separate download"):
+        load("lingbot_video_moe_text_to_video").build_refiner(pipe)

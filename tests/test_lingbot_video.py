@@ -223,3 +223,158 @@ def test_expert_parallel_over_peer_memory_matches_single_gpu():
         got = spawn(2, "tiny-moe", mode, backend="nccl", dtype=torch.bfloat16, overrides=over, **kw)
         err = ((got - ref).norm() / ref.norm()).item()
         assert err < 2e-2, (mode, err)
+
+
+def test_request_side_contracts(tmp_path):
+    import hashlib
+    import json
+
+    from telefuser_b200.pipelines.lingbot_video import data as D
+
+    # the guidance-branch captions are strings the text encoder was trained with: pinned by content hash
+    assert hashlib.sha256(D.DEFAULT_NEGATIVE_PROMPT.encode()).hexdigest()[:16] == "43704d85b3951aed"
+    assert hashlib.sha256(D.DEFAULT_NEGATIVE_PROMPT_IMAGE.encode()).hexdigest()[:16] == "7e277788a8bb3d2f"
+    video, image = (json.loads(D.default_negative_caption(n))["universal_negative"] for n in (81, 1))
+    assert "temporal_and_motion_stability" in video and "temporal_and_motion_stability" not in image
+    assert "subtitles" in video["composition_and_content"] and "subtitles" not in image["composition_and_content"]
+    assert list(video) == ["visual_quality", "artistic_style", "composition_and_content", "temporal_and_motion_stability", "material_and_structure"]
+
+    assert [D.num_frames_from_duration(d) for d in (0, 0.1, 1, 3.3, 5)] == [1, 5, 25, 81, 121] and D.num_frames_from_duration(2, 16) == 33
+    for bad in ((-1, 24), (1, 0)):
+        with pytest.raises(ValueError):
+            D.num_frames_from_duration(*bad)
+    assert D.validate_frame_count(1) == 1 and D.validate_frame_count(81) == 81
+    with pytest.raises(ValueError, match="4n\\+1"):
+        D.validate_frame_count(80)
+
+    sample = {"subject": "a fox", "scene": {"time": "dawn"}, "duration": 5, "fps": 24, "resolution": "480p"}
+    assert D.parse_lingbot_video_prompt(sample) == ('{"subject":"a fox","scene":{"time":"dawn"}}', 5.0)  # run-time fields stay out
+    assert D.parse_lingbot_video_prompt([{"caption": "plain text"}]) == ("plain text", None)
+    assert D.parse_lingbot_video_prompt({"caption": {"主体": "狐狸"}, "duration": "2.5"}) == ('{"主体":"狐狸"}', 2.5)
+    for bad, msg in (([], "empty list"), ("text", "is a dict"), ({"caption": ""}, "empty caption")):
+        with pytest.raises(ValueError, match=msg):
+            D.parse_lingbot_video_prompt(bad)
+    (tmp_path / "p.json").write_text(json.dumps([sample]), encoding="utf-8")
+    assert D.load_lingbot_video_prompt(tmp_path / "p.json")[1] == 5.0
+
+    cfg = {"depth": 48, "hidden_size": 2048, "num_attention_heads": 16, "in_channels": 16, "patch_size": [1, 2, 2], "text_dim": 2560,
+           "intermediate_size": 768, "num_experts": 128, "num_experts_per_tok": 8}  # fmt: skip
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    moe = D.load_lingbot_video_model_config(tmp_path, variant="moe")
+    assert (moe.num_layers, moe.num_heads, moe.patch_size, moe.num_experts, moe.top_k) == (48, 16, (1, 2, 2), 128, 8)
+    dense = {k: v for k, v in cfg.items() if not k.startswith("num_experts")}
+    (tmp_path / "dense.json").write_text(json.dumps(dense))
+    assert D.load_lingbot_video_model_config(tmp_path / "dense.json").top_k == 0
+    with pytest.raises(ValueError, match="needs num_experts"):
+        D.load_lingbot_video_model_config(tmp_path / "dense.json", variant="refiner")
+    (tmp_path / "short.json").write_text(json.dumps({"depth": 2}))
+    with pytest.raises(ValueError, match="lacks"):
+        D.load_lingbot_video_model_config(tmp_path / "short.json")
+    with pytest.raises(ValueError, match="not 'turbo'"):
+        D.LingBotVideoModelConfig(variant="turbo")
+
+    assert D.smart_resize(1080, 1920, factor=32) == (1088, 1920) and D.smart_resize(20, 20, factor=32) == (64, 64)
+    big = D.smart_resize(6000, 9000, factor=32)
+    assert big[0] % 32 == 0 and big[1] % 32 == 0 and big[0] * big[1] <= 16384 * 28**2 and abs(big[0] / big[1] - 2 / 3) < 0.01
+    with pytest.raises(ValueError, match="thinner"):
+        D.smart_resize(10, 4000, factor=32)
+
+    img = torch.arange(3 * 40 * 60, dtype=torch.float32).reshape(1, 3, 40, 60) % 256
+    frame = D.preprocess_ti2v_image(img, 32, 32)
+    assert frame.shape == (1, 3, 1, 32, 32) and 0 <= frame.min() and frame.max() <= 1
+    assert torch.equal(frame * 255, (frame * 255).round())  # uint8 interpolation: only whole grey levels come out
+    same = D.preprocess_ti2v_image(img, 40, 60)
+    assert torch.equal(same[:, :, 0] * 255, img)  # no resize needed: the frame is the image
+    with pytest.raises(ValueError, match="condition image"):
+        D.preprocess_ti2v_image(img[0], 32, 32)
+
+
+def test_default_negative_follows_the_request_mode():
+    from telefuser_b200.core.config import ModelRuntimeConfig
+    from telefuser_b200.core.module_manager import ModuleManager
+    from telefuser_b200.pipelines.lingbot_video import LingBotVideoPipeline, LingBotVideoPipelineConfig, LingBotVideoRequest
+    from telefuser_b200.pipelines.lingbot_video import data as D
+
+    m = make_model("tiny")
+    seen = []
+
+    def text_stage(caption):
+        seen.append(caption)
+        g = torch.Generator().manual_seed(len(caption))
+        return torch.randn(1, 5, m.config.text_dim, generator=g)
+
+    mm = ModuleManager(torch_dtype=torch.float32, device="cpu")
+    mm.add_module(m, "lingbot_video_transformer")
+    rc = lambda: ModelRuntimeConfig(device_type="cpu", torch_dtype=torch.float32)  # noqa: E731
+    pipe = LingBotVideoPipeline(device="cpu", torch_dtype=torch.float32)
+    pipe.init(mm, LingBotVideoPipelineConfig(text_encoding_config=rc(), dit_config=rc(), vae_config=rc(), num_inference_steps=1), text_stage=text_stage)
+    pipe.generate(LingBotVideoRequest("a fox", num_frames=5, height=32, width=32), decode=False)
+    pipe.generate(LingBotVideoRequest("a fox", num_frames=1, height=32, width=32), decode=False)
+    pipe.generate(LingBotVideoRequest("a fox", num_frames=1, height=32, width=32), negative_caption="mine", decode=False)
+    assert seen == ["a fox", D.DEFAULT_NEGATIVE_PROMPT, "a fox", D.DEFAULT_NEGATIVE_PROMPT_IMAGE, "a fox", "mine"]
+    with pytest.raises(ValueError, match="one-frame request"):
+        pipe.generate(LingBotVideoRequest("a fox", num_frames=1, height=32, width=32, image=torch.zeros(1, 3, 32, 32)), decode=False)
+
+
+def test_refiner_hand_off_from_video_to_video(tmp_path):
+    import numpy as np
+    from PIL import Image
+
+    from telefuser_b200.core.config import ModelRuntimeConfig
+    from telefuser_b200.core.module_manager import ModuleManager
+    from telefuser_b200.models.wan_vae import WanVideoVAE
+    from telefuser_b200.pipelines.lingbot_video import LingBotVideoPipeline, LingBotVideoPipelineConfig
+    from telefuser_b200.pipelines.lingbot_video import refiner as R
+    from telefuser_b200.testing.synthetic import random_init_
+
+    # frame budget: clips faster than the training rate are thinned, counts are cut to 4n+1, short clips repeat their end
+    assert R.compute_training_frame_budget(81, 16) == (81, 16.0, 21)
+    frames, fps, latents = R.compute_training_frame_budget(121, 30)
+    assert (frames, latents) == (93, 24) and abs(fps - 93 / 121 * 30) < 1e-9
+    assert R.compute_training_frame_budget(0, 24) == (1, 0.0, 1)
+    with pytest.raises(ValueError, match="positive"):
+        R.compute_training_frame_budget(10, 0)
+    assert R.compute_training_aligned_indices(9, 5).tolist() == [0, 2, 4, 6, 8] and R.compute_training_aligned_indices(3, 5).tolist() == [0, 1, 2, 2, 2]
+    assert R.compute_training_aligned_indices(0, 2).tolist() == [0, 0] and R.compute_training_aligned_indices(4, 0).numel() == 0
+    clip = torch.linspace(-1, 1, 30).view(1, 1, 30, 1, 1).expand(1, 3, 30, 8, 12).contiguous()
+    up, facts = R.prepare_refiner_video(clip, 30.0, 16, 24, max_frames=13)
+    assert up.shape == (1, 3, 13, 16, 24) and facts["truncated_by_max_frames"] and facts["sample_frame_uncapped"] == 21 and facts["t_vae"] == 4
+    assert torch.allclose(up[0, 0, :, 0, 0], clip[0, 0, np.linspace(0, 29, 13, dtype=int), 0, 0], atol=1e-6)  # constant frames survive the resize
+    same, f2 = R.prepare_refiner_video(clip[:, :, :9], 16.0, 8, 12)
+    assert torch.equal(same, clip[:, :, :9]) and not f2["truncated_by_max_frames"]
+    with pytest.raises(ValueError, match=r"\[B, 3, F, H, W\]"):
+        R.prepare_refiner_video(clip[0], 16.0, 8, 12)
+    assert R.refiner_size(480, 832) == (1088, 1872)
+
+    # a wide image is cropped to the LOW-resolution run's aspect ratio before it is resized
+    arr = np.zeros((40, 120, 3), dtype=np.uint8)
+    arr[:, 40:80] = 255  # white centre third
+    Image.fromarray(arr).save(tmp_path / "first.png")
+    first = R.first_frame_for_refiner(tmp_path / "first.png", 32, 32, geometry_height=16, geometry_width=16)
+    assert first.shape == (1, 3, 1, 32, 32) and first.min() >= -1 and first.max() <= 1 and first.mean() > 0.95  # only the centre is left
+
+    mm = ModuleManager(torch_dtype=torch.float32, device="cpu")
+    mm.add_module(make_model("tiny-moe"), "lingbot_video_moe_transformer")
+    mm.add_module(random_init_(WanVideoVAE(dim=8).float(), std=0.05).eval(), "wan_video_vae")
+    rc = lambda: ModelRuntimeConfig(device_type="cpu", torch_dtype=torch.float32)  # noqa: E731
+    pipe = LingBotVideoPipeline(device="cpu", torch_dtype=torch.float32)
+    pipe.init(mm, LingBotVideoPipelineConfig(text_encoding_config=rc(), dit_config=rc(), vae_config=rc(), num_inference_steps=2))
+    stage = R.LingBotVideoRefinerStage(pipe.denoising_stage, pipe.vae_stage, device="cpu", torch_dtype=torch.float32)
+    pos, neg = torch.randn(1, 6, 32), torch.randn(1, 4, 32)
+    low = torch.rand(1, 3, 9, 16, 16) * 2 - 1
+    video, _ = R.prepare_refiner_video(low, 16.0, 32, 32)
+    called = []
+    out = stage.refine(video, pos, neg, num_inference_steps=4, t_thresh=0.5, tail_steps=1, seed=3, before_decode=lambda: called.append(1))
+    assert out.shape == (1, 3, 9, 32, 32) and torch.isfinite(out).all() and called == [1]
+    assert torch.equal(out, stage.refine(video, pos, neg, num_inference_steps=4, t_thresh=0.5, tail_steps=1, seed=3))
+    lat = stage.refine(video, pos, neg, num_inference_steps=4, t_thresh=0.5, tail_steps=1, seed=3, decode=False)
+    # the stage is the pipeline's latent-level `refine` with the VAE around it
+    enc = pipe.vae_stage.process("encode_video", video).float()
+    assert torch.allclose(lat, pipe.refine(enc, pos, neg, t_thresh=0.5, num_inference_steps=4, tail_steps=1, seed=3), atol=1e-5)
+    # image-conditioned: frame 0 of the result is the clean first frame's latent
+    clean = torch.rand(1, 3, 32, 32) * 2 - 1
+    lat_c = stage.refine(video, pos, neg, num_inference_steps=4, t_thresh=0.5, seed=3, clean_first_frame=clean, decode=False)
+    want0 = pipe.vae_stage.process("encode_video", clean.unsqueeze(2)).float()[:, :, :1]
+    assert torch.allclose(lat_c[:, :, :1], want0, atol=1e-6) and not torch.allclose(lat_c[:, :, 1:], lat[:, :, 1:])
+    with pytest.raises(ValueError, match="injected noise"):
+        stage.refine(video, pos, neg, noise=torch.zeros(1, 16, 1, 4, 4))
