@@ -121,6 +121,13 @@ def keys_from_chunk(chunk: dict) -> set | None:
         names = chunk["keys"]
     elif "directions" in chunk:
         names = chunk["directions"]
+    elif isinstance(chunk.get("controls"), (list, tuple, set)):
+        # the browser's canonical keyboard state, `{"type": "control_state", "controls": ["w", "j"]}`: taken whole or not
+        # at all, so that a client with names this service does not know cannot half-steer the camera
+        names = list(chunk["controls"])
+        if not all(isinstance(n, str) and canonical_key(n) is not None for n in names):
+            logger.warning(f"control state {names!r} holds names that are not controls; ignored")
+            return None
     else:
         return None
     return {k for k in map(canonical_key, names) if k is not None}
@@ -288,6 +295,7 @@ class LingBotWorldFastService:
                         if state.unsampled_snapshot:
                             state.controls_superseded += 1
                         state.held_keys, state.unsampled_snapshot = keys, True
+                        report_state = kind == "control_state"
         if ack is not None:
             self._enqueue(state, {"type": "control_ack", "session_id": session_id, "revision": ack,
                                   "elapsed_s": time.monotonic() - state.created_mono})  # fmt: skip

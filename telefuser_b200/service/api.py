@@ -442,10 +442,34 @@ class ApiServer:
                 raise HTTPException(503, "Stream service is not running")
             return self.stream_service
 
+        async def close_both(session_id: str, reason: str) -> bool:
+            """A streaming session has two owners, the pipeline-side session and (over WebRTC) a peer connection: both
+            are closed; either one being there counts as found, and a failure on one side does not keep the other open."""
+            found = False
+            mgr = getattr(self, "webrtc", None)
+            if mgr is not None and session_id in mgr.connections:
+                found = True
+                try:
+                    await mgr.close_connection(session_id)
+                except Exception as e:  # noqa: BLE001 - the pipeline session is still closed below
+                    logger.warning(f"closing the WebRTC connection of session {session_id} failed: {e}")
+            try:
+                found = await sessions.close(session_id, reason=reason) or found
+            except Exception as e:  # noqa: BLE001
+                logger.warning(f"closing the pipeline session {session_id} failed: {e}")
+            return found
+
         @r.delete("/sessions/{session_id}")
         async def close_session(session_id: str) -> dict:
             require()
-            if not await sessions.close(session_id, reason="stream_session_delete"):
+            if not await close_both(session_id, "stream_session_delete"):
+                raise HTTPException(404, f"Session {session_id} not found")
+            return {"session_id": session_id, "status": "closed"}
+
+        @r.delete("/webrtc/{session_id}")
+        async def close_webrtc(session_id: str) -> dict:
+            require()
+            if not await close_both(session_id, "webrtc_delete"):
                 raise HTTPException(404, f"Session {session_id} not found")
             return {"session_id": session_id, "status": "closed"}
 

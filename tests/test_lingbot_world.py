@@ -157,6 +157,11 @@ def test_interactive_service_session():
     assert st5.held_keys == {"l"}
     svc.push_chunk(sid5, {"keys": ["ArrowLeft", "KeyI", "F13"]})
     assert st5.held_keys == {"a", "i"}
+    svc.push_chunk(sid5, {"type": "control_state", "controls": ["w", "KeyJ"]})  # the browser's canonical keyboard state
+    assert st5.held_keys == {"w", "j"}
+    svc.push_chunk(sid5, {"type": "control_state", "controls": ["w", "F13"]})  # an unknown name voids the whole message
+    assert st5.held_keys == {"w", "j"}
+    svc.push_chunk(sid5, {"keys": ["ArrowLeft", "KeyI"]})
     svc.push_chunk(sid5, {"poses": random_walk_trajectory(2, seed=5), "relative": True})
     svc.push_chunk(sid5, {"key": "w", "event": "hold"})  # unknown event: ignored
     assert st5.held_keys == {"a", "i"} and len(st5.explicit_chunks) <= 1
@@ -170,7 +175,7 @@ def test_interactive_service_session():
     prev = [m for m in msgs5 if m["type"] == "preview"]
     assert len(prev) == 1 and prev[0]["frames"].shape == (1, 32, 32, 3) and prev[0]["frames"].dtype == np.uint8 and prev[0]["chunk_index"] == -1
     states = [m["controls"] for m in msgs5 if m["type"] == "status" and m.get("stage") == "control_state"]
-    assert states[:3] == [["w"], ["l", "w"], ["l"]] and states[-2:] == [[], []]
+    assert states[:3] == [["w"], ["l", "w"], ["l"]] and ["j", "w"] in states and states[-2:] == [[], []]
     svc.close_session(sid5)
     with pytest.raises(ValueError, match="at most 20 s"):
         svc.create_session({"image": img, "prompt_emb": emb, "max_duration_seconds": 30.0})

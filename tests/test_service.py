@@ -367,6 +367,21 @@ def test_stream_websocket_bidirectional(tmp_path):
             assert json.loads(ws.receive_text())["type"] == "done"
         assert client.get("/v1/stream/sessions/abc/status").json()["status"] == "unknown"
         assert client.post("/v1/stream/webrtc/offer", json={"sdp": "x", "task": "t2v"}).status_code == 501
+        assert client.delete("/v1/stream/webrtc/abc").status_code == 404 and client.delete("/v1/stream/sessions/abc").status_code == 404
+
+        class FakeConnections:  # a peer connection without a pipeline session behind it still counts as found
+            def __init__(self):
+                self.connections, self.closed = {"rtc-1": object(), "rtc-2": object()}, []
+
+            async def close_connection(self, sid):
+                self.connections.pop(sid)
+                self.closed.append(sid)
+                if sid == "rtc-2":
+                    raise RuntimeError("peer already gone")
+
+        api.webrtc = FakeConnections()
+        assert client.delete("/v1/stream/webrtc/rtc-1").json() == {"session_id": "rtc-1", "status": "closed"}
+        assert client.delete("/v1/stream/sessions/rtc-2").status_code == 200 and api.webrtc.closed == ["rtc-1", "rtc-2"]
         ui = client.get("/ui")  # the browser front end: one static page that talks to the WebSocket transport
         assert ui.status_code == 200 and "text/html" in ui.headers["content-type"] and "/v1/stream/ws" in ui.text
 
