@@ -47,8 +47,9 @@ def _validate(path: str, level: str) -> dict:
 @click.option("--security-level", default="strict", type=LEVELS, help="Pipeline file validation level")
 @click.option("--skip-validation", is_flag=True, default=False, help="Skip security validation")
 @click.option("--validate-only", is_flag=True, default=False, help="Validate the pipeline file and exit")
-@click.option("--enable-latent-cache/--disable-latent-cache", default=None, help="Latent cache on/off")
-@click.option("--cache-mode", default=None, type=click.Choice(["read", "write", "readwrite"]), help="Latent cache mode")
+@click.option("--enable-latent-cache/--disable-latent-cache", default=None, help="Latent cache on/off (default: the pipeline file's CACHE_CONFIG, else off)")
+@click.option("--cache-mode", default=None, type=click.Choice(["read", "write", "readwrite", "read_only", "write_only", "read_write"]),
+              help="Latent cache mode (default: the pipeline file's CACHE_CONFIG, else readwrite)")
 @click.option("--rate-limit/--no-rate-limit", default=True, help="Sliding-window rate limit")
 def serve(pipe_path, task, port, host, cache_dir, parallelism, num_replicas, security_level, skip_validation,
           validate_only, enable_latent_cache, cache_mode, rate_limit) -> None:  # fmt: skip

@@ -158,7 +158,8 @@ class ApiServer:
         self.task_manager = TaskManager(self.config.max_queue_size, self.config.cleanup_keep_count, num_workers)
         cache = None
         if self.config.enable_latent_cache:
-            cache = LatentCache(str(Path(self.config.cache_dir) / "latent_cache"), self.config.latent_cache_mode)
+            cache = LatentCache(self.config.latent_cache_dir or str(Path(self.config.cache_dir) / "latent_cache"),
+                                self.config.latent_cache_mode, self.config.latent_cache_min_similarity)  # fmt: skip
         self.latent_cache = cache
         self.generation = MediaGenerationService(self.file_service, inference_service, self.artifacts, cache)
         self.processor = AsyncTaskProcessor(self.task_manager, self.generation, num_workers, self.config.task_timeout,

@@ -199,3 +199,94 @@ def validate_required_task_parameters(contract: PipelineContract, task: str, dat
     for n, pc in tc.parameters.items():
         if n in data:
             pc.check(n, data[n])
+
+
+# ---- CACHE_CONFIG: the pipeline file's own latent-cache settings --------------------------------------------------
+CACHE_MODES = {"read": "read", "read_only": "read", "write": "write", "write_only": "write", "readwrite": "readwrite",
+               "read_write": "readwrite"}  # fmt: skip
+
+
+def _literal(node, env):
+    """Value of an expression that is a literal, a container of such, or one of `os.getenv(name, default)`,
+    `os.environ.get(name, default)`, `int / float / str / bool(<such>)`, `os.path.join(<such>, ...)`."""
+    import ast
+    import os
+
+    if isinstance(node, ast.Constant):
+        return node.value
+    if isinstance(node, (ast.List, ast.Tuple)):
+        return [_literal(e, env) for e in node.elts]
+    if isinstance(node, ast.Dict):
+        return {_literal(k, env): _literal(v, env) for k, v in zip(node.keys, node.values)}
+    if isinstance(node, ast.UnaryOp) and isinstance(node.op, ast.USub):
+        return -_literal(node.operand, env)
+    if isinstance(node, ast.Name) and node.id in env:
+        return env[node.id]
+    if isinstance(node, ast.Call):
+        name = ast.unparse(node.func)
+        args = [_literal(a, env) for a in node.args]
+        if name in ("os.getenv", "os.environ.get"):
+            return os.environ.get(args[0], args[1] if len(args) > 1 else None)
+        if name in ("int", "float", "str", "bool") and len(args) == 1:
+            return {"int": int, "float": float, "str": str, "bool": bool}[name](args[0])
+        if name == "os.path.join":
+            return os.path.join(*args)
+        if name == "dict" and not args:
+            return {kw.arg: _literal(kw.value, env) for kw in node.keywords}
+    raise ValueError(f"not a plain value: {ast.unparse(node)}")
+
+
+def load_cache_config(pipe_path: str) -> dict | None:
+    """The `CACHE_CONFIG` mapping a pipeline file declares (or None), read WITHOUT importing the file: the server decides
+    about the latent cache before any pipeline (or replica process) is started. Values may be literals, environment
+    look-ups with defaults and simple casts of those; an entry written any other way is skipped."""
+    import ast
+
+    try:
+        tree = ast.parse(open(pipe_path, encoding="utf-8").read())
+    except (OSError, SyntaxError):
+        return None
+    env: dict = {}
+    found = None
+    for node in tree.body:
+        if not (isinstance(node, ast.Assign) and len(node.targets) == 1 and isinstance(node.targets[0], ast.Name)):
+            continue
+        target = node.targets[0].id
+        if target != "CACHE_CONFIG":
+            try:
+                env[target] = _literal(node.value, env)  # module-level constants the mapping may refer to
+            except (ValueError, TypeError, KeyError):
+                pass
+            continue
+        entries: list = []
+        if isinstance(node.value, ast.Dict):
+            entries = [(k.value, v) for k, v in zip(node.value.keys, node.value.values) if isinstance(k, ast.Constant)]
+        elif isinstance(node.value, ast.Call) and ast.unparse(node.value.func) == "dict":
+            entries = [(kw.arg, kw.value) for kw in node.value.keywords if kw.arg]
+        found = {}
+        for key, value in entries:
+            try:
+                found[key] = _literal(value, env)
+            except (ValueError, TypeError, KeyError):
+                continue
+    return found
+
+
+def resolve_latent_cache_settings(pipe_path: str, enable: bool | None, mode: str | None) -> dict:
+    """What the server should do about the latent cache: explicit arguments (the CLI) win, then the pipeline file's
+    `CACHE_CONFIG`, then off / read-write. Returns {enabled, mode, directory, min_similarity, source}."""
+    declared = load_cache_config(pipe_path) or {}
+    out = {"enabled": bool(declared.get("enable_latent_cache", False)), "mode": "readwrite", "directory": declared.get("latent_cache_dir"),
+           "min_similarity": declared.get("rerank_score_threshold"), "source": "pipeline file" if declared else "default"}  # fmt: skip
+    declared_mode = declared.get("cache_mode")
+    if declared_mode is not None:
+        if str(declared_mode) not in CACHE_MODES:
+            raise ValueError(f"{pipe_path}: CACHE_CONFIG cache_mode {declared_mode!r} is not one of {sorted(CACHE_MODES)}")
+        out["mode"] = CACHE_MODES[str(declared_mode)]
+    if enable is not None:
+        out["enabled"], out["source"] = bool(enable), "command line"
+    if mode:
+        if mode not in CACHE_MODES:
+            raise ValueError(f"cache mode {mode!r} is not one of {sorted(CACHE_MODES)}")
+        out["mode"] = CACHE_MODES[mode]
+    return out

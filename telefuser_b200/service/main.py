@@ -87,10 +87,16 @@ def run_server(pipe_path: str, task: str | None, port: int, host: str, cache_dir
     cfg.host, cfg.port, cfg.num_replicas = host, port, num_replicas
     if cache_dir:
         cfg.cache_dir = str(Path(cache_dir))
-    if enable_latent_cache is not None:
-        cfg.enable_latent_cache = enable_latent_cache
-    if cache_mode:
-        cfg.latent_cache_mode = cache_mode
+    from .contract import resolve_latent_cache_settings
+
+    cache = resolve_latent_cache_settings(pipe_path, enable_latent_cache, cache_mode)  # CLI > the file's CACHE_CONFIG > off
+    cfg.enable_latent_cache, cfg.latent_cache_mode = cache["enabled"], cache["mode"]
+    if cache["directory"]:
+        cfg.latent_cache_dir = str(cache["directory"])
+    if cache["min_similarity"] is not None:
+        cfg.latent_cache_min_similarity = float(cache["min_similarity"])
+    if cfg.enable_latent_cache:
+        logger.info(f"latent cache on ({cache['mode']}, decided by the {cache['source']})")
     if security_level:
         cfg.security_level = security_level.lower()
     container = ServiceContainer(cfg)

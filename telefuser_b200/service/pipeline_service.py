@@ -59,6 +59,8 @@ class ServerConfig(BaseSettings):
     stream_fps: int = 16
     enable_latent_cache: bool = False
     latent_cache_mode: str = "readwrite"
+    latent_cache_dir: str | None = None  # default: <cache_dir>/latent_cache
+    latent_cache_min_similarity: float = 0.85
 
 
 def resolve_replica_device_ids(num_replicas: int, parallelism: int, available: list[int] | None = None) -> list[list[int]]:

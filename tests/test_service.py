@@ -498,3 +498,59 @@ def test_clients_against_live_server(tmp_path, ppl_file):
     finally:
         server.should_exit = True
         th.join(10)
+
+
+def test_pipeline_file_cache_config_and_cli_precedence(tmp_path, monkeypatch):
+    from pathlib import Path
+
+    from click.testing import CliRunner
+
+    from telefuser_b200.entrypoints import cli
+    from telefuser_b200.service import main as service_main
+    from telefuser_b200.service.contract import load_cache_config, resolve_latent_cache_settings
+
+    example = str(Path(__file__).resolve().parents[1] / "examples" / "wan_video" / "wan22_14b_text_to_video_service.py")
+    monkeypatch.delenv("TELEFUSER_LATENT_CACHE_DIR", raising=False)
+    monkeypatch.setenv("TELEFUSER_CACHE_MODE", "write_only")
+    declared = load_cache_config(example)  # read from the source text: nothing of the file is imported or run
+    assert declared == {"enable_latent_cache": True, "latent_cache_dir": "./latent_cache/wan22_t2v", "cache_mode": "write_only"}
+    got = resolve_latent_cache_settings(example, None, None)
+    assert (got["enabled"], got["mode"], got["directory"], got["source"]) == (True, "write", "./latent_cache/wan22_t2v", "pipeline file")
+    assert resolve_latent_cache_settings(example, False, None)["enabled"] is False  # the command line wins
+    assert resolve_latent_cache_settings(example, None, "read_only")["mode"] == "read"
+    with pytest.raises(ValueError, match="not one of"):
+        resolve_latent_cache_settings(example, None, "sometimes")
+
+    f = tmp_path / "ppl.py"
+    f.write_text("import os\nROOT = os.path.join('/data', 'cache')\nTHRESH = float(os.getenv('NO_SUCH_VAR_FOR_TEST', '0.9'))\n"
+                 "CACHE_CONFIG = {'enable_latent_cache': True, 'latent_cache_dir': ROOT, 'rerank_score_threshold': THRESH,\n"
+                 "                'key_steps': [5, 10], 'odd': open('/etc/hostname').read(), 'neg': -1}\n")
+    declared = load_cache_config(str(f))
+    assert declared == {"enable_latent_cache": True, "latent_cache_dir": "/data/cache", "rerank_score_threshold": 0.9, "key_steps": [5, 10], "neg": -1}
+    assert resolve_latent_cache_settings(str(f), None, None)["min_similarity"] == 0.9
+    plain = tmp_path / "plain.py"
+    plain.write_text("PPL_CONFIG = {}\n")
+    assert load_cache_config(str(plain)) is None and resolve_latent_cache_settings(str(plain), None, None)["enabled"] is False
+    bad = tmp_path / "bad.py"
+    bad.write_text("CACHE_CONFIG = dict(enable_latent_cache=True, cache_mode='sometimes')\n")
+    with pytest.raises(ValueError, match="cache_mode 'sometimes'"):
+        resolve_latent_cache_settings(str(bad), None, None)
+
+    seen = {}
+
+    class FakeContainer:
+        def __init__(self, cfg):
+            seen["cfg"] = cfg
+
+        def initialize_all(self, *a, **k):
+            return True
+
+    monkeypatch.setattr(service_main, "ServiceContainer", FakeContainer)
+    monkeypatch.setattr(service_main, "_run", lambda *a, **k: None)
+    runner = CliRunner()
+    assert runner.invoke(cli.main, ["serve", str(f), "-t", "t2v"]).exit_code == 0
+    cfg = seen["cfg"]
+    assert cfg.enable_latent_cache and cfg.latent_cache_dir == "/data/cache" and cfg.latent_cache_min_similarity == 0.9 and cfg.latent_cache_mode == "readwrite"
+    assert runner.invoke(cli.main, ["serve", str(f), "-t", "t2v", "--disable-latent-cache", "--cache-mode", "read_only"]).exit_code == 0
+    assert not seen["cfg"].enable_latent_cache and seen["cfg"].latent_cache_mode == "read"
+    assert runner.invoke(cli.main, ["serve", str(plain), "-t", "t2v"]).exit_code == 0 and not seen["cfg"].enable_latent_cache
