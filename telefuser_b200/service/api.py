@@ -28,7 +28,7 @@ from telefuser_b200.utils.logging import logger
 from .contract import infer_media_type_for_task, validate_task_name_format
 from .files import ArtifactStore, FileService, MediaError, MediaType
 from .pipeline_service import ServerConfig
-from .stream_service import StreamPipelineService, StreamSessionManager, frame_to_jpeg, webrtc_available
+from .stream_service import AudioChunk, StreamPipelineService, StreamSessionManager, frame_to_jpeg, webrtc_available
 from .task_manager import ACTIVE, NoCapacityError, QueueFullError, TaskManager, TaskStatus
 from .task_processor import AsyncTaskProcessor, LatentCache, MediaGenerationService, validate_and_fill
 
@@ -495,7 +495,8 @@ class ApiServer:
         @r.websocket("/ws")
         async def ws(websocket: WebSocket) -> None:
             """First client message: JSON session config. Server -> client: JSON chunk messages, each
-            followed by `num_frames` binary JPEG messages. Client -> server (bidirectional mode): JSON
+            followed by `num_frames` binary JPEG messages and, when the message has an `audio` entry, one binary message of
+            interleaved PCM16. Client -> server (bidirectional mode): JSON
             chunks (e.g. key controls); `{"type": "close"}` ends the session."""
             await websocket.accept()
             if self.stream_service is None or not self.stream_service.is_running:
@@ -515,8 +516,11 @@ class ApiServer:
                 while True:
                     frames, msg = await s.outbound.get()
                     await websocket.send_text(json.dumps(msg))
-                    for f in frames:
-                        await websocket.send_bytes(f if isinstance(f, (bytes, bytearray)) else frame_to_jpeg(f))
+                    for f in frames:  # video frames as JPEG; a chunk's audio (announced in msg["audio"]) last, as raw PCM16
+                        if isinstance(f, AudioChunk):
+                            await websocket.send_bytes(f.pcm16)
+                        else:
+                            await websocket.send_bytes(f if isinstance(f, (bytes, bytearray)) else frame_to_jpeg(f))
                     s.chunks_sent += 1
                     if msg.get("type") == "done" or msg.get("error"):
                         return

@@ -172,10 +172,46 @@ class StreamPipelineService:
 # ---------------------------------------------------------------------------
 # Transport-independent session plumbing
 # ---------------------------------------------------------------------------
+@dataclass
+class AudioChunk:
+    """Interleaved signed 16-bit PCM that belongs to one chunk. It rides at the end of the chunk's media list: the
+    WebSocket transport sends it as one more binary message, the WebRTC transport feeds its audio track."""
+
+    pcm16: bytes
+    sample_rate: int = 48000
+    channels: int = 1
+
+    @property
+    def num_samples(self) -> int:
+        return len(self.pcm16) // (2 * max(1, self.channels))
+
+
+def audio_from_chunk(chunk: dict) -> AudioChunk | None:
+    """`audio_b64` (base64 PCM16, the wire form) or `audio` (int16 array, or float array / tensor in [-1, 1], shaped
+    [samples] or [samples, channels]) with `audio_sample_rate` (48000) and `audio_channels` (1)."""
+    rate, channels = int(chunk.get("audio_sample_rate") or 48000), int(chunk.get("audio_channels") or 1)
+    if chunk.get("audio_b64"):
+        import base64
+
+        return AudioChunk(base64.b64decode(chunk["audio_b64"]), rate, channels)
+    a = chunk.get("audio")
+    if a is None:
+        return None
+    if isinstance(a, torch.Tensor):
+        a = a.detach().cpu().numpy()
+    a = np.asarray(a)
+    if a.ndim == 2 and "audio_channels" not in chunk:
+        channels = a.shape[1]
+    if a.dtype != np.int16:
+        a = (np.clip(a.astype(np.float32), -1.0, 1.0) * 32767.0).round().astype(np.int16)
+    return AudioChunk(np.ascontiguousarray(a).tobytes(), rate, channels)
+
+
 class ChunkRouter:
-    """Splits a pipeline chunk into media frames and a JSON message."""
+    """Splits a pipeline chunk into media (video frames, then at most one `AudioChunk`) and a JSON message."""
 
     FRAME_KEYS = ("frames", "video", "frame")
+    AUDIO_KEYS = ("audio", "audio_b64")
 
     def __init__(self, fps: int = 16) -> None:
         self.fps = fps
@@ -183,6 +219,11 @@ class ChunkRouter:
     def route(self, chunk: dict, session_id: str, index: int) -> tuple[list, dict]:
         frames: list = []
         media_keys: set = set()
+        if chunk.get("frames_b64"):  # base64 JPEG strings: what server-push services written for HTTP clients produce
+            import base64
+
+            frames.extend(base64.b64decode(f) for f in chunk["frames_b64"])
+            media_keys.add("frames_b64")
         for k in self.FRAME_KEYS:
             v = chunk.get(k)
             if v is None:
@@ -203,9 +244,16 @@ class ChunkRouter:
                 frames.append(v)
                 media_keys.add(k)
             # anything else under these names (a frame count, a flag) is ordinary data and stays in the message
+        audio = audio_from_chunk(chunk)
+        if audio is not None:
+            media_keys.update(self.AUDIO_KEYS)
         msg = {"type": "chunk", "session_id": session_id, "index": index, "num_frames": len(frames),
                "data": serialisable_chunk({k: v for k, v in chunk.items() if k not in media_keys}),
                "timestamp": time.time()}  # fmt: skip
+        if audio is not None:
+            msg["audio"] = {"sample_rate": audio.sample_rate, "channels": audio.channels, "num_samples": audio.num_samples,
+                            "format": "pcm_s16le"}  # fmt: skip
+            frames.append(audio)
         if chunk.get("error"):
             msg["error"] = str(chunk["error"])
         return frames, msg

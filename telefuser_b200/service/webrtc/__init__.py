@@ -6,6 +6,6 @@ Role parity: telefuser/service/webrtc/{track,session_manager,chunk_router}.py an
 """
 
 from .session_manager import WebRTCSessionManager, answer_offer, backend
-from .track import FramePacer, frame_to_rgb
+from .track import AudioPacer, FramePacer, frame_to_rgb
 
-__all__ = ["FramePacer", "WebRTCSessionManager", "answer_offer", "backend", "frame_to_rgb"]
+__all__ = ["AudioPacer", "FramePacer", "WebRTCSessionManager", "answer_offer", "backend", "frame_to_rgb"]

@@ -1,7 +1,8 @@
 """Per-connection state of the WebRTC transport.
 
 One `WebRTCSessionManager` lives in the API server. For every SDP offer it opens a streaming session
-(`StreamSessionManager.open`), builds a peer connection with one paced video track and answers the offer. A pump
+(`StreamSessionManager.open`), builds a peer connection with one paced video track (plus a paced audio track when the
+offer's config asks for `audio`) and answers the offer. A pump
 task moves the session's outbound items to the track (frames) and to the "control" data channel (JSON chunk
 messages); client messages on that channel are forwarded to the pipeline (bidirectional services) or close the
 session. Connection-state changes map onto the session manager's disconnect grace / reconnect / close.
@@ -21,7 +22,10 @@ import time
 import uuid
 from dataclasses import dataclass, field
 
-from .track import FramePacer, make_track
+from telefuser_b200.utils.logging import logger
+
+from ..stream_service import AudioChunk
+from .track import AudioPacer, FramePacer, make_audio_track, make_track
 
 
 def backend():
@@ -43,6 +47,8 @@ class WebRTCConnection:
     messages_sent: int = 0
     messages_received: int = 0
     state: str = "new"
+    audio_pacer: AudioPacer | None = None
+    audio_unsent_chunks: int = 0
 
 
 class WebRTCSessionManager:
@@ -101,6 +107,12 @@ class WebRTCSessionManager:
         conn = WebRTCConnection(s.session_id, pc, pacer)
         self.connections[s.session_id] = conn
         pc.addTrack(make_track(pacer, aiortc, av))
+        audio = config.get("audio")
+        if audio:  # tracks are fixed at negotiation time: a client that wants the service's sound asks for it in the offer
+            opts = audio if isinstance(audio, dict) else {}
+            conn.audio_pacer = AudioPacer(int(opts.get("sample_rate") or config.get("audio_sample_rate") or 48000),
+                                          int(opts.get("channels") or config.get("audio_channels") or 1), self.max_buffer_seconds)  # fmt: skip
+            pc.addTrack(make_audio_track(conn.audio_pacer, aiortc, av))
         self.set_video_codec_preferences(pc)
 
         @pc.on("datachannel")
@@ -149,7 +161,16 @@ class WebRTCSessionManager:
         try:
             while not s.closed:
                 frames, msg = await s.outbound.get()
-                conn.pacer.push_frames(frames)
+                conn.pacer.push_frames([f for f in frames if not isinstance(f, AudioChunk)])
+                for a in (f for f in frames if isinstance(f, AudioChunk)):
+                    if conn.audio_pacer is None:
+                        conn.audio_unsent_chunks += 1  # the client did not ask for an audio track
+                        continue
+                    try:
+                        conn.audio_pacer.push(a.pcm16, a.sample_rate, a.channels)
+                    except ValueError as e:
+                        conn.audio_unsent_chunks += 1
+                        logger.warning(f"session {s.session_id}: {e}")
                 ch = conn.channel
                 if ch is not None and getattr(ch, "readyState", "open") == "open":
                     ch.send(json.dumps(msg))
@@ -175,7 +196,9 @@ class WebRTCSessionManager:
 
     def stats(self) -> dict:
         return {sid: {"state": c.state, "age_s": round(time.time() - c.created, 3), "sent": c.messages_sent,
-                      "received": c.messages_received, **c.pacer.stats()} for sid, c in self.connections.items()}  # fmt: skip
+                      "received": c.messages_received, **c.pacer.stats(),
+                      **({"audio": c.audio_pacer.stats()} if c.audio_pacer is not None else {}),
+                      "audio_unsent_chunks": c.audio_unsent_chunks} for sid, c in self.connections.items()}  # fmt: skip
 
 
 async def answer_offer(api, body: dict) -> dict:

@@ -31,6 +31,12 @@ def frame_to_rgb(frame):
         if t.shape[-1] == 1:
             t = t.expand(*t.shape[:-1], 3)
         return np.ascontiguousarray(t.numpy())
+    if isinstance(frame, (bytes, bytearray)):  # an encoded picture (JPEG / PNG)
+        import io
+
+        from PIL import Image
+
+        frame = Image.open(io.BytesIO(bytes(frame))).convert("RGB")
     arr = np.asarray(frame)
     if arr.ndim == 2:
         arr = np.stack([arr] * 3, axis=-1)
@@ -119,3 +125,78 @@ def make_track(pacer: FramePacer, aiortc, av):
             return vf
 
     return PipelineVideoTrack()
+
+
+class AudioPacer:
+    """The audio counterpart of `FramePacer`: chunks of interleaved PCM16 go in, fixed 20 ms packets come out on a
+    real-time grid. While nothing is queued the packets are silence, so the track never stalls the connection; when the
+    client falls more than `max_buffer_seconds` behind, the oldest samples are dropped."""
+
+    PACKET_SECONDS = 0.02
+
+    def __init__(self, sample_rate: int = 48000, channels: int = 1, max_buffer_seconds: float = 4.0, clock=time.monotonic) -> None:
+        if sample_rate < 8000 or channels not in (1, 2):
+            raise ValueError(f"audio tracks carry mono or stereo at 8 kHz or more, got {channels} channel(s) at {sample_rate} Hz")
+        self.sample_rate, self.channels, self.clock = sample_rate, channels, clock
+        self.packet_samples = int(round(sample_rate * self.PACKET_SECONDS))
+        self.capacity_bytes = int(sample_rate * max_buffer_seconds) * 2 * channels
+        self.buffer = bytearray()
+        self.pts = 0
+        self.t0: float | None = None
+        self.dropped_samples = self.silent_packets = 0
+
+    def push(self, pcm16: bytes, sample_rate: int | None = None, channels: int | None = None) -> None:
+        if (sample_rate or self.sample_rate) != self.sample_rate or (channels or self.channels) != self.channels:
+            raise ValueError(f"this track was negotiated as {self.channels} channel(s) at {self.sample_rate} Hz; the chunk has "
+                             f"{channels} at {sample_rate}")  # fmt: skip
+        self.buffer.extend(pcm16)
+        over = len(self.buffer) - self.capacity_bytes
+        if over > 0:
+            frame = 2 * self.channels
+            over = -(-over // frame) * frame
+            del self.buffer[:over]
+            self.dropped_samples += over // frame
+
+    async def next_packet(self):
+        """-> (PCM16 bytes of one packet, pts in samples, time base). Sleeps until the packet's slot."""
+        if self.t0 is None:
+            self.t0 = self.clock()
+        delay = self.t0 + self.pts / self.sample_rate - self.clock()
+        if delay > 0:
+            await asyncio.sleep(delay)
+        need = self.packet_samples * 2 * self.channels
+        if len(self.buffer) >= need:
+            data = bytes(self.buffer[:need])
+            del self.buffer[:need]
+        else:  # not enough for a whole packet: play what there is, pad with silence
+            data = bytes(self.buffer) + bytes(need - len(self.buffer))
+            self.silent_packets += 1
+            self.buffer.clear()
+        pts = self.pts
+        self.pts += self.packet_samples
+        return data, pts, fractions.Fraction(1, self.sample_rate)
+
+    def stats(self) -> dict:
+        return {"queued_samples": len(self.buffer) // (2 * self.channels), "sent_samples": self.pts,
+                "dropped_samples": self.dropped_samples, "silent_packets": self.silent_packets}  # fmt: skip
+
+
+def make_audio_track(pacer: AudioPacer, aiortc, av):
+    """An audio `MediaStreamTrack` of the given aiortc module whose packets come from `pacer`."""
+    import numpy as np
+
+    class PipelineAudioTrack(aiortc.MediaStreamTrack):
+        kind = "audio"
+
+        def __init__(self) -> None:
+            super().__init__()
+            self.pacer = pacer
+
+        async def recv(self):
+            data, pts, time_base = await pacer.next_packet()
+            samples = np.frombuffer(data, dtype=np.int16).reshape(1, -1)  # packed layout: one plane, channels interleaved
+            af = av.AudioFrame.from_ndarray(samples, format="s16", layout="stereo" if pacer.channels == 2 else "mono")
+            af.sample_rate, af.pts, af.time_base = pacer.sample_rate, pts, time_base
+            return af
+
+    return PipelineAudioTrack()

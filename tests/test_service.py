@@ -86,7 +86,10 @@ FAKE_STREAM = textwrap.dedent('''
             while True:
                 c = await self.q[sid].get()
                 frames = torch.zeros(2, 8, 8, 3, dtype=torch.uint8)
-                yield {"frames": frames, "echo": c.get("key"), "done": c.get("key") == "end"}
+                out = {"frames": frames, "echo": c.get("key"), "done": c.get("key") == "end"}
+                if c.get("key") == "sound":  # a chunk with half a second of stereo sound
+                    out.update(audio=torch.zeros(8000, 2), audio_sample_rate=16000)
+                yield out
         def close_session(self, sid):
             self.q.pop(sid, None)
 
@@ -360,6 +363,12 @@ def test_stream_websocket_bidirectional(tmp_path):
             assert msg["type"] == "chunk" and msg["index"] == 0 and msg["num_frames"] == 2 and msg["data"]["echo"] == "w"
             jpegs = [ws.receive_bytes() for _ in range(2)]
             assert all(j[:3] == b"\xff\xd8\xff" for j in jpegs)
+            ws.send_text(json.dumps({"key": "sound"}))
+            msg = json.loads(ws.receive_text())
+            assert msg["num_frames"] == 2 and msg["audio"] == {"sample_rate": 16000, "channels": 2, "num_samples": 8000, "format": "pcm_s16le"}
+            assert "audio" not in msg["data"]
+            [ws.receive_bytes() for _ in range(2)]
+            assert len(ws.receive_bytes()) == 8000 * 2 * 2  # interleaved PCM16 after the pictures
             ws.send_text(json.dumps({"key": "end"}))
             msg = json.loads(ws.receive_text())
             assert msg["data"]["done"] is True

@@ -223,3 +223,104 @@ def test_offer_answer_pump_and_connection_states():
     assert kinds == ["push", "disconnected", "reconnected", "close", "close"]
     assert sessions.events[0][2] == {"keys": ["w"]} and sessions.events[-1][2] == "webrtc failed"
     assert "s1" not in mgr.connections and sessions.session.chunks_sent == 2
+
+
+# ---------------------------------------------------------------------------------------------------
+# audio and encoded frames
+# ---------------------------------------------------------------------------------------------------
+class FakeAudioFrame:
+    def __init__(self, arr, fmt, layout):
+        self.arr, self.format, self.layout = arr, fmt, layout
+        self.sample_rate = self.pts = self.time_base = None
+
+    @classmethod
+    def from_ndarray(cls, arr, format="s16", layout="mono"):  # noqa: A002
+        assert arr.dtype == np.int16 and arr.ndim == 2 and arr.shape[0] == 1
+        return cls(arr, format, layout)
+
+
+def test_chunk_router_takes_encoded_frames_and_audio_in_every_form():
+    import base64
+    import io
+
+    from PIL import Image
+
+    from telefuser_b200.service.stream_service import AudioChunk, ChunkRouter, audio_from_chunk
+
+    def jpeg(value):
+        buf = io.BytesIO()
+        Image.fromarray(np.full((8, 8, 3), value, dtype=np.uint8)).save(buf, format="JPEG")
+        return buf.getvalue()
+
+    pics = [jpeg(10), jpeg(200)]
+    pcm = (np.arange(960, dtype=np.int16) - 480)
+    chunk = {"type": "chunk", "index": 7, "fps": 24, "frames_b64": [base64.b64encode(p).decode() for p in pics],
+             "audio_b64": base64.b64encode(pcm.tobytes()).decode(), "audio_sample_rate": 24000, "prompt": "waves"}
+    media, msg = ChunkRouter().route(chunk, "s", 7)
+    assert media[:2] == pics and isinstance(media[2], AudioChunk) and media[2].pcm16 == pcm.tobytes()
+    assert msg["num_frames"] == 2 and msg["audio"] == {"sample_rate": 24000, "channels": 1, "num_samples": 960, "format": "pcm_s16le"}
+    assert msg["data"] == {"type": "chunk", "index": 7, "fps": 24, "audio_sample_rate": 24000, "prompt": "waves"}  # no payload twice
+    assert frame_to_rgb(pics[1]).shape == (8, 8, 3) and abs(int(frame_to_rgb(pics[1])[0, 0, 0]) - 200) <= 2
+    stereo = audio_from_chunk({"audio": torch.tensor([[0.0, 1.0], [-1.0, 0.5]])})
+    assert (stereo.channels, stereo.sample_rate, stereo.num_samples) == (2, 48000, 2)
+    assert np.frombuffer(stereo.pcm16, dtype=np.int16).tolist() == [0, 32767, -32767, 16384]
+    assert audio_from_chunk({"audio": pcm}).pcm16 == pcm.tobytes() and audio_from_chunk({"frames": []}) is None
+    _, plain = ChunkRouter().route({"frames": [np.zeros((4, 4, 3), dtype=np.uint8)]}, "s", 0)
+    assert "audio" not in plain and plain["num_frames"] == 1
+
+
+def test_audio_pacer_packets_silence_and_drops():
+    from telefuser_b200.service.webrtc import AudioPacer
+    from telefuser_b200.service.webrtc.track import make_audio_track
+
+    async def run():
+        now = [0.0]
+        p = AudioPacer(48000, 1, max_buffer_seconds=0.05, clock=lambda: now[0])
+        p.push((np.arange(1500, dtype=np.int16)).tobytes())
+        now[0] = 10.0  # behind schedule: no sleeping
+        return p, [await p.next_packet() for _ in range(3)]
+
+    p, out = asyncio.run(run())
+    first, second, third = (np.frombuffer(o[0], dtype=np.int16) for o in out)
+    assert first.tolist() == list(range(960)) and second[:540].tolist() == list(range(960, 1500)) and not second[540:].any()
+    assert not third.any() and [o[1] for o in out] == [0, 960, 1920] and out[0][2].denominator == 48000
+    assert p.stats()["silent_packets"] == 2 and p.packet_samples == 960
+    p.push(bytes(2 * 5000))  # capacity is 0.05 s = 2400 samples
+    assert p.stats()["queued_samples"] == 2400 and p.dropped_samples == 2600
+    with pytest.raises(ValueError, match="negotiated"):
+        p.push(b"\0\0", sample_rate=16000)
+    with pytest.raises(ValueError, match="mono or stereo"):
+        AudioPacer(48000, 6)
+    aiortc, av = fake_modules()
+    av.AudioFrame = FakeAudioFrame
+    st = AudioPacer(48000, 2, clock=lambda: 10.0)
+    st.push(np.arange(2 * 960, dtype=np.int16).tobytes())
+    frame = asyncio.run(make_audio_track(st, aiortc, av).recv())
+    assert frame.layout == "stereo" and frame.arr.shape == (1, 1920) and frame.sample_rate == 48000 and frame.pts == 0
+
+
+def test_offer_with_audio_adds_a_second_track_and_feeds_it():
+    from telefuser_b200.service.stream_service import AudioChunk
+
+    async def run(want_audio):
+        sessions = FakeSessions()
+        aiortc, av = fake_modules()
+        av.AudioFrame = FakeAudioFrame
+        mgr = WebRTCSessionManager(sessions, types.SimpleNamespace(stream_mode="server_push"), fps=500, modules=(aiortc, av))
+        body = {"sdp": "v=0 offer", "session_id": "a1", "config": {"audio": {"sample_rate": 24000} if want_audio else False}}
+        await mgr.answer(body)
+        conn = mgr.connections["a1"]
+        pcm = np.ones(480, dtype=np.int16).tobytes()
+        media = [torch.zeros(3, 8, 8), AudioChunk(pcm, 24000, 1)]
+        await sessions.session.outbound.put((media, {"type": "chunk", "index": 0}))
+        await sessions.session.outbound.put(([AudioChunk(pcm, 48000, 1)], {"type": "chunk", "index": 1}))  # not what was negotiated
+        await sessions.session.outbound.put(([], {"type": "done"}))
+        await asyncio.wait_for(conn.pump_task, 2.0)
+        return mgr, conn
+
+    mgr, conn = asyncio.run(run(True))
+    assert [t.kind for t in conn.pc.tracks] == ["video", "audio"] and conn.audio_pacer.sample_rate == 24000
+    assert conn.audio_pacer.stats()["queued_samples"] == 480 and conn.audio_unsent_chunks == 1 and list(conn.pacer.queue)[0].shape == (3, 8, 8)
+    assert mgr.stats()["a1"]["audio"]["queued_samples"] == 480
+    mgr, conn = asyncio.run(run(False))
+    assert [t.kind for t in conn.pc.tracks] == ["video"] and conn.audio_unsent_chunks == 2 and len(conn.pacer.queue) == 1
