@@ -155,6 +155,7 @@ class ApiServer:
         self.artifacts = ArtifactStore(str(Path(self.config.cache_dir) / "artifacts"), self.config.artifact_retention_hours,
                                        self.config.artifact_max_gb)  # fmt: skip
         self.metrics = ServiceMetrics() if self.config.metrics_enabled else None
+        self.num_workers = num_workers
         self.task_manager = TaskManager(self.config.max_queue_size, self.config.cleanup_keep_count, num_workers)
         cache = None
         if self.config.enable_latent_cache:
@@ -373,6 +374,9 @@ class ApiServer:
         @r.get("/metadata")
         async def metadata() -> dict:
             meta = dict(self.inference_service.metadata()) if self.inference_service is not None else {}
+            if meta:
+                meta.update(service_effective_max_concurrent_tasks=self.task_manager.queue_status().get("processing_slots", 1),
+                            service_configured_max_concurrent_tasks=self.num_workers, max_queue_size=self.config.max_queue_size)  # fmt: skip
             if self.stream_service is not None:
                 meta["stream"] = self.stream_service.server_metadata()
             meta["webrtc_available"] = webrtc_available()

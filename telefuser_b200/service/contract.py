@@ -135,7 +135,9 @@ class PipelineContract:
         return {"contract_version": self.contract_version, "pipeline_name": self.pipeline_name,
                 "supported_tasks": list(self.supported_tasks), "supported_media_types": list(self.supported_media_types),
                 "execution_mode": self.execution_mode, "effective_max_concurrent_tasks": self.effective_max_concurrent_tasks,
-                "tasks": {t: c.to_metadata() for t, c in self.task_contracts.items()}}  # fmt: skip
+                "entrypoints": {"get_pipeline": self.get_pipeline, "run_with_file": self.run_with_file},
+                "task_contracts": {t: c.to_metadata() for t, c in self.task_contracts.items()},
+                "tasks": {t: c.to_metadata() for t, c in self.task_contracts.items()}}  # fmt: skip  ("tasks": older clients)
 
 
 TASK_TEMPLATES = {
@@ -165,6 +167,12 @@ def legacy_contract_from_module(module: ModuleType, task: str, name: str) -> Pip
     tc["parameters"] = params
     return PipelineContract.from_mapping({"pipeline_name": name, "supported_tasks": [task], "task_contracts": {task: tc}},
                                          fallback_name=name)  # fmt: skip
+
+
+def declares_contract(module: ModuleType) -> bool:
+    """Whether the pipeline file states its own contract (else one is derived from `run_with_file`'s signature)."""
+    return any(isinstance(getattr(module, a, None), dict) for a in ("PIPELINE_MANIFEST", "PIPELINE_CONTRACT")) \
+        or callable(getattr(module, "get_pipeline_contract", None))  # fmt: skip
 
 
 def load_contract(module: ModuleType, task: str | None, name: str) -> PipelineContract:

@@ -140,6 +140,7 @@ class PipelineService:
         self.runner: PipelineRunner | None = None
         self.task: str | None = None
         self.ppl_file: str | None = None
+        self.parallelism = 1
 
     @property
     def ready(self) -> bool:
@@ -151,7 +152,7 @@ class PipelineService:
                 "warnings": [v.to_dict() for v in res.warnings]}  # fmt: skip
 
     def start_pipeline(self, ppl_file: str, task: str | None = None, parallelism: int = 1, skip_validation=False) -> dict:
-        self.ppl_file, self.task = ppl_file, task
+        self.ppl_file, self.task, self.parallelism = ppl_file, task, parallelism
         self.module = load_pipeline_module(ppl_file, None if skip_validation else self.validator)
         self.contract = load_contract(self.module, task, Path(ppl_file).stem)
         get = getattr(self.module, self.contract.get_pipeline)
@@ -162,7 +163,15 @@ class PipelineService:
         return self.metadata()
 
     def metadata(self) -> dict:
-        return {} if self.contract is None else self.contract.to_metadata()
+        """The running pipeline as front ends and gateways should see it: the file, how it was started, and its
+        contract (tasks, required inputs, typed parameters with defaults)."""
+        if self.contract is None:
+            return {}
+        from .contract import declares_contract
+
+        return {"pipeline_file": self.ppl_file, "parallelism": self.parallelism, "task": self.task,
+                "security_level": str(self.config.security_level).upper(), "runner": type(self.runner).__name__,
+                "declared_pipeline_contract": declares_contract(self.module), **self.contract.to_metadata()}  # fmt: skip
 
     def run_task_with_stop_event(self, data: dict, stop_event: threading.Event | None = None) -> TaskResponse:
         if self.runner is None:

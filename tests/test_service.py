@@ -251,7 +251,11 @@ def test_http_task_flow(tmp_path, ppl_file):
         assert client.get("/v1/service/health").json() == {"status": "ok"}
         assert client.get("/v1/service/ready").status_code == 200
         meta = client.get("/v1/service/metadata").json()
-        assert meta["pipeline_name"] == "fake_t2v" and "t2v" in meta["tasks"]
+        assert meta["pipeline_name"] == "fake_t2v" and "t2v" in meta["tasks"] and meta["task_contracts"] == meta["tasks"]
+        assert meta["pipeline_file"] == ppl_file and meta["parallelism"] == 1 and meta["task"] == "t2v" and meta["runner"] == "PipelineRunner"
+        assert isinstance(meta["declared_pipeline_contract"], bool) and meta["entrypoints"] == {"get_pipeline": "get_pipeline", "run_with_file": "run_with_file"}
+        assert meta["max_queue_size"] == 100 and meta["service_configured_max_concurrent_tasks"] == 1 and meta["security_level"]
+        assert set(meta["task_contracts"]["t2v"]) == {"media_type", "required_inputs", "optional_inputs", "parameters"}
         r = client.post("/v1/tasks/create", json={"task": "t2v", "prompt": "hello", "seed": 7, "mode": "slow"})
         assert r.status_code == 200, r.text
         tid = r.json()["task_id"]
