@@ -168,7 +168,8 @@ class ApiServer:
         self.sessions = None
         if stream_service is not None:
             self.sessions = StreamSessionManager(stream_service, self.config.stream_fps,
-                                                 disconnect_grace_s=self.config.webrtc_disconnect_grace_s)  # fmt: skip
+                                                 disconnect_grace_s=self.config.webrtc_disconnect_grace_s,
+                                                 max_sessions=self.config.stream_max_sessions)  # fmt: skip
         self.started = time.time()
         self.app = self._build_app()
 
@@ -492,9 +493,17 @@ class ApiServer:
             require()
             if not webrtc_available():
                 raise HTTPException(501, "WebRTC transport needs the aiortc package; use the WebSocket transport /v1/stream/ws")
+            from .stream_service import SessionConflict, SessionLimitReached
             from .webrtc import answer_offer
 
-            return await answer_offer(self, body)
+            try:
+                return await answer_offer(self, body)
+            except SessionLimitReached as e:
+                raise HTTPException(503, str(e)) from None
+            except SessionConflict as e:
+                raise HTTPException(409, str(e)) from None
+            except (KeyError, ValueError, TypeError) as e:  # no / malformed SDP, a config the service refuses
+                raise HTTPException(400, f"offer rejected: {e}") from None
 
         @r.websocket("/ws")
         async def ws(websocket: WebSocket) -> None:

@@ -57,6 +57,7 @@ class ServerConfig(BaseSettings):
     webrtc_disconnect_grace_s: float = 10.0
     webrtc_datachannel_timeout_s: float = 30.0
     stream_fps: int = 16
+    stream_max_sessions: int = 0  # 0: no limit; else further session requests are refused (HTTP 503) while this many are open
     enable_latent_cache: bool = False
     latent_cache_mode: str = "readwrite"
     latent_cache_dir: str | None = None  # default: <cache_dir>/latent_cache

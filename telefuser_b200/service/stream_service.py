@@ -294,9 +294,18 @@ class StreamSession:
     disconnect_deadline: float | None = None
 
 
+class SessionLimitReached(RuntimeError):
+    """The server already runs as many streaming sessions as it is configured for."""
+
+
+class SessionConflict(ValueError):
+    """A session with the requested id exists."""
+
+
 class StreamSessionManager:
     def __init__(self, service: StreamPipelineService, fps: int = 16, max_queue: int = 64, disconnect_grace_s: float = 10.0,
-                 idle_timeout_s: float = 600.0) -> None:  # fmt: skip
+                 idle_timeout_s: float = 600.0, max_sessions: int = 0) -> None:  # fmt: skip
+        self.max_sessions = max_sessions
         self.service, self.router = service, ChunkRouter(fps)
         self.max_queue, self.grace, self.idle = max_queue, disconnect_grace_s, idle_timeout_s
         self.sessions: dict[str, StreamSession] = {}
@@ -306,8 +315,18 @@ class StreamSessionManager:
 
     async def open(self, config: dict) -> StreamSession:
         """Creates the pipeline session (bidirectional) or starts the generator (server push)."""
+        if self.max_sessions and len(self.sessions) >= self.max_sessions:
+            raise SessionLimitReached(f"{len(self.sessions)} streaming sessions are open (limit {self.max_sessions})")
+        wanted = config.get("session_id")
+        if wanted is not None and str(wanted) in self.sessions:
+            raise SessionConflict(f"streaming session {wanted!r} already exists")
         if self.service.stream_mode == "bidirectional":
-            sid = await asyncio.to_thread(self.service.create_session, config)
+            try:
+                sid = await asyncio.to_thread(self.service.create_session, config)
+            except ValueError as e:
+                if "already exists" in str(e):
+                    raise SessionConflict(str(e)) from e
+                raise
             source = self.service.pull_chunks(sid)
         else:
             sid = str(config.get("session_id") or uuid.uuid4())

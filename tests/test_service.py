@@ -380,6 +380,18 @@ def test_stream_websocket_bidirectional(tmp_path):
             assert json.loads(ws.receive_text())["type"] == "done"
         assert client.get("/v1/stream/sessions/abc/status").json()["status"] == "unknown"
         assert client.post("/v1/stream/webrtc/offer", json={"sdp": "x", "task": "t2v"}).status_code == 501
+        # a second session under a live id is a conflict; beyond the configured number of sessions the server is busy
+        api.sessions.max_sessions = 1
+        with client.websocket_connect("/v1/stream/ws") as first:
+            first.send_text(json.dumps({"session_id": "only"}))
+            assert json.loads(first.receive_text())["type"] == "session"
+            with client.websocket_connect("/v1/stream/ws") as second:
+                second.send_text(json.dumps({"session_id": "other"}))
+                assert "limit 1" in json.loads(second.receive_text())["error"]
+            api.sessions.max_sessions = 0
+            with client.websocket_connect("/v1/stream/ws") as again:
+                again.send_text(json.dumps({"session_id": "only"}))
+                assert "already exists" in json.loads(again.receive_text())["error"]
         assert client.delete("/v1/stream/webrtc/abc").status_code == 404 and client.delete("/v1/stream/sessions/abc").status_code == 404
 
         class FakeConnections:  # a peer connection without a pipeline session behind it still counts as found
@@ -567,3 +579,31 @@ def test_pipeline_file_cache_config_and_cli_precedence(tmp_path, monkeypatch):
     assert runner.invoke(cli.main, ["serve", str(f), "-t", "t2v", "--disable-latent-cache", "--cache-mode", "read_only"]).exit_code == 0
     assert not seen["cfg"].enable_latent_cache and seen["cfg"].latent_cache_mode == "read"
     assert runner.invoke(cli.main, ["serve", str(plain), "-t", "t2v"]).exit_code == 0 and not seen["cfg"].enable_latent_cache
+
+
+def test_webrtc_offer_status_codes(tmp_path, monkeypatch):
+    import telefuser_b200.service.api as api_mod
+    import telefuser_b200.service.webrtc as webrtc_mod
+    from telefuser_b200.service.stream_service import SessionConflict, SessionLimitReached
+
+    p = tmp_path / "fake_stream.py"
+    p.write_text(FAKE_STREAM)
+    config = ServerConfig(cache_dir=str(tmp_path / "cache"))
+    svc = StreamPipelineService(config)
+    svc.start_service(str(p))
+    api = ApiServer(config, None, svc)
+    monkeypatch.setattr(api_mod, "webrtc_available", lambda: True)
+    outcome = {}
+
+    async def fake_answer(server, body):
+        if isinstance(outcome["value"], Exception):
+            raise outcome["value"]
+        return outcome["value"]
+
+    monkeypatch.setattr(webrtc_mod, "answer_offer", fake_answer)
+    with TestClient(api.app) as client:
+        for value, status in (({"session_id": "s", "sdp": "v=0", "type": "answer"}, 200), (SessionLimitReached("4 open (limit 4)"), 503),
+                              (SessionConflict("session 's' already exists"), 409), (KeyError("sdp"), 400), (ValueError("bad SDP"), 400)):  # fmt: skip
+            outcome["value"] = value
+            r = client.post("/v1/stream/webrtc/offer", json={"sdp": "x", "type": "offer", "task": "bidirectional"})
+            assert r.status_code == status, (value, r.text)
