@@ -331,7 +331,8 @@ class ApiServer:
             q = self.task_manager.queue_status()
             c = q["counts"]
             active = c["pending"] + c["processing"] + c["streaming"]
-            return {"is_processing": c["processing"] > 0, "pending_count": c["pending"], "active_count": active,
+            return {"is_processing": c["processing"] > 0, "current_task": self.task_manager.current_task_id(),
+                    "pending_count": c["pending"], "active_count": active,
                     "queue_size": q["max_queue_size"], "queue_available": q["max_queue_size"] - active, **q}  # fmt: skip
 
         @r.get("/{task_id}/status")
@@ -385,7 +386,17 @@ class ApiServer:
 
         @r.get("/health")
         async def health() -> dict:
-            return {"status": "ok"}
+            from datetime import datetime, timezone
+            from importlib.metadata import PackageNotFoundError, version
+
+            try:
+                ver = version("telefuser-b200")
+            except PackageNotFoundError:
+                ver = "source"
+            ready = bool((self.inference_service and self.inference_service.ready)
+                         or (self.stream_service and self.stream_service.is_running))  # fmt: skip
+            return {"status": "healthy", "timestamp": datetime.now(timezone.utc).isoformat(timespec="seconds"),
+                    "version": ver, "pipeline_ready": ready}  # fmt: skip
 
         @r.get("/ready")
         async def ready():

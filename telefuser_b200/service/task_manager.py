@@ -94,6 +94,12 @@ class TaskManager:
         t = self.get_task(task_id)
         return None if t is None else t.to_dict()
 
+    def current_task_id(self) -> str | None:
+        """The task that has been in a processing slot the longest (None while idle)."""
+        with self._lock:
+            live = [t for t in self._processing if t in self._tasks]
+            return min(live, key=lambda t: self._tasks[t].start_time) if live else None
+
     def queue_status(self) -> dict:
         with self._lock:
             counts = {s.value: 0 for s in TaskStatus}

@@ -248,7 +248,8 @@ def test_rate_limiter_window():
 def test_http_task_flow(tmp_path, ppl_file):
     api = make_api(tmp_path, ppl_file)
     with TestClient(api.app) as client:
-        assert client.get("/v1/service/health").json() == {"status": "ok"}
+        health = client.get("/v1/service/health").json()
+        assert health["status"] == "healthy" and health["pipeline_ready"] is True and health["version"] and health["timestamp"].endswith("+00:00")
         assert client.get("/v1/service/ready").status_code == 200
         meta = client.get("/v1/service/metadata").json()
         assert meta["pipeline_name"] == "fake_t2v" and "t2v" in meta["tasks"] and meta["task_contracts"] == meta["tasks"]
