@@ -57,6 +57,7 @@ class ImageResponseData(BaseModel):
     revised_prompt: str | None = None
     file_path: str | None = None
     artifact_id: str | None = None
+    artifact_metadata: dict[str, Any] | None = None
 
 
 class ImageResponse(BaseModel):
@@ -93,6 +94,7 @@ class VideoResponse(BaseModel):
     error: dict[str, Any] | None = None
     file_path: str | None = None
     artifact_id: str | None = None
+    artifact_metadata: dict[str, Any] | None = None
     peak_memory_mb: float | None = None
     inference_time_s: float | None = None
 
@@ -135,6 +137,18 @@ def build_openai_routers(api) -> list[APIRouter]:
     videos = APIRouter(prefix="/v1/videos", tags=["videos"])
     video_jobs: dict[str, dict] = {}
 
+    def artifact_facts(task_id: str, path: str | None, media_type: str) -> dict | None:
+        """Where a finished output lives, for callers that fetch it from the store rather than through the URL."""
+        if not path or not Path(path).is_file():
+            return None
+        p = Path(path).resolve()
+        try:
+            rel = str(p.relative_to(Path(api.config.cache_dir).resolve()))
+        except ValueError:
+            rel = p.name
+        return {"backend": "local", "relative_path": rel, "task_id": task_id, "media_type": media_type, "filename": p.name,
+                "size_bytes": p.stat().st_size}  # fmt: skip
+
     async def run_image(task: str, req, request: Request, extra: dict) -> ImageResponse:
         from .api import b64_file
 
@@ -150,7 +164,8 @@ def build_openai_routers(api) -> list[APIRouter]:
                 raise HTTPException(500, st.get("error") or f"image task {st['status']}")
             path = st["output_path"]
             peak, secs = st.get("peak_memory_mb"), st.get("inference_time_s")
-            d = ImageResponseData(file_path=path, artifact_id=resp.task_id, revised_prompt=req.prompt)
+            d = ImageResponseData(file_path=path, artifact_id=resp.task_id, revised_prompt=req.prompt,
+                                  artifact_metadata=artifact_facts(resp.task_id, path, "image"))  # fmt: skip
             if req.response_format == "b64_json":
                 d.b64_json = b64_file(path)
             else:
@@ -201,6 +216,7 @@ def build_openai_routers(api) -> list[APIRouter]:
                           peak_memory_mb=st.get("peak_memory_mb"), inference_time_s=st.get("inference_time_s"))  # fmt: skip
         if status == "completed":
             v.file_path, v.artifact_id = st.get("output_path"), vid
+            v.artifact_metadata = artifact_facts(vid, v.file_path, "video")
             v.url = f"{api.base_url(request)}/v1/videos/{vid}/content"
             v.completed_at = int(time.time())
         elif status == "failed":

@@ -324,6 +324,9 @@ def test_openai_routes(tmp_path, ppl_file):
         r = client.post("/v1/images/generations", json={"prompt": "a cat"})
         url = r.json()["data"][0]["url"]
         assert client.get(url.replace("http://testserver", "")).status_code == 200
+        facts = r.json()["data"][0]["artifact_metadata"]
+        assert facts["backend"] == "local" and facts["media_type"] == "image" and facts["filename"].endswith(".png") and facts["size_bytes"] > 0
+        assert facts["task_id"] == r.json()["data"][0]["artifact_id"] and not facts["relative_path"].startswith("/")
         v = client.post("/v1/videos", json={"prompt": "waves", "seconds": 2, "size": "1280x720"}).json()
         assert v["object"] == "video" and v["status"] in ("queued", "generating", "completed") and v["size"] == "1280x720"
         for _ in range(200):
@@ -332,6 +335,7 @@ def test_openai_routes(tmp_path, ppl_file):
                 break
             time.sleep(0.02)
         assert v["status"] == "completed" and v["progress"] == 100
+        assert v["artifact_metadata"]["media_type"] == "video" and v["artifact_metadata"]["task_id"] == v["id"]
         assert client.get(f"/v1/videos/{v['id']}/content").content.startswith(b"\x00\x00\x00\x18ftyp")
         lst = client.get("/v1/videos").json()
         assert lst["object"] == "list" and lst["data"][0]["id"] == v["id"]
