@@ -232,6 +232,57 @@ def quantize_model_(model: nn.Module, quant, quantize_modules, skip_modules=()) 
 SIDECAR_FORMAT = "telefuser_b200.quantized_linears.v1"
 
 
+def stored_format(lin: nn.Module) -> str:
+    """How a linear's weight is stored: "dense", "fp8", "int8", "mxfp8", "nvfp4" or "nf4"."""
+    w = lin.weight
+    if w.dtype == torch.float8_e4m3fn:
+        return "mxfp8" if getattr(lin, "weight_scale_mx", None) is not None else "fp8"
+    if w.dtype == torch.int8:
+        return "int8"
+    if w.dtype == torch.uint8:
+        return "nvfp4" if getattr(lin, "weight_global_scale", None) is not None else "nf4"
+    return "dense"
+
+
+def dense_weight(lin: nn.Module) -> torch.Tensor:
+    """The fp32 matrix [out, in] a (possibly quantised) linear stands for."""
+    kind, w = stored_format(lin), lin.weight.data
+    if kind == "dense":
+        return w.float()
+    if kind in ("fp8", "int8"):
+        return w.float() * lin.weight_scale.float().reshape(-1, 1)
+    if kind == "mxfp8":
+        sf = TF.mx_untile_scales(lin.weight_scale_mx, w.shape[0]).float()
+        return (w.float().reshape(w.shape[0], -1, 32) * torch.exp2(sf - 127.0).unsqueeze(-1)).reshape(w.shape)
+    if kind == "nvfp4":
+        from .nvfp4 import dequantize_nvfp4
+
+        return dequantize_nvfp4(w, lin.weight_scale, lin.weight_global_scale, torch.float32)
+    from .nf4 import NF4_BLOCK, dequantize_nf4_reference
+
+    shape = (w.shape[0], w.shape[1] * 2)
+    return dequantize_nf4_reference(w.reshape(-1), lin.absmax, shape, getattr(w, "tfb_nf4_block", NF4_BLOCK), torch.float32)
+
+
+def update_weight_(lin: nn.Module, new_dense: torch.Tensor, dtype=torch.bfloat16) -> nn.Module:
+    """Replaces what the linear stands for by `new_dense` [out, in], keeping its stored format: the matrix is quantised
+    again with fresh scales (used to merge weight deltas such as LoRAs into quantised layers)."""
+    kind = stored_format(lin)
+    if kind == "dense":
+        lin.weight.data.copy_(new_dense.to(lin.weight.dtype))
+        return lin
+    lin.weight = nn.Parameter(new_dense.to(device=lin.weight.device, dtype=dtype), requires_grad=False)
+    if kind == "nvfp4":
+        from .nvfp4 import quantize_linear_nvfp4_
+
+        return quantize_linear_nvfp4_(lin)
+    if kind == "nf4":
+        from .nf4 import quantize_linear_nf4_
+
+        return quantize_linear_nf4_(lin)
+    return {"fp8": quantize_linear_fp8_, "int8": quantize_linear_int8_, "mxfp8": quantize_linear_mxfp8_}[kind](lin)
+
+
 def quantized_state(model: nn.Module) -> dict:
     """Tensors of the quantised linears only, keyed like a state dict: `<name>.weight` (e4m3 bytes as uint8, int8 values
     as they are, or packed NVFP4 codes) with `<name>.weight_scale` (fp32 per output channel; e4m3 per 16 inputs for

@@ -119,15 +119,32 @@ class LoRALoader:
             lora = load_state_dict(str(lora))
         params = dict(model.named_parameters())
         params.update(dict(model.named_buffers()))
-        merged, missing = 0, []
+        owners = {f"{name}.weight": m for name, m in model.named_modules() if isinstance(m, nn.Linear)} \
+            if callable(getattr(model, "named_modules", None)) else {}  # fmt: skip
+        merged, missing, requantised = 0, [], 0
         for key, entry in self.extract_lora_pairs(lora).items():
             p = params.get(key)
             if p is None:
                 missing.append(key)
                 continue
+            owner = owners.get(key)
+            if owner is not None and p.dtype in (torch.int8, torch.uint8, torch.float8_e4m3fn):
+                # a quantised layer in any stored format: merge on the matrix it stands for, then quantise again
+                from telefuser_b200.ops.quant import dense_weight, stored_format, update_weight_
+
+                if stored_format(owner) != "fp8":  # per-channel FP8 keeps the in-place path below (same result, no re-allocation)
+                    dense = dense_weight(owner)
+                    update_weight_(owner, dense + self._delta(entry, alpha, strength, dense.device).reshape(dense.shape))
+                    merged, requantised = merged + 1, requantised + 1
+                    continue
             scale = params.get(key[: -len(".weight")] + ".weight_scale")
             self._add_(p.data, self._delta(entry, alpha, strength, p.device), None if scale is None else scale.data)
             merged += 1
+            requantised += scale is not None  # in-place FP8: new scales, and fused views hold copies of the old ones
+        if requantised and isinstance(model, nn.Module):
+            from telefuser_b200.ops.quant import invalidate_fused_caches
+
+            invalidate_fused_caches(model)
         for key, diff in self.extract_lora_diffs(lora).items():
             p = params.get(key)
             if p is None or p.numel() != diff.numel():

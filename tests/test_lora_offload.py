@@ -1,6 +1,7 @@
 """LoRA merging (key spellings, alpha, diff keys, fp8 weights, run-time network), layer offload
 (async ring and sequential) and single-rank weight sharding: outputs must not change."""
 
+import pytest
 import torch
 from torch import nn
 
@@ -56,6 +57,53 @@ def test_lora_merge_into_fp8_weight():
     want = w + up @ down
     assert (got - want).abs().max() / want.abs().max() < 0.08  # e4m3: 3 mantissa bits
     assert not torch.allclose(lin.weight_scale, scale)
+
+
+@pytest.mark.parametrize("kind,limit", [("fp8", 0.08), ("int8", 0.03), ("mxfp8", 0.08), ("nvfp4", 0.3), ("nf4", 0.3)])
+def test_lora_merge_into_every_stored_format_of_a_model(kind, limit):
+    """The merge works on the matrix a quantised layer stands for and stores it back in the same format; fused QKV views
+    (which hold copies of scales) are rebuilt, so the model's output follows the merged weights."""
+    from telefuser_b200.ops.quant import dense_weight, stored_format, update_weight_
+
+    torch.manual_seed(0)
+    model = make_tiny_model()
+    blk = model.blocks[0]
+    dense_q = blk.self_attn.q.weight.detach().clone()
+    rank = 4
+    up, down = torch.randn(dense_q.shape[0], rank) * 0.15, torch.randn(rank, dense_q.shape[1]) * 0.15
+    lora = {"blocks.0.self_attn.q.lora_B.weight": up, "blocks.0.self_attn.q.lora_A.weight": down,
+            "blocks.0.ffn.0.lora_B.weight": torch.randn(blk.ffn[0].out_features, rank) * 0.15,
+            "blocks.0.ffn.0.lora_A.weight": torch.randn(rank, blk.ffn[0].in_features) * 0.15}  # fmt: skip
+    reference = make_tiny_model()
+    LoRALoader().apply_lora(reference, lora)
+    want = _tiny_forward(reference)
+
+    model.enable_quant(kind)
+    assert stored_format(blk.self_attn.q) == kind and stored_format(model.head.head) == "dense"
+    before = _tiny_forward(model)  # also builds the fused QKV view of the un-merged weights
+    res = LoRALoader().apply_lora(model, lora)
+    assert res["merged"] == 2 and stored_format(blk.self_attn.q) == kind and stored_format(blk.ffn[0]) == kind
+    merged = dense_weight(blk.self_attn.q)
+    target = dense_q + up @ down
+    assert ((merged - target).norm() / target.norm()).item() < limit
+    unmerged = dense_weight(make_quantised_copy(dense_q, kind))
+    assert (merged - target).norm() < 0.5 * (unmerged - target).norm()  # the delta went in: far closer than the old weights
+    after = _tiny_forward(model)
+    assert not torch.allclose(after, before) and ((after - want).norm() / want.norm()).item() < 1.5 * limit
+    # the two helpers on their own: a round trip through the dense view keeps the format and (nearly) the values
+    lin = blk.self_attn.o
+    d0 = dense_weight(lin)
+    update_weight_(lin, d0)
+    assert stored_format(lin) == kind and ((dense_weight(lin) - d0).norm() / d0.norm()).item() < 0.02
+
+
+def make_quantised_copy(weight, kind):
+    from telefuser_b200.ops.quant import quantize_model_
+
+    lin = nn.Sequential(nn.Linear(weight.shape[1], weight.shape[0], bias=False))
+    lin[0].weight.data.copy_(weight)
+    quantize_model_(lin, kind, ("*",))
+    return lin[0]
 
 
 def test_runtime_lora_network_switch():
