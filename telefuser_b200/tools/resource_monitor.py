@@ -8,10 +8,13 @@ service's processes over hours, and tells a leak from a plateau.
 count / open files of every process whose command line contains `--match` (or the given `--pid` and its children).
 `report` fits a line through every series after the warm-up window and prints, per series, first / last / min / max,
 the slope per hour and whether the growth is a leak: slope above the threshold AND the last quarter of the run still
-rising (a cache that fills and plateaus is not flagged).
+rising (a cache that fills and plateaus is not flagged), OR the local maxima of the series rise faster than the threshold:
+a serving process breathes with its requests, and the trend of its peaks shows what each request leaves behind.
+`--plot` also draws every series (smoothed) as one line of characters.
 
 Role: tools/deploy/docker_monitor.py (sampling a running deployment into a CSV) and tools/deploy/show_stat.py
-(leak-trend summary) of the reference, for processes instead of containers and with a textual verdict instead of plots.
+(moving average, peak trend, leak-trend summary) of the reference, for processes instead of containers and with a textual
+verdict and terminal plots instead of matplotlib figures.
 """
 
 from __future__ import annotations
@@ -107,6 +110,38 @@ def fit_slope(ts: list[float], ys: list[float]) -> float:
     return 0.0 if den == 0 else sum((t - mt) * (y - my) for t, y in zip(ts, ys)) / den
 
 
+def local_maxima(ys: list[float], window: int = 5) -> list[int]:
+    """Indices whose value exceeds every sample up to `window` places before them and is not exceeded by any up to
+    `window` places after them (so a plateau counts once, at its start)."""
+    out = []
+    for i, y in enumerate(ys):
+        left, right = ys[max(0, i - window) : i], ys[i + 1 : i + window + 1]
+        if (not left or y > max(left)) and (not right or y >= max(right)):
+            out.append(i)
+    return out
+
+
+def moving_average(ys: list[float], window: int) -> list[float]:
+    out, acc = [], 0.0
+    for i, y in enumerate(ys):
+        acc += y
+        if i >= window:
+            acc -= ys[i - window]
+        out.append(acc / min(i + 1, window))
+    return out
+
+
+def sparkline(ys: list[float], width: int = 72) -> str:
+    """One line of block characters for a series (resampled to `width` points by averaging)."""
+    if not ys:
+        return ""
+    bars = " .:-=+*#%@"
+    step = max(1, len(ys) // width)
+    pts = [sum(ys[i : i + step]) / len(ys[i : i + step]) for i in range(0, len(ys), step)]
+    lo, hi = min(pts), max(pts)
+    return "".join(bars[int((p - lo) / (hi - lo) * (len(bars) - 1))] if hi > lo else bars[0] for p in pts)
+
+
 def analyse(rows: list[dict], warmup_s: float = 0.0, leak_per_hour: float = 50.0) -> dict:
     """Per numeric series: summary statistics, slope per hour after the warm-up, and the leak verdict for memory series."""
     if not rows:
@@ -123,8 +158,15 @@ def analyse(rows: list[dict], warmup_s: float = 0.0, leak_per_hour: float = 50.0
         tail_slope_h = fit_slope([p[0] for p in tail], [p[1] for p in tail]) * 3600.0 if len(tail) >= 2 else 0.0
         entry = {"first": ys[0], "last": ys[-1], "min": min(ys), "max": max(ys), "mean": round(sum(ys) / len(ys), 3),
                  "slope_per_hour": round(slope_h, 3), "tail_slope_per_hour": round(tail_slope_h, 3)}  # fmt: skip
+        # a serving process breathes with its requests: the trend of its PEAKS says more about a leak than the mean does
+        peaks = local_maxima(ys, max(2, len(ys) // 40))
+        peak_slope_h = fit_slope([ts[i] for i in peaks], [ys[i] for i in peaks]) * 3600.0 if len(peaks) >= 3 else None
+        entry["peaks"] = len(peaks)
+        entry["peak_slope_per_hour"] = None if peak_slope_h is None else round(peak_slope_h, 3)
         if k.endswith("_mb"):
-            entry["leak"] = bool(slope_h > leak_per_hour and tail_slope_h > leak_per_hour / 2)
+            by_mean = slope_h > leak_per_hour and tail_slope_h > leak_per_hour / 2
+            by_peaks = peak_slope_h is not None and peak_slope_h > leak_per_hour and slope_h > 0
+            entry["leak"] = bool(by_mean or by_peaks)
         out[k] = entry
     return out
 
@@ -151,6 +193,7 @@ def main(argv=None) -> int:
     p.add_argument("csv")
     p.add_argument("--warmup-s", type=float, default=0.0)
     p.add_argument("--leak-mb-per-hour", type=float, default=50.0)
+    p.add_argument("--plot", action="store_true", help="also draw every series as a line of characters (smoothed)")
     a = ap.parse_args(argv)
     if a.cmd == "record":
         n = record(a.output, a.interval, a.max_seconds, a.match, a.pid)
@@ -158,6 +201,12 @@ def main(argv=None) -> int:
         return 0
     rep = report(a.csv, a.warmup_s, a.leak_mb_per_hour)
     print(json.dumps(rep, indent=1))
+    if a.plot:
+        with open(a.csv, newline="") as f:
+            rows = [r for r in csv.DictReader(f) if float(r["t"]) >= a.warmup_s]
+        for k in rep["series"]:
+            ys = [float(r[k]) for r in rows if r.get(k) not in ("", None)]
+            print(f"{k:>24} {sparkline(moving_average(ys, max(1, len(ys) // 50)))}")
     return 1 if rep["leaking_series"] else 0
 
 

@@ -120,3 +120,33 @@ def test_resource_monitor_records_and_tells_a_leak_from_a_plateau(tmp_path):
     assert rep["series"]["processes"]["min"] >= 1
     assert M.main(["report", path, "--warmup-s", "120"]) == 1  # non-zero exit when something leaks
     assert M.fit_slope([0, 1, 2], [1, 3, 5]) == pytest.approx(2.0) and M.analyse([]) == {}
+
+
+def test_resource_monitor_reads_a_leak_from_the_peaks_of_a_breathing_process(tmp_path, capsys):
+    import csv
+    import math
+
+    from telefuser_b200.tools import resource_monitor as M
+
+    assert M.local_maxima([0, 1, 0, 2, 0, 3, 0], window=1) == [1, 3, 5] and M.local_maxima([5, 5, 5, 5], window=1) == [0]
+    assert M.moving_average([1, 3, 5, 7], 2) == [1.0, 2.0, 4.0, 6.0] and len(M.sparkline(list(range(200)), 50)) == 50
+    assert M.sparkline([]) == "" and set(M.sparkline([2.0, 2.0])) == {" "}
+
+    def write(name, drift_mb_per_sample):
+        # every request allocates ~400 MB of working memory and frees it again; `drift` is what each one leaves behind
+        path = tmp_path / name
+        with open(path, "w", newline="") as f:
+            w = csv.writer(f)
+            w.writerow(["t", "rss_mb", "gpu0_util"])
+            for i in range(400):
+                w.writerow([i * 10.0, round(3000 + 400 * max(0.0, math.sin(i * 2 * math.pi / 20)) + drift_mb_per_sample * i, 3), 50])
+        return str(path)
+
+    steady, leaking = M.report(write("steady.csv", 0.0), 0.0, 50.0), M.report(write("leaking.csv", 0.2), 0.0, 50.0)
+    assert steady["leaking_series"] == [] and steady["series"]["rss_mb"]["peaks"] >= 10
+    assert abs(steady["series"]["rss_mb"]["peak_slope_per_hour"]) < 5
+    assert leaking["leaking_series"] == ["rss_mb"] and leaking["series"]["rss_mb"]["peak_slope_per_hour"] == pytest.approx(72.0, rel=0.05)
+    assert "leak" not in leaking["series"]["gpu0_util"]
+    assert M.main(["report", str(tmp_path / "steady.csv"), "--plot"]) == 0
+    out = capsys.readouterr().out
+    assert "rss_mb" in out.splitlines()[-2] and len(out.splitlines()[-2].split(" ", 1)[1].strip()) > 20
