@@ -14,11 +14,13 @@
   every transformer block at the first step and the latent after every step; under `torchrun` the model runs with
   the given layout (`cfg2`, `u<N>`, `--expert-parallel`, `--fsdp`) and rank 0 writes the file.
 * `compare`: two captures tensor by tensor (max abs, relative L2, cosine); non-zero exit above the tolerance.
+* `refiner-handoff`: the base-model -> refiner hand-off on a tiny random-init model: frame budget, sigma tail, the starting
+  mix of encoded video and noise, clean-first-frame conditioning, seed determinism; non-zero exit if a check fails.
 * `bench`: device-timed denoising steps of the full-size model on N GPUs (CUDA events, max over ranks, warm-up
   first), one JSON line: ms per step, per-stage breakdown of the first timed step, layout, tokens.
 
 Role: tools/validation/ of the reference (checkpoint inspection, reference capture and replay, dense / MoE /
-sequence-parallel parity runs, distributed run, benchmark), folded into one entry point.
+sequence-parallel parity runs, distributed run, refiner hand-off validation, benchmark), folded into one entry point.
 """
 
 from __future__ import annotations
@@ -323,6 +325,62 @@ def bench(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------
+# refiner hand-off
+# ---------------------------------------------------------------------------------------------------
+def refiner_handoff(args) -> int:
+    """Checks the base-model -> refiner hand-off on a tiny random-init model: frame selection and resize facts, the
+    low-noise sigma schedule, that the latent the refiner starts from is the stated mix of encoded video and noise,
+    that an image-conditioned run keeps its clean first frame, and that the same seed gives the same video."""
+    import numpy as np
+
+    from telefuser_b200.core.config import ModelRuntimeConfig
+    from telefuser_b200.core.module_manager import ModuleManager
+    from telefuser_b200.models.wan_vae import WanVideoVAE
+    from telefuser_b200.pipelines.lingbot_video import LingBotVideoPipeline, LingBotVideoPipelineConfig, compute_refiner_sigmas
+    from telefuser_b200.pipelines.lingbot_video import refiner as R
+    from telefuser_b200.testing.lingbot_video_checks import make_model
+    from telefuser_b200.testing.synthetic import random_init_
+
+    sample, fps, lat = R.compute_training_frame_budget(args.source_frames, args.source_fps, args.sample_fps)
+    sig = compute_refiner_sigmas(1.0, 0.0, args.steps, args.shift, args.t_thresh, args.tail_steps)
+    report = {"source": {"frames": args.source_frames, "fps": args.source_fps}, "sampled_frames": sample, "represented_fps": round(fps, 4),
+              "latent_frames": lat, "sigmas": [round(float(v), 6) for v in sig], "denoising_steps": len(sig), "checks": {}}  # fmt: skip
+    dev, dt = "cpu", torch.float32
+    mm = ModuleManager(torch_dtype=dt, device=dev)
+    mm.add_module(make_model("tiny-moe" if args.moe else "tiny"), "lingbot_video_moe_transformer" if args.moe else "lingbot_video_transformer")
+    mm.add_module(random_init_(WanVideoVAE(dim=8).float(), std=0.05).eval(), "wan_video_vae")
+    rc = lambda: ModelRuntimeConfig(device_type=dev, torch_dtype=dt)  # noqa: E731
+    pipe = LingBotVideoPipeline(device=dev, torch_dtype=dt)
+    pipe.init(mm, LingBotVideoPipelineConfig(text_encoding_config=rc(), dit_config=rc(), vae_config=rc(), num_inference_steps=1))
+    stage = R.LingBotVideoRefinerStage(pipe.denoising_stage, pipe.vae_stage, device=dev, torch_dtype=dt)
+    g = torch.Generator().manual_seed(args.seed)
+    low = torch.rand(1, 3, min(args.source_frames, 9), 16, 16, generator=g) * 2 - 1
+    video, facts = R.prepare_refiner_video(low, args.source_fps, 32, 32, args.sample_fps, max_frames=9)
+    report["tiny_run"] = facts
+    pos, neg = torch.randn(1, 6, 32, generator=g), torch.randn(1, 4, 32, generator=g)
+    kw = dict(num_inference_steps=args.steps, shift=args.shift, t_thresh=args.t_thresh, tail_steps=args.tail_steps, seed=args.seed)
+    enc = pipe.vae_stage.process("encode_video", video).float()
+    noise = torch.randn(enc.shape, generator=torch.Generator().manual_seed(args.seed))
+    start = R.prepare_refiner_latent(enc, noise, float(sig[0]))
+    checks = report["checks"]
+    checks["start_is_the_stated_mix"] = bool(torch.allclose(start, (1 - float(sig[0])) * enc + float(sig[0]) * noise, atol=1e-6))
+    lat_a = stage.refine(video, pos, neg, decode=False, **kw)
+    checks["finite"] = bool(torch.isfinite(lat_a).all())
+    checks["same_seed_same_result"] = bool(torch.equal(lat_a, stage.refine(video, pos, neg, decode=False, **kw)))
+    checks["other_seed_other_result"] = not torch.equal(lat_a, stage.refine(video, pos, neg, decode=False, **{**kw, "seed": args.seed + 1}))
+    clean = torch.rand(1, 3, 32, 32, generator=g) * 2 - 1
+    lat_c = stage.refine(video, pos, neg, decode=False, clean_first_frame=clean, **kw)
+    first = pipe.vae_stage.process("encode_video", clean.unsqueeze(2)).float()[:, :, :1]
+    checks["clean_first_frame_kept"] = bool(torch.allclose(lat_c[:, :, :1], first, atol=1e-6))
+    out = stage.refine(video, pos, neg, **kw)
+    checks["decoded_shape"] = list(out.shape)
+    checks["schedule_descends_from_threshold"] = bool(abs(float(sig[0]) - args.t_thresh) < 1e-6 and np.all(np.diff(sig) < 0))
+    report["passed"] = all(v for k, v in checks.items() if isinstance(v, bool))
+    print(json.dumps(report, indent=1))
+    return 0 if report["passed"] else 1
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -352,7 +410,19 @@ def main(argv=None) -> int:
     p.add_argument("a")
     p.add_argument("b")
     p.add_argument("--tol", type=float, default=2e-2)
+    p = sub.add_parser("refiner-handoff")
+    p.add_argument("--source-frames", type=int, default=81)
+    p.add_argument("--source-fps", type=float, default=24.0)
+    p.add_argument("--sample-fps", type=int, default=24)
+    p.add_argument("--steps", type=int, default=8)
+    p.add_argument("--shift", type=float, default=3.0)
+    p.add_argument("--t-thresh", type=float, default=0.85)
+    p.add_argument("--tail-steps", type=int, default=2)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--moe", action="store_true")
     a = ap.parse_args(argv)
+    if a.cmd == "refiner-handoff":
+        return refiner_handoff(a)
     if a.cmd == "inspect":
         print(json.dumps(inspect_shapes(read_checkpoint_shapes(a.path)), indent=1))
         return 0

@@ -150,3 +150,16 @@ def test_resource_monitor_reads_a_leak_from_the_peaks_of_a_breathing_process(tmp
     assert M.main(["report", str(tmp_path / "steady.csv"), "--plot"]) == 0
     out = capsys.readouterr().out
     assert "rss_mb" in out.splitlines()[-2] and len(out.splitlines()[-2].split(" ", 1)[1].strip()) > 20
+
+
+def test_lingbot_video_validation_tool_refiner_handoff(capsys):
+    import json
+
+    from telefuser_b200.tools import lingbot_video_validation as V
+
+    assert V.main(["refiner-handoff", "--source-frames", "121", "--source-fps", "30", "--steps", "6", "--t-thresh", "0.5", "--tail-steps", "1",
+                   "--moe"]) == 0  # fmt: skip
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["passed"] and rep["sampled_frames"] == 93 and rep["latent_frames"] == 24  # 121 frames at 30 fps thinned to 24 fps
+    assert rep["sigmas"][0] == 0.5 and rep["denoising_steps"] == len(rep["sigmas"]) and all(rep["checks"][k] for k in (
+        "start_is_the_stated_mix", "finite", "same_seed_same_result", "other_seed_other_result", "clean_first_frame_kept"))
