@@ -32,7 +32,6 @@ from dataclasses import dataclass, field
 from typing import Collection, Mapping
 
 from .streaming_types import (
-    StageOrdering,
     StreamingActorBusyError,
     StreamingActorFailedError,
     StreamingActorHealth,

@@ -1,6 +1,4 @@
 """GPU numerics: every native kernel against the fp32 PyTorch reference of the same op."""
-import math
-
 import pytest
 import torch
 

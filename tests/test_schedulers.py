@@ -1,6 +1,4 @@
 """Schedulers: flow-match sigma schedules / Euler step, UniPC exactness and convergence order."""
-import math
-
 import torch
 
 from telefuser_b200.schedulers.flow_match import FlowMatchScheduler, schedule_wan, schedule_wan_mix

@@ -12,7 +12,7 @@ import torch
 from fastapi.testclient import TestClient
 
 from telefuser_b200.service.api import ApiServer, RateLimiter
-from telefuser_b200.service.contract import apply_task_contract_defaults, load_contract, validate_required_task_parameters
+from telefuser_b200.service.contract import apply_task_contract_defaults, validate_required_task_parameters
 from telefuser_b200.service.files import ArtifactStore, FileService, MediaError, MediaType, handler_for
 from telefuser_b200.service.pipeline_service import (PipelinePool, PipelineService, ServerConfig,
                                                      resolve_replica_device_ids)  # fmt: skip
