@@ -15,7 +15,7 @@ PPL_CONFIG = dict(name="lingbot_video_dense_t2v", model_root=os.path.join(TF_MOD
                   num_frames=81, height=480, width=832, num_inference_steps=50, guidance_scale=3.0, shift=3.0, seed=42,
                   target_fps=24, supports_refiner=False)  # fmt: skip
 PIPELINE_MANIFEST = {"tasks": ["t2v", "i2v", "t2i"], "media_type": "video",
-                     "required_inputs": {"t2v": ["prompt"], "i2v": ["prompt", "image_path"], "t2i": ["prompt"]}}  # fmt: skip
+                     "required_inputs": {"t2v": ["prompt"], "i2v": ["prompt", "first_image_path"], "t2i": ["prompt"]}}  # fmt: skip
 
 
 def get_pipeline(parallelism: int = 1) -> LingBotVideoPipeline:
@@ -27,7 +27,7 @@ def get_pipeline(parallelism: int = 1) -> LingBotVideoPipeline:
 
 def run_with_file(pipeline, prompt: str, output_path: str, seed: int = PPL_CONFIG["seed"],
                   num_frames: int = PPL_CONFIG["num_frames"], height: int = PPL_CONFIG["height"],
-                  width: int = PPL_CONFIG["width"], image_path: str | None = None, negative_prompt: str | None = None):  # fmt: skip
+                  width: int = PPL_CONFIG["width"], first_image_path: str | None = None, negative_prompt: str | None = None):  # fmt: skip
     """Same request handling as the MoE example (prompt files, one-frame requests saved as PNG); no refiner."""
     import importlib.util
 
@@ -37,7 +37,7 @@ def run_with_file(pipeline, prompt: str, output_path: str, seed: int = PPL_CONFI
     spec.loader.exec_module(moe)
     moe.PPL_CONFIG = {**moe.PPL_CONFIG, "target_fps": PPL_CONFIG["target_fps"]}
     return moe.run_with_file(pipeline, prompt, output_path, seed=seed, num_frames=num_frames, height=height, width=width,
-                             image_path=image_path, negative_prompt=negative_prompt, refine=False)  # fmt: skip
+                             first_image_path=first_image_path, negative_prompt=negative_prompt, refine=False)  # fmt: skip
 
 
 if __name__ == "__main__":
@@ -50,6 +50,6 @@ if __name__ == "__main__":
     @click.option("--num_frames", default=PPL_CONFIG["num_frames"], type=int)
     @click.option("--output", default="work_dirs/lingbot_video_dense.mp4")
     def main(gpu_num, prompt, image_path, num_frames, output):
-        print(run_with_file(get_pipeline(gpu_num), prompt, output, num_frames=num_frames, image_path=image_path))
+        print(run_with_file(get_pipeline(gpu_num), prompt, output, num_frames=num_frames, first_image_path=image_path))
 
     main()

@@ -29,7 +29,7 @@ PPL_CONFIG = dict(name="lingbot_video_moe_t2v", model_root=os.path.join(TF_MODEL
                   refiner_steps=8, refiner_guidance_scale=3.0, refiner_shift=3.0, refiner_t_thresh=0.85, refiner_tail_steps=2,
                   refiner_co_resident=False)  # fmt: skip
 PIPELINE_MANIFEST = {"tasks": ["t2v", "i2v", "t2i"], "media_type": "video",
-                     "required_inputs": {"t2v": ["prompt"], "i2v": ["prompt", "image_path"], "t2i": ["prompt"]}}  # fmt: skip
+                     "required_inputs": {"t2v": ["prompt"], "i2v": ["prompt", "first_image_path"], "t2i": ["prompt"]}}  # fmt: skip
 
 
 def get_pipeline(parallelism: int = 1) -> LingBotVideoPipeline:
@@ -60,13 +60,14 @@ def build_refiner(pipeline: LingBotVideoPipeline) -> LingBotVideoRefinerStage:
 
 def run_with_file(pipeline, prompt: str, output_path: str, seed: int = PPL_CONFIG["seed"],
                   num_frames: int = PPL_CONFIG["num_frames"], height: int = PPL_CONFIG["height"],
-                  width: int = PPL_CONFIG["width"], image_path: str | None = None, negative_prompt: str | None = None,
+                  width: int = PPL_CONFIG["width"], first_image_path: str | None = None, negative_prompt: str | None = None,
                   refine: bool = PPL_CONFIG["enable_refiner"]):  # fmt: skip
     if prompt.endswith(".json") and os.path.isfile(prompt):
         prompt, duration = load_lingbot_video_prompt(prompt)
         if duration is not None:
             num_frames = num_frames_from_duration(duration, PPL_CONFIG["target_fps"])
     image = None
+    image_path = first_image_path
     if image_path:
         import numpy as np
         from PIL import Image
@@ -117,6 +118,6 @@ if __name__ == "__main__":
     @click.option("--output", default="work_dirs/lingbot_video.mp4")
     def main(gpu_num, prompt, image_path, num_frames, refine, output):
         pipe = get_pipeline(gpu_num)
-        print(run_with_file(pipe, prompt, output, num_frames=num_frames, image_path=image_path, refine=refine))
+        print(run_with_file(pipe, prompt, output, num_frames=num_frames, first_image_path=image_path, refine=refine))
 
     main()

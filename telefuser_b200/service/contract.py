@@ -175,11 +175,51 @@ def declares_contract(module: ModuleType) -> bool:
         or callable(getattr(module, "get_pipeline_contract", None))  # fmt: skip
 
 
+def signature_parameters(module: ModuleType) -> dict:
+    """`run_with_file`'s keyword defaults as parameter entries (inputs such as image paths and the plumbing arguments
+    are not parameters)."""
+    fn = getattr(module, "run_with_file", None)
+    if fn is None:
+        return {}
+    return {n: {"default": p.default} for n, p in inspect.signature(fn).parameters.items()
+            if n not in INPUT_FIELDS and n not in ("pipeline", "pipe", "output_path", "task", "kwargs", "stop_event", "latent_data")
+            and p.default is not inspect.Parameter.empty}  # fmt: skip
+
+
+def expand_short_manifest(raw: dict, module: ModuleType | None, name: str) -> dict:
+    """The compact manifest form pipeline files may use,
+
+        PIPELINE_MANIFEST = {"tasks": ["t2v", "i2v"], "media_type": "video", "required_inputs": {"t2v": ["prompt"], ...}}
+
+    spelled out as a full contract mapping: one task contract per listed task with its required (and optional) inputs,
+    the media type, and the keyword defaults of `run_with_file` as the task's parameters. A mapping that already has
+    `supported_tasks` is returned unchanged."""
+    if raw.get("supported_tasks") or not isinstance(raw.get("tasks"), (list, tuple)):
+        return raw
+    per_task = {key: raw.get(key) if isinstance(raw.get(key), dict) else {} for key in ("required_inputs", "optional_inputs", "parameters")}
+    shared = signature_parameters(module) if module is not None else {}
+    contracts = {}
+    for t in raw["tasks"]:
+        tc = dict(TASK_TEMPLATES.get(t, {}))
+        if t in per_task["required_inputs"]:
+            tc["required_inputs"] = list(per_task["required_inputs"][t])
+        if t in per_task["optional_inputs"]:
+            tc["optional_inputs"] = list(per_task["optional_inputs"][t])
+        if isinstance(raw.get("media_type"), str) and len(raw["tasks"]) == 1:
+            tc["media_type"] = raw["media_type"]  # with several tasks each keeps the media type its name implies (t2i next to t2v)
+        inputs = set(tc.get("required_inputs", ())) | set(tc.get("optional_inputs", ()))
+        tc["parameters"] = {**{n: v for n, v in shared.items() if n not in inputs}, **per_task["parameters"].get(t, {})}
+        contracts[t] = tc
+    rest = {k: v for k, v in raw.items() if k not in ("tasks", "media_type", "required_inputs", "optional_inputs", "parameters")}
+    return {"pipeline_name": raw.get("pipeline_name") or (getattr(module, "PPL_CONFIG", None) or {}).get("name") or name,
+            "supported_tasks": list(raw["tasks"]), "task_contracts": contracts, **rest}  # fmt: skip
+
+
 def load_contract(module: ModuleType, task: str | None, name: str) -> PipelineContract:
     for attr in ("PIPELINE_MANIFEST", "PIPELINE_CONTRACT"):
         raw = getattr(module, attr, None)
         if isinstance(raw, dict):
-            return PipelineContract.from_mapping(raw, fallback_name=name)
+            return PipelineContract.from_mapping(expand_short_manifest(raw, module, name), fallback_name=name)
     fn = getattr(module, "get_pipeline_contract", None)
     if callable(fn):
         raw = fn()

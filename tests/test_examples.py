@@ -126,8 +126,11 @@ def test_example_imports_and_exposes_the_service_entry_points(path):
     import importlib.util
     import inspect
 
+    import sys
+
     spec = importlib.util.spec_from_file_location("example_" + Path(path).stem, path)
     mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod  # as the service's loader does (dataclasses look their module up there)
     spec.loader.exec_module(mod)
     if hasattr(mod, "get_service"):
         assert callable(mod.get_service)
@@ -210,7 +213,7 @@ def test_lingbot_video_example_request_handling(tmp_path, monkeypatch):
         return LingBotVideoRefinerStage(pipeline.denoising_stage, pipeline.vae_stage, device="cpu", torch_dtype=torch.float32)
 
     monkeypatch.setattr(moe, "build_refiner", fake_refiner)
-    ref = moe.run_with_file(pipe, "a fox", str(tmp_path / "c.mp4"), num_frames=5, height=16, width=32, image_path=str(tmp_path / "first.png"),
+    ref = moe.run_with_file(pipe, "a fox", str(tmp_path / "c.mp4"), num_frames=5, height=16, width=32, first_image_path=str(tmp_path / "first.png"),
                             negative_prompt="bad", refine=True)  # fmt: skip
     assert ref["refined"] and built == [1] and captions[-1] == "bad"
     import cv2
@@ -220,3 +223,72 @@ def test_lingbot_video_example_request_handling(tmp_path, monkeypatch):
     cap.release()
     with pytest.raises(FileNotFoundError, match="separate download"):
         load("lingbot_video_moe_text_to_video").build_refiner(pipe)
+
+
+def test_template_example_runs_quantises_and_its_checkpoints_are_recognised(tmp_path):
+    import importlib.util
+
+    from telefuser_b200.core.module_manager import ModuleManager
+    from telefuser_b200.utils.model_weight import save_state_dict
+
+    import sys
+
+    spec = importlib.util.spec_from_file_location("_example_custom", EXAMPLES / "custom" / "minimal_custom_pipeline.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    pipe = mod.get_pipeline()
+    out = mod.run_with_file(pipe, "a template", str(tmp_path / "img" / "a.png"))
+    from PIL import Image
+
+    assert Image.open(out["output_path"]).size == (32, 32)
+    a = pipe("a template", seed=1)
+    assert a.shape == (1, 3, 32, 32) and torch.isfinite(a).all() and torch.equal(a, pipe("a template", seed=1))
+    assert not torch.equal(a, pipe("another prompt", seed=1))
+    dit = pipe.denoise_stage.dit
+    assert dit.enable_quant("int8") == 8 and dit.blocks[0].qkv.weight.dtype == torch.int8 and dit.head.weight.dtype == torch.float32
+    b = pipe("a template", seed=1)
+    assert ((b - a).norm() / a.norm()).item() < 0.1
+    # a checkpoint written from the class is identified by its key fingerprint
+    fresh = mod.TinyDiT(mod.PPL_CONFIG["dim"], mod.PPL_CONFIG["heads"], mod.PPL_CONFIG["depth"])
+    save_state_dict(fresh.state_dict(), str(tmp_path / "tiny.safetensors"))
+    mm = ModuleManager(torch_dtype=torch.float32, device="cpu")
+    assert mm.load_model(str(tmp_path / "tiny.safetensors"))
+    loaded = mm.fetch_module("tiny_custom_dit")
+    assert type(loaded).__name__ == "TinyDiT" and torch.equal(loaded.head.weight, fresh.head.weight)  # (the class of whichever import registered first)
+    svc = PipelineService(ServerConfig(security_level="strict"))
+    meta = svc.start_pipeline(str(EXAMPLES / "custom" / "minimal_custom_pipeline.py"), "t2i")
+    assert meta["supported_tasks"] == ["t2i"] and meta["declared_pipeline_contract"] is True
+    res = svc.run_task_with_stop_event({"task": "t2i", "prompt": "served", "output_path": str(tmp_path / "served.png")})
+    assert os.path.getsize(res.output_path) > 0
+
+
+@pytest.mark.parametrize("path", REQUEST_FILES, ids=lambda p: Path(p).stem)
+def test_example_manifest_becomes_a_service_contract(path):
+    """What `telefuser serve FILE` does before it builds the pipeline: the file's manifest (all examples use the compact form)
+    must turn into a contract whose tasks, required inputs and parameter defaults match `run_with_file`."""
+    import inspect
+    import sys
+
+    from telefuser_b200.service.contract import apply_task_contract_defaults, load_contract, validate_required_task_parameters
+    from telefuser_b200.service.pipeline_service import load_pipeline_module
+
+    mod = load_pipeline_module(path)
+    if hasattr(mod, "get_service"):
+        pytest.skip("a streaming service file")
+    contract = load_contract(mod, None, Path(path).stem)
+    assert list(contract.supported_tasks) == list(mod.PIPELINE_MANIFEST["tasks"]) and contract.pipeline_name == mod.PPL_CONFIG["name"]
+    sig = inspect.signature(mod.run_with_file).parameters
+    for task, tc in contract.task_contracts.items():
+        assert list(tc.required_inputs) == list(mod.PIPELINE_MANIFEST["required_inputs"][task])
+        assert tc.media_type == ("image" if task in ("t2i", "i2i", "edit") else "video")
+        for name, pc in tc.parameters.items():
+            assert name in sig and sig[name].default == pc.default, (task, name)
+        request = {k: "x" for k in tc.required_inputs}
+        filled = apply_task_contract_defaults(contract, task, request)
+        validate_required_task_parameters(contract, task, filled)
+        with pytest.raises(ValueError, match="missing required"):
+            validate_required_task_parameters(contract, task, {})
+    meta = contract.to_metadata()
+    assert meta["task_contracts"].keys() == set(contract.supported_tasks)
+    assert sys.modules  # (the loader registers the module; nothing else to check here)

@@ -530,6 +530,32 @@ def test_clients_against_live_server(tmp_path, ppl_file):
         th.join(10)
 
 
+def test_compact_manifest_expands_to_a_full_contract():
+    import types
+
+    from telefuser_b200.service.contract import expand_short_manifest, load_contract
+
+    def run_with_file(pipeline, prompt, output_path, first_image_path=None, seed=3, steps=20, resolution="720p", stop_event=None):
+        return output_path
+
+    mod = types.SimpleNamespace(PPL_CONFIG={"name": "demo"}, run_with_file=run_with_file, get_pipeline=lambda parallelism=1: None,
+                                PIPELINE_MANIFEST={"tasks": ["t2v", "i2v", "t2i"], "media_type": "video",
+                                                   "required_inputs": {"t2v": ["prompt"], "i2v": ["prompt", "first_image_path"]},
+                                                   "parameters": {"t2i": {"resolution": {"default": "1024x1024", "enum": ["1024x1024"]}}},
+                                                   "effective_max_concurrent_tasks": 2})  # fmt: skip
+    c = load_contract(mod, None, "file_stem")
+    assert c.pipeline_name == "demo" and c.supported_tasks == ("t2v", "i2v", "t2i") and c.effective_max_concurrent_tasks == 2
+    assert c.task_contracts["i2v"].required_inputs == ("prompt", "first_image_path") and c.task_contracts["t2i"].required_inputs == ("prompt",)
+    assert c.task_contracts["t2i"].media_type == "image" and c.task_contracts["t2v"].media_type == "video"
+    params = c.task_contracts["t2v"].parameters
+    assert set(params) == {"seed", "steps", "resolution"} and params["steps"].default == 20 and params["steps"].type == "integer"
+    assert c.task_contracts["t2i"].parameters["resolution"].default == "1024x1024" and c.task_contracts["t2i"].parameters["resolution"].enum == ("1024x1024",)
+    full = {"supported_tasks": ["t2v"], "tasks": ["ignored"]}
+    assert expand_short_manifest(full, mod, "x") is full  # a complete mapping is left as it is
+    single = expand_short_manifest({"tasks": ["vsr"], "media_type": "video"}, None, "upscaler")
+    assert single["pipeline_name"] == "upscaler" and single["task_contracts"]["vsr"]["required_inputs"] == ["ref_video_path"]
+
+
 def test_pipeline_file_cache_config_and_cli_precedence(tmp_path, monkeypatch):
     from pathlib import Path
 
