@@ -47,8 +47,11 @@ def layout_for(gpus: int) -> dict:
 def get_pipeline(parallelism: int = 1, model: str | None = None) -> Wan21VideoPipeline:
     folder, preset = _PRESETS[(model or PPL_CONFIG["model"]).lower()]
     if os.environ.get("TFB_RANDOM_INIT") == "1":
-        return Wan21VideoPipeline.from_random_init(preset, device="cuda" if torch.cuda.is_available() else "cpu",
-                                                   torch_dtype=torch.bfloat16, **layout_for(parallelism))  # fmt: skip
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+        if os.environ.get("TFB_TINY") == "1":  # a few-thousand-parameter model of the same structure: CPU tests of the serving path
+            return Wan21VideoPipeline.from_random_init("tiny", device=device, torch_dtype=torch.bfloat16 if device == "cuda" else torch.float32,
+                                                       vae_dim=8, **layout_for(parallelism))  # fmt: skip
+        return Wan21VideoPipeline.from_random_init(preset, device=device, torch_dtype=torch.bfloat16, **layout_for(parallelism))
     return Wan21VideoPipeline.from_pretrained(os.path.join(TF_MODEL_ZOO_PATH, folder), **layout_for(parallelism))
 
 

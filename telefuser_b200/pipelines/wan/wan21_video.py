@@ -207,8 +207,9 @@ class Wan21VideoPipeline(BasePipeline):
 
     @classmethod
     def from_random_init(cls, preset="wan2.1-t2v-1.3b", device="cuda", torch_dtype=torch.bfloat16, parallel_devices=None,
-                         text_encoder_layers: int = 2, seed: int = 0, **kwargs):  # fmt: skip
-        """Random weights of the named DiT architecture, the real VAE architecture and a short UMT5 stack."""
+                         text_encoder_layers: int = 2, seed: int = 0, vae_dim: int | None = None, **kwargs):  # fmt: skip
+        """Random weights of the named DiT architecture, the real VAE architecture (`vae_dim`: a narrower one for CPU
+        tests) and a short UMT5 stack."""
         from telefuser_b200.models.umt5 import WanTextEncoder
         from telefuser_b200.models.wan_dit import WanModel, WanModelConfig
         from telefuser_b200.models.wan_vae import WanVideoVAE
@@ -222,7 +223,8 @@ class Wan21VideoPipeline(BasePipeline):
                                 num_heads=max(1, cfgm.text_dim // 64), num_layers=text_encoder_layers)  # fmt: skip
         dit = random_init_(dit.to_empty(device=device).to(torch_dtype), seed)
         te = random_init_(te.to_empty(device=device).to(torch_dtype), seed + 1)
-        vae = random_init_(WanVideoVAE().to(device=device, dtype=torch_dtype), seed + 2, std=0.03)
+        vae = random_init_((WanVideoVAE() if vae_dim is None else WanVideoVAE(dim=vae_dim)).to(device=device, dtype=torch_dtype),
+                           seed + 2, std=0.03)  # fmt: skip
         mm = ModuleManager(torch_dtype=torch_dtype, device=str(device))
         mm.add_module(dit.eval(), "wan_video_dit")
         mm.add_module(vae.eval(), "wan_video_vae")

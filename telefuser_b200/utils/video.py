@@ -26,8 +26,18 @@ _SHORT_SIDE = {"480p": 480, "540p": 540, "720p": 720, "1080p": 1080}
 
 
 def get_target_video_size_from_ratio(resolution: str = "720p", aspect_ratio: str = "16:9", multiple: int = 16):
-    """(height, width) with the short side given by `resolution`, both rounded down to `multiple`."""
-    short = _SHORT_SIDE.get(resolution.lower())
+    """(height, width) with the short side given by `resolution` ("480p", "720p", any "<n>p", or an explicit
+    "WIDTHxHEIGHT"), both rounded down to `multiple`."""
+    res = resolution.lower().strip()
+    if "x" in res:  # explicit "WIDTHxHEIGHT": taken as given (rounded down to the multiple), whatever the aspect ratio says
+        try:
+            w, h = (int(v) for v in res.split("x", 1))
+        except ValueError:
+            raise ValueError(f"unknown resolution {resolution!r}") from None
+        if w < multiple or h < multiple:
+            raise ValueError(f"resolution {resolution!r} is smaller than one {multiple}-pixel tile")
+        return h // multiple * multiple, w // multiple * multiple
+    short = _SHORT_SIDE.get(res) or (int(res[:-1]) if res.endswith("p") and res[:-1].isdigit() else None)
     if short is None:
         raise ValueError(f"unknown resolution {resolution!r}")
     a, b = _RATIOS[aspect_ratio]

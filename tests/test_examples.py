@@ -292,3 +292,36 @@ def test_example_manifest_becomes_a_service_contract(path):
     meta = contract.to_metadata()
     assert meta["task_contracts"].keys() == set(contract.supported_tasks)
     assert sys.modules  # (the loader registers the module; nothing else to check here)
+
+
+def test_wan21_example_serves_a_request_over_http(tmp_path, monkeypatch):
+    """`telefuser serve examples/wan_video/wan21_text_to_video.py -t t2v`, with a tiny random-init model: metadata built from
+    the file's compact manifest, a task through the queue, parameter defaults from `run_with_file`, the video download."""
+    from fastapi.testclient import TestClient
+
+    from telefuser_b200.service.api import ApiServer
+
+    monkeypatch.setenv("TFB_RANDOM_INIT", "1")
+    monkeypatch.setenv("TFB_TINY", "1")
+    config = ServerConfig(cache_dir=str(tmp_path / "cache"), security_level="strict")
+    svc = PipelineService(config)
+    svc.start_pipeline(str(EXAMPLES / "wan_video" / "wan21_text_to_video.py"), "t2v")
+    with TestClient(ApiServer(config, svc).app) as client:
+        meta = client.get("/v1/service/metadata").json()
+        assert meta["pipeline_name"] == "wan21_t2v" and meta["supported_tasks"] == ["t2v"] and meta["declared_pipeline_contract"]
+        params = meta["task_contracts"]["t2v"]["parameters"]
+        assert params["num_inference_steps"]["default"] == 50 and params["resolution"]["default"] == "480p" and "prompt" not in params
+        assert client.post("/v1/tasks/create", json={"task": "i2v", "prompt": "x"}).status_code == 400  # not a task of this pipeline
+        r = client.post("/v1/tasks/create", json={"task": "t2v", "prompt": "a fox in snow", "num_frames": 5, "num_inference_steps": 2,
+                                                  "resolution": "64x48", "seed": 3})  # fmt: skip
+        assert r.status_code == 200, r.text
+        tid = r.json()["task_id"]
+        for _ in range(600):
+            st = client.get(f"/v1/tasks/{tid}/status").json()
+            if st["status"] in ("completed", "failed"):
+                break
+            time.sleep(0.05)
+        assert st["status"] == "completed", st
+        video = client.get(f"/v1/tasks/{tid}/result").content
+        assert len(video) > 500 and b"ftyp" in video[:32]
+    svc.stop()
