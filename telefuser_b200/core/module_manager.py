@@ -20,6 +20,7 @@ import torch.nn as nn
 
 from telefuser_b200.core.config import QuantConfig
 from telefuser_b200.core.model_registry import ModelRegistry
+from telefuser_b200.utils.logging import logger
 from telefuser_b200.utils.model_weight import expand_checkpoint_paths, init_weights_on_device, load_state_dict
 
 
@@ -80,6 +81,10 @@ class ModuleManager:
         if not files:
             return False
         state_dict = load_state_dict(files)
+        # a checkpoint quantised offline: recognise and build from its dense form, then put the stored payloads back
+        from telefuser_b200.ops.quant import apply_quantized_state_, quantized_state_from_checkpoint
+
+        state_dict, offline_quant = quantized_state_from_checkpoint(state_dict)
         if model_class is not None:
             names, classes, resource = [name or model_class.__name__], [model_class], model_resource
         else:
@@ -92,6 +97,13 @@ class ModuleManager:
         for n, cls in zip(names, classes):
             model = build_model_from_state_dict(state_dict, cls, resource, torch_dtype, device, low_cpu_mem_usage,
                                                 converter_kwargs, quant_config)  # fmt: skip
+            if offline_quant:
+                known = {name for name, _ in model.named_modules()}
+                usable = {k: v for k, v in offline_quant.items() if k.rsplit(".", 1)[0] in known}
+                done = apply_quantized_state_(model, usable, strict=False)
+                total = sum(1 for k in offline_quant if k.endswith(".weight"))
+                logger.info(f"{n}: {done} of {total} offline-quantised layers keep their stored form"
+                            + ("" if done == total else " (the others were renamed by the key converter and stay dense)"))
             self.add_module(model, n, path=file_path)
         return True
 

@@ -334,6 +334,42 @@ def load_quantized_sidecar(model: nn.Module, path: str, strict: bool = True) -> 
         if meta.get("format") != SIDECAR_FORMAT:
             raise ValueError(f"{path} is not a quantised side-car (format {meta.get('format')!r})")
         state = {k: f.get_tensor(k) for k in f.keys()}
+    return apply_quantized_state_(model, state, strict)
+
+
+def quantized_state_from_checkpoint(state_dict: dict) -> tuple[dict, dict]:
+    """Splits a checkpoint written by the offline converter (`tools/convert.py --quantized`) into (dense state dict,
+    quantised layer state in side-car naming). The dense dict holds the de-quantised matrices under the original keys,
+    so the model class is recognised and built as usual; the second dict puts the stored payloads and scales back
+    afterwards (`apply_quantized_state_`), so the offline-quantised values are used as they are, not quantised again.
+    MXFP4 / MXFP6 layers and MXFP8 layers whose width the block-scaled GEMM cannot take stay dense."""
+    sides = (".weight_scale", ".weight_sf", ".weight_global_scale", ".weight_mx_format")
+    if not any(k.endswith(sides) for k in state_dict):
+        return state_dict, {}
+    from telefuser_b200.tools.convert import dequantize_model
+
+    dense, _ = dequantize_model(state_dict, torch.bfloat16)
+    quant: dict = {}
+    for k, v in state_dict.items():
+        if not k.endswith(".weight"):
+            continue
+        base = k[: -len(".weight")]
+        scale, sf = state_dict.get(f"{base}.weight_scale"), state_dict.get(f"{base}.weight_sf")
+        if f"{base}.weight_mx_format" in state_dict or (scale is None and sf is None):
+            continue
+        if f"{base}.weight_global_scale" in state_dict:
+            quant.update({k: v, f"{base}.weight_scale": scale, f"{base}.weight_global_scale": state_dict[f"{base}.weight_global_scale"]})
+        elif sf is not None:
+            if v.shape[1] % 128 == 0:
+                quant.update({k: v, f"{base}.weight_scale_mx": TF.mx_tile_scales(sf.to(torch.uint8))})
+        else:
+            quant.update({k: v, f"{base}.weight_scale": scale.float().reshape(-1, 1)})
+    return dense, quant
+
+
+def apply_quantized_state_(model: nn.Module, state: dict, strict: bool = True) -> int:
+    """`state`: `<name>.weight` payloads with `<name>.weight_scale` / `.weight_scale_mx` / `.weight_global_scale` (the
+    side-car naming). Every named linear of `model` takes the stored form in place; returns the number converted."""
     modules = dict(model.named_modules())
     n = 0
     for key in [k for k in state if k.endswith(".weight")]:

@@ -4,6 +4,7 @@ import json
 import wave
 
 import numpy as np
+import pytest
 import torch
 from PIL import Image
 
@@ -110,3 +111,35 @@ def test_artifact_save_stage(tmp_path):
     meta2 = stage.process([Image.new("RGB", (8, 8))] * 2, request_id="frames", config=cfg, file_ext=".png",
                           make_date_subdir=False)  # fmt: skip
     assert (tmp_path / "run_.._x" / "frames" / "1.png").is_file() and meta2["num_frames"] == 2
+
+
+@pytest.mark.parametrize("kind", ["fp8", "int8", "mxfp8", "nvfp4", "mxfp4"])
+def test_offline_quantised_checkpoint_loads_with_its_stored_payloads(tmp_path, kind):
+    """convert --quantized -> ModuleManager.load_model: the model class is recognised from the dense form of the checkpoint,
+    the layers come back in their stored format with the stored values (formats without a run-time path stay dense)."""
+    from telefuser_b200.core.module_manager import ModuleManager
+    from telefuser_b200.models.wan_dit import WanModel
+    from telefuser_b200.ops.quant import dense_weight, stored_format
+    from telefuser_b200.testing.distributed_checks import make_tiny_inputs, make_tiny_model
+    from telefuser_b200.tools import convert
+    from telefuser_b200.utils.model_weight import load_state_dict, save_state_dict
+
+    src = make_tiny_model()
+    save_state_dict(src.state_dict(), str(tmp_path / "dit.safetensors"))
+    convert.main(["-s", str(tmp_path / "dit.safetensors"), "-o", str(tmp_path / "q"), "--quantized", "--linear_dtype", kind,
+                  "--quantize_modules", "self_attn", "cross_attn", "ffn"])  # fmt: skip
+    mm = ModuleManager(torch_dtype=torch.float32, device="cpu")
+    assert mm.load_model(str(tmp_path / "q" / "converted.safetensors"), model_class=WanModel, name="wan_video_dit")
+    dit = mm.fetch_module("wan_video_dit")
+    lin = dit.blocks[0].ffn[0]
+    assert stored_format(lin) == ("dense" if kind == "mxfp4" else kind) and stored_format(dit.head.head) == "dense"
+    stored = load_state_dict(str(tmp_path / "q" / "converted.safetensors"))
+    if kind not in ("mxfp4",):
+        assert torch.equal(lin.weight.data.view(torch.uint8), stored["blocks.0.ffn.0.weight"].view(torch.uint8))  # not re-quantised
+    want = convert.dequantize_model(stored, torch.float32)[0]["blocks.0.ffn.0.weight"]
+    assert torch.allclose(dense_weight(lin), want, atol=1e-2 * want.abs().max().item())
+    lat, ctx, _ = make_tiny_inputs()
+    t = torch.tensor([500.0])
+    with torch.no_grad():
+        ref, out = src(lat, t, ctx), dit(lat, t, ctx)
+    assert torch.isfinite(out).all() and ((out - ref).norm() / ref.norm()).item() < (0.3 if kind == "mxfp4" else 0.1)
