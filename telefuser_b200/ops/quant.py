@@ -344,7 +344,8 @@ def quantized_state_from_checkpoint(state_dict: dict) -> tuple[dict, dict]:
     afterwards (`apply_quantized_state_`), so the offline-quantised values are used as they are, not quantised again.
     MXFP4 / MXFP6 layers and MXFP8 layers whose width the block-scaled GEMM cannot take stay dense."""
     sides = (".weight_scale", ".weight_sf", ".weight_global_scale", ".weight_mx_format")
-    if not any(k.endswith(sides) for k in state_dict):
+    low = (torch.float8_e4m3fn, torch.int8, torch.uint8)
+    if not any(k.endswith(sides) and getattr(state_dict.get(k.rsplit(".", 1)[0] + ".weight"), "dtype", None) in low for k in state_dict):
         return state_dict, {}
     from telefuser_b200.tools.convert import dequantize_model
 
@@ -355,7 +356,7 @@ def quantized_state_from_checkpoint(state_dict: dict) -> tuple[dict, dict]:
             continue
         base = k[: -len(".weight")]
         scale, sf = state_dict.get(f"{base}.weight_scale"), state_dict.get(f"{base}.weight_sf")
-        if f"{base}.weight_mx_format" in state_dict or (scale is None and sf is None):
+        if f"{base}.weight_mx_format" in state_dict or (scale is None and sf is None) or v.dtype not in low:
             continue
         if f"{base}.weight_global_scale" in state_dict:
             quant.update({k: v, f"{base}.weight_scale": scale, f"{base}.weight_global_scale": state_dict[f"{base}.weight_global_scale"]})

@@ -167,13 +167,15 @@ def dequantize_model(sd: dict, dtype=torch.bfloat16) -> tuple[dict, int]:
     """Inverse of `quantize_model` for every format it writes: quantised `<name>.weight` entries become dense
     `dtype` matrices and their side tensors are dropped, so a 4- / 6- / 8-bit checkpoint loads anywhere."""
     out, n = {}, 0
+    payload_bases = {k[: -len(".weight")] for k, v in sd.items()
+                     if k.endswith(".weight") and v.dtype in (torch.float8_e4m3fn, torch.int8, torch.uint8)}  # fmt: skip
     for k, v in sd.items():
-        if k.endswith(_SIDE_TENSORS):
+        if k.endswith(_SIDE_TENSORS) and k.rsplit(".", 1)[0] in payload_bases:
             continue
         base = k[: -len(".weight")] if k.endswith(".weight") else None
         scale, sf = (sd.get(f"{base}.weight_scale"), sd.get(f"{base}.weight_sf")) if base else (None, None)
-        if base is None or (scale is None and sf is None):
-            out[k] = v
+        if base is None or (scale is None and sf is None) or v.dtype not in (torch.float8_e4m3fn, torch.int8, torch.uint8):
+            out[k] = v  # not a quantised payload (a dense weight next to a tensor that merely shares the suffix)
             continue
         n += 1
         if f"{base}.weight_mx_format" in sd:
