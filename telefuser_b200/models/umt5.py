@@ -155,8 +155,21 @@ class WanTextEncoder(BaseModel):
 
 
 class WanTextEncoderStateDictConverter:
+    """Keys are used as published; sizes that differ from UMT5-XXL (smaller encoders, test models) are read off the tensors."""
+
     def from_official(self, state_dict):
-        return dict(state_dict), {}
+        sd, ctor = dict(state_dict), {}
+        emb, q, fc1 = sd.get("token_embedding.weight"), sd.get("blocks.0.attn.q.weight"), sd.get("blocks.0.ffn.fc1.weight")
+        pos = sd.get("blocks.0.pos_embedding.embedding.weight")
+        if emb is not None and q is not None and fc1 is not None and tuple(emb.shape) != (256384, 4096):
+            layers = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("blocks."))
+            ctor = dict(vocab=int(emb.shape[0]), dim=int(emb.shape[1]), dim_attn=int(q.shape[0]), dim_ffn=int(fc1.shape[0]), num_layers=layers)
+            shared = sd.get("pos_embedding.embedding.weight")
+            if pos is not None:
+                ctor.update(num_buckets=int(pos.shape[0]), num_heads=int(pos.shape[1]))
+            elif shared is not None:
+                ctor.update(num_buckets=int(shared.shape[0]), num_heads=int(shared.shape[1]), shared_pos=True)
+        return sd, ctor
 
     from_civitai = from_official
     from_diffusers = from_official

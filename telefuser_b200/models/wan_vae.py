@@ -569,9 +569,15 @@ class WanVideoVAEStateDictConverter:
     def from_official(self, state_dict: dict):
         if "model_state" in state_dict:
             state_dict = state_dict["model_state"]
-        if any(k.startswith("model.") for k in state_dict):
-            return dict(state_dict), {}
-        return {"model." + k: v for k, v in state_dict.items()}, {}
+        sd = dict(state_dict) if any(k.startswith("model.") for k in state_dict) else {"model." + k: v for k, v in state_dict.items()}
+        # width and latent channels follow from the decoder's ends (96 / 16 in the published file; narrower in test models)
+        ctor = {}
+        head, entry = sd.get("model.decoder.head.2.weight"), sd.get("model.conv2.weight")
+        if head is not None and head.shape[1] != 96:
+            ctor["dim"] = int(head.shape[1])
+        if entry is not None and entry.shape[0] != 16:
+            ctor["z_dim"] = int(entry.shape[0])
+        return sd, ctor
 
     from_civitai = from_official
     from_diffusers = from_official

@@ -21,12 +21,48 @@ from typing import Any
 import torch
 
 
+_INIT_FUNCTIONS = ("uniform_", "normal_", "trunc_normal_", "constant_", "ones_", "zeros_", "eye_", "dirac_", "xavier_uniform_",
+                   "xavier_normal_", "kaiming_uniform_", "kaiming_normal_", "orthogonal_", "sparse_")  # fmt: skip
+
+
 @contextlib.contextmanager
 def init_weights_on_device(device: torch.device | str = "meta", include_buffers: bool = False):
-    """Modules constructed inside allocate parameters (and optionally buffers) on `device`."""
-    del include_buffers  # torch.device() as a context already covers buffers and factory calls
-    with torch.device(device):
+    """Modules constructed inside get their PARAMETERS on `device` (the meta device: no storage, to be adopted from a
+    checkpoint with `load_state_dict(assign=True)`), while everything else a constructor computes stays real: buffers
+    (unless `include_buffers`), and plain tensor attributes such as normalisation constants or frequency tables, which
+    no checkpoint restores. A blanket `torch.device("meta")` context would turn those into meta tensors as well.
+    Weight initialisers are skipped while the context is open (their results would be thrown away), so the short-lived
+    host allocation of a large layer is never written to and costs no time."""
+    from torch import nn
+
+    dev = torch.device(device)
+    register_parameter, register_buffer = nn.Module.register_parameter, nn.Module.register_buffer
+
+    def parameter_on_device(module, name, param):
+        register_parameter(module, name, param)
+        if param is not None and param.device != dev:
+            cls, extra = type(param), dict(param.__dict__)
+            moved = cls(param.data.to(dev), requires_grad=param.requires_grad)
+            moved.__dict__.update(extra)
+            module._parameters[name] = moved
+
+    def buffer_on_device(module, name, tensor, persistent=True):
+        register_buffer(module, name, tensor, persistent=persistent)
+        if tensor is not None and tensor.device != dev:
+            module._buffers[name] = tensor.to(dev)
+
+    saved = {n: getattr(nn.init, n) for n in _INIT_FUNCTIONS if hasattr(nn.init, n)}
+    nn.Module.register_parameter = parameter_on_device
+    if include_buffers:
+        nn.Module.register_buffer = buffer_on_device
+    for n in saved:
+        setattr(nn.init, n, lambda tensor, *a, **k: tensor)
+    try:
         yield
+    finally:
+        nn.Module.register_parameter, nn.Module.register_buffer = register_parameter, register_buffer
+        for n, fn in saved.items():
+            setattr(nn.init, n, fn)
 
 
 def _load_one(path: str, device: str = "cpu") -> dict[str, torch.Tensor]:
