@@ -136,3 +136,30 @@ def test_resolve_quant_kind_reads_configs_types_and_names():
     assert resolve_quant_kind(QuantType.BNB_NF4) == "nf4" and resolve_quant_kind("nf4") == "nf4"
     assert resolve_quant_kind(QuantConfig(enabled=True, quant_type=QuantType.INT8)) == "int8"
     assert resolve_quant_kind(QuantType.TORCHAO_FP8) == "fp8"
+
+
+@pytest.mark.parametrize("family", list(CASES))
+def test_every_family_builds_without_weight_storage_and_adopts_a_checkpoint(family):
+    """What `ModuleManager` does for every checkpoint: construct with parameters on the meta device (constructor constants
+    and buffers stay real), adopt the tensors, run. The result must equal the model the tensors came from, bit for bit."""
+    from telefuser_b200.utils.model_weight import init_weights_on_device
+
+    torch.manual_seed(0)
+    model, run, _ = CASES[family]()
+    state = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    moves = torch.nn.Module.to
+    torch.nn.Module.to = lambda self, *a, **k: self  # the test builders cast / move; the loader does that after adopting
+    try:
+        with init_weights_on_device("meta"):
+            empty, _, _ = CASES[family]()
+    finally:
+        torch.nn.Module.to = moves
+    params = list(empty.parameters())
+    assert params and all(p.is_meta for p in params), [n for n, p in empty.named_parameters() if not p.is_meta][:3]
+    assert not any(b.is_meta for b in empty.buffers())
+    missing, unexpected = empty.load_state_dict(state, assign=True, strict=False)
+    assert not unexpected and not [k for k in missing if k in dict(empty.named_parameters())]
+    assert not any(p.is_meta for p in empty.parameters())
+    with torch.no_grad():
+        want, got = run(model), run(empty)  # the same inputs for both
+    assert torch.equal(got, want)
