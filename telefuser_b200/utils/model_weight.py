@@ -16,11 +16,13 @@ import glob
 import hashlib
 import json
 import os
+import threading
 from typing import Any
 
 import torch
 
 
+_CONSTRUCTION_LOCK = threading.RLock()
 _INIT_FUNCTIONS = ("uniform_", "normal_", "trunc_normal_", "constant_", "ones_", "zeros_", "eye_", "dirac_", "xavier_uniform_",
                    "xavier_normal_", "kaiming_uniform_", "kaiming_normal_", "orthogonal_", "sparse_")  # fmt: skip
 
@@ -36,7 +38,6 @@ def init_weights_on_device(device: torch.device | str = "meta", include_buffers:
     from torch import nn
 
     dev = torch.device(device)
-    register_parameter, register_buffer = nn.Module.register_parameter, nn.Module.register_buffer
 
     def parameter_on_device(module, name, param):
         register_parameter(module, name, param)
@@ -51,18 +52,23 @@ def init_weights_on_device(device: torch.device | str = "meta", include_buffers:
         if tensor is not None and tensor.device != dev:
             module._buffers[name] = tensor.to(dev)
 
-    saved = {n: getattr(nn.init, n) for n in _INIT_FUNCTIONS if hasattr(nn.init, n)}
-    nn.Module.register_parameter = parameter_on_device
-    if include_buffers:
-        nn.Module.register_buffer = buffer_on_device
-    for n in saved:
-        setattr(nn.init, n, lambda tensor, *a, **k: tensor)
-    try:
-        yield
-    finally:
-        nn.Module.register_parameter, nn.Module.register_buffer = register_parameter, register_buffer
-        for n, fn in saved.items():
-            setattr(nn.init, n, fn)
+    # The hooks below are process-wide while the context is open, so loaders in different threads take turns; a module
+    # that some other thread constructs in the meantime would get meta parameters too: construct models under this
+    # context (or not at all) while one is open.
+    with _CONSTRUCTION_LOCK:
+        register_parameter, register_buffer = nn.Module.register_parameter, nn.Module.register_buffer
+        saved = {n: getattr(nn.init, n) for n in _INIT_FUNCTIONS if hasattr(nn.init, n)}
+        nn.Module.register_parameter = parameter_on_device
+        if include_buffers:
+            nn.Module.register_buffer = buffer_on_device
+        for n in saved:
+            setattr(nn.init, n, lambda tensor, *a, **k: tensor)
+        try:
+            yield
+        finally:
+            nn.Module.register_parameter, nn.Module.register_buffer = register_parameter, register_buffer
+            for n, fn in saved.items():
+                setattr(nn.init, n, fn)
 
 
 def _load_one(path: str, device: str = "cpu") -> dict[str, torch.Tensor]:
