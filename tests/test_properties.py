@@ -10,7 +10,7 @@ from torch import nn
 
 from telefuser_b200.utils.packing import ALIGN, PackedBlock
 
-FAST = settings(max_examples=40, deadline=None)
+FAST = settings(max_examples=40, deadline=None, derandomize=True, database=None)  # the same cases on every run
 
 
 @FAST
