@@ -201,6 +201,14 @@ def resolve_quant_kind(quant) -> str:
     for key, out in (("nvfp4", "nvfp4"), ("nf4", "nf4"), ("mxfp8", "mxfp8"), ("int8", "int8")):
         if key in name:
             return out
+    # MXFP4 / MXFP6 are checkpoint storage formats here (`ops/mxfp.py`); at run time the nearest format with a compute
+    # path stands in: the other 4-bit block-scaled format for MXFP4, block-scaled FP8 for MXFP6
+    for key, out in (("mxfp4", "nvfp4"), ("mxfp6", "mxfp8")):
+        if key in name:
+            from telefuser_b200.utils.logging import logger
+
+            logger.warning(f"{key.upper()} has no run-time kernel; layers are quantised as {out.upper()} instead")
+            return out
     return "fp8"
 
 

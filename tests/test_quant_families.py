@@ -136,6 +136,7 @@ def test_resolve_quant_kind_reads_configs_types_and_names():
     assert resolve_quant_kind(QuantType.BNB_NF4) == "nf4" and resolve_quant_kind("nf4") == "nf4"
     assert resolve_quant_kind(QuantConfig(enabled=True, quant_type=QuantType.INT8)) == "int8"
     assert resolve_quant_kind(QuantType.TORCHAO_FP8) == "fp8"
+    assert resolve_quant_kind(QuantType.MXFP4) == "nvfp4" and resolve_quant_kind(QuantType.MXFP6) == "mxfp8"  # nearest run-time formats
 
 
 @pytest.mark.parametrize("family", list(CASES))
