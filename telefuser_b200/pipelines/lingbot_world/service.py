@@ -36,7 +36,7 @@ _VALID_KEYS = set(KEY_MOVES) | set(KEY_TURNS)
 KEY_ALIASES = {**{k: k for k in _VALID_KEYS}, **{f"key{k}": k for k in _VALID_KEYS}, **DIRECTION_KEYS,
                "arrowup": "w", "arrowdown": "s", "arrowleft": "a", "arrowright": "d", "up": "w", "down": "s", "left": "a", "right": "d",
                "pageup": "e", "pagedown": "q", "space": "e"}  # fmt: skip
-MAX_GENERATION_SECONDS = 20.0  # longest session a client may ask for (the rolling KV cache bounds memory, this bounds occupancy)
+MAX_GENERATION_SECONDS = 20.0  # longest session a client may ask for unless the operator configures longer ones (bounds occupancy)
 
 
 def canonical_key(name) -> str | None:
@@ -150,9 +150,12 @@ def overlay_control_hud(frames: np.ndarray, keys) -> np.ndarray:
 
 class LingBotWorldFastService:
     def __init__(self, pipeline, default_config: LingBotWorldFastSessionConfig | None = None, warmup: bool = False,
-                 max_generation_seconds: float = MAX_GENERATION_SECONDS) -> None:  # fmt: skip
+                 max_generation_seconds: float | None = None) -> None:  # fmt: skip
         self.pipeline, self.default_config, self._warmup = pipeline, default_config or LingBotWorldFastSessionConfig(), warmup
-        self.max_generation_seconds = float(max_generation_seconds)
+        # what a client may ask for: the operator's limit, else the larger of 20 s and the session length the operator
+        # configured as the default (a service set up for two-minute sessions serves two-minute sessions)
+        self.max_generation_seconds = (float(max_generation_seconds) if max_generation_seconds is not None
+                                       else max(MAX_GENERATION_SECONDS, float(self.default_config.max_duration_seconds)))  # fmt: skip
         self._sessions: dict[str, LingBotWorldFastSessionState] = {}
         self._lock = threading.Lock()
         self._started = False

@@ -179,6 +179,9 @@ def test_interactive_service_session():
     svc.close_session(sid5)
     with pytest.raises(ValueError, match="at most 20 s"):
         svc.create_session({"image": img, "prompt_emb": emb, "max_duration_seconds": 30.0})
+    # an operator who configures two-minute sessions gets two-minute sessions; an explicit limit wins over both
+    assert LingBotWorldFastService(pipe, LingBotWorldFastSessionConfig(max_duration_seconds=120.0)).max_generation_seconds == 120.0
+    assert LingBotWorldFastService(pipe, LingBotWorldFastSessionConfig(max_duration_seconds=120.0), max_generation_seconds=60).max_generation_seconds == 60.0
     # explicit pose chunks and an early stop
     poses = random_walk_trajectory(2, seed=3)
     sid2 = svc.create_session({"image": img, "prompt_emb": emb, "seed": 1, "max_duration_seconds": 3.0, "hud": False,
