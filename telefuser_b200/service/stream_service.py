@@ -195,11 +195,13 @@ def audio_from_chunk(chunk: dict) -> AudioChunk | None:
 
         return AudioChunk(base64.b64decode(chunk["audio_b64"]), rate, channels)
     a = chunk.get("audio")
-    if a is None:
+    if a is None or isinstance(a, (bool, int, float, str, dict)):  # a flag or a description under that name is ordinary data
         return None
     if isinstance(a, torch.Tensor):
         a = a.detach().cpu().numpy()
     a = np.asarray(a)
+    if a.ndim not in (1, 2) or a.size == 0:
+        return None
     if a.ndim == 2 and "audio_channels" not in chunk:
         channels = a.shape[1]
     if a.dtype != np.int16:

@@ -265,8 +265,8 @@ def test_chunk_router_takes_encoded_frames_and_audio_in_every_form():
     assert (stereo.channels, stereo.sample_rate, stereo.num_samples) == (2, 48000, 2)
     assert np.frombuffer(stereo.pcm16, dtype=np.int16).tolist() == [0, 32767, -32767, 16384]
     assert audio_from_chunk({"audio": pcm}).pcm16 == pcm.tobytes() and audio_from_chunk({"frames": []}) is None
-    _, plain = ChunkRouter().route({"frames": [np.zeros((4, 4, 3), dtype=np.uint8)]}, "s", 0)
-    assert "audio" not in plain and plain["num_frames"] == 1
+    _, plain = ChunkRouter().route({"frames": [np.zeros((4, 4, 3), dtype=np.uint8)], "audio": False}, "s", 0)
+    assert "audio" not in plain and plain["num_frames"] == 1 and plain["data"] == {"audio": False}  # a flag is not sound
 
 
 def test_audio_pacer_packets_silence_and_drops():
